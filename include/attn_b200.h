@@ -1,0 +1,148 @@
+/*
+ * attn_b200.h -- C ABI of the B200-native attention backend (libattn_b200.so).
+ *
+ * The reference project (SJTU-IPADS/MetaAttention) has no stable C ABI: its
+ * native parts are per-instantiation pybind modules generated at run time.
+ * Each entry point below names the reference interface it stands in for.
+ *
+ * Conventions
+ *   - every pointer in an *Args struct is a DEVICE pointer unless it says host;
+ *   - tensors are borrowed for the duration of the call, outputs are written
+ *     in place into caller-allocated buffers;
+ *   - kernels are enqueued on the given stream of the CURRENT device and the
+ *     call returns without synchronising;
+ *   - every function returns an int status: 0 = ok, negative = error
+ *     (ATTN_B200_E_*).  Nothing here exits, aborts or traps.  Device-side
+ *     waits are bounded; a wait that runs out records a code that
+ *     attn_b200_last_device_status() reports after the stream is synchronised;
+ *   - thread-compatible: concurrent calls are fine as long as calls that
+ *     target the same stream are serialised by the caller.
+ */
+#ifndef ATTN_B200_H_
+#define ATTN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATTN_B200_OK 0
+#define ATTN_B200_E_INVALID_ARG (-1)   /* null pointer, bad enum, negative size            */
+#define ATTN_B200_E_UNSUPPORTED (-2)   /* shape / dtype / stride the kernels do not cover   */
+#define ATTN_B200_E_LAUNCH (-3)        /* CUDA runtime or driver error at launch            */
+#define ATTN_B200_E_DEVICE_TIMEOUT (-4)/* a bounded device-side wait ran out                */
+#define ATTN_B200_E_WORKSPACE (-5)     /* workspace missing or too small                    */
+
+#define ATTN_B200_DTYPE_FP16 0
+#define ATTN_B200_DTYPE_BF16 1
+
+#define ATTN_B200_MASK_NONE 0
+#define ATTN_B200_MASK_CAUSAL 1        /* keep q_idx >= kv_idx (top-left aligned)           */
+
+/* Built-in functors of the parallel pattern (score_mod + online_func pairs
+ * recognised by the front-end).  Anything else is compiled from the traced
+ * DAG into its own library exporting attn_b200_parallel_fwd_jit. */
+#define ATTN_B200_FUNCTOR_SOFTMAX 0    /* fparams[0] = scale; p = exp(scale*(s - rowmax))   */
+
+#define ATTN_B200_MAX_CUSTOM 4
+#define ATTN_B200_MAX_ROWSCALES 4
+
+/* Arguments of the parallel-pattern forward: O = epilogue(sum_tiles P.V),
+ * P = online_fwd(score_mod(mask + Q.K^T)).
+ * q,k: [batch, seq, heads, dim_qk], v,o: [batch, seq, heads, dim_v] as seen
+ * through the element strides (last dimension contiguous). */
+typedef struct AttnB200ParallelArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* final_rowscales[ATTN_B200_MAX_ROWSCALES]; /* each [batch, heads, seq_q] fp32, or NULL */
+  int32_t batch, heads, seq_q, seq_kv, dim_qk, dim_v;
+  int64_t q_stride[3];   /* element strides of (batch, seq, head) */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  int32_t dtype;         /* ATTN_B200_DTYPE_*  */
+  int32_t mask_kind;     /* ATTN_B200_MASK_*   */
+  int32_t functor;       /* ATTN_B200_FUNCTOR_* (ignored by *_jit libraries) */
+  int32_t reserved;
+  float fparams[8];      /* functor scalars */
+  const void* custom[ATTN_B200_MAX_CUSTOM];          /* custom_fwd_inputs tensors */
+  int64_t custom_stride[ATTN_B200_MAX_CUSTOM][4];    /* element strides of (batch, heads, seq_len, seq_len_kv); 0 = broadcast */
+} AttnB200ParallelArgs;
+
+/* Replaces the generated TileLang forward kernel and its launcher
+ * (attention_engine/core/template/tl_template/attn/attn_tl.py:93-190, :656-667)
+ * and the CuTe forward (core/template/cute_template/flash_api.cpp:283-460). */
+int attn_b200_parallel_fwd(const AttnB200ParallelArgs* args, void* cuda_stream);
+
+/* Arguments of the chunked linear-attention / retention forward
+ *   h_{c+1} = h_c * exp(g_last) + (K * exp(g_last - g))^T V
+ *   O       = (scale*Q h_c) * exp(g) + tril((scale*Q K^T) * exp(g_i - g_j)) V
+ * with g the within-chunk inclusive cumulative sum of log_decay.
+ * q,k: [batch, heads, seq, dim_qk]; v,o: [batch, heads, seq, dim_v] contiguous;
+ * log_decay: [batch, heads, seq] fp32 (natural log of the per-token decay). */
+typedef struct AttnB200LinearArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* log_decay;
+  void* o;
+  int32_t batch, heads, seq, dim_qk, dim_v;
+  int32_t dtype;
+  int32_t normalize;     /* 0: raw output; 1: per-(token, head) group norm over dim_v, eps below, no affine */
+  float q_scale;         /* q_mod of the form q * const */
+  float norm_eps;
+} AttnB200LinearArgs;
+
+/* Replaces chunk_local_cumsum_scalar + chunk_fwd_h + chunk_o and their wrapper
+ * (core/template/tl_template/linear/linear_tl.py:36-60, :146-223, :321-401, :1240-1268). */
+int attn_b200_linear_fwd(const AttnB200LinearArgs* args, void* cuda_stream);
+
+/* MLA decode problem shape: one query token per sequence, one shared latent KV head. */
+typedef struct AttnB200MlaShape {
+  int32_t batch, heads_q, seq_kv, dim_qk, dim_v;
+} AttnB200MlaShape;
+
+/* Split-KV plan.  Replaces get_mla_metadata
+ * (core/template/cute_template_kvshared/flash_api.cpp:23-59,
+ *  kernels/get_mla_metadata.cu:8-82): chooses how many KV splits each
+ * sequence gets so that sm_count SMs are evenly loaded.  Host-side, integer. */
+int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t* num_splits_out);
+
+/* Bytes of scratch (fp32 partial outputs + partial log-sum-exp) the decode
+ * needs for a given plan. */
+int64_t attn_b200_mla_workspace_bytes(const AttnB200MlaShape* shape, int32_t num_splits);
+
+typedef struct AttnB200MlaArgs {
+  const void* q;     /* [batch, heads_q, dim_qk] */
+  const void* kv;    /* [batch, seq_kv, dim_qk] latent KV, contiguous per sequence; V = first dim_v columns */
+  void* o;           /* [batch, heads_q, dim_v] */
+  float* lse;        /* [batch, heads_q] fp32 natural-log sum-exp of scaled scores, or NULL */
+  void* workspace;   /* attn_b200_mla_workspace_bytes() bytes */
+  int64_t workspace_bytes;
+  AttnB200MlaShape shape;
+  int32_t num_splits;
+  int32_t dtype;
+  float scale;       /* softmax scale, e.g. 1/sqrt(dim_qk) */
+} AttnB200MlaArgs;
+
+/* Split-KV decode + combine.  Replaces flash_fwd_splitkv_mla_kernel and
+ * flash_fwd_mla_combine_kernel with their launcher
+ * (core/template/cute_template_kvshared/kernels/splitkv_mla.cu:1061-1471,
+ *  kernels/mla_combine.cu:14-203, flash_api.cpp:61-210) and the TileLang
+ * variant (core/template/tl_template/attn/mla_decode_tl.py:154-303). */
+int attn_b200_mla_decode(const AttnB200MlaArgs* args, void* cuda_stream);
+
+/* Reads and clears the device-side status word of device `device`
+ * (0 = no kernel reported a problem).  Synchronises the device. */
+int attn_b200_last_device_status(int32_t device, int32_t* status_out);
+
+/* Library version, major*10000 + minor*100 + patch. */
+int attn_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATTN_B200_H_ */

@@ -1,0 +1,217 @@
+"""ctypes binding of libattn_b200.so (the C ABI declared in include/attn_b200.h).
+
+This is the only place where Python touches the native library.  There is no
+fallback: if the library is missing or an entry point fails, the call raises.
+Tensors are passed as raw device pointers + element strides; kernels run on
+the current CUDA stream of the current device, as the reference's native
+entry points do (core/template/cute_template_kvshared/flash_api.cpp:46-47,133,188).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+CSRC_DIR = os.path.join(_PKG_DIR, "csrc")
+INCLUDE_DIR = os.path.join(os.path.dirname(_PKG_DIR), "include")
+LIB_PATH = os.path.join(_PKG_DIR, "libattn_b200.so")
+
+NVCC_ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"]
+
+MAX_CUSTOM = 4
+MAX_ROWSCALES = 4
+
+OK = 0
+ERRORS = {
+    -1: "invalid argument",
+    -2: "unsupported shape / dtype / stride",
+    -3: "CUDA launch error",
+    -4: "device-side wait timed out",
+    -5: "workspace missing or too small",
+}
+
+DTYPE_CODES = {torch.float16: 0, torch.bfloat16: 1}
+MASK_NONE, MASK_CAUSAL = 0, 1
+FUNCTOR_SOFTMAX = 0
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class ParallelArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+        ("final_rowscales", C.c_void_p * MAX_ROWSCALES),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("seq_q", C.c_int32), ("seq_kv", C.c_int32),
+        ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
+        ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
+        ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("functor", C.c_int32), ("reserved", C.c_int32),
+        ("fparams", C.c_float * 8),
+        ("custom", C.c_void_p * MAX_CUSTOM),
+        ("custom_stride", (C.c_int64 * 4) * MAX_CUSTOM),
+    ]
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("log_decay", C.c_void_p), ("o", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
+        ("dtype", C.c_int32), ("normalize", C.c_int32), ("q_scale", C.c_float), ("norm_eps", C.c_float),
+    ]
+
+
+class MlaShape(C.Structure):
+    _fields_ = [("batch", C.c_int32), ("heads_q", C.c_int32), ("seq_kv", C.c_int32),
+                ("dim_qk", C.c_int32), ("dim_v", C.c_int32)]
+
+
+class MlaArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("kv", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("shape", MlaShape), ("num_splits", C.c_int32), ("dtype", C.c_int32), ("scale", C.c_float),
+    ]
+
+
+# symbol name -> (restype, argtypes); must list every function of include/attn_b200.h
+SIGNATURES = {
+    "attn_b200_parallel_fwd": (C.c_int, [C.POINTER(ParallelArgs), C.c_void_p]),
+    "attn_b200_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
+    "attn_b200_mla_workspace_bytes": (C.c_int64, [C.POINTER(MlaShape), C.c_int32]),
+    "attn_b200_mla_decode": (C.c_int, [C.POINTER(MlaArgs), C.c_void_p]),
+    "attn_b200_last_device_status": (C.c_int, [C.c_int32, C.POINTER(C.c_int32)]),
+    "attn_b200_device_status_word": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p)]),
+    "attn_b200_version": (C.c_int, []),
+}
+
+_lib = None
+
+
+def library_sources() -> list[str]:
+    return [os.path.join(CSRC_DIR, f) for f in ("attn_b200.cu", "mla_decode.cu", "linear_fwd.cu")]
+
+
+def build_library(force: bool = False, verbose: bool = False) -> str:
+    """Compile libattn_b200.so for sm_100a with nvcc (cross-compiles without a GPU)."""
+    srcs = library_sources()
+    deps = srcs + [os.path.join(CSRC_DIR, f) for f in os.listdir(CSRC_DIR) if f.endswith(".cuh")] + \
+        [os.path.join(INCLUDE_DIR, "attn_b200.h")]
+    if not force and os.path.exists(LIB_PATH) and \
+            os.path.getmtime(LIB_PATH) >= max(os.path.getmtime(d) for d in deps):
+        return LIB_PATH
+    objs = []
+    procs = []
+    for src in srcs:
+        obj = src[:-3] + ".o"
+        cmd = ["nvcc", *NVCC_ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+               "-I", INCLUDE_DIR, "-c", src, "-o", obj]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objs.append(obj)
+    for cmd, pr in procs:
+        out, _ = pr.communicate()
+        if verbose and out:
+            print(out)
+        if pr.returncode != 0:
+            raise NativeError(f"nvcc failed: {' '.join(cmd)}\n{out}")
+    tmp = LIB_PATH + f".tmp{os.getpid()}"
+    link = ["nvcc", *NVCC_ARCH_FLAGS, "-shared", "-o", tmp, *objs]
+    r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise NativeError(f"link failed: {' '.join(link)}\n{r.stdout}")
+    os.replace(tmp, LIB_PATH)
+    return LIB_PATH
+
+
+def bind(lib: C.CDLL, names=None) -> C.CDLL:
+    for name in (names or SIGNATURES):
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype, fn.argtypes = SIGNATURES[name]
+    return lib
+
+
+def load_library() -> C.CDLL:
+    """Load (once) the native library.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NativeError(
+                f"{LIB_PATH} not found: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "from the repository root (there is no non-native fallback)")
+        _lib = bind(C.CDLL(LIB_PATH))
+    return _lib
+
+
+def check(rc: int, what: str):
+    if rc != OK:
+        raise NativeError(f"{what} failed: {ERRORS.get(rc, 'error')} (code {rc})")
+
+
+def current_stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def device_status_word(device: int) -> int:
+    out = C.c_void_p()
+    check(load_library().attn_b200_device_status_word(device, C.byref(out)), "attn_b200_device_status_word")
+    return out.value
+
+
+def last_device_status(device: int | None = None) -> int:
+    """Synchronise and return (then clear) the device status word: 0, or
+    100 + id of the device-side wait that gave up."""
+    if device is None:
+        device = torch.cuda.current_device()
+    out = C.c_int32(0)
+    check(load_library().attn_b200_last_device_status(device, C.byref(out)), "attn_b200_last_device_status")
+    return out.value
+
+
+def _strides_bsh(t: torch.Tensor):
+    """Element strides (batch, seq, head) of a [B, S, H, D] tensor view."""
+    return (t.stride(0), t.stride(1), t.stride(2))
+
+
+def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=(), final_rowscales=(),
+                       custom=(), custom_strides=()) -> ParallelArgs:
+    """q,k: [B,S,H,D]; v,o: [B,S,H,Dv] CUDA tensors (any strides with a contiguous last dim)."""
+    for t in (q, k, v, o):
+        if not t.is_cuda:
+            raise NativeError("parallel forward needs CUDA tensors")
+        if t.stride(-1) != 1:
+            raise NativeError("last dimension must be contiguous")
+    if q.dtype not in DTYPE_CODES or k.dtype != q.dtype or v.dtype != q.dtype or o.dtype != q.dtype:
+        raise NativeError(f"q, k, v, o must share dtype float16 or bfloat16 (got {q.dtype}, {k.dtype}, {v.dtype}, {o.dtype})")
+    a = ParallelArgs()
+    a.q, a.k, a.v, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    for i, t in enumerate(final_rowscales):
+        a.final_rowscales[i] = t.data_ptr() if t is not None else None
+    B, Sq, H, D = q.shape
+    a.batch, a.heads, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, Sq, k.shape[1], D, v.shape[3]
+    a.q_stride[:] = _strides_bsh(q)
+    a.k_stride[:] = _strides_bsh(k)
+    a.v_stride[:] = _strides_bsh(v)
+    a.o_stride[:] = _strides_bsh(o)
+    a.dtype = DTYPE_CODES[q.dtype]
+    a.mask_kind = mask_kind
+    a.functor = functor
+    for i, f in enumerate(fparams):
+        a.fparams[i] = float(f)
+    for i, t in enumerate(custom):
+        a.custom[i] = t.data_ptr()
+        for j, s in enumerate(custom_strides[i]):
+            a.custom_stride[i][j] = int(s)
+    return a
+
+
+def parallel_fwd(args: ParallelArgs):
+    check(load_library().attn_b200_parallel_fwd(C.byref(args), current_stream_ptr()), "attn_b200_parallel_fwd")

@@ -1,0 +1,366 @@
+// Kernel family (1): parallel-pattern attention forward for sm_100a.
+//
+//   O = epilogue( sum over KV tiles of  o_scale-rescaled  P.V ),
+//   P = online_fwd( score_mod( mask + Q.K^T ) )
+//
+// with score_mod / online_fwd / epilogue supplied by a device functor F (the
+// lowered form of the user's score_mod and OnlineFunc).  Replaces the
+// generated TileLang kernel of the reference
+// (attention_engine/core/template/tl_template/attn/attn_tl.py:93-190) and its
+// CuTe warp-specialised forward (core/template/cute_template/flash_fwd_kernel.h:28-199).
+//
+// One CTA owns two 128-row query tiles of one (batch, head) and walks the KV
+// sequence in 128-row tiles:
+//   warp 8      TMA producer: Q once, then K and V tiles into 2-stage rings
+//   warp 9      tcgen05.mma issuer (one thread): S_t = Q_t.K^T into TMEM,
+//               O_t += P_t.V with P_t read from TMEM (aliasing S_t)
+//   warps 0-3   row-per-thread functor stage for query tile 0
+//   warps 4-7   same for query tile 1
+// The two query tiles ping-pong: while the functor stage of one tile runs on
+// the CUDA cores, the tensor pipe works on the other tile.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+DV) O1 [256+DV,256+2DV).
+#pragma once
+
+#include "sm100.cuh"
+
+namespace b200 {
+
+constexpr int kMaxCustom = 4;
+constexpr int kMaxRowScales = 4;
+
+struct FunctorArgs {
+  float f[8];
+  const void* custom[kMaxCustom];
+  long long cstride[kMaxCustom][4];  // element strides of (batch, heads, seq_len, seq_len_kv)
+};
+
+// What a functor knows about the row it is working on.
+struct RowCtx {
+  int b, h, q_idx;   // batch, head, query position of this thread's row
+  int kv0;           // first KV position of the current tile
+  int seq_q, seq_kv;
+  const FunctorArgs* fa;
+};
+
+// Position (1..3) of the head / sequence / batch coordinate inside a 4-D
+// tensor map whose dimension 0 is the feature dimension; the host sorts the
+// three outer dimensions by stride.
+struct CoordOrder {
+  int pos_s, pos_h, pos_b;
+};
+
+struct ParallelParams {
+  void* o;
+  float* final_out[kMaxRowScales];
+  int batch, heads, seq_q, seq_kv;
+  long long o_sb, o_ss, o_sh;  // element strides of o
+  int mask_kind;               // 0 none, 1 causal (keep q_idx >= kv_idx)
+  CoordOrder oq, ok, ov;
+  int* status;
+  FunctorArgs fa;
+};
+
+__device__ __forceinline__ void tma_load_rows(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int s, int h,
+                                              int b, const CoordOrder& o) {
+  const int c1 = (o.pos_s == 1) ? s : (o.pos_h == 1) ? h : b;
+  const int c2 = (o.pos_s == 2) ? s : (o.pos_h == 2) ? h : b;
+  const int c3 = (o.pos_s == 3) ? s : (o.pos_h == 3) ? h : b;
+  tma_load_4d(dst, tm, bar, c0, c1, c2, c3);
+}
+
+// wait-site ids reported through the device status word
+enum ParallelWaitSite {
+  kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePReady, kSiteODone, kSiteOFinal
+};
+
+template <int D, int DV>
+struct ParallelSmem {
+  static constexpr int kBM = 128, kBN = 128, kStages = 2;
+  static constexpr int kQBytes = kBM * D * 2;
+  static constexpr int kKBytes = kBN * D * 2;
+  static constexpr int kVBytes = kBN * DV * 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kOffQ + 2 * kQBytes;
+  static constexpr int kOffV = kOffK + kStages * kKBytes;
+  static constexpr int kOffBar = kOffV + kStages * kVBytes;
+  static constexpr int kNumBars = 1 + 4 * kStages + 6;
+  static constexpr int kOffMisc = kOffBar + 8 * kNumBars;
+  static constexpr int kBytes = kOffMisc + 16 + 1024;  // + slack for manual 1024-byte alignment
+};
+
+template <class F, int D, int DV, bool kBf16>
+__global__ void __launch_bounds__(320, 1)
+parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const ParallelParams p) {
+  using L = ParallelSmem<D, DV>;
+  constexpr int BM = L::kBM, BN = L::kBN, ST = L::kStages;
+  static_assert(D % 64 == 0 && DV % 64 == 0 && D <= 128 && DV <= 128, "unsupported head dims");
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::kOffQ;
+  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sV = smem + L::kOffV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = k_full + ST;
+  uint64_t* v_full = k_empty + ST;
+  uint64_t* v_empty = v_full + ST;
+  uint64_t* s_full = v_empty + ST;   // [2] one per query tile
+  uint64_t* p_ready = s_full + 2;    // [2]
+  uint64_t* o_done = p_ready + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const AbortState ab{abort_flag, p.status};
+
+  const bool causal = p.mask_kind == 1;
+  // heaviest query tiles (largest KV range under a causal mask) are launched first
+  const int m_pair = causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int m0 = m_pair * 2 * BM;
+  const int n_kv_tiles = (p.seq_kv + BN - 1) / BN;
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int row0 = m0 + t * BM;
+    int n = 0;
+    if (row0 < p.seq_q) {
+      n = n_kv_tiles;
+      if (causal) n = min(n, (row0 + BM + BN - 1) / BN);
+    }
+    n_t[t] = n;
+  }
+  const int n_max = max(n_t[0], n_t[1]);
+
+  // ---------------- setup ----------------
+  if (threadIdx.x == 0) {
+    *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_ready[t], 128);
+      mbar_init(&o_done[t], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 8 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // =============== TMA producer ===============
+    if (lane == 0 && n_max > 0 && !*abort_flag) {
+      const int nq = (n_t[1] > 0) ? 2 : 1;
+      mbar_arrive_expect_tx(q_full, nq * L::kQBytes);
+      for (int t = 0; t < nq; ++t)
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, q_full, c * 64, m0 + t * BM, h, b, p.oq);
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % ST;
+        const uint32_t ph = (j / ST) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, ab, kSiteKEmpty)) break;
+        mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, j * BN, h, b, p.ok);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, ab, kSiteVEmpty)) break;
+        mbar_arrive_expect_tx(&v_full[st], L::kVBytes);
+        for (int c = 0; c < DV / 64; ++c)
+          tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, j * BN, h, b, p.ov);
+      }
+    }
+  } else if (warp == 9) {
+    // =============== MMA issuer ===============
+    if (lane == 0 && n_max > 0 && !*abort_flag) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(BM, BN, kBf16, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_f16(BM, DV, kBf16, false, true);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      auto issue_qk = [&](int t, int st) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
+          const uint64_t adesc = make_smem_desc(q_addr + t * L::kQBytes + off, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(k_addr + st * L::kKBytes + off, 16, 1024);
+          umma_ss(tmem_base + kColS + t * BN, adesc, bdesc, idesc_qk, ks > 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int st, bool first) {
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          const uint64_t bdesc = make_smem_desc(v_addr + st * L::kVBytes + ks * 2048, BN * 128, 1024);
+          umma_ts(tmem_base + kColO + t * DV, tmem_base + kColS + t * BN + ks * 8, bdesc, idesc_pv,
+                  (!first || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_done[t]);
+      };
+      bool ok = mbar_wait(q_full, 0, ab, kSiteQFull);
+      ok = ok && mbar_wait(&k_full[0], 0, ab, kSiteKFull);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int t = 0; t < 2; ++t)
+          if (n_t[t] > 0) issue_qk(t, 0);
+        umma_commit(&k_empty[0]);
+        for (int j = 0; j < n_max && ok; ++j) {
+          const int st = j % ST;
+          const int stn = (j + 1) % ST;
+          ok = mbar_wait(&v_full[st], (j / ST) & 1, ab, kSiteVFull);
+          if (ok && j + 1 < n_max) ok = mbar_wait(&k_full[stn], ((j + 1) / ST) & 1, ab, kSiteKFull);
+          if (!ok) break;
+          for (int t = 0; t < 2; ++t) {
+            if (j < n_t[t]) {
+              ok = mbar_wait(&p_ready[t], j & 1, ab, kSitePReady);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue_pv(t, st, j == 0);
+              if (j + 1 < n_t[t]) issue_qk(t, stn);
+            }
+          }
+          if (!ok) break;
+          umma_commit(&v_empty[st]);
+          if (j + 1 < n_max) umma_commit(&k_empty[stn]);
+        }
+      }
+    }
+  } else {
+    // =============== functor stage: one query row per thread ===============
+    const int t = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int q_idx = m0 + t * BM + row;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + kColS + t * BN;
+    const uint32_t tO = tmem_base + lane_base + kColO + t * DV;
+    const int n = n_t[t];
+    float rs[F::kRowScales > 0 ? F::kRowScales : 1];
+    RowCtx ctx{b, h, q_idx, 0, p.seq_q, p.seq_kv, &p.fa};
+    F::init(rs, ctx);
+    bool ok = (n > 0) && !*abort_flag;
+    for (int j = 0; j < n && ok; ++j) {
+      ok = mbar_wait(&s_full[t], j & 1, ab, kSiteSFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld32f(tS + c * 32, &s[c * 32]);
+      tmem_wait_ld();
+      const int kv0 = j * BN;
+      ctx.kv0 = kv0;
+      // a tile needs element masking when it crosses the causal diagonal or the end of the KV sequence
+      const bool crosses = (causal && (kv0 + BN - 1 > m0 + t * BM)) || (kv0 + BN > p.seq_kv);
+      if (crosses) {
+        if (F::kNegInfMask) {
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            const int kv = kv0 + i;
+            const bool keep = (kv < p.seq_kv) && (!causal || kv <= q_idx);
+            s[i] = keep ? s[i] : -INFINITY;
+          }
+        }
+      }
+      const float o_scale = F::template tile<BN>(s, rs, ctx);
+      // P (16-bit, two per column) overwrites the first BN/2 columns of S
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pk[i] = pack2<kBf16>(s[c * 64 + 2 * i], s[c * 64 + 2 * i + 1]);
+        tmem_st32(tS + c * 32, pk);
+      }
+      if (!F::kUnitOScale && j > 0) {
+        const bool need = (o_scale != 1.0f);
+        if (__any_sync(0xffffffffu, need)) {
+          ok = mbar_wait(&o_done[t], (j - 1) & 1, ab, kSiteODone);
+          if (ok) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < DV / 32; ++c) {
+              float o[32];
+              tmem_ld32f(tO + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= o_scale;
+              tmem_st32f(tO + c * 32, o);
+            }
+          }
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&p_ready[t]);
+    }
+    if (ok && n > 0) {
+      ok = mbar_wait(&o_done[t], (n - 1) & 1, ab, kSiteOFinal);
+      if (ok) {
+        tc_fence_after_sync();
+        const bool in_range = q_idx < p.seq_q;
+        uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
+                        2 * (static_cast<long long>(b) * p.o_sb + static_cast<long long>(q_idx) * p.o_ss +
+                             static_cast<long long>(h) * p.o_sh);
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          float o[32];
+          tmem_ld32f(tO + c * 32, o);
+          tmem_wait_ld();
+          F::template epilogue<32>(o, rs, ctx);
+          if (in_range) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
+              pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
+              pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
+              pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
+              *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
+            }
+          }
+        }
+        if (in_range) {
+#pragma unroll
+          for (int i = 0; i < F::kFinal; ++i) {
+            if (p.final_out[i] != nullptr) {
+              p.final_out[i][(static_cast<long long>(b) * p.heads + h) * p.seq_q + q_idx] = F::final_rowscale(i, rs, ctx);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait was abandoned: give copies and MMAs still in flight time to land before the CTA's
+    // shared and tensor memory are released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace b200

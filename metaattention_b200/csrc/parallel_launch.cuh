@@ -1,0 +1,142 @@
+// Host side of kernel family (1): argument validation, tensor-map encoding
+// and launch.  Header-only so that functor libraries compiled at run time
+// instantiate the same launcher as the built-in functors.
+#pragma once
+
+#include <algorithm>
+#include <cstring>
+
+#include "../../include/attn_b200.h"
+#include "parallel_fwd.cuh"
+
+namespace b200 {
+
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                           CUtensorMapFloatOOBfill);
+
+inline TensorMapEncodeTiledFn tensor_map_encoder() {
+  static TensorMapEncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<TensorMapEncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor map over a 16-bit tensor addressed as [batch][seq][head][dim] through
+// element strides (dim contiguous).  Dimension 0 of the map is `dim`; the
+// other three are ordered by increasing stride, and `order` tells the kernel
+// where each coordinate goes.  Box: 64 elements (128 bytes, the swizzle span)
+// of one head and one batch entry by `box_rows` sequence positions.
+inline int encode_rows_map(CUtensorMap* tm, CoordOrder* order, const void* base, int dtype, int dim, int batch,
+                           int seq, int heads, const int64_t stride_bsh[3], int box_rows) {
+  TensorMapEncodeTiledFn enc = tensor_map_encoder();
+  if (enc == nullptr) return ATTN_B200_E_LAUNCH;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  struct Dim { int which; uint64_t size; int64_t stride; };  // which: 0 batch, 1 seq, 2 head
+  Dim dims[3] = {{0, (uint64_t)batch, stride_bsh[0]}, {1, (uint64_t)seq, stride_bsh[1]}, {2, (uint64_t)heads, stride_bsh[2]}};
+  for (auto& d : dims) {
+    if (d.size > 1 && (d.stride <= 0 || (d.stride % 8) != 0)) return ATTN_B200_E_UNSUPPORTED;
+  }
+  // extent-1 dimensions carry no addressing information: move them last
+  std::stable_sort(dims, dims + 3, [](const Dim& a, const Dim& b) {
+    const bool a1 = a.size <= 1, b1 = b.size <= 1;
+    if (a1 != b1) return b1;
+    if (a1 && b1) return false;
+    return a.stride < b.stride;
+  });
+  int64_t next = dim;
+  for (auto& d : dims) {
+    if (d.size <= 1) d.stride = next;
+    next = std::max<int64_t>(next, d.stride * (int64_t)d.size);
+  }
+  cuuint64_t gdim[4] = {(cuuint64_t)dim, dims[0].size, dims[1].size, dims[2].size};
+  cuuint64_t gstride[3] = {(cuuint64_t)dims[0].stride * 2, (cuuint64_t)dims[1].stride * 2, (cuuint64_t)dims[2].stride * 2};
+  cuuint32_t box[4] = {64, 1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  int pos[3] = {0, 0, 0};
+  for (int i = 0; i < 3; ++i) {
+    pos[dims[i].which] = i + 1;
+    if (dims[i].which == 1) box[i + 1] = (cuuint32_t)box_rows;
+  }
+  order->pos_b = pos[0];
+  order->pos_s = pos[1];
+  order->pos_h = pos[2];
+  const CUtensorMapDataType dt = dtype == ATTN_B200_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(tm, dt, 4, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ATTN_B200_OK : ATTN_B200_E_UNSUPPORTED;
+}
+
+inline int validate_parallel_args(const AttnB200ParallelArgs* a) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr) return ATTN_B200_E_INVALID_ARG;
+  if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0) return ATTN_B200_E_INVALID_ARG;
+  if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
+  if (a->mask_kind != ATTN_B200_MASK_NONE && a->mask_kind != ATTN_B200_MASK_CAUSAL) return ATTN_B200_E_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  for (int i = 0; i < 3; ++i)
+    if (a->o_stride[i] % 8 != 0) return ATTN_B200_E_UNSUPPORTED;
+  if (a->heads > 65535 || a->batch > 65535) return ATTN_B200_E_UNSUPPORTED;
+  return ATTN_B200_OK;
+}
+
+template <class F, int D, int DV, bool kBf16>
+int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
+  using L = ParallelSmem<D, DV>;
+  if (a->dim_qk != D || a->dim_v != DV) return ATTN_B200_E_UNSUPPORTED;
+  if (device_status == nullptr) return ATTN_B200_E_INVALID_ARG;
+  CUtensorMap tmQ, tmK, tmV;
+  ParallelParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc = encode_rows_map(&tmQ, &p.oq, a->q, a->dtype, D, a->batch, a->seq_q, a->heads, a->q_stride, L::kBM);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_rows_map(&tmK, &p.ok, a->k, a->dtype, D, a->batch, a->seq_kv, a->heads, a->k_stride, L::kBN);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_rows_map(&tmV, &p.ov, a->v, a->dtype, DV, a->batch, a->seq_kv, a->heads, a->v_stride, L::kBN);
+  if (rc != ATTN_B200_OK) return rc;
+  p.o = a->o;
+  for (int i = 0; i < kMaxRowScales; ++i) p.final_out[i] = a->final_rowscales[i];
+  p.batch = a->batch;
+  p.heads = a->heads;
+  p.seq_q = a->seq_q;
+  p.seq_kv = a->seq_kv;
+  p.o_sb = a->o_stride[0];
+  p.o_ss = a->o_stride[1];
+  p.o_sh = a->o_stride[2];
+  p.mask_kind = a->mask_kind;
+  p.status = device_status;
+  for (int i = 0; i < 8; ++i) p.fa.f[i] = a->fparams[i];
+  for (int i = 0; i < kMaxCustom; ++i) {
+    p.fa.custom[i] = a->custom[i];
+    for (int j = 0; j < 4; ++j) p.fa.cstride[i][j] = a->custom_stride[i][j];
+  }
+  auto kernel = parallel_fwd_kernel<F, D, DV, kBf16>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return ATTN_B200_E_LAUNCH;
+  }
+  dim3 grid((a->seq_q + 2 * L::kBM - 1) / (2 * L::kBM), a->heads, a->batch);
+  kernel<<<grid, 320, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
+  if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  return ATTN_B200_OK;
+}
+
+// Dispatch over the head-dimension / dtype instantiations compiled for functor F.
+template <class F>
+int dispatch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
+  const int rc = validate_parallel_args(a);
+  if (rc != ATTN_B200_OK) return rc;
+  const bool bf16 = a->dtype == ATTN_B200_DTYPE_BF16;
+  if (a->dim_qk == 128 && a->dim_v == 128)
+    return bf16 ? launch_parallel<F, 128, 128, true>(a, stream, device_status)
+                : launch_parallel<F, 128, 128, false>(a, stream, device_status);
+  if (a->dim_qk == 64 && a->dim_v == 64)
+    return bf16 ? launch_parallel<F, 64, 64, true>(a, stream, device_status)
+                : launch_parallel<F, 64, 64, false>(a, stream, device_status);
+  return ATTN_B200_E_UNSUPPORTED;
+}
+
+}  // namespace b200
