@@ -1,0 +1,319 @@
+"""Benchmark of the hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # our arm
+    python bench.py --impl reference --gpus N --steps K ...   # the reference's PyTorch math on the host cores
+
+Headline workload (N=1): BASELINE config 2 -- causal softmax MHA forward, bf16, B=8 H=32 S=4096 D=128,
+output bf16 + per-row log-sum-exp fp32.  A step is one forward over one batch of synthetic inputs.
+With N>1 every rank runs the same workload on its own batch shard (batch x head sharding, no
+collective on the data path): weak scaling, value = total FLOPs of all ranks / max-over-ranks time.
+
+Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` is the same
+forward through AttentionEngine.__call__ with pinned HOST buffers, host<->device copies inside the
+timed region; `roofline` is the forward kernel against the measured bf16 tensor peak; `cpu_baseline`
+is the CPU oracle on a bounded sample; `extras` holds the other BASELINE configs (device-timed).
+"""
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "metaattention_b200"), os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+from oracle import inputs as oracle_inputs  # noqa: E402  (input factory shared with the parity tests)
+
+WORKLOAD = "C2: softmax MHA fwd causal bf16 B=8 H=32 S=4096 D=128 (+lse)"
+C2 = oracle_inputs.CONFIGS["C2"]
+C3 = oracle_inputs.CONFIGS["C3"]
+METRIC = "fwd_attention_tflops"
+UNIT = "TFLOP/s"
+
+# DRAM bytes (read+write) of one forward-kernel launch at the C2 shape from an ncu capture
+# (profiles/parallel_fwd_softmax_c2.md); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def c2_flops(B=C2["B"], H=C2["H"], S=C2["S"], D=C2["D"], Dv=C2["Dv"], causal=True):
+    """Algorithmic FLOPs: 2*B*H*S^2*(D+Dv), halved for a causal mask (reference convention,
+    attention_engine/benchmark/bench_utils.py:770-771)."""
+    f = 2.0 * B * H * S * S * (D + Dv)
+    return f * (0.5 if causal else 1.0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [x for x in sm if x > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_softmax_engine():
+    import programs
+    return programs.softmax_engine(C2["B"], C2["H"], C2["S"], C2["D"], C2["Dv"], dtype=torch.bfloat16, is_causal=True)
+
+
+def build_sigmoid_engine():
+    import programs
+    return programs.sigmoid_engine(C3["B"], C3["H"], C3["S"], C3["D"], C3["Dv"], dtype=torch.bfloat16, is_causal=False,
+                                   scale=C3["D"] ** -0.5)
+
+
+def prebuild_functors():
+    """Compile (without a GPU) the functor libraries the benchmark needs."""
+    import metaattention_b200  # noqa: F401
+    build_softmax_engine()
+    build_sigmoid_engine()
+
+
+def cpu_softmax_sample(n_heads: int, threads: int):
+    """Seconds for the CPU oracle on `n_heads` (batch, head) slices of the C2 problem."""
+    from oracle import reference_math as rm
+    torch.set_num_threads(threads)
+    S, D = C2["S"], C2["D"]
+    q, k, v = oracle_inputs.attention_bshd(1, n_heads, S, D, D, C2["seed"], dtype=torch.bfloat16)
+    rm.softmax_attention(q[:, :, :1], k[:, :, :1], v[:, :, :1], True)  # warm-up
+    t0 = time.perf_counter()
+    for h in range(n_heads):
+        rm.softmax_attention(q[:, :, h:h + 1], k[:, :, h:h + 1], v[:, :, h:h + 1], True)
+        rm.softmax_lse(q[:, :, h:h + 1], k[:, :, h:h + 1], True)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    """The reference's PyTorch reference math (restated in oracle/) on the host cores."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    heads_per_step = 4
+    flops_per_step = c2_flops(B=1, H=heads_per_step)
+    for _ in range(args.warmup):
+        cpu_softmax_sample(1, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_softmax_sample(heads_per_step, threads)
+    dt = time.perf_counter() - t0
+    value = flops_per_step * args.steps / dt / 1e12
+    sample = f"{heads_per_step} of {C2['B'] * C2['H']} (batch, head) slices per step, fp32 PyTorch, softmax + lse"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample": sample},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_device(fn, steps, warmup, barrier):
+    for _ in range(warmup):
+        fn()
+    barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1)  # ms for all steps
+
+
+def extras_parallel(steps, warmup):
+    """Device-timed numbers for BASELINE config 3 (sigmoid attention)."""
+    out = {}
+    try:
+        eng = build_sigmoid_engine()
+        q, k, v = [t.cuda() for t in oracle_inputs.attention_bshd(C3["B"], C3["H"], C3["S"], C3["D"], C3["Dv"], C3["seed"])]
+        bias = torch.tensor([C3["bias"]], device="cuda")
+        ms = time_device(lambda: eng(q, k, v, bias), steps, warmup, lambda: None) / steps
+        fl = c2_flops(causal=False)
+        out["C3_sigmoid_noncausal"] = {"ms": ms, "tflops": fl / ms / 1e9}
+        del q, k, v
+    except Exception as exc:  # a missing extra must not take the headline number down
+        out["C3_sigmoid_noncausal"] = {"error": repr(exc)[:200]}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="shrink the batch of the headline workload (for small profiler captures; not a headline number)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import metaattention_b200  # noqa: F401
+    from core.native import lib
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    lib.load_library()
+    eng = build_softmax_engine()
+    B, H, S, D = C2["B"] if args.batch is None else args.batch, C2["H"], C2["S"], C2["D"]
+    # every rank draws its own shard of the global batch (seed offset by rank): weak scaling
+    q, k, v = oracle_inputs.attention_bshd(B, H, S, D, D, C2["seed"] + rank)
+    hq, hk, hv = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    dq, dk, dv = hq.cuda(non_blocking=True), hk.cuda(non_blocking=True), hv.cuda(non_blocking=True)
+    torch.cuda.synchronize()
+    flops = c2_flops(B=B)
+
+    # ---- device-resident timing ----
+    sampler = ClockSampler(local_rank)
+    for _ in range(args.warmup):
+        eng(dq, dk, dv)
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        eng(dq, dk, dv)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    status = lib.last_device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status}: a kernel wait timed out")
+
+    # ---- end to end through the public API with host buffers ----
+    ho = torch.empty((B, S, H, D), dtype=torch.bfloat16).pin_memory()
+    hl = torch.empty((B, H, S), dtype=torch.float32).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        a, b_, c = hq.cuda(non_blocking=True), hk.cuda(non_blocking=True), hv.cuda(non_blocking=True)
+        o = eng(a, b_, c)
+        ho.copy_(o, non_blocking=True)
+        hl.copy_(eng.last_final_rowscales["lse"], non_blocking=True)
+    e2e_ms = time_device(e2e_step, e2e_steps, 1, barrier) / e2e_steps
+
+    t = torch.tensor([ms_total, e2e_ms], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = t.tolist()
+    ms_step = ms_total / args.steps
+    value = flops * world / ms_step / 1e9
+    e2e_value = flops * world / e2e_ms / 1e9
+
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved = flops / ms_step / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD if args.batch is None else WORKLOAD + f" [batch overridden to {B}]", "global_batch": B * world, "seq_len": S, "heads": H, "head_dim": D,
+                       "parallelism": f"batch-shard x{world}, no collective",
+                       "l2": "inputs (805 MB) larger than L2, no flush needed"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 3 * hq.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2 + hl.numel() * 4},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
+                         "frac_of_nominal_2250": achieved / 2250.0},
+        }
+        if world == 1:
+            threads = os.cpu_count() or 1
+            n_heads = 8
+            secs = cpu_softmax_sample(n_heads, threads)
+            line["cpu_baseline"] = {"value": c2_flops(B=1, H=n_heads) / secs / 1e12, "unit": UNIT, "cores": threads,
+                                    "kind": "port", "sample": f"{n_heads} of {B * H} (batch, head) slices, fp32 PyTorch"}
+            if not args.no_extras:
+                del dq, dk, dv
+                torch.cuda.empty_cache()
+                line["extras"] = extras_parallel(10, 3)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,230 @@
+"""``AttentionEngine`` / ``OnlineFunc``: the user-facing API of the reference
+(attention_engine/attn_engine/attn_engine.py:16-105 ``OnlineFunc``, :108-116
+constructor, :227-343 pattern selection, :399-408 ``__call__``) on top of the
+native sm_100a backend.
+
+What happens at construction: the shapes in ``qkv_meta`` select a pattern
+(same rules as the reference), the user's ``score_mod`` / ``online_func`` are
+traced once into a DAG, ``mask_mod`` is classified, and the DAG is either
+recognised as a built-in functor of ``libattn_b200.so`` or lowered to a C++
+device functor that is compiled (and cached) for the forward-kernel template.
+Tuning arguments are accepted and ignored: kernel configurations are fixed.
+
+There is no CPU or eager fallback: calling an engine needs CUDA tensors, the
+native library and an sm_100a device.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from core.lower import functor as functor_lowering
+from core.lower.trace import probe_softmax_scale, trace_parallel
+from core.native import jit as native_jit
+from core.native import lib as native
+from core.transform.core import CustomIO, SymbolicArray, SymbolScalar, Var, _eval_mask_2d, \
+    mask_depends_on_batch_head
+from core.lower.trace import custom_axes
+
+
+class OnlineFunc:
+    """Base class of user-defined online functions (same protocol as the reference).
+
+    ``__init__`` declares ``online_rowscales`` (running per-row values, each a
+    ``SymbolScalar(name, Var(initial_value_string))``) and ``final_rowscales``
+    (per-row outputs).  ``online_fwd`` maps one score tile and the running row
+    scales to (new scores, new row scales, o_scale); ``online_fwd_epilogue``
+    maps the accumulator and the row scales to (output, final row scales);
+    ``combine`` gives the per-split output scale of a split-KV kernel.
+    ``forward`` / ``backward`` describe the backward recomputation and are not
+    used by the forward-only backend.
+    """
+
+    def __init__(self, online_rowscales: dict, final_rowscales: dict, external_fwd_tensors: CustomIO):
+        self.online_rowscales = online_rowscales
+        self.final_rowscales = final_rowscales
+        self.vars = {"scores": SymbolicArray(), "o_scale": None}
+        self.external_fwd_tensors = external_fwd_tensors
+        self.doosum_rowscales = SymbolicArray("doosum", Var("doosum"), shape_idx=["block_M"])
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        return scores, online_rowscales, SymbolScalar("o_scale", Var("1"))
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        return o, online_rowscales
+
+    @staticmethod
+    def forward(scores, final_rowscales, b, h, q_idx, kv_idx):
+        return scores
+
+    @staticmethod
+    def backward(dp, scores, final_rowscales, doosum_rowscales, b, h, q_idx, kv_idx):
+        return dp
+
+    @staticmethod
+    def combine(final_rowscales):
+        return SymbolScalar("o_scale", Var("1"))
+
+
+class _ForwardOnly(torch.autograd.Function):
+    """Keeps autograd graphs well-formed: the forward runs the native kernel,
+    the backward states clearly that it does not exist."""
+
+    @staticmethod
+    def forward(ctx, runner, *tensors):
+        return runner(*[t.detach() for t in tensors])
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("the B200-native backend implements the forward pass only")
+
+
+def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int) -> int:
+    """MASK_NONE / MASK_CAUSAL for a ``mask_mod(b, h, q_idx, kv_idx)``.  The mask is
+    evaluated on CPU for one (b, h) over the [q_len, kv_len] grid (never the
+    B*H*S*S tensor the reference materialises at core/lower/lower.py:729)."""
+    if mask_mod is None:
+        return native.MASK_NONE
+    if mask_depends_on_batch_head(mask_mod, B, H, q_len, kv_len, "cpu"):
+        raise NotImplementedError("mask_mod depending on batch or head index is not supported by the native backend yet")
+    dense = _eval_mask_2d(mask_mod, 0, 0, q_len, kv_len, "cpu")
+    if bool(dense.all()):
+        return native.MASK_NONE
+    causal = torch.ones(q_len, kv_len, dtype=torch.bool).tril()
+    if torch.equal(dense, causal):
+        return native.MASK_CAUSAL
+    raise NotImplementedError("only mask_mod=None, all-true and causal (q_idx >= kv_idx) masks are supported by the "
+                              "native backend yet")
+
+
+class AttentionEngine:
+    def __init__(self, qkv_meta, custom_fwd_inputs, score_mod, mask_mod, online_func, mask_value="-inf",
+                 device=None, backend="tl", tune=False, tune_file="", tune_bwd=False, tune_file_bwd="",
+                 infer_mask=True, infer_mask_block_M=128, infer_mask_block_N=128, extern_block_mask=False,
+                 use_varlen=False, kv_shared=False):
+        if backend not in ("tl", "cute", "cute_v2"):
+            raise ValueError(f"unknown backend {backend!r}")
+        self.backend = backend          # accepted for source compatibility; every value runs the native kernels
+        self.use_varlen = use_varlen
+        self.block_mask = None
+        self.qkv_meta = qkv_meta
+        self.custom_fwd_inputs = custom_fwd_inputs if custom_fwd_inputs is not None else CustomIO()
+        self.last_final_rowscales: dict[str, torch.Tensor] = {}
+        q_meta, k_meta, v_meta = qkv_meta
+        B, H, Sq, D = q_meta.shape
+        Hkv, Skv = v_meta.shape[1], v_meta.shape[2]
+        Dv = v_meta.shape[3]
+        dtype = q_meta.dtype
+        if dtype not in native.DTYPE_CODES:
+            raise TypeError(f"dtype {dtype} is not supported: use torch.float16 or torch.bfloat16")
+        self.dtype = dtype
+        self.pattern = self._select_pattern(Sq, Skv, H, Hkv, kv_shared)
+        if self.pattern == "mla_decode":
+            from attn_engine.mla import build_mla_decode
+            self.attention = build_mla_decode(self, B, H, Hkv, Skv, D, Dv, dtype, backend)
+        elif self.pattern == "parallel":
+            self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value)
+        else:
+            raise NotImplementedError(
+                f"pattern {self.pattern!r} (q_len={Sq}, kv_len={Skv}, heads={H}, kv_heads={Hkv}) is not covered by the "
+                "native backend yet: it implements the parallel MHA forward, chunked linear attention and MLA decode")
+
+    # pattern selection by shape, as attn_engine.py:227-343 of the reference
+    @staticmethod
+    def _select_pattern(q_len, kv_len, heads, heads_kv, kv_shared) -> str:
+        if kv_shared:
+            return "mla_decode"
+        if q_len != kv_len and heads > heads_kv:
+            return "gqa_decode"
+        if q_len != kv_len and heads == heads_kv:
+            return "mha_decode"
+        if q_len == kv_len and heads == heads_kv:
+            return "parallel"
+        return "gqa"
+
+    # ------------------------------------------------------------------
+    def _build_parallel(self, B, H, S, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value):
+        if (D, Dv) not in ((64, 64), (128, 128)):
+            raise NotImplementedError(f"head dims (qk={D}, v={Dv}) are not covered by the forward kernel yet "
+                                      "(supported: 64/64 and 128/128)")
+        self.mask_kind = classify_mask(mask_mod, B, H, S, S)
+        neg_inf_mask = str(mask_value).strip() in ("-inf", "-float('inf')")
+        self.traced = trace_parallel(score_mod, online_func, self.custom_fwd_inputs)
+        tr = self.traced
+        if len(tr.custom) > native.MAX_CUSTOM:
+            raise NotImplementedError(f"at most {native.MAX_CUSTOM} custom inputs are supported")
+        if len(tr.final) > native.MAX_ROWSCALES or len(tr.rowscale_in) > native.MAX_ROWSCALES:
+            raise NotImplementedError(f"at most {native.MAX_ROWSCALES} row scales are supported")
+        self.final_names = list(tr.final.keys())
+        self.custom_names = list(tr.custom.keys())
+        self._custom_syms = [tr.custom[n] for n in self.custom_names]
+        input_ctype = "__nv_bfloat16" if dtype == torch.bfloat16 else "__half"
+        self._custom_dtypes = [torch.float32 if functor_lowering.custom_kind(s) == "scalar" else dtype
+                               for s in self._custom_syms]
+
+        scale = probe_softmax_scale(tr) if neg_inf_mask else None
+        if scale is not None:
+            self.functor_kind = "builtin_softmax"
+            self._fparams = [scale]
+            self._jit_fn = None
+            native.load_library() if torch.cuda.is_available() else None
+        else:
+            self.functor_kind = "lowered"
+            self._fparams = []
+            fs = functor_lowering.emit_functor(tr, neg_inf_mask=neg_inf_mask, input_ctype=input_ctype)
+            self.functor_source = functor_lowering.translation_unit(fs, D, Dv, dtype == torch.bfloat16)
+            # compile now (works without a GPU); loading is deferred to the first call
+            native_jit.build(self.functor_source)
+            self._jit_fn = None
+        self.attention = self._run_parallel
+
+    def _run_parallel(self, q, k, v, *custom):
+        if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
+            return _ForwardOnly.apply(self._run_parallel_impl, q, k, v, *custom)
+        return self._run_parallel_impl(q, k, v, *custom)
+
+    def _run_parallel_impl(self, q, k, v, *custom):
+        if len(custom) != len(self.custom_names):
+            raise TypeError(f"expected {len(self.custom_names)} custom input tensor(s) {self.custom_names}, got {len(custom)}")
+        if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+            raise ValueError("q, k, v must be [batch, seq, heads, dim]")
+        B, S, H, _ = q.shape
+        Dv = v.shape[3]
+        o = torch.empty((B, S, H, Dv), dtype=q.dtype, device=q.device)
+        finals = [torch.empty((B, H, S), dtype=torch.float32, device=q.device) for _ in self.final_names]
+        tensors, strides = [], []
+        for sym, t, want in zip(self._custom_syms, custom, self._custom_dtypes):
+            t = t.to(device=q.device, dtype=want)
+            st = [0, 0, 0, 0]
+            for dim, ax in enumerate(custom_axes(sym)):
+                if ax is not None and t.shape[dim] > 1:
+                    st[ax] = t.stride(dim)
+            tensors.append(t)
+            strides.append(st)
+        args = native.fill_parallel_args(q, k, v, o, mask_kind=self.mask_kind, functor=native.FUNCTOR_SOFTMAX,
+                                         fparams=self._fparams, final_rowscales=finals, custom=tensors,
+                                         custom_strides=strides)
+        if self.functor_kind == "builtin_softmax":
+            native.parallel_fwd(args)
+        else:
+            if self._jit_fn is None:
+                self._jit_fn = native_jit.load(self.functor_source)
+            status = native.device_status_word(q.device.index if q.device.index is not None else torch.cuda.current_device())
+            native.check(self._jit_fn(C.byref(args), native.current_stream_ptr(), status), "attn_b200_parallel_fwd_jit")
+        self.last_final_rowscales = dict(zip(self.final_names, finals))
+        return o
+
+    # ------------------------------------------------------------------
+    def __call__(self, *args, **kargs):
+        if kargs.get("block_mask") is not None:
+            args = args + (kargs["block_mask"],)
+        elif self.block_mask is not None:
+            args = args + (self.block_mask,)
+        if self.use_varlen:
+            args = args + (kargs.get("cache_seqlens"),)
+        return self.attention(*args)

@@ -1,0 +1,306 @@
+"""Tracing of the user's parallel-pattern callables into one DAG, and a torch
+interpreter of that DAG.
+
+``trace_parallel`` calls ``score_mod``, ``OnlineFunc.online_fwd`` and
+``OnlineFunc.online_fwd_epilogue`` on symbolic inputs the way the reference's
+lowering does (attention_engine/core/lower/lower.py:476-496 for score_mod,
+:319-400 for the online function), but keeps the result as a graph of
+``SymbolScalar`` objects instead of emitting TileLang text.
+
+``run_traced_attention`` executes the traced graph tile by tile on torch
+tensors in the order of the reference kernel's main loop
+(core/template/tl_template/attn/attn_tl.py:133-188): mask prefill, GEMM-1,
+score_mod, online_fwd, rescale of the accumulator, GEMM-2, row-scale update,
+epilogue.  It is used to recognise known patterns by probing and by the tests
+as a CPU statement of what a lowered functor must compute; the product path
+never calls it on user data.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from core.transform.core import (CustomIO, SymbolicArray, SymbolicTensor, SymbolScalar)
+from core.transform.graph import Var
+
+NEG_INF_SENTINEL = -1.0e38  # the reference lowers a "-inf" initial row scale to -1e38 (lower.py:24-30)
+
+
+def init_value(name: str) -> float:
+    """Numeric value of a row-scale initialiser given as a string."""
+    text = str(name).strip()
+    if text in ("-inf", "-INF", "-float('inf')"):
+        return NEG_INF_SENTINEL
+    if text in ("inf", "+inf"):
+        return -NEG_INF_SENTINEL
+    return float(text)
+
+
+@dataclass
+class TracedParallel:
+    scores_in: SymbolScalar
+    index_leaves: dict[str, SymbolScalar]
+    custom: dict[str, SymbolicTensor]
+    rowscale_in: dict[str, SymbolScalar]
+    rowscale_init: dict[str, float]
+    scores_out: SymbolScalar
+    rowscale_out: dict[str, SymbolScalar]
+    o_scale: SymbolScalar | None          # None: identically 1
+    o_in: SymbolScalar
+    o_out: SymbolScalar
+    final: dict[str, SymbolScalar] = field(default_factory=dict)
+
+
+def _is_unit(sym) -> bool:
+    if sym is None:
+        return True
+    code = sym.code
+    if code.type == "Var" and not sym.prev:
+        try:
+            return float(code.name) == 1.0
+        except ValueError:
+            return False
+    if code.type == "Const":
+        return float(code.value) == 1.0
+    return False
+
+
+def trace_parallel(score_mod, online_func, custom_fwd_inputs: CustomIO | None) -> TracedParallel:
+    custom_fwd_inputs = custom_fwd_inputs if custom_fwd_inputs is not None else CustomIO()
+    scores = SymbolicArray("scores", Var("scores"))
+    idx = {
+        "b": SymbolScalar("b", Var("b")),
+        "h": SymbolScalar("h", Var("h")),
+        "q_idx": SymbolScalar("q_idx", Var("q_idx")),
+        "kv_idx": SymbolicArray("kv_idx", Var("kv_idx")),
+    }
+    s1 = scores
+    if score_mod is not None:
+        s1 = score_mod(scores, custom_fwd_inputs, idx["b"], idx["h"], idx["q_idx"], idx["kv_idx"])
+        if not isinstance(s1, SymbolScalar):
+            raise TypeError("score_mod must return the traced score")
+    o_in = SymbolicArray("acc_o", Var("acc_o"), shape_idx=["block_M", "dimv"])
+    if online_func is None:
+        # identity online function (reference examples *_v2.py pass online_func=None)
+        return TracedParallel(scores, idx, dict(custom_fwd_inputs.input_tensors), {}, {}, s1, {}, None, o_in, o_in, {})
+    rs_in = dict(online_func.online_rowscales)
+    rs_init = {k: init_value(v.code.name) for k, v in rs_in.items()}
+    if isinstance(s1, SymbolicArray):
+        s_for_online = s1
+    else:  # a score_mod that returned a plain SymbolScalar tile: re-wrap so get_reduce exists
+        s_for_online = SymbolicArray(s1.varname, s1.code, s1.prev)
+        s_for_online.uid = s1.uid
+    s2, rs_out, o_scale = online_func.online_fwd(s_for_online, rs_in, idx["b"], idx["h"], idx["q_idx"])
+    missing = set(rs_in) - set(rs_out)
+    if missing:
+        raise ValueError(f"online_fwd did not return row scales {sorted(missing)}")
+    o_out, final = online_func.online_fwd_epilogue(o_in, rs_in, idx["b"], idx["h"], idx["q_idx"])
+    extra = dict(getattr(online_func, "external_fwd_tensors", CustomIO()).input_tensors)
+    custom = dict(custom_fwd_inputs.input_tensors)
+    custom.update(extra)
+    return TracedParallel(scores, idx, custom, rs_in, rs_init, s2, dict(rs_out),
+                          None if _is_unit(o_scale) else o_scale, o_in, o_out, dict(final))
+
+
+# --------------------------------------------------------------------------
+# torch interpreter
+# --------------------------------------------------------------------------
+
+_LOG2E = 1.4426950408889634
+
+
+def _eval(sym: SymbolScalar, env: dict, memo: dict):
+    key = id(sym)
+    if key in memo:
+        return memo[key]
+    if key in env:
+        memo[key] = env[key]
+        return env[key]
+    t = sym.code.type
+    if t == "Const":
+        val = float(sym.code.value)
+    elif t == "Var":
+        # an un-bound leaf: numeric initialiser such as Var("1")
+        val = init_value(sym.code.name)
+    else:
+        a = [_eval(p, env, memo) for p in sym.prev]
+        T = torch.as_tensor
+        if t == "Add":
+            val = a[0] + a[1]
+        elif t == "Sub":
+            val = a[0] - a[1]
+        elif t == "Mul":
+            val = a[0] * a[1]
+        elif t == "Div":
+            val = a[0] / a[1]
+        elif t == "Neg":
+            val = -a[0]
+        elif t == "Abs":
+            val = torch.abs(T(a[0]))
+        elif t == "Exp":
+            val = torch.exp(T(a[0]))
+        elif t == "Exp2":
+            val = torch.exp2(T(a[0]))
+        elif t == "Log":
+            val = torch.log(T(a[0]))
+        elif t == "Log2":
+            val = torch.log2(T(a[0]))
+        elif t == "Tanh":
+            val = torch.tanh(T(a[0]))
+        elif t == "Max":
+            val = torch.maximum(T(a[0], dtype=torch.float32), T(a[1], dtype=torch.float32))
+        elif t == "Min":
+            val = torch.minimum(T(a[0], dtype=torch.float32), T(a[1], dtype=torch.float32))
+        elif t == "ReduceSum":
+            val = a[0].sum(-1, keepdim=True)
+        elif t == "ReduceMax":
+            val = a[0].max(-1, keepdim=True).values
+        elif t == "ReduceAbsSum":
+            val = a[0].abs().sum(-1, keepdim=True)
+        elif t == "ColReduceSum":
+            val = a[0].sum(0, keepdim=True)
+        elif t == "ColReduceMax":
+            val = a[0].max(0, keepdim=True).values
+        elif t == "ColReduceAbsSum":
+            val = a[0].abs().sum(0, keepdim=True)
+        else:
+            raise NotImplementedError(f"op {t} in interpreter")
+    memo[key] = val
+    return val
+
+
+def evaluate(outputs, env: dict):
+    """Evaluate traced values given ``env``: {id(leaf symbol): tensor or float}.
+    Tiles are [M, N] tensors, per-row values [M, 1]."""
+    memo: dict = {}
+    return [None if o is None else _eval(o, env, memo) for o in outputs]
+
+
+def custom_axes(sym: SymbolicTensor):
+    """Map a custom tensor's declared shape to the four broadcast axes
+    (batch, heads, seq_len, seq_len_kv): list of axis index or None per dim."""
+    names = {"batch": 0, "heads": 1, "seq_len": 2, "seq_len_kv": 3}
+    return [names.get(s) for s in sym.shape_idx]
+
+
+def _custom_slice(sym: SymbolicTensor, tensor: torch.Tensor, b, h, q0, q1, k0, k1):
+    """[M, N]-broadcastable view of a custom tensor for one (b, h, q range, kv range)."""
+    index = []
+    view_rows, view_cols = 1, 1
+    for dim, ax in enumerate(custom_axes(sym)):
+        size = tensor.shape[dim]
+        if ax == 0:
+            index.append(b if size > 1 else 0)
+        elif ax == 1:
+            index.append(h if size > 1 else 0)
+        elif ax == 2:
+            index.append(slice(q0, q1))
+            view_rows = q1 - q0
+        elif ax == 3:
+            index.append(slice(k0, k1))
+            view_cols = k1 - k0
+        else:
+            index.append(0)
+    out = tensor[tuple(index)].float()
+    return out.reshape(view_rows, view_cols)
+
+
+def run_traced_attention(tr: TracedParallel, q, k, v, custom_tensors=(), causal=False, neg_inf_mask=True,
+                         block_n: int = 128, block_m: int = 128):
+    """Reference-order execution of the traced functor.  q,k: [B,S,H,D], v: [B,S,H,Dv]
+    (any float dtype; computed in fp32).  Returns (o [B,S,H,Dv] fp32, {name: [B,H,S] fp32})."""
+    q, k, v = q.float(), k.float(), v.float()
+    B, Sq, H, _ = q.shape
+    Skv, Dv = k.shape[1], v.shape[3]
+    names = list(tr.custom.keys())
+    tensors = dict(zip(names, custom_tensors))
+    o = torch.zeros(B, Sq, H, Dv)
+    finals = {name: torch.zeros(B, H, Sq) for name in tr.final}
+    qi = torch.arange(Sq).view(-1, 1)
+    for b in range(B):
+        for h in range(H):
+            acc = torch.zeros(Sq, Dv)
+            rs = {name: torch.full((Sq, 1), tr.rowscale_init[name]) for name in tr.rowscale_in}
+            n_tiles = -(-Skv // block_n)
+            for j in range(n_tiles):
+                k0, k1 = j * block_n, min(Skv, (j + 1) * block_n)
+                kvi = torch.arange(k0, k1).view(1, -1)
+                s = q[b, :, h] @ k[b, k0:k1, h].T
+                if causal and neg_inf_mask:
+                    s = s.masked_fill(qi < kvi, float("-inf"))
+                env = {id(tr.scores_in): s,
+                       id(tr.index_leaves["b"]): float(b), id(tr.index_leaves["h"]): float(h),
+                       id(tr.index_leaves["q_idx"]): qi.float(),
+                       id(tr.index_leaves["kv_idx"]): kvi.float().expand(Sq, -1)}
+                for name, sym in tr.custom.items():
+                    env[id(sym)] = _custom_slice(sym, tensors[name], b, h, 0, Sq, k0, k1)
+                for name, sym in tr.rowscale_in.items():
+                    env[id(sym)] = rs[name]
+                outs = evaluate([tr.scores_out, tr.o_scale] + [tr.rowscale_out[n] for n in tr.rowscale_in], env)
+                p, o_scale, new_rs = outs[0], outs[1], outs[2:]
+                if causal and not neg_inf_mask:
+                    # mask_value "0": nothing is masked element-wise; a block of block_m query rows
+                    # simply stops at its diagonal tile (the causal loop bound, attn_tl.py:129-131)
+                    rows_active = ((qi // block_m + 1) * block_m > k0).float()
+                    p = p * rows_active
+                    if o_scale is not None:
+                        o_scale = torch.where(rows_active.bool(), torch.as_tensor(o_scale).expand(Sq, 1), torch.ones(Sq, 1))
+                    new_rs = [torch.where(rows_active.bool(), torch.as_tensor(nv).expand(Sq, 1), rs[n])
+                              for nv, n in zip(new_rs, tr.rowscale_in)]
+                if o_scale is not None:
+                    acc = acc * o_scale
+                acc = acc + torch.as_tensor(p).expand(Sq, k1 - k0) @ v[b, k0:k1, h]
+                for name, nv in zip(tr.rowscale_in, new_rs):
+                    rs[name] = torch.as_tensor(nv, dtype=torch.float32).expand(Sq, 1).clone()
+            env = {id(tr.o_in): acc, id(tr.index_leaves["b"]): float(b), id(tr.index_leaves["h"]): float(h),
+                   id(tr.index_leaves["q_idx"]): qi.float()}
+            for name, sym in tr.rowscale_in.items():
+                env[id(sym)] = rs[name]
+            outs = evaluate([tr.o_out] + list(tr.final.values()), env)
+            o[b, :, h] = torch.as_tensor(outs[0]).expand(Sq, Dv)
+            for name, val in zip(tr.final, outs[1:]):
+                finals[name][b, h] = torch.as_tensor(val).expand(Sq, 1).reshape(Sq)
+    return o, finals
+
+
+def probe_softmax_scale(tr: TracedParallel) -> float | None:
+    """If the traced functor computes online softmax of ``scale * score`` (any
+    algebraically equivalent form, natural or base-2 exponentials) with outputs
+    o / rowsum and a single final row scale equal to the log-sum-exp, return
+    ``scale``; else None.  Decided by running the trace on a small random
+    problem and comparing with the closed form."""
+    if tr.custom or len(tr.final) != 1 or tr.o_scale is None or len(tr.rowscale_in) != 2:
+        return None
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(1, 48, 2, 16, generator=g)
+    k = torch.randn(1, 48, 2, 16, generator=g)
+    v = torch.randn(1, 48, 2, 8, generator=g)
+    try:
+        o, finals = run_traced_attention(tr, q, k, v, causal=True, block_n=16)
+    except Exception:
+        return None
+    lse = next(iter(finals.values()))
+    s = torch.einsum("bshd,bthd->bhst", q, k)
+    causal = torch.ones(48, 48, dtype=torch.bool).tril()
+    # the scale is identified from the lse of rows with two unmasked entries
+    for scale in _candidate_scales(s, lse):
+        sm = (s * scale).masked_fill(~causal, float("-inf"))
+        want_lse = torch.logsumexp(sm, -1)
+        want_o = torch.einsum("bhst,bthd->bshd", torch.softmax(sm, -1), v)
+        if torch.allclose(lse, want_lse, atol=1e-4, rtol=1e-4) and torch.allclose(o, want_o, atol=1e-4, rtol=1e-4):
+            return float(scale)
+    return None
+
+
+def _candidate_scales(s, lse):
+    # row 0 attends to one key: lse = scale * s[0,0]
+    s00 = s[0, 0, 0, 0].item()
+    if abs(s00) < 1e-6:
+        return []
+    c = lse[0, 0, 0].item() / s00
+    if not math.isfinite(c) or c <= 0:
+        return []
+    return [c]

@@ -318,22 +318,20 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
                         2 * (static_cast<long long>(b) * p.o_sb + static_cast<long long>(q_idx) * p.o_ss +
                              static_cast<long long>(h) * p.o_sh);
+        float o[DV];
 #pragma unroll
-        for (int c = 0; c < DV / 32; ++c) {
-          float o[32];
-          tmem_ld32f(tO + c * 32, o);
-          tmem_wait_ld();
-          F::template epilogue<32>(o, rs, ctx);
-          if (in_range) {
+        for (int c = 0; c < DV / 32; ++c) tmem_ld32f(tO + c * 32, &o[c * 32]);
+        tmem_wait_ld();
+        F::template epilogue<DV>(o, rs, ctx);
+        if (in_range) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
-              pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
-              pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
-              pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
-              *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
-            }
+          for (int v = 0; v < DV / 8; ++v) {
+            uint4 pk;
+            pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
+            pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
+            pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
+            pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
+            *reinterpret_cast<uint4*>(orow + v * 16) = pk;
           }
         }
         if (in_range) {

@@ -1,0 +1,116 @@
+"""User-level programs against the AttentionEngine API, written for the tests
+and the benchmark (the reference's examples/*.py are exercised directly from
+the reference checkout where one is present; these cover the same patterns)."""
+
+import math
+
+import torch
+from attn_engine import AttentionEngine, LinearAttentionEngine, OnlineFunc
+from core import CustomIO, SymbolScalar, Var, meta_tensor
+
+
+def _meta(B, H, S, D, Dv, dtype):
+    return (meta_tensor(B, H, S, D, dtype=dtype), meta_tensor(B, H, S, D, dtype=dtype),
+            meta_tensor(B, H, S, Dv, dtype=dtype))
+
+
+def causal(b, h, q_idx, kv_idx):
+    return q_idx >= kv_idx
+
+
+class NaturalSoftmax(OnlineFunc):
+    """Online softmax with natural exponentials on pre-scaled scores."""
+
+    def __init__(self):
+        super().__init__({"m": SymbolScalar("m", Var("-inf")), "r": SymbolScalar("r", Var("0.0"))},
+                         {"lse": SymbolScalar("lse", Var("0.0"))}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        m, r = online_rowscales["m"], online_rowscales["r"]
+        m_new = m.max(scores.get_reduce("max"))
+        shrink = (m - m_new).exp()
+        p = (scores - m_new).exp()
+        return p, {"m": m_new, "r": r * shrink + p.get_reduce("sum")}, shrink
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        r, m = online_rowscales["r"], online_rowscales["m"]
+        return o / r, {"lse": r.log() + m}
+
+
+def softmax_engine(B, H, S, D, Dv, dtype=torch.bfloat16, is_causal=True, scale=None):
+    scale = D ** -0.5 if scale is None else scale
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({}), score_mod=score_mod,
+                           mask_mod=causal if is_causal else None, online_func=NaturalSoftmax())
+
+
+def softmax_engine_noprobe(B, H, S, D, Dv, dtype=torch.bfloat16, is_causal=True):
+    """Same math, but with a second (unused by the output) final row scale so that the
+    built-in softmax functor is NOT selected: exercises the generic lowering of an online
+    function with running row scales and accumulator rescaling."""
+    scale = D ** -0.5
+
+    class TwoFinals(NaturalSoftmax):
+        def __init__(self):
+            OnlineFunc.__init__(self, {"m": SymbolScalar("m", Var("-inf")), "r": SymbolScalar("r", Var("0.0"))},
+                                {"lse": SymbolScalar("lse", Var("0.0")), "rowmax": SymbolScalar("rowmax", Var("0.0"))},
+                                CustomIO())
+
+        @staticmethod
+        def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+            r, m = online_rowscales["r"], online_rowscales["m"]
+            return o / r, {"lse": r.log() + m, "rowmax": m}
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({}), score_mod=score_mod,
+                           mask_mod=causal if is_causal else None, online_func=TwoFinals())
+
+
+def sigmoid_engine(B, H, S, D, Dv, dtype=torch.bfloat16, is_causal=False, scale=1.0, online="identity"):
+    """score = sigmoid(scale * q.k + bias) in tanh form; ``bias`` is a (1,) fp32 custom input."""
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        x = score * scale + custom.input_tensors["softmax_bias"]
+        return ((x * 0.5).tanh() + 1) * 0.5
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({"softmax_bias": (1,)}), score_mod=score_mod,
+                           mask_mod=causal if is_causal else None,
+                           online_func=None if online is None else OnlineFunc({}, {}, CustomIO()))
+
+
+def relu_engine(B, H, S, D, Dv, dtype=torch.bfloat16):
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return (score * scale).max(0)
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({}), score_mod=score_mod, mask_mod=None,
+                           online_func=None)
+
+
+class AbsSumNormaliser(OnlineFunc):
+    """Retention's normaliser: divide by max(running sum of |scores|, 1)."""
+
+    def __init__(self):
+        super().__init__({"acc": SymbolScalar("acc", Var("0.0")), "den": SymbolScalar("den", Var("0.0"))},
+                         {"den": SymbolScalar("den", Var("0.0"))}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        acc = online_rowscales["acc"] + scores.get_reduce("abssum")
+        den_new = acc.max(1.0)
+        return scores / den_new, {"acc": acc, "den": den_new}, online_rowscales["den"] / den_new
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        return o, {"den": online_rowscales["den"]}
+
+
+def retention_parallel_engine(B, H, S, D, Dv, dtype=torch.bfloat16):
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * custom.input_tensors["mask"]
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({"mask": (1, "heads", "seq_len", "seq_len_kv")}),
+                           score_mod=score_mod, mask_mod=causal, online_func=AbsSumNormaliser(), mask_value="0")

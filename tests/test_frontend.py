@@ -1,0 +1,142 @@
+"""Front-end behaviour on CPU: tracing objects, pattern selection, mask
+classification, pattern probing and the meaning of lowered functors (checked
+through the torch interpreter of the traced DAG against the oracle)."""
+
+import math
+import os
+
+import pytest
+import torch
+
+import programs
+from attn_engine import AttentionEngine, OnlineFunc
+from core import CustomIO, SymbolicArray, SymbolScalar, Var, meta_tensor
+from core.lower import functor as fl
+from core.lower.trace import probe_softmax_scale, run_traced_attention, trace_parallel
+from core.transform.core import create_block_mask, is_causal_mask, is_less_causal_mask
+from oracle import inputs, reference_math as rm
+
+
+def test_symbolic_ops_build_dag():
+    s = SymbolicArray("scores", Var("scores"))
+    m = SymbolScalar("m", Var("-inf"))
+    m_new = m.max(s.get_reduce("max"))
+    p = (s - m_new).exp()
+    assert isinstance(p, SymbolicArray) and p.shape_idx == ["block_M", "block_N"]
+    assert m_new.shape_idx == ["block_M"] and m_new.code.type == "Max"
+    assert str(p.code).startswith("Exp(Sub(")
+    assert (2.0 - s).code.type == "Sub" and (1.0 / s).code.type == "Div"
+    with pytest.raises(NotImplementedError):
+        p.backward()
+
+
+def test_customio_decorator_registers_tensor():
+    io = CustomIO({"bias": (1,)})
+    io("extra", (1, "heads"))
+    assert set(io.input_tensors) == {"bias", "extra"}
+    with pytest.raises(ValueError):
+        io("bias", (1,))
+
+
+def test_block_mask_helpers():
+    causal = lambda b, h, q, kv: q >= kv
+    bm = create_block_mask(causal, 2, 3, 512, 512, "cpu")
+    assert bm.shape == (2, 3, 4, 4) and bm.dtype == torch.int8
+    assert bool(is_causal_mask(bm, 128, 128)) and bool(is_less_causal_mask(bm, 128, 128))
+    window = lambda b, h, q, kv: (q >= kv) & (q - kv < 100)
+    bw = create_block_mask(window, 1, 1, 512, 512, "cpu")
+    assert not bool(is_causal_mask(bw, 128, 128)) and bool(is_less_causal_mask(bw, 128, 128))
+    per_head = lambda b, h, q, kv: q >= kv + h
+    bh = create_block_mask(per_head, 1, 2, 256, 256, "cpu", 64, 64)
+    assert bh.shape == (1, 2, 4, 4)
+
+
+def test_pattern_selection_follows_reference_rules():
+    sel = AttentionEngine._select_pattern
+    assert sel(1, 4096, 128, 1, True) == "mla_decode"
+    assert sel(1, 4096, 32, 8, False) == "gqa_decode"
+    assert sel(1, 4096, 16, 16, False) == "mha_decode"
+    assert sel(2048, 2048, 16, 16, False) == "parallel"
+    assert sel(2048, 2048, 32, 8, False) == "gqa"
+
+
+def test_unsupported_patterns_raise_clearly():
+    meta = (meta_tensor(1, 16, 1, 128, dtype=torch.float16), meta_tensor(1, 16, 4096, 128, dtype=torch.float16),
+            meta_tensor(1, 16, 4096, 128, dtype=torch.float16))
+    with pytest.raises(NotImplementedError, match="mha_decode"):
+        AttentionEngine(meta, CustomIO({}), None, None, None)
+    with pytest.raises(TypeError):
+        AttentionEngine(programs._meta(1, 2, 128, 64, 64, torch.float32), CustomIO({}), None, None, None)
+
+
+def test_softmax_forms_are_recognised_as_builtin():
+    e = programs.softmax_engine(1, 2, 256, 64, 64)
+    assert e.functor_kind == "builtin_softmax" and abs(e._fparams[0] - 0.125) < 1e-6 and e.mask_kind == 1
+    e2 = programs.softmax_engine(1, 2, 256, 128, 128, is_causal=False, scale=0.3)
+    assert e2.functor_kind == "builtin_softmax" and abs(e2._fparams[0] - 0.3) < 1e-6 and e2.mask_kind == 0
+    assert programs.softmax_engine_noprobe(1, 2, 256, 64, 64).functor_kind == "lowered"
+    assert programs.sigmoid_engine(1, 2, 256, 64, 64).functor_kind == "lowered"
+
+
+def _interp(engine, q, k, v, custom=(), causal=False, neg_inf=True):
+    return run_traced_attention(engine.traced, q, k, v, custom, causal=causal, neg_inf_mask=neg_inf)
+
+
+def test_traced_softmax_means_softmax():
+    q, k, v = inputs.attention_bshd(1, 2, 200, 64, 64, 3, dtype=torch.float32)
+    e = programs.softmax_engine_noprobe(1, 2, 200, 64, 64)
+    o, fin = _interp(e, q, k, v, causal=True)
+    assert torch.allclose(o, rm.softmax_attention(q, k, v, True), atol=1e-5)
+    assert torch.allclose(fin["lse"], rm.softmax_lse(q, k, True), atol=1e-5)
+
+
+def test_traced_sigmoid_relu_retention_mean_the_reference_math():
+    q, k, v = inputs.attention_bshd(1, 2, 160, 64, 64, 4, dtype=torch.float32)
+    bias = torch.tensor([-2.0])
+    e = programs.sigmoid_engine(1, 2, 160, 64, 64, is_causal=True)
+    o, _ = _interp(e, q, k, v, (bias,), causal=True)
+    assert torch.allclose(o, rm.sigmoid_attention(q, k, v, bias, True), atol=1e-5)
+    o, _ = _interp(programs.relu_engine(1, 2, 160, 64, 64), q, k, v)
+    assert torch.allclose(o, rm.relu_attention(q, k, v), atol=1e-4)
+    mask = torch.rand(1, 2, 160, 160, generator=torch.Generator().manual_seed(1)).tril()
+    e = programs.retention_parallel_engine(1, 2, 160, 64, 64)
+    o, fin = _interp(e, q, k, v, (mask,), causal=True, neg_inf=False)
+    assert torch.allclose(o, rm.retention_parallel(q, k, v, mask), atol=1e-5)
+
+
+def test_emitted_functor_source_shape():
+    e = programs.sigmoid_engine(1, 2, 256, 128, 128)
+    src = e.functor_source
+    assert "kUnitOScale = true" in src and "fast_tanh(fmaf(s[i]" in src
+    assert "attn_b200_parallel_fwd_jit" in src
+    e = programs.softmax_engine_noprobe(1, 2, 256, 64, 64)
+    # exp(s*scale - m) must collapse to one FMA feeding exp2
+    assert "b200::fast_exp2(fmaf(s[i]" in e.functor_source and "kFinal = 2" in e.functor_source
+
+
+def test_engine_needs_cuda_tensors():
+    e = programs.softmax_engine(1, 2, 128, 64, 64)
+    q, k, v = inputs.attention_bshd(1, 2, 128, 64, 64, 1)
+    with pytest.raises(Exception):
+        e(q, k, v)   # CPU tensors: there is no CPU fallback
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/examples"), reason="reference checkout not present")
+def test_reference_examples_construct_unchanged():
+    """The reference's own example programs run unchanged on top of this package."""
+    import importlib
+    import sys
+    sys.path.insert(0, "/root/reference")
+    try:
+        mha = importlib.import_module("examples.mha")
+        assert mha.causal_softmax_attention(1, 4, 512, 128, 128, dtype=torch.bfloat16).functor_kind == "builtin_softmax"
+        v2 = importlib.import_module("examples.mha_v2")
+        assert v2.causal_softmax_attention(1, 4, 512, 128, 128).functor_kind == "builtin_softmax"
+        sg = importlib.import_module("examples.sigmoid_attn")
+        assert sg.sigmoid_attention(1, 4, 512, 128, 128).functor_kind == "lowered"
+        sg2 = importlib.import_module("examples.sigmoid_attn_v2")
+        assert sg2.sigmoid_attention(1, 4, 512, 128, 128).functor_kind == "lowered"
+        relu = importlib.import_module("examples.reluattn")
+        assert relu.relu_attention(1, 6, 512, 64, 64).mask_kind == 0
+    finally:
+        sys.path.remove("/root/reference")
