@@ -197,6 +197,33 @@ def extras_parallel(steps, warmup):
     return out
 
 
+def extras_mla(steps, warmup):
+    """Device-timed numbers for BASELINE config 5 (MLA decode): algorithmic bytes = latent KV + Q + O."""
+    c = oracle_inputs.CONFIGS["C5"]
+    out = {}
+    try:
+        from attn_engine.mla import mla_decode_forward, plan_splits
+        B, H, S, D, Dv = c["B"], c["H"], c["S"], c["D"], c["Dv"]
+        g = torch.Generator(device="cuda").manual_seed(c["seed"])
+        q = torch.randn(B, H, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        kv = torch.empty(B, S, D, device="cuda", dtype=torch.bfloat16)
+        for b0 in range(0, B, 16):  # drawn in slices to bound the fp32 staging buffer
+            kv[b0:b0 + 16] = torch.randn(16, S, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        splits = plan_splits(B, H, S, D, Dv, torch.cuda.get_device_properties(0).multi_processor_count)
+        ms = time_device(lambda: mla_decode_forward(q, kv, Dv, D ** -0.5, num_splits=splits), steps, warmup, lambda: None) / steps
+        bytes_alg = (B * S * D + B * H * D + B * H * Dv) * 2
+        flops = 2.0 * B * H * S * (D + Dv)
+        peaks = measured_peaks()
+        out["C5_mla_decode"] = {"ms": ms, "gbs": bytes_alg / ms / 1e6, "tflops": flops / ms / 1e9, "num_splits": splits,
+                                "frac_of_hbm_peak": bytes_alg / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
+                                "algorithmic_bytes": bytes_alg}
+        del q, kv
+    except Exception as exc:
+        out["C5_mla_decode"] = {"error": repr(exc)[:200]}
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -310,6 +337,7 @@ def main():
                 del dq, dk, dv
                 torch.cuda.empty_cache()
                 line["extras"] = extras_parallel(10, 3)
+                line["extras"].update(extras_mla(10, 3))
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -116,16 +116,23 @@ int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t*
 int64_t attn_b200_mla_workspace_bytes(const AttnB200MlaShape* shape, int32_t num_splits);
 
 typedef struct AttnB200MlaArgs {
-  const void* q;     /* [batch, heads_q, dim_qk] */
-  const void* kv;    /* [batch, seq_kv, dim_qk] latent KV, contiguous per sequence; V = first dim_v columns */
-  void* o;           /* [batch, heads_q, dim_v] */
-  float* lse;        /* [batch, heads_q] fp32 natural-log sum-exp of scaled scores, or NULL */
-  void* workspace;   /* attn_b200_mla_workspace_bytes() bytes */
+  const void* q;        /* [batch, heads_q, dim_qk], or its first dim_v columns when q_rope is given      */
+  const void* kv;       /* [batch, seq_kv, dim_qk] latent KV, or its first dim_v columns when kv_rope is given;
+                           V = the first dim_v columns of a latent row                                    */
+  const void* q_rope;   /* NULL, or the last dim_qk-dim_v query columns held in a separate tensor         */
+  const void* kv_rope;  /* NULL, or the last dim_qk-dim_v latent columns held in a separate tensor        */
+  int64_t q_stride[2];        /* element strides of (batch, head)  of q        */
+  int64_t kv_stride[2];       /* element strides of (batch, token) of kv       */
+  int64_t q_rope_stride[2];   /* same for q_rope  (ignored when q_rope  is NULL) */
+  int64_t kv_rope_stride[2];  /* same for kv_rope (ignored when kv_rope is NULL) */
+  void* o;              /* [batch, heads_q, dim_v] contiguous */
+  float* lse;           /* [batch, heads_q] fp32 natural-log sum-exp of scaled scores, or NULL */
+  void* workspace;      /* attn_b200_mla_workspace_bytes() bytes */
   int64_t workspace_bytes;
   AttnB200MlaShape shape;
   int32_t num_splits;
   int32_t dtype;
-  float scale;       /* softmax scale, e.g. 1/sqrt(dim_qk) */
+  float scale;          /* softmax scale, e.g. 1/sqrt(dim_qk) */
 } AttnB200MlaArgs;
 
 /* Split-KV decode + combine.  Replaces flash_fwd_splitkv_mla_kernel and

@@ -1,5 +1,132 @@
-"""placeholder, filled in with the MLA decode kernel"""
+"""MLA decode on the native split-KV kernels (``kv_shared=True`` engines).
+
+Two calling conventions of the reference are kept:
+
+* ``backend="tl"`` -- ``mod(q, q_pe, kv, k_pe) -> o`` with q ``[B,1,H,Dv]``,
+  q_pe ``[B,1,H,D-Dv]``, kv ``[B,S,1,Dv]``, k_pe ``[B,S,1,D-Dv]``
+  (core/template/tl_template/attn/mla_decode_tl.py:450-465, testing/test.py:842-848);
+* ``backend="cute"`` -- ``mod(q, KV) -> (out, lse)`` with q ``[B,1,H,D]`` and the
+  latent cache as 64-token pages ``[B*S/64, 64, 1, D]`` under an identity block
+  table (attn_engine.py:199-224, cute_template_kvshared/flash_mla_interface.py:98-115).
+
+As in the reference's MLA lowering (core/lower/lower_decode_mla.py:25-38) the
+softmax is fixed: ``score_mod`` / ``online_func`` passed to the engine are not
+consulted; the scale is 1/sqrt(D).  The rope part may live in separate tensors:
+the kernel reads both through their own tensor maps, nothing is concatenated.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from core.native import lib as native
+
+_sm_count_cache: dict[int, int] = {}
 
 
-def build_mla_decode(*a, **k):
-    raise NotImplementedError("MLA decode not built yet")
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count_cache:
+        _sm_count_cache[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count_cache[idx]
+
+
+def plan_splits(batch: int, heads: int, seq_kv: int, dim_qk: int, dim_v: int, sm_count: int) -> int:
+    shape = native.MlaShape(batch, heads, seq_kv, dim_qk, dim_v)
+    out = C.c_int32(0)
+    native.check(native.load_library().attn_b200_mla_plan(C.byref(shape), sm_count, C.byref(out)), "attn_b200_mla_plan")
+    return out.value
+
+
+def workspace_bytes(batch: int, heads: int, seq_kv: int, dim_qk: int, dim_v: int, num_splits: int) -> int:
+    shape = native.MlaShape(batch, heads, seq_kv, dim_qk, dim_v)
+    return int(native.load_library().attn_b200_mla_workspace_bytes(C.byref(shape), num_splits))
+
+
+def _rows(t: torch.Tensor, what: str):
+    """[B, R, C] view of a [B,R,C], [B,1,R,C] or [B,R,1,C] tensor, last dim contiguous."""
+    if t.dim() == 4:
+        if t.shape[1] == 1:
+            t = t[:, 0]
+        elif t.shape[2] == 1:
+            t = t[:, :, 0]
+        else:
+            raise ValueError(f"{what}: expected a singleton axis, got shape {tuple(t.shape)}")
+    if t.dim() != 3 or t.stride(-1) != 1:
+        raise ValueError(f"{what}: expected [batch, rows, cols] with contiguous columns, got {tuple(t.shape)}")
+    return t
+
+
+def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=None, num_splits: int | None = None,
+                       workspace: torch.Tensor | None = None):
+    """q: [B,H,D] (or [B,1,H,D]); kv: [B,S,D] (or [B,S,1,D]).  With ``q_rope`` /
+    ``kv_rope`` given, q and kv hold only the first ``dim_v`` columns.
+    Returns (o [B,H,dim_v] in the input dtype, lse [B,H] fp32)."""
+    q3, kv3 = _rows(q, "q"), _rows(kv, "kv")
+    if not q3.is_cuda:
+        raise native.NativeError("MLA decode needs CUDA tensors")
+    B, H, dq = q3.shape
+    S = kv3.shape[1]
+    rope_dim = 0
+    qr3 = kr3 = None
+    if (q_rope is None) != (kv_rope is None):
+        raise ValueError("q_rope and kv_rope must be given together")
+    if q_rope is not None:
+        qr3, kr3 = _rows(q_rope, "q_rope"), _rows(kv_rope, "kv_rope")
+        rope_dim = qr3.shape[2]
+    dim_qk = dq + rope_dim
+    if q3.dtype not in native.DTYPE_CODES or kv3.dtype != q3.dtype:
+        raise native.NativeError("q and kv must share dtype float16 or bfloat16")
+    with torch.cuda.device(q3.device):
+        if num_splits is None:
+            num_splits = plan_splits(B, H, S, dim_qk, dim_v, _sm_count(q3.device))
+        need = workspace_bytes(B, H, S, dim_qk, dim_v, num_splits)
+        if need < 0:
+            raise native.NativeError(f"MLA decode does not support dims qk={dim_qk} v={dim_v}")
+        if need > 0 and (workspace is None or workspace.numel() * workspace.element_size() < need):
+            workspace = torch.empty(need, dtype=torch.uint8, device=q3.device)
+        o = torch.empty((B, H, dim_v), dtype=q3.dtype, device=q3.device)
+        lse = torch.empty((B, H), dtype=torch.float32, device=q3.device)
+        a = native.MlaArgs()
+        a.q, a.kv = q3.data_ptr(), kv3.data_ptr()
+        a.q_stride[:] = (q3.stride(0), q3.stride(1))
+        a.kv_stride[:] = (kv3.stride(0), kv3.stride(1))
+        if qr3 is not None:
+            a.q_rope, a.kv_rope = qr3.data_ptr(), kr3.data_ptr()
+            a.q_rope_stride[:] = (qr3.stride(0), qr3.stride(1))
+            a.kv_rope_stride[:] = (kr3.stride(0), kr3.stride(1))
+        a.o, a.lse = o.data_ptr(), lse.data_ptr()
+        a.workspace = workspace.data_ptr() if need > 0 else None
+        a.workspace_bytes = need
+        a.shape = native.MlaShape(B, H, S, dim_qk, dim_v)
+        a.num_splits = num_splits
+        a.dtype = native.DTYPE_CODES[q3.dtype]
+        a.scale = float(scale)
+        native.check(native.load_library().attn_b200_mla_decode(C.byref(a), native.current_stream_ptr()),
+                     "attn_b200_mla_decode")
+    return o, lse
+
+
+def build_mla_decode(engine, B, H, Hkv, Skv, D, Dv, dtype, backend):
+    if Hkv != 1:
+        raise NotImplementedError("MLA decode expects a single shared latent KV head")
+    scale = D ** -0.5
+    engine.mla_scale = scale
+
+    if backend == "tl":
+        def attention(q, q_pe, kv, k_pe):
+            o, lse = mla_decode_forward(q, kv, Dv, scale, q_rope=q_pe, kv_rope=k_pe)
+            engine.last_final_rowscales = {"lse": lse}
+            return o.view(o.shape[0], 1, o.shape[1], o.shape[2])
+        return attention
+
+    def attention_paged(q, kv_pages):
+        # identity block table over 64-token pages: the pages of one sequence are contiguous
+        Bq = q.shape[0]
+        kv = kv_pages.reshape(Bq, -1, kv_pages.shape[-1])
+        o, lse = mla_decode_forward(q, kv, Dv, scale)
+        engine.last_final_rowscales = {"lse": lse}
+        return o.view(Bq, 1, o.shape[1], o.shape[2]), lse.view(Bq, lse.shape[1], 1)
+    return attention_paged

@@ -74,7 +74,10 @@ class MlaShape(C.Structure):
 
 class MlaArgs(C.Structure):
     _fields_ = [
-        ("q", C.c_void_p), ("kv", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("q", C.c_void_p), ("kv", C.c_void_p), ("q_rope", C.c_void_p), ("kv_rope", C.c_void_p),
+        ("q_stride", C.c_int64 * 2), ("kv_stride", C.c_int64 * 2),
+        ("q_rope_stride", C.c_int64 * 2), ("kv_rope_stride", C.c_int64 * 2),
+        ("o", C.c_void_p), ("lse", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("shape", MlaShape), ("num_splits", C.c_int32), ("dtype", C.c_int32), ("scale", C.c_float),
     ]

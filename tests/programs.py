@@ -114,3 +114,14 @@ def retention_parallel_engine(B, H, S, D, Dv, dtype=torch.bfloat16):
         return score * custom.input_tensors["mask"]
     return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({"mask": (1, "heads", "seq_len", "seq_len_kv")}),
                            score_mod=score_mod, mask_mod=causal, online_func=AbsSumNormaliser(), mask_value="0")
+
+
+def mla_engine(B, H, S, D, Dv, dtype=torch.bfloat16, backend="tl"):
+    """MLA decode engine: one query token, a single latent KV head shared by all query heads."""
+    meta = (meta_tensor(B, H, 1, D, dtype=dtype), meta_tensor(B, 1, S, D, dtype=dtype), meta_tensor(B, 1, S, Dv, dtype=dtype))
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=NaturalSoftmax(),
+                           kv_shared=True, backend=backend)
