@@ -224,6 +224,28 @@ def extras_mla(steps, warmup):
     return out
 
 
+def extras_retention(steps, warmup):
+    """Device-timed numbers for BASELINE config 4 (chunked RetNet retention, group-normalised output)."""
+    c = oracle_inputs.CONFIGS["C4"]
+    out = {}
+    try:
+        from attn_engine.linear_attn_engine import linear_attention_forward
+        B, H, S, Dk, Dv, C = c["B"], c["H"], c["S"], c["D"], c["Dv"], c["chunk"]
+        q, k, v, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(B, H, S, Dk, Dv, c["seed"])]
+        ld = decay.log()
+        flops = float(B * H * S) * (2 * C * (Dk + Dv) + 4 * Dk * Dv)   # chunked count with the reference's chunk of 64
+        io_bytes = (2 * B * H * S * Dk + 2 * B * H * S * Dv) * 2
+        for name, norm in (("C4_retention_normalised", True), ("C4_retention_raw", False)):
+            ms = time_device(lambda: linear_attention_forward(q, k, v, ld, q_scale=Dk ** -0.5, normalize=norm),
+                             steps, warmup, lambda: None) / steps
+            out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "gbs_min_io": io_bytes / ms / 1e6}
+        del q, k, v
+    except Exception as exc:
+        out["C4_retention"] = {"error": repr(exc)[:200]}
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -338,6 +360,7 @@ def main():
                 torch.cuda.empty_cache()
                 line["extras"] = extras_parallel(10, 3)
                 line["extras"].update(extras_mla(10, 3))
+                line["extras"].update(extras_retention(10, 3))
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -94,7 +94,12 @@ typedef struct AttnB200LinearArgs {
   int32_t normalize;     /* 0: raw output; 1: per-(token, head) group norm over dim_v, eps below, no affine */
   float q_scale;         /* q_mod of the form q * const */
   float norm_eps;
+  void* workspace;       /* attn_b200_linear_workspace_bytes() bytes (only needed with normalize = 1) */
+  int64_t workspace_bytes;
 } AttnB200LinearArgs;
+
+/* Bytes of scratch the linear forward needs: per-row (sum, sum of squares) fp32 when normalize = 1, else 0. */
+int64_t attn_b200_linear_workspace_bytes(const AttnB200LinearArgs* args);
 
 /* Replaces chunk_local_cumsum_scalar + chunk_fwd_h + chunk_o and their wrapper
  * (core/template/tl_template/linear/linear_tl.py:36-60, :146-223, :321-401, :1240-1268). */

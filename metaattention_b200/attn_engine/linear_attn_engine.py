@@ -1,6 +1,206 @@
-"""placeholder, filled in with the chunked linear-attention kernel"""
+"""``LinearAttentionEngine``: chunked linear attention / retention on the native
+sm_100a kernel (reference: attention_engine/attn_engine/linear_attn_engine.py:11-65,
+lowering core/lower/lower_linear.py:290-409, wrapper linear_tl.py:1240-1268).
+
+``mod(q, k, v, decay, *custom)`` with q ``[B,HQ,T,Dk]``, k ``[B,HK,T,Dk]``,
+v ``[B,H,T,Dv]``, decay ``[B,H,T]`` fp32 returns o ``[B,H,T,Dv]``.
+
+The user's ``decay_mod`` / ``k_mod`` / ``v_mod`` are traced once and applied as
+whole-tensor torch operations on the device before the kernel, which is what
+the reference does with generated PyTorch statements (lower_linear.py:138-206);
+``decay_mod`` must produce the natural log of the per-token decay (RetNet:
+``decay.log()``).  A ``q_mod`` of the form ``q * const`` is folded into the
+kernel (the reference fuses q_mod into its output kernel, linear_tl.py:368-370);
+any other ``q_mod`` is applied like the others.  Tuning arguments are accepted
+and ignored.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from core.native import lib as native
+from core.transform.core import CustomIO, SymbolicArray, SymbolScalar
+from core.transform.graph import Var
+
+
+def _align(a, b):
+    """Broadcast rule of the reference's whole-tensor statements (codegen/tl_gen.py:253-262):
+    operands are aligned on their LEADING axes; the shorter one gets trailing singleton axes."""
+    if isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor) and a.dim() != b.dim():
+        if a.dim() < b.dim():
+            a = a.reshape(a.shape + (1,) * (b.dim() - a.dim()))
+        else:
+            b = b.reshape(b.shape + (1,) * (a.dim() - b.dim()))
+    return a, b
+
+
+def eval_tensor_expr(sym: SymbolScalar, env: dict, memo: dict | None = None):
+    """Evaluate a traced whole-tensor expression with torch (on whatever device the leaves live)."""
+    memo = {} if memo is None else memo
+    key = id(sym)
+    if key in memo:
+        return memo[key]
+    if key in env:
+        return env[key]
+    t = sym.code.type
+    if t == "Const":
+        val = float(sym.code.value)
+    elif t == "Var":
+        raise ValueError(f"free variable {sym.code.name!r} in a linear-attention mod")
+    else:
+        a = [eval_tensor_expr(p, env, memo) for p in sym.prev]
+        if len(a) == 2:
+            a = list(_align(a[0], a[1]))
+        as_t = lambda x: x if isinstance(x, torch.Tensor) else torch.tensor(x)  # noqa: E731
+        if t == "Add":
+            val = a[0] + a[1]
+        elif t == "Sub":
+            val = a[0] - a[1]
+        elif t == "Mul":
+            val = a[0] * a[1]
+        elif t == "Div":
+            val = a[0] / a[1]
+        elif t == "Neg":
+            val = -a[0]
+        elif t == "Abs":
+            val = torch.abs(as_t(a[0]))
+        elif t == "Exp":
+            val = torch.exp(as_t(a[0]))
+        elif t == "Exp2":
+            val = torch.exp2(as_t(a[0]))
+        elif t == "Log":
+            val = torch.log(as_t(a[0]))
+        elif t == "Log2":
+            val = torch.log2(as_t(a[0]))
+        elif t == "Tanh":
+            val = torch.tanh(as_t(a[0]))
+        elif t == "Max":
+            val = torch.maximum(*[x if isinstance(x, torch.Tensor) else torch.tensor(x, device=as_t(a[0]).device if isinstance(a[0], torch.Tensor) else a[1].device, dtype=torch.float32) for x in a])
+        else:
+            raise NotImplementedError(f"op {t} in a linear-attention mod")
+    memo[key] = val
+    return val
+
+
+def _constant_multiple(out: SymbolScalar, leaf: SymbolScalar):
+    """If ``out`` is ``leaf * c`` (or ``c * leaf``, ``leaf / c``) for a Python constant c, return c."""
+    if out is leaf:
+        return 1.0
+    if out.code.type in ("Mul", "Div") and len(out.prev) == 2:
+        a, b = out.prev
+        if a is leaf and b.code.type == "Const":
+            c = float(b.code.value)
+            return c if out.code.type == "Mul" else 1.0 / c
+        if out.code.type == "Mul" and b is leaf and a.code.type == "Const":
+            return float(a.code.value)
+    return None
+
+
+def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize: bool = False, eps: float = 1e-5):
+    """q,k: [B,H,T,Dk]; v: [B,H,T,Dv] (fp16/bf16 CUDA); log_decay: [B,H,T] fp32, natural log of the
+    per-token decay.  Returns o [B,H,T,Dv].  ``normalize`` applies a per-(batch, head, token)
+    normalisation over Dv (zero mean, unit variance, no affine) to the output."""
+    if not q.is_cuda:
+        raise native.NativeError("linear attention needs CUDA tensors")
+    if q.dtype not in native.DTYPE_CODES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise native.NativeError("q, k, v must share dtype float16 or bfloat16")
+    B, H, T, Dk = q.shape
+    Dv = v.shape[-1]
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    log_decay = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
+    with torch.cuda.device(q.device):
+        o = torch.empty((B, H, T, Dv), dtype=q.dtype, device=q.device)
+        a = native.LinearArgs()
+        a.q, a.k, a.v, a.log_decay, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), log_decay.data_ptr(), o.data_ptr()
+        a.batch, a.heads, a.seq, a.dim_qk, a.dim_v = B, H, T, Dk, Dv
+        a.dtype = native.DTYPE_CODES[q.dtype]
+        a.normalize = 1 if normalize else 0
+        a.q_scale = float(q_scale)
+        a.norm_eps = float(eps)
+        lib = native.load_library()
+        need = int(lib.attn_b200_linear_workspace_bytes(C.byref(a)))
+        ws = None
+        if need > 0:
+            ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+            a.workspace, a.workspace_bytes = ws.data_ptr(), need
+        native.check(lib.attn_b200_linear_fwd(C.byref(a), native.current_stream_ptr()), "attn_b200_linear_fwd")
+    return o
+
+
+class _ForwardOnly(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, runner, *tensors):
+        return runner(*[t.detach() for t in tensors])
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("the B200-native backend implements the forward pass only")
 
 
 class LinearAttentionEngine:
-    def __init__(self, *a, **k):
-        raise NotImplementedError("linear attention engine not built yet")
+    def __init__(self, qkv_meta, q_mod=None, k_mod=None, v_mod=None, decay_mod=None, custom_io=None,
+                 tune=False, tune_filename="tune_result", tune_bwd=False):
+        self.qkv_meta = qkv_meta
+        self.custom_io = custom_io if custom_io is not None else CustomIO()
+        self.custom_names = list(self.custom_io.input_tensors.keys())
+        self.normalize_output = False
+        B, HQ, T, Dk = qkv_meta[0].shape
+        self.HK = qkv_meta[1].shape[1]
+        self.H = qkv_meta[2].shape[1]
+        self.Dv = qkv_meta[2].shape[3]
+        if Dk not in (64, 128, 256) or self.Dv % 128 != 0:
+            raise NotImplementedError(f"linear attention kernel covers dim_qk in (64,128,256) and dim_v a multiple of 128 "
+                                      f"(got {Dk}, {self.Dv})")
+        # trace the mods once
+        self._leaves = {
+            "q": SymbolicArray("q", Var("q"), shape_idx=["B", "H", "T", "D"]),
+            "k": SymbolicArray("k", Var("k"), shape_idx=["B", "H", "T", "D"]),
+            "v": SymbolicArray("v", Var("v"), shape_idx=["B", "H", "T", "D"]),
+            "decay": SymbolicArray("decay", Var("decay"), shape_idx=["B", "H", "T"]),
+        }
+        self._mods = {}
+        for name, fn in (("q", q_mod), ("k", k_mod), ("v", v_mod), ("decay", decay_mod)):
+            self._mods[name] = fn(self._leaves[name], self.custom_io) if fn is not None else None
+        self.q_scale = 1.0
+        if self._mods["q"] is not None:
+            c = _constant_multiple(self._mods["q"], self._leaves["q"])
+            if c is not None:
+                self.q_scale = c
+                self._mods["q"] = None
+        self.attention = self._run
+
+    def _apply(self, name, tensor, custom_env):
+        out = self._mods[name]
+        if out is None:
+            return tensor
+        env = dict(custom_env)
+        env[id(self._leaves[name])] = tensor.float()
+        res = eval_tensor_expr(out, env)
+        return res if name == "decay" else res.to(tensor.dtype)
+
+    def _run(self, q, k, v, decay, *custom):
+        if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
+            return _ForwardOnly.apply(self._run_impl, q, k, v, decay, *custom)
+        return self._run_impl(q, k, v, decay, *custom)
+
+    def _run_impl(self, q, k, v, decay, *custom):
+        if len(custom) != len(self.custom_names):
+            raise TypeError(f"expected custom tensors {self.custom_names}")
+        cenv = {id(self.custom_io.input_tensors[n]): t.float() for n, t in zip(self.custom_names, custom)}
+        q = self._apply("q", q, cenv)
+        k = self._apply("k", k, cenv)
+        v = self._apply("v", v, cenv)
+        log_decay = self._apply("decay", decay.float(), cenv)
+        B, _, T, _ = q.shape
+        H = v.shape[1]
+        if q.shape[1] != H:
+            q = q.expand(B, H, T, q.shape[-1])
+        if k.shape[1] != H:
+            k = k.expand(B, H, T, k.shape[-1])
+        return linear_attention_forward(q, k, v, log_decay, q_scale=self.q_scale, normalize=self.normalize_output)
+
+    def __call__(self, *args, **kargs):
+        return self.attention(*args, **kargs)

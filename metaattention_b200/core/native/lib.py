@@ -64,6 +64,7 @@ class LinearArgs(C.Structure):
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("log_decay", C.c_void_p), ("o", C.c_void_p),
         ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
         ("dtype", C.c_int32), ("normalize", C.c_int32), ("q_scale", C.c_float), ("norm_eps", C.c_float),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -87,6 +88,7 @@ class MlaArgs(C.Structure):
 SIGNATURES = {
     "attn_b200_parallel_fwd": (C.c_int, [C.POINTER(ParallelArgs), C.c_void_p]),
     "attn_b200_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "attn_b200_linear_workspace_bytes": (C.c_int64, [C.POINTER(LinearArgs)]),
     "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
     "attn_b200_mla_workspace_bytes": (C.c_int64, [C.POINTER(MlaShape), C.c_int32]),
     "attn_b200_mla_decode": (C.c_int, [C.POINTER(MlaArgs), C.c_void_p]),

@@ -1,5 +1,519 @@
-// placeholder until the chunked linear-attention kernel lands
+// Kernel family (2): chunked linear attention / retention forward for sm_100a.
+//
+//   o_i = sum_{j<=i} exp(G_i - G_j) (scale * q_i . k_j) v_j,      G = cumulative sum of log_decay
+//
+// evaluated block by block with a running state, the chunked ("recurrent") pattern of the
+// reference (attention_engine/core/template/tl_template/linear/linear_tl.py: chunk-local cumsum
+// :36-60, state kernel chunk_fwd_h :146-223, output kernel chunk_o :321-401, wrapper :1240-1268):
+//
+//   S        = Q K^T                                  [tokens x tokens]   (tcgen05, SS)
+//   P_ij     = scale * S_ij * exp(g_i - g_j), j <= i   (threads, one row each; written to TMEM)
+//   O        = diag(scale * exp(g)) (Q h) + P V        (tcgen05: SS into O, row rescale, TS on top)
+//   h       <- exp(g_last) h + (V * exp(g_last - g))^T K
+//
+// with g the cumulative log-decay inside the block.  Differences from the reference design:
+// one fused kernel instead of cumsum + state + output kernels; the state never goes to HBM (the
+// reference writes every chunk's state as bf16, 1.07 GB at B=8 H=8 S=4096 256/512, and reads it
+// back); the state is kept in fp32 in tensor memory, only its MMA operand copy is bf16.  Blocks
+// are 128 tokens (the MMA M) instead of the reference's default 64; the result does not depend on
+// the block size.
+//
+// One CTA per (128-column slice of dim_v, batch*head), walking the sequence in 128-token blocks.
+// The state is held transposed, hT[dv_slice=128][dim_qk], so that its MMAs have M = 128 for any
+// dim_qk: TMEM columns [0, DK) = hT, [256, 384) = S / P, [384, 512) = O.
+// Shared memory: Q, K (DK/64 chunks of 128 rows x 128 B each), V (2 chunks), bf16 hT (DK/64 chunks).
+// Phases of one block are separated by CTA-wide barriers; thread 0 issues TMA and MMAs.
+#include <cstring>
+
 #include "../../include/attn_b200.h"
-extern "C" {
-int attn_b200_linear_fwd(const AttnB200LinearArgs*, void*) { return ATTN_B200_E_UNSUPPORTED; }
+#include "common_host.cuh"
+#include "parallel_launch.cuh"  // tensor_map_encoder()
+#include "sm100.cuh"
+
+namespace b200 {
+
+constexpr int kLinT = 128;    // tokens per block
+constexpr int kLinDvs = 128;  // dim_v columns per CTA
+constexpr int kLinThreads = 256;
+
+struct LinearParams {
+  void* o;                 // [B,H,S,DV] 16-bit
+  const float* log_decay;  // [B,H,S] natural log of the per-token decay
+  float* stats;            // [B,H,S,2] (sum, sum of squares) over dim_v, or null
+  int seq, dim_v, bh;
+  float q_scale;
+  int split_p;             // 1: P is written as a 16-bit high part plus a 16-bit remainder (two PV passes)
+  int* status;
+};
+
+__device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
+
+enum LinearWaitSite { kLinQFull = 41, kLinKvFull, kLinMma };
+
+template <int DK>
+struct LinearSmem {
+  static constexpr int kQBytes = kLinT * DK * 2;
+  static constexpr int kVBytes = kLinT * kLinDvs * 2;
+  static constexpr int kHBytes = kLinDvs * DK * 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kOffQ + kQBytes;
+  static constexpr int kOffV = kOffK + kQBytes;
+  static constexpr int kOffH = kOffV + kVBytes;
+  static constexpr int kOffG = kOffH + kHBytes;          // float g2[2][128] + float wsum[8]
+  static constexpr int kOffBar = kOffG + 2 * kLinT * 4 + 32;
+  static constexpr int kOffMisc = kOffBar + 8 * 3;
+  static constexpr int kBytes = kOffMisc + 16 + 1024;
+};
+
+template <int DK, bool kBf16>
+__global__ void __launch_bounds__(kLinThreads, 1)
+linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const LinearParams p) {
+  using L = LinearSmem<DK>;
+  constexpr int T = kLinT, DVS = kLinDvs, KC = DK / 64;
+  static_assert(DK % 64 == 0 && DK <= 256, "unsupported dim_qk");
+  constexpr uint32_t kTmemCols = 512, kColH = 0, kColS = 256, kColO = 384;
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::kOffQ;
+  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sV = smem + L::kOffV;
+  uint8_t* sH = smem + L::kOffH;
+  float* g2 = reinterpret_cast<float*>(smem + L::kOffG);  // [2][T] cumulative log2-decay inside a block
+  float* wsum = g2 + 2 * T;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* mma_bar = bars + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2;                 // 0: row work on S / O, 1: V rescale; both convert the state
+  const int row = (warp & 3) * 32 + lane;   // TMEM lane owned by this thread
+  const AbortState ab{abort_flag, p.status};
+  const int slice = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int nblk = (p.seq + T - 1) / T;
+  const float* ld_row = p.log_decay + static_cast<long long>(bh) * p.seq;
+
+  if (tid == 0) {
+    *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    mbar_init(q_full, 1);
+    mbar_init(kv_full, 1);
+    mbar_init(mma_bar, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+  const uint32_t tH = tmem_base + lane_base + kColH;
+  const uint32_t tS = tmem_base + lane_base + kColS;
+  const uint32_t tO = tmem_base + lane_base + kColO;
+
+  auto load_q = [&](int t) {
+    mbar_arrive_expect_tx(q_full, L::kQBytes);
+    for (int c = 0; c < KC; ++c) tma_load_3d(sQ + c * (T * 128), &tmQ, q_full, c * 64, t * T, bh);
+  };
+  auto load_kv = [&](int t) {
+    mbar_arrive_expect_tx(kv_full, L::kQBytes + L::kVBytes);
+    for (int c = 0; c < KC; ++c) tma_load_3d(sK + c * (T * 128), &tmK, kv_full, c * 64, t * T, bh);
+    for (int c = 0; c < DVS / 64; ++c) tma_load_3d(sV + c * (T * 128), &tmV, kv_full, slice * DVS + c * 64, t * T, bh);
+  };
+  // inclusive scan of the block's log2-decays into g2[buf][0..T); two CTA barriers inside
+  auto scan_block = [&](int t, int buf) {
+    float x = 0.0f;
+    if (tid < T) {
+      const int tok = t * T + tid;
+      x = (tok < p.seq) ? ld_row[tok] * kLog2e : 0.0f;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+      }
+      if (lane == 31) wsum[warp] = x;
+    }
+    __syncthreads();
+    if (tid < T) {
+      float pre = 0.0f;
+      for (int w = 0; w < warp; ++w) pre += wsum[w];
+      g2[buf * T + tid] = x + pre;
+    }
+    __syncthreads();
+  };
+
+  bool ok = !*abort_flag;
+  uint32_t mma_n = 0;
+  if (ok && tid == 0) {
+    load_q(0);
+    load_kv(0);
+  }
+  scan_block(0, 0);
+
+  // kind::f16 takes one 16-bit format for both operands: a variant with fp16 intermediates next to
+  // bf16 inputs (A and B formats differing) raised a CUDA fault on B200 and is not offered.
+  constexpr uint32_t idesc_s = make_idesc_f16(T, T, kBf16, false, false);       // S = Q K^T
+  constexpr uint32_t idesc_qh = make_idesc_f16(T, DVS, kBf16, false, false);    // O = Q hT^T (B = hT copy, K-major)
+  constexpr uint32_t idesc_pv = make_idesc_f16(T, DVS, kBf16, false, true);     // O += P V   (B = V, MN-major)
+  constexpr uint32_t idesc_h = make_idesc_f16(DVS, DK, kBf16, true, true);      // hT += V'^T K (A M-major, B MN-major)
+  const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV), h_addr = smem_u32(sH);
+
+  for (int t = 0; t < nblk; ++t) {
+    const int buf = t & 1;
+    const bool last = (t + 1 == nblk);
+    if (!last) scan_block(t + 1, buf ^ 1);
+    // ---- phase 1: S = Q K^T and (t > 0) O = Q h ----
+    ok = mbar_wait(q_full, t & 1, ab, kLinQFull) && mbar_wait(kv_full, t & 1, ab, kLinKvFull);
+    if (!__syncthreads_and(ok)) break;
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < DK / 16; ++ks) {
+        const uint32_t off = (ks >> 2) * (T * 128) + (ks & 3) * 32;
+        umma_ss(tmem_base + kColS, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024), idesc_s, ks > 0);
+      }
+      if (t > 0) {
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (T * 128) + (ks & 3) * 32;
+          umma_ss(tmem_base + kColO, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(h_addr + off, 16, 1024), idesc_qh, ks > 0);
+        }
+      }
+      umma_commit(mma_bar);
+    }
+    ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
+    ++mma_n;
+    tc_fence_after_sync();
+    if (tid == 0 && ok && !last) load_q(t + 1);  // Q is no longer read by any MMA of this block
+    // ---- phase 2: rows of S -> P, rows of O scaled by scale * exp(g_i) ----
+    if (wg == 0) {
+      const float gi = g2[buf * T + row];
+      float s[T];
+#pragma unroll
+      for (int c = 0; c < T / 32; ++c) tmem_ld32f(tS + c * 32, &s[c * 32]);
+      tmem_wait_ld();
+      // P overwrites S: columns [0, 64) hold P (16-bit pairs); with split_p, columns [64, 128) hold the
+      // 16-bit remainder P - round(P), which a second PV pass adds (the whole S row is in registers)
+#pragma unroll
+      for (int c = 0; c < T / 64; ++c) {
+        uint32_t pk[32], pl[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int j0 = c * 64 + 2 * i, j1 = j0 + 1;
+          const float p0 = (j0 <= row) ? s[j0] * p.q_scale * fast_exp2(gi - g2[buf * T + j0]) : 0.0f;
+          const float p1 = (j1 <= row) ? s[j1] * p.q_scale * fast_exp2(gi - g2[buf * T + j1]) : 0.0f;
+          pk[i] = pack2<kBf16>(p0, p1);
+          float h0, h1;
+          if constexpr (kBf16) {
+            const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&pk[i]);
+            h0 = __bfloat162float(h2.x);
+            h1 = __bfloat162float(h2.y);
+          } else {
+            const __half2 h2 = *reinterpret_cast<__half2*>(&pk[i]);
+            h0 = __half2float(h2.x);
+            h1 = __half2float(h2.y);
+          }
+          pl[i] = pack2<kBf16>(p0 - h0, p1 - h1);
+        }
+        tmem_st32(tS + c * 32, pk);
+        if (p.split_p) tmem_st32(tS + 64 + c * 32, pl);
+      }
+      if (t > 0) {
+        const float f = p.q_scale * fast_exp2(gi);
+#pragma unroll
+        for (int c = 0; c < DVS / 32; ++c) {
+          float o[32];
+          tmem_ld32f(tO + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= f;
+          tmem_st32f(tO + c * 32, o);
+        }
+      }
+      tmem_wait_st();
+    }
+    tc_fence_before_sync();
+    if (!__syncthreads_and(ok)) break;
+    // ---- phase 3: O (+)= P V ----
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < T / 16; ++ks)
+        umma_ts(tmem_base + kColO, tmem_base + kColS + ks * 8, make_smem_desc(v_addr + ks * 2048, T * 128, 1024), idesc_pv,
+                (t > 0 || ks > 0) ? 1u : 0u);
+      if (p.split_p) {
+#pragma unroll
+        for (int ks = 0; ks < T / 16; ++ks)
+          umma_ts(tmem_base + kColO, tmem_base + kColS + 64 + ks * 8, make_smem_desc(v_addr + ks * 2048, T * 128, 1024),
+                  idesc_pv, 1u);
+      }
+      umma_commit(mma_bar);
+    }
+    ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
+    ++mma_n;
+    tc_fence_after_sync();
+    // ---- phase 4: store O rows; rescale V rows for the state update ----
+    if (wg == 0) {
+      const int tok = t * T + row;
+      const bool in_range = tok < p.seq;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) + 2 * ((static_cast<long long>(bh) * p.seq + tok) * p.dim_v + slice * DVS);
+      float sum = 0.f, sq = 0.f;
+#pragma unroll
+      for (int c = 0; c < DVS / 32; ++c) {
+        float o[32];
+        tmem_ld32f(tO + c * 32, o);
+        tmem_wait_ld();
+        if (in_range) {
+          if (p.stats == nullptr) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
+              pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
+              pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
+              pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
+              *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
+            }
+          } else {
+            // the row is normalised by a second pass: stage it as fp16 (11 significant bits, clamped to
+            // the fp16 range) so that the only bf16 rounding is the final one
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              pk.x = pack2<false>(clamp_h(o[8 * v + 0]), clamp_h(o[8 * v + 1]));
+              pk.y = pack2<false>(clamp_h(o[8 * v + 2]), clamp_h(o[8 * v + 3]));
+              pk.z = pack2<false>(clamp_h(o[8 * v + 4]), clamp_h(o[8 * v + 5]));
+              pk.w = pack2<false>(clamp_h(o[8 * v + 6]), clamp_h(o[8 * v + 7]));
+              *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          sum += o[i];
+          sq += o[i] * o[i];
+        }
+      }
+      if (p.stats != nullptr && in_range) {
+        float* st = p.stats + (static_cast<long long>(bh) * p.seq + tok) * 2;
+        atomicAdd(st, sum);
+        atomicAdd(st + 1, sq);
+      }
+    } else if (!last) {
+      // token `row` of V is multiplied by exp(g_last - g_row); 16-byte pieces of a row stay inside
+      // its 128-byte line under the swizzle, so the permutation does not matter here
+      const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
+#pragma unroll
+      for (int c = 0; c < DVS / 64; ++c) {
+        uint4* line = reinterpret_cast<uint4*>(sV + c * (T * 128) + row * 128);
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          uint4 x = line[q4];
+          uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo, hi;
+            if constexpr (kBf16) {
+              const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&xs[e]);
+              lo = __bfloat162float(h2.x);
+              hi = __bfloat162float(h2.y);
+            } else {
+              const __half2 h2 = *reinterpret_cast<__half2*>(&xs[e]);
+              lo = __half2float(h2.x);
+              hi = __half2float(h2.y);
+            }
+            xs[e] = pack2<kBf16>(lo * w, hi * w);
+          }
+          line[q4] = x;
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    tc_fence_before_sync();
+    if (!__syncthreads_and(ok)) break;
+    if (last) break;
+    // ---- phase 5: hT (+)= V'^T K ----
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < T / 16; ++ks)
+        umma_ss(tmem_base + kColH, make_smem_desc(v_addr + ks * 2048, T * 128, 1024), make_smem_desc(k_addr + ks * 2048, T * 128, 1024),
+                idesc_h, (t > 0 || ks > 0) ? 1u : 0u);
+      umma_commit(mma_bar);
+    }
+    ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
+    ++mma_n;
+    tc_fence_after_sync();
+    if (tid == 0 && ok) load_kv(t + 1);  // K and V' are no longer read
+    // ---- phase 6: bf16 copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
+    {
+      const float decay_next = fast_exp2(g2[(buf ^ 1) * T + T - 1]);
+      constexpr int kColsPerWg = DK / 2;
+#pragma unroll
+      for (int c = 0; c < kColsPerWg / 32; ++c) {
+        const int col0 = wg * kColsPerWg + c * 32;
+        float hv[32];
+        tmem_ld32f(tH + col0, hv);
+        tmem_wait_ld();
+        uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
+        const int piece0 = (col0 & 63) >> 3;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 pk;
+          pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
+          pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
+          pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
+          pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
+          *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+        tmem_st32f(tH + col0, hv);
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+    }
+    tc_fence_before_sync();
+    if (!__syncthreads_and(ok)) break;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
 }
+
+// In-place normalisation of every (batch, head, token) row of o over dim_v to zero mean and unit
+// variance, from the (sum, sum of squares) the forward kernel accumulated in fp32.  The rows arrive
+// staged as fp16 and leave in the output dtype.  One warp per row.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) linear_norm_kernel(void* __restrict__ o, const float* __restrict__ stats, long long rows,
+                                                        int dim_v, float eps) {
+  const long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float mean = stats[2 * r] / dim_v;
+  const float var = fmaxf(stats[2 * r + 1] / dim_v - mean * mean, 0.0f);
+  const float rstd = rsqrtf(var + eps);
+  uint32_t* line = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(o) + 2 * r * dim_v);
+  for (int i = lane; i < dim_v / 2; i += 32) {
+    uint32_t x = line[i];
+    const __half2 h2 = *reinterpret_cast<__half2*>(&x);  // staged as fp16 by the forward kernel
+    const float lo = __half2float(h2.x), hi = __half2float(h2.y);
+    line[i] = pack2<kBf16>((lo - mean) * rstd, (hi - mean) * rstd);
+  }
+}
+
+inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t outer) {
+  TensorMapEncodeTiledFn enc = tensor_map_encoder();
+  if (enc == nullptr) return ATTN_B200_E_LAUNCH;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  cuuint64_t gdim[3] = {cols, rows, outer};
+  cuuint64_t gstride[2] = {cols * 2, cols * rows * 2};
+  cuuint32_t box[3] = {64, kLinT, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == ATTN_B200_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(tm, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? ATTN_B200_OK : ATTN_B200_E_UNSUPPORTED;
+}
+
+template <int DK, bool kBf16>
+int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status) {
+  using L = LinearSmem<DK>;
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t bh = static_cast<uint64_t>(a->batch) * a->heads;
+  int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, bh);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_rows3(&tmK, a->k, a->dtype, DK, a->seq, bh);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
+  if (rc != ATTN_B200_OK) return rc;
+  LinearParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.o = a->o;
+  p.log_decay = a->log_decay;
+  p.seq = a->seq;
+  p.dim_v = a->dim_v;
+  p.bh = static_cast<int>(bh);
+  p.q_scale = a->q_scale;
+  p.split_p = a->normalize ? 1 : 0;  // the normalised output has an absolute tolerance: spend a second PV pass on P
+  p.status = status;
+  const long long rows = static_cast<long long>(bh) * a->seq;
+  if (a->normalize) {
+    p.stats = static_cast<float*>(a->workspace);
+    if (cudaMemsetAsync(p.stats, 0, rows * 2 * sizeof(float), stream) != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  }
+  auto kernel = linear_fwd_kernel<DK, kBf16>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return ATTN_B200_E_LAUNCH;
+  }
+  dim3 grid(a->dim_v / kLinDvs, static_cast<unsigned>(bh));
+  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
+  if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  if (a->normalize) {
+    const int blocks = static_cast<int>((rows * 32 + 255) / 256);
+    linear_norm_kernel<kBf16><<<blocks, 256, 0, stream>>>(a->o, p.stats, rows, a->dim_v, a->norm_eps);
+    if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  }
+  return ATTN_B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int64_t attn_b200_linear_workspace_bytes(const AttnB200LinearArgs* a) {
+  if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->seq <= 0) return -1;
+  return a->normalize ? static_cast<int64_t>(a->batch) * a->heads * a->seq * 2 * 4 : 0;
+}
+
+int attn_b200_linear_fwd(const AttnB200LinearArgs* a, void* cuda_stream) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr || a->log_decay == nullptr)
+    return ATTN_B200_E_INVALID_ARG;
+  if (a->batch <= 0 || a->heads <= 0 || a->seq <= 0) return ATTN_B200_E_INVALID_ARG;
+  if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
+  if (a->dim_v <= 0 || a->dim_v % b200::kLinDvs != 0) return ATTN_B200_E_UNSUPPORTED;
+  if (static_cast<long long>(a->batch) * a->heads > 65535) return ATTN_B200_E_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  if (a->normalize) {
+    const int64_t need = attn_b200_linear_workspace_bytes(a);
+    if (a->workspace == nullptr || a->workspace_bytes < need) return ATTN_B200_E_WORKSPACE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  int* status = b200::device_status_word(dev);
+  if (status == nullptr) return ATTN_B200_E_LAUNCH;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const bool bf16 = a->dtype == ATTN_B200_DTYPE_BF16;
+  switch (a->dim_qk) {
+    case 64:
+      return bf16 ? b200::launch_linear<64, true>(a, stream, status) : b200::launch_linear<64, false>(a, stream, status);
+    case 128:
+      return bf16 ? b200::launch_linear<128, true>(a, stream, status) : b200::launch_linear<128, false>(a, stream, status);
+    case 256:
+      return bf16 ? b200::launch_linear<256, true>(a, stream, status) : b200::launch_linear<256, false>(a, stream, status);
+    default:
+      return ATTN_B200_E_UNSUPPORTED;
+  }
+}
+
+}  // extern "C"

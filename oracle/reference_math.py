@@ -92,7 +92,10 @@ def retention_recurrent(q, k, v):
     delta = pos.view(-1, 1) - pos.view(1, -1)
     o = torch.empty(B, H, S, v.shape[-1])
     for h in range(H):  # one head at a time keeps the [S,S] decay matrix small
-        decay = torch.exp2(delta * log2_gamma[h]) * (delta >= 0)
+        # The reference multiplies exp2((i-j) log2 gamma) by the 0/1 mask AFTER exponentiating, which
+        # gives inf * 0 = NaN once (S-1) |log2 gamma| > 128 (S >= ~2800 for head 0); masking the
+        # exponent first is the same function wherever the reference is finite.
+        decay = torch.exp2(delta.clamp_min(0.0) * log2_gamma[h]) * (delta >= 0)
         s = torch.einsum("bqd,bkd->bqk", q[:, h] * Dk ** -0.5, k[:, h]) * decay
         o[:, h] = torch.einsum("bqk,bkd->bqd", s, v[:, h])
     return o

@@ -78,7 +78,7 @@ def main():
 
     # RetNet retention (testing/test.py:738-747)
     ref = extract(tree, source, "test_retnet_recurrent", "ref")
-    B, H, S, Dk, Dv = 1, 8, 192, 64, 64
+    B, H, S, Dk, Dv = 1, 8, 192, 64, 128
     q, k, v, _ = inputs.retention_bhsd(B, H, S, Dk, Dv, 41)
     out["retention"] = dict(shape=(B, H, S, Dk, Dv), seed=41, o=ref(q.float(), k.float(), v.float()).contiguous())
 

@@ -125,3 +125,17 @@ def mla_engine(B, H, S, D, Dv, dtype=torch.bfloat16, backend="tl"):
         return score * scale
     return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=NaturalSoftmax(),
                            kv_shared=True, backend=backend)
+
+
+def retnet_engine(B, H, S, Dk, Dv, dtype=torch.bfloat16):
+    """RetNet retention in the chunked pattern: decay holds gamma_h, decay_mod takes its log,
+    q is scaled by 1/sqrt(Dk)."""
+    scale = Dk ** -0.5
+
+    def decay_mod(decay, custom_io):
+        return decay.log()
+
+    def q_mod(q, custom_io):
+        return q * scale
+    meta = (meta_tensor(B, H, S, Dk, dtype=dtype), meta_tensor(B, H, S, Dk, dtype=dtype), meta_tensor(B, H, S, Dv, dtype=dtype))
+    return LinearAttentionEngine(meta, q_mod=q_mod, decay_mod=decay_mod, custom_io=CustomIO({}))
