@@ -39,8 +39,8 @@ METRIC = "fwd_attention_tflops"
 UNIT = "TFLOP/s"
 
 # DRAM bytes (read+write) of one forward-kernel launch at the C2 shape from an ncu capture
-# (profiles/parallel_fwd_softmax_c2.md); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# (profiles/parallel_fwd_softmax_c2.md).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.017e9  # 254.2 MB measured at batch 2, scaled x4 to batch 8
 
 
 def c2_flops(B=C2["B"], H=C2["H"], S=C2["S"], D=C2["D"], Dv=C2["Dv"], causal=True):
