@@ -33,6 +33,7 @@ extern "C" {
 #define ATTN_B200_E_LAUNCH (-3)        /* CUDA runtime or driver error at launch            */
 #define ATTN_B200_E_DEVICE_TIMEOUT (-4)/* a bounded device-side wait ran out                */
 #define ATTN_B200_E_WORKSPACE (-5)     /* workspace missing or too small                    */
+#define ATTN_B200_E_SCRATCH_LIMIT (-6) /* needs more scratch than the built-in static array  */
 
 #define ATTN_B200_DTYPE_FP16 0
 #define ATTN_B200_DTYPE_BF16 1
@@ -146,6 +147,22 @@ typedef struct AttnB200MlaArgs {
  *  kernels/mla_combine.cu:14-203, flash_api.cpp:61-210) and the TileLang
  * variant (core/template/tl_template/attn/mla_decode_tl.py:154-303). */
 int attn_b200_mla_decode(const AttnB200MlaArgs* args, void* cuda_stream);
+
+/* MLA decode that allocates nothing.  NO COUNTERPART IN THE REFERENCE: added for hosts that cannot
+ * call cudaMalloc around the decode (all device memory already owned by their own arena, or a
+ * latency-critical loop that cannot take a driver allocation).  Same arguments and results as
+ * attn_b200_mla_decode, except that
+ *   - the split-KV scratch is a 32 MiB array inside the library's device data segment (every GPU
+ *     that loads the library holds it until exit); args->workspace / workspace_bytes are ignored;
+ *     a problem with attn_b200_mla_workspace_bytes() above 32 MiB returns
+ *     ATTN_B200_E_SCRATCH_LIMIT and launches nothing (num_splits = 1 needs no scratch at all);
+ *   - status_word is a caller-owned 4-byte DEVICE word: cleared by the call, non-zero after the
+ *     stream has been synchronised iff a device-side wait ran out (100 + id of the wait);
+ *   - no cudaMalloc / cudaFree / allocating library routine is called.
+ * The first call made on a device looks up the array's address (once per device); make it before
+ * any stream capture on that device.  All calls on a device share the array and it keeps the
+ * previous call's contents (no part of it needs clearing); calls that overlap on the GPU race. */
+int attn_b200_mla_decode_static(const AttnB200MlaArgs* args, int32_t* status_word, void* cuda_stream);
 
 /* Reads and clears the device-side status word of device `device`
  * (0 = no kernel reported a problem).  Synchronises the device. */

@@ -33,6 +33,7 @@ ERRORS = {
     -3: "CUDA launch error",
     -4: "device-side wait timed out",
     -5: "workspace missing or too small",
+    -6: "problem needs more scratch than the library's built-in static array holds",
 }
 
 DTYPE_CODES = {torch.float16: 0, torch.bfloat16: 1}
@@ -92,6 +93,7 @@ SIGNATURES = {
     "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
     "attn_b200_mla_workspace_bytes": (C.c_int64, [C.POINTER(MlaShape), C.c_int32]),
     "attn_b200_mla_decode": (C.c_int, [C.POINTER(MlaArgs), C.c_void_p]),
+    "attn_b200_mla_decode_static": (C.c_int, [C.POINTER(MlaArgs), C.c_void_p, C.c_void_p]),
     "attn_b200_last_device_status": (C.c_int, [C.c_int32, C.POINTER(C.c_int32)]),
     "attn_b200_device_status_word": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p)]),
     "attn_b200_version": (C.c_int, []),

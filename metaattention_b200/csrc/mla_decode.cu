@@ -21,6 +21,7 @@
 // Combine kernel: log-sum-exp weighted sum of the per-split fp32 partial outputs.
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/attn_b200.h"
 #include "common_host.cuh"
@@ -501,3 +502,87 @@ int attn_b200_mla_decode(const AttnB200MlaArgs* a, void* cuda_stream) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the MLA decode entry point.
+//
+// Who needs it: hosts that must not call cudaMalloc (or anything that does) around the decode.
+// Typical cases are a serving process whose own arena already owns all of the device memory, so
+// that a further cudaMalloc either fails or has to be carved out of that arena by hand, and
+// latency-critical loops that cannot afford the implicit device-wide synchronisation and the
+// unpredictable duration of a driver allocation.  The regular entry point needs two pieces of
+// device memory besides inputs and outputs: the split-KV scratch (fp32 partial outputs and partial
+// log-sum-exps, normally handed in by the caller as `workspace`) and the library's status word
+// (allocated with cudaMalloc on first use).  Here the scratch is a fixed array in the library's
+// own device data segment and the status word is supplied by the caller, so the call performs no
+// allocation of any kind.
+//
+// Cost and limits: every GPU on which the library gets loaded carries the array (32 MiB) until the
+// process exits, used or not.  Problems whose scratch does not fit are refused with
+// ATTN_B200_E_SCRATCH_LIMIT; nothing is launched in that case.  All calls on one device share the
+// one array, and it keeps whatever the previous call left in it.  Nothing in it has to start at
+// zero: every row the combine pass reads was written by the split pass of the same call, and rows
+// it does not read are ignored.  The only word that must start at zero is the caller's status
+// word, which the call clears itself (a memset on the same stream, ahead of the kernels).  Two calls
+// that overlap on the GPU -- different streams, or one stream from two threads without ordering --
+// race on the array and produce garbage; serialise them.
+//
+// Set-up: the address of the array is looked up once per device, on the first call made while
+// that device is current (cudaGetSymbolAddress; the name of the array is only a host-side handle,
+// not a device address, so it cannot be passed to a kernel directly).  Make that first call
+// before any stream capture is started on the device.
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+
+constexpr size_t kMlaStaticScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_mla_static_scratch[kMlaStaticScratchBytes];
+
+// Device address of the array for the current device; null on failure.  Looked up once per device.
+static void* mla_static_scratch_ptr() {
+  constexpr int kMaxDevices = 64;
+  static void* ptrs[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_mla_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+}  // namespace b200
+
+extern "C" int attn_b200_mla_decode_static(const AttnB200MlaArgs* a, int32_t* status_word, void* cuda_stream) {
+  if (a == nullptr || a->q == nullptr || a->kv == nullptr || a->o == nullptr || status_word == nullptr)
+    return ATTN_B200_E_INVALID_ARG;
+  int rc = b200::validate_mla_shape(&a->shape);
+  if (rc != ATTN_B200_OK) return rc;
+  if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
+  if (a->num_splits < 1 || a->num_splits > 32767) return ATTN_B200_E_INVALID_ARG;
+  const int total_tiles = (a->shape.seq_kv + b200::kMlaTileN - 1) / b200::kMlaTileN;
+  if (a->num_splits > total_tiles) return ATTN_B200_E_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0 || (reinterpret_cast<uintptr_t>(status_word) & 3) != 0)
+    return ATTN_B200_E_UNSUPPORTED;
+  const int64_t need = attn_b200_mla_workspace_bytes(&a->shape, a->num_splits);
+  if (need < 0) return ATTN_B200_E_UNSUPPORTED;
+  if (static_cast<uint64_t>(need) > b200::kMlaStaticScratchBytes) return ATTN_B200_E_SCRATCH_LIMIT;
+  void* scratch = b200::mla_static_scratch_ptr();
+  if (scratch == nullptr) return ATTN_B200_E_LAUNCH;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // the kernels give up at once when they find a non-zero status word: start every call from zero
+  if (cudaMemsetAsync(status_word, 0, sizeof(int32_t), stream) != cudaSuccess) {
+    cudaGetLastError();
+    return ATTN_B200_E_LAUNCH;
+  }
+  AttnB200MlaArgs local = *a;  // the caller's workspace fields are ignored
+  local.workspace = need > 0 ? scratch : nullptr;
+  local.workspace_bytes = need;
+  return a->dtype == ATTN_B200_DTYPE_BF16 ? b200::launch_mla<true>(&local, stream, status_word)
+                                          : b200::launch_mla<false>(&local, stream, status_word);
+}
