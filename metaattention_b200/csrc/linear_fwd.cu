@@ -167,7 +167,11 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   constexpr uint32_t idesc_qh = make_idesc_f16(T, DVS, kBf16, false, false);    // O = Q hT^T (B = hT copy, K-major)
   constexpr uint32_t idesc_pv = make_idesc_f16(T, DVS, kBf16, false, true);     // O += P V   (B = V, MN-major)
   constexpr uint32_t idesc_h = make_idesc_f16(DVS, DK, kBf16, true, true);      // hT += V'^T K (A M-major, B MN-major)
-  const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV), h_addr = smem_u32(sH);
+  // descriptors are built once; the issue loops only move the start-address field (units of 16 bytes)
+  const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024), k_desc0 = make_smem_desc(smem_u32(sK), 16, 1024);
+  const uint64_t h_desc0 = make_smem_desc(smem_u32(sH), 16, 1024);
+  const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024), k_mn_desc0 = make_smem_desc(smem_u32(sK), T * 128, 1024);
+  constexpr uint64_t kChunk = (T * 128) >> 4;
 
   for (int t = 0; t < nblk; ++t) {
     const int buf = t & 1;
@@ -179,16 +183,12 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
-      for (int ks = 0; ks < DK / 16; ++ks) {
-        const uint32_t off = (ks >> 2) * (T * 128) + (ks & 3) * 32;
-        umma_ss(tmem_base + kColS, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(k_addr + off, 16, 1024), idesc_s, ks > 0);
-      }
+      for (int ch = 0; ch < KC; ++ch)
+        umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + ch * kChunk, k_desc0 + ch * kChunk, idesc_s, ch > 0 ? 1u : 0u);
       if (t > 0) {
 #pragma unroll
-        for (int ks = 0; ks < DK / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (T * 128) + (ks & 3) * 32;
-          umma_ss(tmem_base + kColO, make_smem_desc(q_addr + off, 16, 1024), make_smem_desc(h_addr + off, 16, 1024), idesc_qh, ks > 0);
-        }
+        for (int ch = 0; ch < KC; ++ch)
+          umma_ss_x4<2, 2>(tmem_base + kColO, q_desc0 + ch * kChunk, h_desc0 + ch * kChunk, idesc_qh, ch > 0 ? 1u : 0u);
       }
       umma_commit(mma_bar);
     }
@@ -249,14 +249,12 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
-      for (int ks = 0; ks < T / 16; ++ks)
-        umma_ts(tmem_base + kColO, tmem_base + kColS + ks * 8, make_smem_desc(v_addr + ks * 2048, T * 128, 1024), idesc_pv,
-                (t > 0 || ks > 0) ? 1u : 0u);
+      for (int g = 0; g < T / 64; ++g)
+        umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + g * 32, v_mn_desc0 + g * 512, idesc_pv, (t > 0 || g > 0) ? 1u : 0u);
       if (p.split_p) {
 #pragma unroll
-        for (int ks = 0; ks < T / 16; ++ks)
-          umma_ts(tmem_base + kColO, tmem_base + kColS + 64 + ks * 8, make_smem_desc(v_addr + ks * 2048, T * 128, 1024),
-                  idesc_pv, 1u);
+        for (int g = 0; g < T / 64; ++g)
+          umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + 64 + g * 32, v_mn_desc0 + g * 512, idesc_pv, 1u);
       }
       umma_commit(mma_bar);
     }
@@ -347,9 +345,8 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
-      for (int ks = 0; ks < T / 16; ++ks)
-        umma_ss(tmem_base + kColH, make_smem_desc(v_addr + ks * 2048, T * 128, 1024), make_smem_desc(k_addr + ks * 2048, T * 128, 1024),
-                idesc_h, (t > 0 || ks > 0) ? 1u : 0u);
+      for (int g = 0; g < T / 64; ++g)   // both operands are MN-major over tokens: 16 tokens = 2048 B per K step
+        umma_ss_x4<128, 128>(tmem_base + kColH, v_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
       umma_commit(mma_bar);
     }
     ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);

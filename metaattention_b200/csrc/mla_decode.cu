@@ -8,17 +8,32 @@
 //  kernels/mla_combine.cu:14-203, kernels/get_mla_metadata.cu:8-82, flash_api.cpp:23-210) and the
 // TileLang variant (core/template/tl_template/attn/mla_decode_tl.py:154-303).
 //
-// Split kernel: one CTA per (half of dim_v, KV split, block of 128 heads, sequence).  The 128
-// heads are the M dimension of the MMAs, so the latent KV is streamed once per CTA for all heads:
-//   warp 4      TMA producer: Q (128 x dim_qk) once, then 32-row KV tiles into a 2-stage ring
-//   warp 5      tcgen05.mma issuer: S = Q.KV^T (K = dim_qk) into a double-buffered TMEM tile,
-//               O += P.V with P read from TMEM and V addressed inside the SAME shared-memory KV
-//               tile (the K-major 64-column chunks of a KV tile are exactly the MN-major chunks
-//               of V), so V is never loaded separately
-//   warps 0-3   one head per thread: online softmax in the exp2 domain with lazy accumulator rescale
-// The fp32 accumulator of 128 heads x 512 columns would fill all 512 TMEM columns and leave none
-// for S, hence the split of dim_v over two CTAs (each recomputes S).
-// Combine kernel: log-sum-exp weighted sum of the per-split fp32 partial outputs.
+// The 128 heads of a block are the M dimension of every MMA, so a latent row is used for all heads
+// at once.  The fp32 accumulator of 128 heads x 512 columns fills the whole tensor memory of an SM
+// (512 columns), leaving no room for the score tile; the work of one (sequence, KV split, head
+// block) is therefore shared by a CLUSTER OF TWO CTAs on two SMs:
+//
+//   score CTA (cluster rank 0)                           value CTA (cluster rank 1)
+//   TMEM: Q[:, :512] as 16-bit pairs (256 columns) and    TMEM: O, 128 x 512 fp32 (512 columns)
+//         two 128-column score tiles
+//   smem: Q[:, 512:] tile, ring of 12 KV chunks           smem: ring of five 32-row V stages, four
+//         (128 rows x 64 columns each)                          64-row P slots
+//   warp 8: TMA, chunk by chunk                           warp 4: TMA
+//   warp 9: S = Q.KV^T over 128 KV rows: 36 MMAs with      warp 5: O += P.V per 64-row half tile
+//           N = 128 (full tensor rate; an MMA costs        warps 0-3: one head per thread: rescale O when
+//           ~50 cycles however small N is), A from                 the score CTA moved the reference
+//           TMEM for the first 512 columns                         maximum; final scaling and store
+//   warps 0-7: one head per thread, the two warp groups    warp 6: re-arms a P slot's barrier and tells
+//           take the two 64-column halves of a tile:               the score CTA when the slot is free
+//           online softmax in the exp2 domain with lazy
+//           rescale; P (16-bit) and the rescale factor go
+//           straight into the VALUE CTA's shared memory
+//           with asynchronous stores that are counted on
+//           its mbarrier (no release fence, no waiting)
+//
+// FLOP balance 576 : 512, no recomputation.  Each latent row is fetched by both CTAs (the second
+// fetch is an L2 hit); no multicast is used.  Split-KV partials are fp32; the combine kernel does
+// the log-sum-exp weighted sum.
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -28,289 +43,474 @@
 #include "parallel_launch.cuh"  // tensor_map_encoder()
 #include "sm100.cuh"
 
+#ifndef MLA_ST_ASYNC
+#define MLA_ST_ASYNC 1
+#endif
 namespace b200 {
 
-constexpr int kMlaHeads = 128;     // heads per CTA (MMA M)
-constexpr int kMlaTileN = 32;      // KV rows per tile
-constexpr int kMlaStages = 2;
-constexpr int kMlaThreads = 192;
+constexpr int kMlaHeads = 128;     // heads per cluster (MMA M)
+constexpr int kMlaTileN = 128;     // KV rows per score tile
+constexpr int kMlaThreads = 320;   // 10 warps
+constexpr int kMlaSmemBytes = 232448;  // the per-block maximum: the value CTA needs all of it
 
 struct MlaParams {
-  void* o;            // [B, H, DV] 16-bit, written when num_splits == 1
-  float* lse;         // [B, H] or null
-  float* part_o;      // [B, splits, H, DV] fp32 (num_splits > 1)
-  float* part_lse;    // [B, splits, H]
-  int batch, heads, seq_kv, num_splits, tiles_per_split;
-  float scale_log2;   // scale * log2(e)
+  const void* q;        // first DV columns of q (read with 16-byte loads)
+  long long q_sb, q_sh; // element strides (batch, head)
+  void* o;              // [B, H, DV] 16-bit, written when num_splits == 1
+  float* lse;           // [B, H] or null
+  float* part_o;        // [B, splits, H, DV] fp32 (num_splits > 1)
+  float* part_lse;      // [B, splits, H]
+  int batch, heads, seq_kv, num_splits, tiles_per_split, head_blocks;
+  float scale_log2;     // scale * log2(e)
   float scale;
   int* status;
 };
 
-enum MlaWaitSite { kMlaQFull = 21, kMlaKvFull, kMlaKvEmpty, kMlaSFull, kMlaPReady, kMlaODone, kMlaOFinal };
+enum MlaWaitSite {
+  kMlaSlotFull = 21, kMlaSlotEmpty, kMlaSFull, kMlaSFree, kMlaPFull, kMlaPFree, kMlaPvGo, kMlaPvDone, kMlaODone,
+  kMlaFinal, kMlaQReady, kMlaOFinal, kMlaSmemLayout, kMlaQrFull, kMlaRowMax, kMlaRowSum
+};
 
-template <int D, int DV>
+// Shared-memory layout, identical in both CTAs so that a local address maps to the peer's copy.
+// Small items first (from the raw base), operand tiles after, aligned to 1024 bytes.
 struct MlaSmem {
-  static constexpr int kChunks = D / 64;
-  static constexpr int kQBytes = kMlaHeads * D * 2;
-  static constexpr int kKvBytes = kMlaTileN * D * 2;
-  static constexpr int kOffQ = 0;
-  static constexpr int kOffKv = kQBytes;
-  static constexpr int kOffBar = kOffKv + kMlaStages * kKvBytes;
-  static constexpr int kNumBars = 1 + 2 * kMlaStages + 2 + 2 + 1;
-  static constexpr int kOffMisc = kOffBar + 8 * kNumBars;
-  static constexpr int kBytes = kOffMisc + 16 + 1024;
+  // barrier indices
+  static constexpr int kSlotFull = 0;    // [12] score: KV chunk ring / value: [5] V stages
+  static constexpr int kSlotEmpty = 12;  // [12]
+  static constexpr int kSFull = 24;      // [2] score
+  static constexpr int kSFree = 26;      // [2] score, 256 arrivals
+  static constexpr int kPFull = 28;      // [4] value: 1 arrival (armed locally) + transaction bytes from the score CTA
+  static constexpr int kPFree = 32;      // [4] score: 1 arrival from the value CTA
+  static constexpr int kPvGo = 36;       // [4] value, 128 arrivals
+  static constexpr int kPvDone = 40;     // [4] value
+  static constexpr int kODone = 44;      // value
+  static constexpr int kFinalFull = 45;  // value, 128 arrivals from the score CTA
+  static constexpr int kQReady = 46;     // score, 256 arrivals
+  static constexpr int kQrFull = 47;     // score
+  static constexpr int kRowMax = 48;     // [2] score, 256 arrivals: both halves of a row's maximum are posted
+  static constexpr int kRowSum = 50;     // score, 128 arrivals
+  static constexpr int kNumBars = 51;
+  static constexpr int kOffBars = 0;
+  static constexpr int kOffSlot = 416;     // TMEM base address
+  static constexpr int kOffAbort = 424;
+  static constexpr int kOffScale = 512;    // value: float [2][128] rescale factor per tile parity and head
+  static constexpr int kOffFinal = 1536;   // value: float [128][2] (1/rowsum, lse)
+  static constexpr int kOffRowMax = 512;   // score (same bytes, other CTA): float [2 bufs][2 halves][128]
+  static constexpr int kOffRowSum = 2560;  // score: float [128]
+  static constexpr int kSmallBytes = 3072;
+  static constexpr int kChunkBytes = kMlaTileN * 128;           // 16384: 128 rows x 64 columns
+  static constexpr int kScoreSlots = 12;
+  static constexpr int kQrBytes = kMlaHeads * 128;              // 16384: Q[:, 512:576]
+  static constexpr int kScoreTileBytes = kQrBytes + kScoreSlots * kChunkBytes;   // 212992
+  static constexpr int kVStageRows = 32;
+  static constexpr int kVStages = 5;
+  static constexpr int kVStageBytes = kVStageRows * 512 * 2;    // 32768: 8 chunks of 32 rows x 128 B
+  static constexpr int kPSlots = 4;
+  static constexpr int kPBytes = kMlaHeads * 64 * 2;            // 16384: 128 heads x 64 KV rows
+  static constexpr int kValueTileBytes = kVStages * kVStageBytes + kPSlots * kPBytes;  // 229376
+  static_assert(kNumBars * 8 <= kOffSlot, "barriers overlap");
+  static_assert(kSmallBytes + kValueTileBytes <= kMlaSmemBytes, "value CTA does not fit");
 };
 
 template <int D, int DV, bool kBf16>
-__global__ void __launch_bounds__(kMlaThreads, 1)
-mla_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmQr,
-                 const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ CUtensorMap tmKVr, const MlaParams p) {
-  using L = MlaSmem<D, DV>;
-  constexpr int N = kMlaTileN, ST = kMlaStages, M = kMlaHeads;
-  constexpr int DVH = DV / 2;                 // columns of the output handled by this CTA
-  static_assert(D % 64 == 0 && DVH % 64 == 0 && DVH <= 256, "unsupported MLA dims");
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMlaThreads, 1)
+mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ CUtensorMap tmKVr,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQr, const MlaParams p) {
+  using L = MlaSmem;
+  constexpr int N = kMlaTileN, M = kMlaHeads;
+  static_assert(D == 576 && DV == 512, "tile bookkeeping below is written for 576/512");
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColO = 0, kColS = 256;  // O: [0, DVH), S buffers: 256 + 32*buf
+  constexpr uint32_t kColQ = 0, kColS = 256;   // score CTA: Q[:, :512] in [0,256), S buffers [256,384) [384,512)
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + L::kOffQ;
-  uint8_t* sKV = smem + L::kOffKv;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
-  uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = kv_full + ST;
-  uint64_t* s_full = kv_empty + ST;  // [2]
-  uint64_t* p_ready = s_full + 2;    // [2]
-  uint64_t* o_done = p_ready + 2;    // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + L::kOffBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + L::kOffSlot);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + L::kOffAbort);
+  float* s_scale = reinterpret_cast<float*>(smem_raw + L::kOffScale);
+  float* s_final = reinterpret_cast<float*>(smem_raw + L::kOffFinal);
+  float* s_rowmax = reinterpret_cast<float*>(smem_raw + L::kOffRowMax);
+  float* s_rowsum = reinterpret_cast<float*>(smem_raw + L::kOffRowSum);
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + L::kSmallBytes + 1023) & ~uintptr_t(1023));
+  // score CTA: [Q rope tile][12 KV chunks];  value CTA: [5 V stages][4 P slots]
+  uint8_t* sQr = tiles;
+  uint8_t* sChunk = tiles + L::kQrBytes;
+  uint8_t* sV = tiles;
+  uint8_t* sP = tiles + L::kVStages * L::kVStageBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0 = score CTA, 1 = value CTA
   const AbortState ab{abort_flag, p.status};
-  const int half = blockIdx.x & 1;
-  const int split = blockIdx.x >> 1;
-  const int hb = blockIdx.y;          // block of 128 heads
+  const int split = blockIdx.y % p.num_splits;
+  const int hb = blockIdx.y / p.num_splits;
   const int b = blockIdx.z;
   const int head0 = hb * M;
   const int total_tiles = (p.seq_kv + N - 1) / N;
   const int tile_begin = split * p.tiles_per_split;
-  const int n = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);
+  const int n = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);  // 128-row tiles of this split
+  constexpr uint32_t kPTxEven = L::kPBytes + M * 4;   // half 0 of a tile also carries the rescale factors
+  constexpr uint32_t kPTxOdd = L::kPBytes;
 
   if (threadIdx.x == 0) {
-    *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
-    mbar_init(q_full, 1);
-    for (int i = 0; i < ST; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    int bad = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    // the operand tiles must end inside the dynamic shared memory that was requested
+    const size_t used = static_cast<size_t>(tiles - smem_raw) + (rank == 0 ? L::kScoreTileBytes : L::kValueTileBytes);
+    if (used > static_cast<size_t>(kMlaSmemBytes)) {
+      atomicCAS(p.status, 0, kStatusTimeoutBase + kMlaSmemLayout);
+      bad = 1;
+    }
+    *abort_flag = bad;
+    for (int i = 0; i < 12; ++i) {
+      mbar_init(&bars[L::kSlotFull + i], 1);
+      mbar_init(&bars[L::kSlotEmpty + i], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&bars[L::kSFull + i], 1);
+      mbar_init(&bars[L::kSFree + i], 256);
+      mbar_init(&bars[L::kRowMax + i], 256);
     }
-    mbar_init(o_done, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&bars[L::kPFull + i], MLA_ST_ASYNC ? 1 : 128);
+      mbar_init(&bars[L::kPFree + i], 1);
+      mbar_init(&bars[L::kPvGo + i], 128);
+      mbar_init(&bars[L::kPvDone + i], 1);
+    }
+    mbar_init(&bars[L::kODone], 1);
+    mbar_init(&bars[L::kFinalFull], 128);
+    mbar_init(&bars[L::kQReady], 256);
+    mbar_init(&bars[L::kQrFull], 1);
+    mbar_init(&bars[L::kRowSum], 128);
     fence_barrier_init();
+    if (rank == 1) {
+      // every P slot expects its first half tile before the score CTA can send anything
+      if (MLA_ST_ASYNC) for (int i = 0; i < 4; ++i) mbar_arrive_expect_tx(&bars[L::kPFull + i], (i & 1) ? kPTxOdd : kPTxEven);
+    }
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmQr);
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tmKV);
     tma_prefetch_desc(&tmKVr);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmQr);
   }
   tc_fence_before_sync();
   __syncthreads();
+  cluster_sync_all();  // both CTAs have initialised (and armed) their barriers before any remote traffic
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const bool run = (n > 0) && !*abort_flag && (*reinterpret_cast<volatile int*>(p.status) == 0);
 
-  if (warp == 4) {
-    // =============== TMA producer ===============
-    if (lane == 0 && n > 0 && !*abort_flag) {
-      mbar_arrive_expect_tx(q_full, L::kQBytes);
-      // the first DV columns come from the main map, the remaining (rope) columns from the second
-      for (int c = 0; c < L::kChunks; ++c)
-        tma_load_3d(sQ + c * (M * 128), c < DV / 64 ? &tmQ : &tmQr, q_full, c < DV / 64 ? c * 64 : c * 64 - DV, head0, b);
-      for (int j = 0; j < n; ++j) {
-        const int st = j % ST;
-        if (!mbar_wait(&kv_empty[st], ((j / ST) & 1) ^ 1, ab, kMlaKvEmpty)) break;
-        mbar_arrive_expect_tx(&kv_full[st], L::kKvBytes);
-        for (int c = 0; c < L::kChunks; ++c)
-          tma_load_3d(sKV + st * L::kKvBytes + c * (N * 128), c < DV / 64 ? &tmKV : &tmKVr, &kv_full[st],
-                      c < DV / 64 ? c * 64 : c * 64 - DV, (tile_begin + j) * N, b);
+  if (rank == 0) {
+    // ===================================== score CTA =====================================
+    if (warp == 8) {
+      if (lane == 0 && run) {
+        mbar_arrive_expect_tx(&bars[L::kQrFull], L::kQrBytes);
+        tma_load_3d(sQr, &tmQr, &bars[L::kQrFull], 0, head0, b);
+        constexpr int kAhead = 3;   // tiles prefetched into L2 ahead of the shared-memory ring
+        auto prefetch_tile = [&](int j) {
+          for (int c = 0; c < 9; ++c) tma_prefetch_l2_3d(c < 8 ? &tmKV : &tmKVr, c < 8 ? c * 64 : 0, (tile_begin + j) * N, b);
+        };
+        for (int j = 0; j < kAhead && j < n; ++j) prefetch_tile(j);
+        for (int g = 0; g < n * 9; ++g) {
+          const int j = g / 9, c = g - j * 9, slot = g % L::kScoreSlots;
+          if (c == 0 && j + kAhead < n) prefetch_tile(j + kAhead);
+          if (!mbar_wait(&bars[L::kSlotEmpty + slot], ((g / L::kScoreSlots) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
+          mbar_arrive_expect_tx(&bars[L::kSlotFull + slot], L::kChunkBytes);
+          tma_load_3d(sChunk + slot * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot], c < 8 ? c * 64 : 0,
+                      (tile_begin + j) * N, b);
+        }
       }
-    }
-  } else if (warp == 5) {
-    // =============== MMA issuer ===============
-    if (lane == 0 && n > 0 && !*abort_flag) {
-      constexpr uint32_t idesc_qk = make_idesc_f16(M, N, kBf16, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_f16(M, DVH, kBf16, false, true);
-      const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV);
-      auto issue_qk = [&](int st, int buf) {
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint64_t adesc = make_smem_desc(q_addr + (ks >> 2) * (M * 128) + (ks & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(kv_addr + st * L::kKvBytes + (ks >> 2) * (N * 128) + (ks & 3) * 32, 16, 1024);
-          umma_ss(tmem_base + kColS + buf * N, adesc, bdesc, idesc_qk, ks > 0);
-        }
-        umma_commit(&s_full[buf]);
-      };
-      auto issue_pv = [&](int st, int buf, bool first) {
-        // V half: chunks [half*DVH/64, ...) of the KV tile, MN-major: 64-column chunks N*128 bytes apart
-        const uint32_t v_addr = kv_addr + st * L::kKvBytes + half * (DVH / 64) * (N * 128);
-#pragma unroll
-        for (int ks = 0; ks < N / 16; ++ks) {
-          const uint64_t bdesc = make_smem_desc(v_addr + ks * 2048, N * 128, 1024);
-          umma_ts(tmem_base + kColO, tmem_base + kColS + buf * N + ks * 8, bdesc, idesc_pv, (!first || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(o_done);
-        umma_commit(&kv_empty[st]);
-      };
-      bool ok = mbar_wait(q_full, 0, ab, kMlaQFull) && mbar_wait(&kv_full[0], 0, ab, kMlaKvFull);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_qk(0, 0);
+    } else if (warp == 9) {
+      if (lane == 0 && run) {
+        constexpr uint32_t idesc = make_idesc_f16(M, N, kBf16, false, false);
+        const uint64_t chunk_desc0 = make_smem_desc(smem_u32(sChunk), 16, 1024);
+        const uint64_t qr_desc0 = make_smem_desc(smem_u32(sQr), 16, 1024);
+        bool ok = mbar_wait(&bars[L::kQReady], 0, ab, kMlaQReady) && mbar_wait(&bars[L::kQrFull], 0, ab, kMlaQrFull);
         for (int j = 0; j < n && ok; ++j) {
-          if (j + 1 < n) {
-            const int stn = (j + 1) % ST;
-            ok = mbar_wait(&kv_full[stn], ((j + 1) / ST) & 1, ab, kMlaKvFull);
+          const int buf = j & 1;
+          ok = mbar_wait(&bars[L::kSFree + buf], ((j >> 1) & 1) ^ 1, ab, kMlaSFree);
+          for (int c = 0; c < 9 && ok; ++c) {
+            const int g = j * 9 + c, slot = g % L::kScoreSlots;
+            ok = mbar_wait(&bars[L::kSlotFull + slot], (g / L::kScoreSlots) & 1, ab, kMlaSlotFull);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_qk(stn, (j + 1) & 1);
+            // four K steps of one 64-column chunk: operands advance by 32 bytes (A: 8 TMEM columns)
+            const uint64_t bdesc = chunk_desc0 + static_cast<uint64_t>(slot * (L::kChunkBytes >> 4));
+            if (c < 8)
+              umma_ts_x4<8, 2>(tmem_base + kColS + buf * N, tmem_base + kColQ + c * 32, bdesc, idesc, c > 0 ? 1u : 0u);
+            else
+              umma_ss_x4<2, 2>(tmem_base + kColS + buf * N, qr_desc0, bdesc, idesc, 1u);
+            umma_commit(&bars[L::kSlotEmpty + slot]);
           }
-          ok = mbar_wait(&p_ready[j & 1], (j >> 1) & 1, ab, kMlaPReady);
+          if (ok) umma_commit(&bars[L::kSFull + buf]);
+        }
+      }
+    } else {
+      // 256 threads: thread (wg, row) owns columns [64*wg, 64*wg+64) of its head's score row
+      const int wg = warp >> 2;
+      const int row = (warp & 3) * 32 + lane;
+      const int head = head0 + row;
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      if (run) {
+        // ---- this head's query row, columns [256*wg, 256*wg+256) -> TMEM as 16-bit pairs ----
+        const bool valid = head < p.heads;
+        const uint4* qm = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + b * p.q_sb +
+                                                         static_cast<long long>(head) * p.q_sh + wg * 256);
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[32];
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint4 x = valid ? qm[c * 8 + v] : make_uint4(0u, 0u, 0u, 0u);
+            w[4 * v + 0] = x.x;
+            w[4 * v + 1] = x.y;
+            w[4 * v + 2] = x.z;
+            w[4 * v + 3] = x.w;
+          }
+          tmem_st32(tmem_base + lane_base + kColQ + wg * 128 + c * 32, w);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&bars[L::kQReady]);
+
+        // ---- online softmax, one 128-row tile at a time; this thread produces half tile `wg` ----
+        float m_ref = -1.0e30f, r_sum = 0.0f;
+        const float c2 = p.scale_log2;
+        const uint32_t peer_p = map_to_cta(smem_u32(sP), 1) + row * 128;
+        const uint32_t peer_scale = map_to_cta(smem_u32(s_scale), 1) + row * 4;
+        const uint32_t peer_pfull = map_to_cta(smem_u32(&bars[L::kPFull]), 1);
+        bool ok = true;
+        for (int j = 0; j < n && ok; ++j) {
+          const int buf = j & 1;
+          const int pslot = (2 * j + wg) & 3;
+          ok = mbar_wait(&bars[L::kSFull + buf], (j >> 1) & 1, ab, kMlaSFull);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_pv(j % ST, j & 1, j == 0);
+          float s[64];
+          tmem_ld32f(tmem_base + lane_base + kColS + buf * N + wg * 64, &s[0]);
+          tmem_ld32f(tmem_base + lane_base + kColS + buf * N + wg * 64 + 32, &s[32]);
+          tmem_wait_ld();
+          tc_fence_before_sync();
+          mbar_arrive(&bars[L::kSFree + buf]);  // this half is in registers
+          const int kv0 = (tile_begin + j) * N + wg * 64;
+          if (kv0 + 64 > p.seq_kv) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) s[i] = (kv0 + i < p.seq_kv) ? s[i] : -INFINITY;
+          }
+          float mx0 = s[0], mx1 = s[1];
+#pragma unroll
+          for (int i = 2; i < 64; i += 2) {
+            mx0 = fmaxf(mx0, s[i]);
+            mx1 = fmaxf(mx1, s[i + 1]);
+          }
+          // the row maximum needs the other half too: post mine, wait for both
+          s_rowmax[(buf * 2 + wg) * M + row] = fmaxf(mx0, mx1);
+          mbar_arrive(&bars[L::kRowMax + buf]);
+          ok = mbar_wait(&bars[L::kRowMax + buf], (j >> 1) & 1, ab, kMlaRowMax);
+          if (!ok) break;
+          const float mx = fmaxf(s_rowmax[(buf * 2) * M + row], s_rowmax[(buf * 2 + 1) * M + row]);
+          float o_scale = 1.0f;
+          if ((mx - m_ref) * c2 > 8.0f) {   // both halves take the same decision from the same numbers
+            o_scale = fast_exp2((m_ref - mx) * c2);
+            m_ref = mx;
+            r_sum *= o_scale;
+          }
+          const float neg = -m_ref * c2;
+          float a0 = 0.f, a1 = 0.f;
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            const float e0 = fast_exp2(fmaf(s[i], c2, neg));
+            const float e1 = fast_exp2(fmaf(s[i + 1], c2, neg));
+            a0 += e0;
+            a1 += e1;
+            pk[i / 2] = pack2<kBf16>(e0, e1);
+          }
+          r_sum += a0 + a1;
+          // P half tile (128-byte row, swizzled like a TMA-written K-major tile) and, with half 0, the rescale
+          // factor go to the value CTA; every byte is counted on its p_full barrier
+          ok = mbar_wait_cluster(&bars[L::kPFree + pslot], ((j >> 1) & 1) ^ 1, ab, kMlaPFree);
+          if (!ok) break;
+          const uint32_t dst = peer_p + pslot * L::kPBytes;
+          const uint32_t bar = peer_pfull + pslot * 8;
+#if MLA_ST_ASYNC
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            st_async_v4(dst + ((q4 ^ (row & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]), bar);
+          if (wg == 0) st_async_f32(peer_scale + (j & 1) * (M * 4), o_scale, bar);
+#else
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            st_cluster_v4(dst + ((q4 ^ (row & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]));
+          if (wg == 0) st_cluster_f32(peer_scale + (j & 1) * (M * 4), o_scale);
+          mbar_arrive_cluster(bar);
+#endif
+        }
+        // ---- final row statistics: sum of both halves ----
+        if (ok) {
+          if (wg == 1) {
+            s_rowsum[row] = r_sum;
+            mbar_arrive(&bars[L::kRowSum]);
+          } else {
+            ok = mbar_wait(&bars[L::kRowSum], 0, ab, kMlaRowSum);
+            if (ok) {
+              const float total = r_sum + s_rowsum[row];
+              const uint32_t peer_final = map_to_cta(smem_u32(s_final), 1) + row * 8;
+              st_cluster_f32(peer_final, 1.0f / total);
+              st_cluster_f32(peer_final + 4, logf(total) + m_ref * p.scale);
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bars[L::kFinalFull]), 1));
+            }
+          }
         }
       }
     }
   } else {
-    // =============== softmax: one head per thread ===============
-    const int row = warp * 32 + lane;
-    const int head = head0 + row;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tO = tmem_base + lane_base + kColO;
-    float m_ref = -1.0e30f, r_sum = 0.0f;
-    const float c2 = p.scale_log2;
-    bool ok = (n > 0) && !*abort_flag;
-    for (int j = 0; j < n && ok; ++j) {
-      const int buf = j & 1;
-      const uint32_t tS = tmem_base + lane_base + kColS + buf * N;
-      ok = mbar_wait(&s_full[buf], (j >> 1) & 1, ab, kMlaSFull);
-      if (!ok) break;
-      tc_fence_after_sync();
-      float s[N];
-      tmem_ld32f(tS, s);
-      tmem_wait_ld();
-      const int kv0 = (tile_begin + j) * N;
-      if (kv0 + N > p.seq_kv) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) s[i] = (kv0 + i < p.seq_kv) ? s[i] : -INFINITY;
+    // ===================================== value CTA =====================================
+    const int n_half = 2 * n;   // 64-row half tiles
+    if (warp == 4) {
+      if (lane == 0 && run) {
+        for (int g = 0; g < n * 4; ++g) {   // 32-row stages
+          const int st = g % L::kVStages;
+          if (!mbar_wait(&bars[L::kSlotEmpty + st], ((g / L::kVStages) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
+          mbar_arrive_expect_tx(&bars[L::kSlotFull + st], L::kVStageBytes);
+          uint8_t* dst = sV + st * L::kVStageBytes;
+          for (int c = 0; c < 8; ++c)
+            tma_load_3d(dst + c * (L::kVStageRows * 128), &tmV, &bars[L::kSlotFull + st], c * 64, tile_begin * N + g * L::kVStageRows, b);
+        }
       }
-      float mx = s[0];
-#pragma unroll
-      for (int i = 1; i < N; ++i) mx = fmaxf(mx, s[i]);
-      float o_scale = 1.0f;
-      if ((mx - m_ref) * c2 > 8.0f) {
-        o_scale = fast_exp2((m_ref - mx) * c2);
-        m_ref = mx;
-        r_sum *= o_scale;
+    } else if (warp == 5) {
+      if (lane == 0 && run) {
+        constexpr uint32_t idesc = make_idesc_f16(M, 256, kBf16, false, true);
+        const uint64_t v_desc0 = make_smem_desc(smem_u32(sV), L::kVStageRows * 128, 1024);
+        const uint64_t p_desc0 = make_smem_desc(smem_u32(sP), 16, 1024);
+        bool ok = true;
+        for (int h = 0; h < n_half && ok; ++h) {
+          const int pslot = h & 3;
+          ok = mbar_wait(&bars[L::kPvGo + pslot], (h >> 2) & 1, ab, kMlaPvGo);
+          for (int s2 = 0; s2 < 2 && ok; ++s2) {
+            const int g = h * 2 + s2, st = g % L::kVStages;
+            ok = mbar_wait(&bars[L::kSlotFull + st], (g / L::kVStages) & 1, ab, kMlaSlotFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            // two K steps of 16 KV rows; each feeds the two 256-column halves of O.  V columns [256*hh, +256):
+            // four 64-column chunks of 32 rows (4096 B apart); a K step is 2048 B further
+            const uint64_t adesc = p_desc0 + static_cast<uint64_t>(pslot * (L::kPBytes >> 4) + s2 * 4);
+            const uint64_t bdesc = v_desc0 + static_cast<uint64_t>(st * (L::kVStageBytes >> 4));
+            constexpr uint64_t kHalf = (4 * L::kVStageRows * 128) >> 4;
+            umma_ss_2d(tmem_base, tmem_base + 256, adesc, bdesc, bdesc + kHalf, idesc, (h > 0 || s2 > 0) ? 1u : 0u);
+            umma_ss_2d(tmem_base, tmem_base + 256, adesc + 2, bdesc + 128, bdesc + kHalf + 128, idesc, 1u);
+            umma_commit(&bars[L::kSlotEmpty + st]);
+          }
+          if (ok) umma_commit(&bars[L::kPvDone + pslot]);
+        }
       }
-      const float neg = -m_ref * c2;
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int i = 0; i < N; i += 2) {
-        s[i] = fast_exp2(fmaf(s[i], c2, neg));
-        s[i + 1] = fast_exp2(fmaf(s[i + 1], c2, neg));
-        a0 += s[i];
-        a1 += s[i + 1];
+    } else if (warp == 6) {
+      if (lane == 0 && run) {
+        const uint32_t peer_pfree = map_to_cta(smem_u32(&bars[L::kPFree]), 0);
+        for (int h = 0; h < n_half; ++h) {
+          const int pslot = h & 3;
+          if (!mbar_wait(&bars[L::kPvDone + pslot], (h >> 2) & 1, ab, kMlaPvDone)) break;
+          // arm the slot for its next half tile BEFORE the score CTA learns that it is free
+          if (MLA_ST_ASYNC && h + 4 < n_half) mbar_arrive_expect_tx(&bars[L::kPFull + pslot], (pslot & 1) ? kPTxOdd : kPTxEven);
+          mbar_arrive_cluster(peer_pfree + pslot * 8);
+        }
       }
-      r_sum += a0 + a1;
-      uint32_t pk[N / 2];
+    } else if (warp < 4) {
+      const int row = warp * 32 + lane;
+      const int head = head0 + row;
+      const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+      const uint32_t tO = tmem_base + lane_base;
+      bool ok = run;
+      for (int h = 0; h < n_half && ok; ++h) {
+        const int pslot = h & 3;
+        ok = mbar_wait_cluster(&bars[L::kPFull + pslot], (h >> 2) & 1, ab, kMlaPFull);
+        if (!ok) break;
+        const float o_scale = (h & 1) ? 1.0f : s_scale[((h >> 1) & 1) * M + row];
+        if (h > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
+          // O must hold everything up to half tile h-1.  A parity wait is only unambiguous if the barrier
+          // cannot be two phases away: these threads run far ahead of the MMAs, so they wait on the ring of
+          // per-slot barriers (slot (h-1)&3 was last completed for half tile h-5, which p_full(h) implies).
+          ok = mbar_wait(&bars[L::kPvDone + ((h - 1) & 3)], ((h - 1) >> 2) & 1, ab, kMlaODone);
+          if (ok) {
+            tc_fence_after_sync();
+#pragma unroll 4
+            for (int c = 0; c < DV / 32; ++c) {
+              float o[32];
+              tmem_ld32f(tO + c * 32, o);
+              tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < N / 2; ++i) pk[i] = pack2<kBf16>(s[2 * i], s[2 * i + 1]);
-      tmem_st16(tS, pk);
-      if (j > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
-        // every MMA that accumulates into O has been committed to o_done: phase j-1 must be complete
-        ok = mbar_wait(o_done, (j - 1) & 1, ab, kMlaODone);
+              for (int i = 0; i < 32; ++i) o[i] *= o_scale;
+              tmem_st32f(tO + c * 32, o);
+            }
+            tmem_wait_st();
+          }
+        }
+        fence_proxy_async_smem();   // P arrived through generic-proxy stores; the MMA reads it through the async proxy
+        tc_fence_before_sync();
+        mbar_arrive(&bars[L::kPvGo + pslot]);
+      }
+      if (ok && n > 0) {
+        ok = mbar_wait_cluster(&bars[L::kFinalFull], 0, ab, kMlaFinal) &&
+             mbar_wait(&bars[L::kPvDone + ((n_half - 1) & 3)], ((n_half - 1) >> 2) & 1, ab, kMlaOFinal);
         if (ok) {
           tc_fence_after_sync();
+          const bool in_range = head < p.heads;
+          const float inv = s_final[row * 2];
+          const float lse = s_final[row * 2 + 1];
+          if (p.num_splits == 1) {
+            uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) + 2 * ((static_cast<long long>(b) * p.heads + head) * DV);
+#pragma unroll 2
+            for (int c = 0; c < DV / 32; ++c) {
+              float o[32];
+              tmem_ld32f(tO + c * 32, o);
+              tmem_wait_ld();
+              if (in_range) {
 #pragma unroll
-          for (int c = 0; c < DVH / 32; ++c) {
-            float o[32];
-            tmem_ld32f(tO + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= o_scale;
-            tmem_st32f(tO + c * 32, o);
-          }
-        }
-      }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(&p_ready[buf]);
-    }
-    if (ok && n > 0) {
-      ok = mbar_wait(o_done, (n - 1) & 1, ab, kMlaOFinal);
-      if (ok) {
-        tc_fence_after_sync();
-        const bool in_range = head < p.heads;
-        const float inv = 1.0f / r_sum;
-        const float lse = logf(r_sum) + m_ref * p.scale;
-        if (p.num_splits == 1) {
-          uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) + 2 * ((static_cast<long long>(b) * p.heads + head) * DV + half * DVH);
-#pragma unroll
-          for (int c = 0; c < DVH / 32; ++c) {
-            float o[32];
-            tmem_ld32f(tO + c * 32, o);
-            tmem_wait_ld();
-            if (in_range) {
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 pk;
-                pk.x = pack2<kBf16>(o[8 * v + 0] * inv, o[8 * v + 1] * inv);
-                pk.y = pack2<kBf16>(o[8 * v + 2] * inv, o[8 * v + 3] * inv);
-                pk.z = pack2<kBf16>(o[8 * v + 4] * inv, o[8 * v + 5] * inv);
-                pk.w = pack2<kBf16>(o[8 * v + 6] * inv, o[8 * v + 7] * inv);
-                *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
+                for (int v = 0; v < 4; ++v) {
+                  uint4 pk;
+                  pk.x = pack2<kBf16>(o[8 * v + 0] * inv, o[8 * v + 1] * inv);
+                  pk.y = pack2<kBf16>(o[8 * v + 2] * inv, o[8 * v + 3] * inv);
+                  pk.z = pack2<kBf16>(o[8 * v + 4] * inv, o[8 * v + 5] * inv);
+                  pk.w = pack2<kBf16>(o[8 * v + 6] * inv, o[8 * v + 7] * inv);
+                  *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
+                }
               }
             }
-          }
-          if (in_range && half == 0 && p.lse != nullptr) p.lse[static_cast<long long>(b) * p.heads + head] = lse;
-        } else {
-          float* prow = p.part_o + ((static_cast<long long>(b) * p.num_splits + split) * p.heads + head) * DV + half * DVH;
+            if (in_range && p.lse != nullptr) p.lse[static_cast<long long>(b) * p.heads + head] = lse;
+          } else {
+            float* prow = p.part_o + ((static_cast<long long>(b) * p.num_splits + split) * p.heads + head) * DV;
+#pragma unroll 2
+            for (int c = 0; c < DV / 32; ++c) {
+              float o[32];
+              tmem_ld32f(tO + c * 32, o);
+              tmem_wait_ld();
+              if (in_range) {
 #pragma unroll
-          for (int c = 0; c < DVH / 32; ++c) {
-            float o[32];
-            tmem_ld32f(tO + c * 32, o);
-            tmem_wait_ld();
-            if (in_range) {
-#pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                float4 f = make_float4(o[4 * v] * inv, o[4 * v + 1] * inv, o[4 * v + 2] * inv, o[4 * v + 3] * inv);
-                *reinterpret_cast<float4*>(prow + c * 32 + v * 4) = f;
+                for (int v = 0; v < 8; ++v)
+                  *reinterpret_cast<float4*>(prow + c * 32 + v * 4) =
+                      make_float4(o[4 * v] * inv, o[4 * v + 1] * inv, o[4 * v + 2] * inv, o[4 * v + 3] * inv);
               }
             }
+            if (in_range) p.part_lse[(static_cast<long long>(b) * p.num_splits + split) * p.heads + head] = lse;
           }
-          if (in_range && half == 0) p.part_lse[(static_cast<long long>(b) * p.num_splits + split) * p.heads + head] = lse;
         }
+      } else if (n == 0 && p.num_splits > 1 && head < p.heads) {
+        // a split with no KV rows contributes nothing
+        p.part_lse[(static_cast<long long>(b) * p.num_splits + split) * p.heads + head] = -INFINITY;
       }
-    } else if (n == 0 && p.num_splits > 1 && head < p.heads && half == 0) {
-      // a split with no KV rows contributes nothing
-      p.part_lse[(static_cast<long long>(b) * p.num_splits + split) * p.heads + head] = -INFINITY;
     }
   }
 
+  // teardown: neither CTA may leave while its peer can still touch its shared memory or barriers
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
-    __syncthreads();
   }
-  if (warp == 5) {
+  cluster_sync_all();
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -391,26 +591,33 @@ inline int validate_mla_shape(const AttnB200MlaShape* s) {
 template <bool kBf16>
 int launch_mla(const AttnB200MlaArgs* a, cudaStream_t stream, int* status) {
   constexpr int D = 576, DV = 512;
-  using L = MlaSmem<D, DV>;
   const AttnB200MlaShape& s = a->shape;
-  CUtensorMap tmQ, tmQr, tmKV, tmKVr;
+  CUtensorMap tmKV, tmKVr, tmV, tmQr;
   const int esz = 2;
   // rope columns: a separate tensor, or columns [DV, D) of the fused rows
   const void* q_rope = a->q_rope != nullptr ? a->q_rope : static_cast<const uint8_t*>(a->q) + DV * esz;
   const void* kv_rope = a->kv_rope != nullptr ? a->kv_rope : static_cast<const uint8_t*>(a->kv) + DV * esz;
   const int64_t* qr_st = a->q_rope != nullptr ? a->q_rope_stride : a->q_stride;
   const int64_t* kr_st = a->kv_rope != nullptr ? a->kv_rope_stride : a->kv_stride;
-  int rc = encode_3d(&tmQ, a->q, a->dtype, DV, s.heads_q, s.batch, a->q_stride[0], a->q_stride[1], kMlaHeads);
-  if (rc != ATTN_B200_OK) return rc;
-  rc = encode_3d(&tmQr, q_rope, a->dtype, D - DV, s.heads_q, s.batch, qr_st[0], qr_st[1], kMlaHeads);
-  if (rc != ATTN_B200_OK) return rc;
-  rc = encode_3d(&tmKV, a->kv, a->dtype, DV, s.seq_kv, s.batch, a->kv_stride[0], a->kv_stride[1], kMlaTileN);
+  // the first DV columns of a q row are read with 16-byte loads straight into tensor memory
+  if ((reinterpret_cast<uintptr_t>(a->q) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  for (int i = 0; i < 2; ++i)
+    if (a->q_stride[i] % 8 != 0) return ATTN_B200_E_UNSUPPORTED;
+  int rc = encode_3d(&tmKV, a->kv, a->dtype, DV, s.seq_kv, s.batch, a->kv_stride[0], a->kv_stride[1], kMlaTileN);
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_3d(&tmKVr, kv_rope, a->dtype, D - DV, s.seq_kv, s.batch, kr_st[0], kr_st[1], kMlaTileN);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_3d(&tmV, a->kv, a->dtype, DV, s.seq_kv, s.batch, a->kv_stride[0], a->kv_stride[1], MlaSmem::kVStageRows);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_3d(&tmQr, q_rope, a->dtype, D - DV, s.heads_q, s.batch, qr_st[0], qr_st[1], kMlaHeads);
   if (rc != ATTN_B200_OK) return rc;
   MlaParams p;
   std::memset(&p, 0, sizeof(p));
   const int total_tiles = (s.seq_kv + kMlaTileN - 1) / kMlaTileN;
+  p.q = a->q;
+  p.q_sb = a->q_stride[0];
+  p.q_sh = a->q_stride[1];
+  p.head_blocks = (s.heads_q + kMlaHeads - 1) / kMlaHeads;
   p.o = a->o;
   p.lse = a->lse;
   p.batch = s.batch;
@@ -426,12 +633,13 @@ int launch_mla(const AttnB200MlaArgs* a, cudaStream_t stream, int* status) {
     p.part_lse = p.part_o + static_cast<long long>(s.batch) * a->num_splits * s.heads_q * DV;
   }
   auto kernel = mla_split_kernel<D, DV, kBf16>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return ATTN_B200_E_LAUNCH;
   }
-  dim3 grid(2 * a->num_splits, (s.heads_q + kMlaHeads - 1) / kMlaHeads, s.batch);
-  kernel<<<grid, kMlaThreads, L::kBytes, stream>>>(tmQ, tmQr, tmKV, tmKVr, p);
+  if (static_cast<long long>(a->num_splits) * p.head_blocks > 65535) return ATTN_B200_E_UNSUPPORTED;
+  dim3 grid(2, a->num_splits * p.head_blocks, s.batch);  // x = the two CTAs of a cluster
+  kernel<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tmKV, tmKVr, tmV, tmQr, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (a->num_splits > 1) {
     const long long warps = static_cast<long long>(s.batch) * s.heads_q;
@@ -450,23 +658,26 @@ int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t*
   int rc = b200::validate_mla_shape(shape);
   if (rc != ATTN_B200_OK) return rc;
   if (num_splits_out == nullptr || sm_count <= 0) return ATTN_B200_E_INVALID_ARG;
-  // CTAs per split level: 2 (halves of dim_v) x head blocks x sequences, one CTA per SM at a time.
-  // Pick the split count that fills whole waves best; every split must keep at least 8 KV tiles
-  // (each CTA re-reads Q, and the combine pass costs one more sweep over the partial outputs).
-  const long long base = 2LL * ((shape->heads_q + b200::kMlaHeads - 1) / b200::kMlaHeads) * shape->batch;
+  // One cluster (two SMs) per (sequence, split, head block): sm_count / 2 clusters run at a time.
+  // Pick the split count that fills whole waves best; every split keeps at least 4 KV tiles of 128 rows (each
+  // cluster re-reads Q, and the combine pass costs one more sweep over the partial outputs).
+  const long long base = static_cast<long long>((shape->heads_q + b200::kMlaHeads - 1) / b200::kMlaHeads) * shape->batch;
   const int total_tiles = (shape->seq_kv + b200::kMlaTileN - 1) / b200::kMlaTileN;
+  sm_count = sm_count / 2 > 0 ? sm_count / 2 : 1;
+  // Cost model fitted to measurements on B200: a cluster spends about 14 tile-times per work unit on
+  // set-up and tear-down (barriers, TMEM, Q into TMEM, pipeline fill, final exchange and store), and
+  // split-KV adds the combine pass over the fp32 partials (about one tile-time per unit per 8 splits).
   int best = 1;
-  double best_score = -1.0;
+  double best_cost = 1e300;
   for (int s = 1; s <= 64; ++s) {
     const int tiles = (total_tiles + s - 1) / s;
-    if (s > 1 && tiles < 8) break;
+    if (s > 1 && tiles < 4) break;
     if ((s - 1) * tiles >= total_tiles) continue;  // last split would be empty
-    const long long ctas = base * s;
-    const long long waves = (ctas + sm_count - 1) / sm_count;
-    const double fill = static_cast<double>(ctas) / static_cast<double>(waves * sm_count);
-    const double score = fill - 0.004 * (s - 1);
-    if (score > best_score + 1e-9) {
-      best_score = score;
+    const long long units = base * s;
+    const long long waves = (units + sm_count - 1) / sm_count;
+    const double cost = static_cast<double>(waves) * (tiles + 14.0) + (s > 1 ? 0.125 * s * waves : 0.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
       best = s;
     }
   }

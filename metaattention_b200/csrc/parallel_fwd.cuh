@@ -68,6 +68,13 @@ __device__ __forceinline__ void tma_load_rows(void* dst, const CUtensorMap* tm, 
   tma_load_4d(dst, tm, bar, c0, c1, c2, c3);
 }
 
+__device__ __forceinline__ void tma_prefetch_rows_l2(const CUtensorMap* tm, int c0, int s, int h, int b, const CoordOrder& o) {
+  const int c1 = (o.pos_s == 1) ? s : (o.pos_h == 1) ? h : b;
+  const int c2 = (o.pos_s == 2) ? s : (o.pos_h == 2) ? h : b;
+  const int c3 = (o.pos_s == 3) ? s : (o.pos_h == 3) ? h : b;
+  tma_prefetch_l2_4d(tm, c0, c1, c2, c3);
+}
+
 // wait-site ids reported through the device status word
 enum ParallelWaitSite {
   kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePReady, kSiteODone, kSiteOFinal
@@ -181,6 +188,11 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int j = 0; j < n_max; ++j) {
         const int st = j % ST;
         const uint32_t ph = (j / ST) & 1;
+        if (j + ST < n_max) {
+          // the tile after the ones the ring can hold goes to L2 now, so its later load does not wait on DRAM
+          for (int c = 0; c < D / 64; ++c) tma_prefetch_rows_l2(&tmK, c * 64, (j + ST) * BN, h, b, p.ok);
+          for (int c = 0; c < DV / 64; ++c) tma_prefetch_rows_l2(&tmV, c * 64, (j + ST) * BN, h, b, p.ov);
+        }
         if (!mbar_wait(&k_empty[st], ph ^ 1, ab, kSiteKEmpty)) break;
         mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
         for (int c = 0; c < D / 64; ++c)
@@ -196,24 +208,25 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0 && n_max > 0 && !*abort_flag) {
       constexpr uint32_t idesc_qk = make_idesc_f16(BM, BN, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(BM, DV, kBf16, false, true);
-      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      // Descriptors are built once; per MMA only the start-address field moves (units of 16 bytes), and four
+      // K steps go out per asm block: the issuing lane's instruction count is latency in front of the tensor pipe.
+      const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc(smem_u32(sV), BN * 128, 1024);
       auto issue_qk = [&](int t, int st) {
+        const uint64_t a = q_desc0 + static_cast<uint64_t>(t * (L::kQBytes >> 4));
+        const uint64_t bq = k_desc0 + static_cast<uint64_t>(st * (L::kKBytes >> 4));
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (BM * 128) + (ks & 3) * 32;
-          const uint64_t adesc = make_smem_desc(q_addr + t * L::kQBytes + off, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(k_addr + st * L::kKBytes + off, 16, 1024);
-          umma_ss(tmem_base + kColS + t * BN, adesc, bdesc, idesc_qk, ks > 0);
-        }
+        for (int ch = 0; ch < D / 64; ++ch)
+          umma_ss_x4<2, 2>(tmem_base + kColS + t * BN, a + ch * ((BM * 128) >> 4), bq + ch * ((BN * 128) >> 4), idesc_qk, ch > 0 ? 1u : 0u);
         umma_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, int st, bool first) {
+        const uint64_t bv = v_desc0 + static_cast<uint64_t>(st * (L::kVBytes >> 4));
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint64_t bdesc = make_smem_desc(v_addr + st * L::kVBytes + ks * 2048, BN * 128, 1024);
-          umma_ts(tmem_base + kColO + t * DV, tmem_base + kColS + t * BN + ks * 8, bdesc, idesc_pv,
-                  (!first || ks > 0) ? 1u : 0u);
-        }
+        for (int g = 0; g < BN / 64; ++g)   // 16 KV rows (2048 B) per K step, P advances 8 TMEM columns
+          umma_ts_x4<8, 128>(tmem_base + kColO + t * DV, tmem_base + kColS + t * BN + g * 32, bv + g * 512, idesc_pv,
+                             (!first || g > 0) ? 1u : 0u);
         umma_commit(&o_done[t]);
       };
       bool ok = mbar_wait(q_full, 0, ab, kSiteQFull);

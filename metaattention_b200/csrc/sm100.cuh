@@ -55,14 +55,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
+// A waiting thread is suspended by the hardware (up to this hint) instead of polling, so that warps
+// parked on a barrier do not take issue slots from the warp that feeds the tensor pipe.
+constexpr uint32_t kSuspendHintNs = 20000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -98,6 +102,79 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 }
 
 // ---------------------------------------------------------------------------
+// thread-block clusters: distributed shared memory and cross-CTA barriers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the peer CTA's copy of a shared-memory location (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Asynchronous store into another CTA's shared memory; the 16 bytes are counted on that CTA's mbarrier
+// (complete_tx) when they have landed, so the writer needs no release fence and does not wait.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint4 v, uint32_t cluster_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(cluster_mbar) : "memory");
+}
+__device__ __forceinline__ void st_async_f32(uint32_t cluster_addr, float v, uint32_t cluster_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(cluster_addr), "r"(__float_as_uint(v)), "r"(cluster_mbar) : "memory");
+}
+// Arrive on a barrier of another CTA of the cluster; releases this thread's earlier writes at cluster scope.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a local barrier whose arrivals come from the peer CTA (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const AbortState& ab, int site) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0xff) == 0) {
+      if (*ab.cta_flag) return false;
+      if (*reinterpret_cast<volatile int*>(ab.device_status) != 0) {
+        *ab.cta_flag = 1;
+        return false;
+      }
+      if (clock64() - t0 > kWaitCycleLimit) {
+        *ab.cta_flag = 1;
+        atomicCAS(ab.device_status, 0, kStatusTimeoutBase + site);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), plain per-CTA loads only
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
@@ -116,6 +193,17 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* t
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+
+// Prefetch of a tile into L2 only: no shared memory, no barrier.  Issued a few tiles ahead it takes the
+// DRAM latency out of the later load into shared memory, so the depth of the shared-memory ring only has
+// to cover the L2 latency.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* tm, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tm), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* tm, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -238,6 +326,57 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Batched issue: four MMAs over four consecutive K steps from ONE asm block.  The issuing thread is a
+// single lane, so every instruction it spends per MMA (descriptor arithmetic, predicate set-up) is
+// serial latency in front of the tensor pipe; here the operand descriptors advance by immediates:
+// kAStep / kBStep in descriptor units of 16 bytes (2 = 32 B = 16 K-major elements inside a 128-byte
+// swizzle chunk, 128 = 2048 B = 16 rows of an MN-major tile); for a TMEM operand kAStep is in columns.
+// The first MMA uses `acc_first` as its accumulate flag, the other three always accumulate.
+template <int kAStep, int kBStep>
+__device__ __forceinline__ void umma_ss_x4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 pt, %3, %3;\n\t"
+      "add.s64 a1, %1, %5;\n\tadd.s64 b1, %2, %6;\n\t"
+      "add.s64 a2, a1, %5;\n\tadd.s64 b2, b1, %6;\n\t"
+      "add.s64 a3, a2, %5;\n\tadd.s64 b3, b2, %6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, pt;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc_first), "n"(kAStep), "n"(kBStep)
+      : "memory");
+}
+template <int kAStep, int kBStep>
+__device__ __forceinline__ void umma_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, pt;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 b1, b2, b3;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 pt, %3, %3;\n\t"
+      "add.u32 a1, %1, %5;\n\tadd.s64 b1, %2, %6;\n\t"
+      "add.u32 a2, a1, %5;\n\tadd.s64 b2, b1, %6;\n\t"
+      "add.u32 a3, a2, %5;\n\tadd.s64 b3, b2, %6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc_first), "n"(kAStep), "n"(kBStep)
+      : "memory");
+}
+// Two MMAs that share the A operand and differ in accumulator and B operand (two N halves of one K step).
+__device__ __forceinline__ void umma_ss_2d(uint32_t d0, uint32_t d1, uint64_t adesc, uint64_t bdesc0, uint64_t bdesc1,
+                                           uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %3, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], %2, %4, %5, p;\n\t}"
+      ::"r"(d0), "r"(d1), "l"(adesc), "l"(bdesc0), "l"(bdesc1), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrives once on `bar` when every tcgen05.mma issued so far by this thread has completed.

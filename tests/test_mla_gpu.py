@@ -42,7 +42,7 @@ def test_against_reference_golden_tl_convention():
 
 @pytest.mark.parametrize("B,H,S,splits", [
     (2, 128, 1024, 1), (2, 128, 1024, 4), (1, 128, 8192, None), (3, 64, 500, 3), (1, 16, 37, 1),
-    (1, 128, 97, 2), (2, 256, 640, 2),
+    (1, 128, 297, 2), (2, 256, 640, 2), (1, 128, 129, 1),
 ])
 def test_shapes_and_splits(B, H, S, splits):
     D, Dv = 576, 512

@@ -80,7 +80,7 @@ def test_static_entry_refuses_what_does_not_fit():
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     # 128 sequences x 4 splits x 128 heads of fp32 partials = 134 MB of scratch: beyond the 32 MiB array
     q = torch.zeros(128, 128, 576, dtype=torch.bfloat16, device="cuda")
-    kv = torch.zeros(128, 256, 576, dtype=torch.bfloat16, device="cuda")
+    kv = torch.zeros(128, 1024, 576, dtype=torch.bfloat16, device="cuda")
     o = torch.zeros(128, 128, 512, dtype=torch.bfloat16, device="cuda")
     lse = torch.zeros(128, 128, dtype=torch.float32, device="cuda")
     rc = native.attn_b200_mla_decode_static(C.byref(_args(q, kv, o, lse, 4)), status.data_ptr(), lib.current_stream_ptr())
