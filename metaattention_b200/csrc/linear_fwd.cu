@@ -54,7 +54,8 @@ template <int DK>
 struct LinearSmem {
   static constexpr int kQBytes = kLinT * DK * 2;
   static constexpr int kVBytes = kLinT * kLinDvs * 2;
-  static constexpr int kHBytes = kLinDvs * DK * 2;
+  // operand copy of the state; the same bytes stage one block of output rows (128 x 256 B)
+  static constexpr int kHBytes = (kLinDvs * DK * 2 > kLinT * kLinDvs * 2) ? kLinDvs * DK * 2 : kLinT * kLinDvs * 2;
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + kQBytes;
@@ -68,7 +69,7 @@ struct LinearSmem {
 template <int DK, bool kBf16>
 __global__ void __launch_bounds__(kLinThreads, 1)
 linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const LinearParams p) {
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const LinearParams p) {
   using L = LinearSmem<DK>;
   constexpr int T = kLinT, DVS = kLinDvs, KC = DK / 64;
   static_assert(DK % 64 == 0 && DK <= 256, "unsupported dim_qk");
@@ -108,6 +109,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -197,23 +199,27 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc_fence_after_sync();
     if (tid == 0 && ok && !last) load_q(t + 1);  // Q is no longer read by any MMA of this block
     // ---- phase 2: rows of S -> P, rows of O scaled by scale * exp(g_i) ----
-    if (wg == 0) {
+    // Both warp groups work on every row: group `wg` owns columns [64*wg, 64*wg+64) of S and of O (a single
+    // warp per scheduler running dependent arithmetic is latency-bound; two interleave).
+    {
       const float gi = g2[buf * T + row];
-      float s[T];
-#pragma unroll
-      for (int c = 0; c < T / 32; ++c) tmem_ld32f(tS + c * 32, &s[c * 32]);
+      const float qs = p.q_scale;
+      const float* gcol = g2 + buf * T + wg * 64;
+      float s[64];
+      tmem_ld32f(tS + wg * 64, &s[0]);
+      tmem_ld32f(tS + wg * 64 + 32, &s[32]);
       tmem_wait_ld();
-      // P overwrites S: columns [0, 64) hold P (16-bit pairs); with split_p, columns [64, 128) hold the
-      // 16-bit remainder P - round(P), which a second PV pass adds (the whole S row is in registers)
+      uint32_t pk[32], pl[32];
 #pragma unroll
-      for (int c = 0; c < T / 64; ++c) {
-        uint32_t pk[32], pl[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int j0 = c * 64 + 2 * i, j1 = j0 + 1;
-          const float p0 = (j0 <= row) ? s[j0] * p.q_scale * fast_exp2(gi - g2[buf * T + j0]) : 0.0f;
-          const float p1 = (j1 <= row) ? s[j1] * p.q_scale * fast_exp2(gi - g2[buf * T + j1]) : 0.0f;
-          pk[i] = pack2<kBf16>(p0, p1);
+      for (int i = 0; i < 32; ++i) {
+        const int j0 = wg * 64 + 2 * i, j1 = j0 + 1;
+        // computed for every column and selected afterwards: a per-lane branch here diverges in every warp
+        const float e0 = s[2 * i] * qs * fast_exp2(fminf(gi - gcol[2 * i], 0.0f));
+        const float e1 = s[2 * i + 1] * qs * fast_exp2(fminf(gi - gcol[2 * i + 1], 0.0f));
+        const float p0 = (j0 <= row) ? e0 : 0.0f;
+        const float p1 = (j1 <= row) ? e1 : 0.0f;
+        pk[i] = pack2<kBf16>(p0, p1);
+        if (p.split_p) {
           float h0, h1;
           if constexpr (kBf16) {
             const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&pk[i]);
@@ -226,19 +232,25 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           }
           pl[i] = pack2<kBf16>(p0 - h0, p1 - h1);
         }
-        tmem_st32(tS + c * 32, pk);
-        if (p.split_p) tmem_st32(tS + 64 + c * 32, pl);
       }
+      // P overwrites S: 16-bit pairs in columns [0, 64), and with split_p the 16-bit remainder P - round(P) in
+      // columns [64, 128) for a second PV pass.  Those columns belong to the other group's half of S, so
+      // every thread must have its S values in registers first.
+      tc_fence_before_sync();
+      __syncthreads();
+      tc_fence_after_sync();
+      tmem_st32(tS + wg * 32, pk);
+      if (p.split_p) tmem_st32(tS + 64 + wg * 32, pl);
       if (t > 0) {
-        const float f = p.q_scale * fast_exp2(gi);
+        const float f = qs * fast_exp2(gi);
 #pragma unroll
-        for (int c = 0; c < DVS / 32; ++c) {
+        for (int c = 0; c < 2; ++c) {
           float o[32];
-          tmem_ld32f(tO + c * 32, o);
+          tmem_ld32f(tO + wg * 64 + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= f;
-          tmem_st32f(tO + c * 32, o);
+          tmem_st32f(tO + wg * 64 + c * 32, o);
         }
       }
       tmem_wait_st();
@@ -262,62 +274,62 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     ++mma_n;
     tc_fence_after_sync();
     // ---- phase 4: store O rows; rescale V rows for the state update ----
-    if (wg == 0) {
+    {
+      // The rows go out through shared memory: the buffer of the state's operand copy is idle between the
+      // Q.h MMA of this block and the conversion pass at its end.  Group `wg` writes the 64-column chunk
+      // `wg` of its row as one swizzled 128-byte line (the layout TMA expects); one TMA store per chunk
+      // writes full lines, and rows past the end of the sequence are clipped by the tensor map.
       const int tok = t * T + row;
-      const bool in_range = tok < p.seq;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) + 2 * ((static_cast<long long>(bh) * p.seq + tok) * p.dim_v + slice * DVS);
       float sum = 0.f, sq = 0.f;
+      uint8_t* line = sH + wg * (T * 128) + row * 128;
 #pragma unroll
-      for (int c = 0; c < DVS / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         float o[32];
-        tmem_ld32f(tO + c * 32, o);
+        tmem_ld32f(tO + wg * 64 + c * 32, o);
         tmem_wait_ld();
-        if (in_range) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 pk;
           if (p.stats == nullptr) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
-              pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
-              pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
-              pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
-              *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
-            }
+            pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
+            pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
+            pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
+            pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
           } else {
-            // the row is normalised by a second pass: stage it as fp16 (11 significant bits, clamped to
-            // the fp16 range) so that the only bf16 rounding is the final one
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 pk;
-              pk.x = pack2<false>(clamp_h(o[8 * v + 0]), clamp_h(o[8 * v + 1]));
-              pk.y = pack2<false>(clamp_h(o[8 * v + 2]), clamp_h(o[8 * v + 3]));
-              pk.z = pack2<false>(clamp_h(o[8 * v + 4]), clamp_h(o[8 * v + 5]));
-              pk.w = pack2<false>(clamp_h(o[8 * v + 6]), clamp_h(o[8 * v + 7]));
-              *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
-            }
+            // normalised by a second pass: staged as fp16 (11 significant bits, clamped to the fp16 range)
+            pk.x = pack2<false>(clamp_h(o[8 * v + 0]), clamp_h(o[8 * v + 1]));
+            pk.y = pack2<false>(clamp_h(o[8 * v + 2]), clamp_h(o[8 * v + 3]));
+            pk.z = pack2<false>(clamp_h(o[8 * v + 4]), clamp_h(o[8 * v + 5]));
+            pk.w = pack2<false>(clamp_h(o[8 * v + 6]), clamp_h(o[8 * v + 7]));
           }
+          *reinterpret_cast<uint4*>(line + (((c * 4 + v) ^ (row & 7)) << 4)) = pk;
         }
+        if (p.stats != nullptr) {
+          float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          sum += o[i];
-          sq += o[i] * o[i];
+          for (int i = 0; i < 32; i += 2) {
+            s0 += o[i];
+            s1 += o[i + 1];
+            q0 = fmaf(o[i], o[i], q0);
+            q1 = fmaf(o[i + 1], o[i + 1], q1);
+          }
+          sum += s0 + s1;
+          sq += q0 + q1;
         }
       }
-      if (p.stats != nullptr && in_range) {
+      if (p.stats != nullptr && tok < p.seq) {
         float* st = p.stats + (static_cast<long long>(bh) * p.seq + tok) * 2;
         atomicAdd(st, sum);
         atomicAdd(st + 1, sq);
       }
-    } else if (!last) {
-      // token `row` of V is multiplied by exp(g_last - g_row); 16-byte pieces of a row stay inside
-      // its 128-byte line under the swizzle, so the permutation does not matter here
-      const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
-#pragma unroll
-      for (int c = 0; c < DVS / 64; ++c) {
-        uint4* line = reinterpret_cast<uint4*>(sV + c * (T * 128) + row * 128);
+      if (!last) {
+        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row); the 16-byte pieces of a row stay
+        // inside its 128-byte line under the swizzle, so the permutation does not matter here
+        const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
+        uint4* vline = reinterpret_cast<uint4*>(sV + wg * (T * 128) + row * 128);
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
-          uint4 x = line[q4];
+          uint4 x = vline[q4];
           uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -333,13 +345,17 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             xs[e] = pack2<kBf16>(lo * w, hi * w);
           }
-          line[q4] = x;
+          vline[q4] = x;
         }
       }
       fence_proxy_async_smem();
     }
     tc_fence_before_sync();
     if (!__syncthreads_and(ok)) break;
+    if (tid == 0) {
+      for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
+      tma_store_commit();
+    }
     if (last) break;
     // ---- phase 5: hT (+)= V'^T K ----
     if (tid == 0) {
@@ -347,6 +363,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
       for (int g = 0; g < T / 64; ++g)   // both operands are MN-major over tokens: 16 tokens = 2048 B per K step
         umma_ss_x4<128, 128>(tmem_base + kColH, v_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
+      // the output stores read the buffer that the conversion pass below overwrites: the barrier that
+      // releases that pass is only committed once they have finished reading
+      tma_store_wait_read();
       umma_commit(mma_bar);
     }
     ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
@@ -385,6 +404,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (!__syncthreads_and(ok)) break;
   }
 
+  if (tid == 0) tma_store_wait_all();
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
@@ -435,13 +455,15 @@ inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t c
 template <int DK, bool kBf16>
 int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status) {
   using L = LinearSmem<DK>;
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   const uint64_t bh = static_cast<uint64_t>(a->batch) * a->heads;
   int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_rows3(&tmK, a->k, a->dtype, DK, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
+  if (rc != ATTN_B200_OK) return rc;
+  rc = encode_rows3(&tmO, a->o, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
   LinearParams p;
   std::memset(&p, 0, sizeof(p));
@@ -464,7 +486,7 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
     return ATTN_B200_E_LAUNCH;
   }
   dim3 grid(a->dim_v / kLinDvs, static_cast<unsigned>(bh));
-  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
+  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (a->normalize) {
     const int blocks = static_cast<int>((rows * 32 + 255) / 256);
