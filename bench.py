@@ -246,6 +246,28 @@ def extras_retention(steps, warmup):
     return out
 
 
+def run_profile_case(kind, steps, warmup):
+    """A small case of the MLA decode or the chunked retention kernel: inputs larger than L2 (126 MB) but well
+    under a GB, so that an ncu capture of a launch or two ends by itself quickly.  Prints its CUDA-event time."""
+    import metaattention_b200  # noqa: F401
+    torch.cuda.set_device(0)
+    if kind == "mla":
+        from attn_engine.mla import mla_decode_forward
+        B, H, S, D, Dv = 74, 128, 4096, 576, 512     # one cluster per sequence: a single full wave; KV = 349 MB
+        q, kv = [t.cuda() for t in oracle_inputs.mla_inputs(B, H, S, D, Dv, 5)]
+        fn = lambda: mla_decode_forward(q, kv, Dv, D ** -0.5, num_splits=1)  # noqa: E731
+        work = {"bytes": (B * S * D + B * H * D + B * H * Dv) * 2}
+    else:
+        from attn_engine.linear_attn_engine import linear_attention_forward
+        B, H, S, Dk, Dv = 2, 8, 4096, 256, 512       # q,k,v,o = 201 MB
+        q, k, v, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(B, H, S, Dk, Dv, 4)]
+        ld = decay.log()
+        fn = lambda: linear_attention_forward(q, k, v, ld, q_scale=Dk ** -0.5)  # noqa: E731
+        work = {"flops": float(B * H * S) * (2 * 64 * (Dk + Dv) + 4 * Dk * Dv)}
+    ms = time_device(fn, steps, warmup, lambda: None) / steps
+    print(json.dumps({"profile_case": kind, "ms": ms, **work}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,6 +275,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--profile-kernel", choices=["mla", "linear"], default=None,
+                    help="run a few launches of one of the other kernel families on a small case and exit (for ncu captures)")
     ap.add_argument("--batch", type=int, default=None,
                     help="shrink the batch of the headline workload (for small profiler captures; not a headline number)")
     args = ap.parse_args()
@@ -263,6 +287,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.profile_kernel is not None:
+        run_profile_case(args.profile_kernel, args.steps, args.warmup)
         return
 
     import metaattention_b200  # noqa: F401
@@ -347,6 +374,7 @@ def main():
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
                          "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
+                         "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
                          "frac_of_nominal_2250": achieved / 2250.0},
         }
         if world == 1:

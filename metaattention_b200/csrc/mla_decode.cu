@@ -16,8 +16,8 @@
 //   score CTA (cluster rank 0)                           value CTA (cluster rank 1)
 //   TMEM: Q[:, :512] as 16-bit pairs (256 columns) and    TMEM: O, 128 x 512 fp32 (512 columns)
 //         two 128-column score tiles
-//   smem: Q[:, 512:] tile, ring of 12 KV chunks           smem: ring of five 32-row V stages, four
-//         (128 rows x 64 columns each)                          64-row P slots
+//   smem: Q[:, 512:] tile, ring of 4 slots of three KV    smem: ring of five 32-row V stages, four
+//         chunks (128 rows x 64 columns) each                   64-row P slots
 //   warp 8: TMA, chunk by chunk                           warp 4: TMA
 //   warp 9: S = Q.KV^T over 128 KV rows: 36 MMAs with      warp 5: O += P.V per 64-row half tile
 //           N = 128 (full tensor rate; an MMA costs        warps 0-3: one head per thread: rescale O when
@@ -99,9 +99,10 @@ struct MlaSmem {
   static constexpr int kOffRowSum = 2560;  // score: float [128]
   static constexpr int kSmallBytes = 3072;
   static constexpr int kChunkBytes = kMlaTileN * 128;           // 16384: 128 rows x 64 columns
-  static constexpr int kScoreSlots = 12;
+  static constexpr int kScoreSlots = 4;                         // each slot holds three chunks: a tile is 3 slots
   static constexpr int kQrBytes = kMlaHeads * 128;              // 16384: Q[:, 512:576]
-  static constexpr int kScoreTileBytes = kQrBytes + kScoreSlots * kChunkBytes;   // 212992
+  static constexpr int kSlotBytes = 3 * kChunkBytes;            // 49152
+  static constexpr int kScoreTileBytes = kQrBytes + kScoreSlots * kSlotBytes;    // 212992
   static constexpr int kVStageRows = 32;
   static constexpr int kVStages = 5;
   static constexpr int kVStageBytes = kVStageRows * 512 * 2;    // 32768: 8 chunks of 32 rows x 128 B
@@ -208,18 +209,13 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
       if (lane == 0 && run) {
         mbar_arrive_expect_tx(&bars[L::kQrFull], L::kQrBytes);
         tma_load_3d(sQr, &tmQr, &bars[L::kQrFull], 0, head0, b);
-        constexpr int kAhead = 3;   // tiles prefetched into L2 ahead of the shared-memory ring
-        auto prefetch_tile = [&](int j) {
-          for (int c = 0; c < 9; ++c) tma_prefetch_l2_3d(c < 8 ? &tmKV : &tmKVr, c < 8 ? c * 64 : 0, (tile_begin + j) * N, b);
-        };
-        for (int j = 0; j < kAhead && j < n; ++j) prefetch_tile(j);
-        for (int g = 0; g < n * 9; ++g) {
-          const int j = g / 9, c = g - j * 9, slot = g % L::kScoreSlots;
-          if (c == 0 && j + kAhead < n) prefetch_tile(j + kAhead);
+        for (int g = 0; g < n * 3; ++g) {   // slot loads: three 64-column chunks of one 128-row tile each
+          const int j = g / 3, c0 = (g - j * 3) * 3, slot = g % L::kScoreSlots;
           if (!mbar_wait(&bars[L::kSlotEmpty + slot], ((g / L::kScoreSlots) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
-          mbar_arrive_expect_tx(&bars[L::kSlotFull + slot], L::kChunkBytes);
-          tma_load_3d(sChunk + slot * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot], c < 8 ? c * 64 : 0,
-                      (tile_begin + j) * N, b);
+          mbar_arrive_expect_tx(&bars[L::kSlotFull + slot], L::kSlotBytes);
+          for (int c = c0; c < c0 + 3; ++c)
+            tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot],
+                        c < 8 ? c * 64 : 0, (tile_begin + j) * N, b);
         }
       }
     } else if (warp == 9) {
@@ -231,17 +227,23 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         for (int j = 0; j < n && ok; ++j) {
           const int buf = j & 1;
           ok = mbar_wait(&bars[L::kSFree + buf], ((j >> 1) & 1) ^ 1, ab, kMlaSFree);
-          for (int c = 0; c < 9 && ok; ++c) {
-            const int g = j * 9 + c, slot = g % L::kScoreSlots;
+          for (int u = 0; u < 3 && ok; ++u) {
+            const int g = j * 3 + u, slot = g % L::kScoreSlots;
             ok = mbar_wait(&bars[L::kSlotFull + slot], (g / L::kScoreSlots) & 1, ab, kMlaSlotFull);
             if (!ok) break;
             tc_fence_after_sync();
-            // four K steps of one 64-column chunk: operands advance by 32 bytes (A: 8 TMEM columns)
-            const uint64_t bdesc = chunk_desc0 + static_cast<uint64_t>(slot * (L::kChunkBytes >> 4));
-            if (c < 8)
-              umma_ts_x4<8, 2>(tmem_base + kColS + buf * N, tmem_base + kColQ + c * 32, bdesc, idesc, c > 0 ? 1u : 0u);
-            else
-              umma_ss_x4<2, 2>(tmem_base + kColS + buf * N, qr_desc0, bdesc, idesc, 1u);
+            // three 64-column chunks, four K steps each: operands advance by 32 bytes (A: 8 TMEM columns);
+            // one barrier check and one commit per twelve MMAs keep the issuing lane's overhead small
+            const uint64_t bdesc = chunk_desc0 + static_cast<uint64_t>(slot * (L::kSlotBytes >> 4));
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+              const int c = u * 3 + k;
+              const uint64_t bd = bdesc + static_cast<uint64_t>(k * (L::kChunkBytes >> 4));
+              if (c < 8)
+                umma_ts_x4<8, 2>(tmem_base + kColS + buf * N, tmem_base + kColQ + c * 32, bd, idesc, c > 0 ? 1u : 0u);
+              else
+                umma_ss_x4<2, 2>(tmem_base + kColS + buf * N, qr_desc0, bd, idesc, 1u);
+            }
             umma_commit(&bars[L::kSlotEmpty + slot]);
           }
           if (ok) umma_commit(&bars[L::kSFull + buf]);

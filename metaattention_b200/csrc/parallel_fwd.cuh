@@ -68,13 +68,6 @@ __device__ __forceinline__ void tma_load_rows(void* dst, const CUtensorMap* tm, 
   tma_load_4d(dst, tm, bar, c0, c1, c2, c3);
 }
 
-__device__ __forceinline__ void tma_prefetch_rows_l2(const CUtensorMap* tm, int c0, int s, int h, int b, const CoordOrder& o) {
-  const int c1 = (o.pos_s == 1) ? s : (o.pos_h == 1) ? h : b;
-  const int c2 = (o.pos_s == 2) ? s : (o.pos_h == 2) ? h : b;
-  const int c3 = (o.pos_s == 3) ? s : (o.pos_h == 3) ? h : b;
-  tma_prefetch_l2_4d(tm, c0, c1, c2, c3);
-}
-
 // wait-site ids reported through the device status word
 enum ParallelWaitSite {
   kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePReady, kSiteODone, kSiteOFinal
@@ -188,11 +181,6 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int j = 0; j < n_max; ++j) {
         const int st = j % ST;
         const uint32_t ph = (j / ST) & 1;
-        if (j + ST < n_max) {
-          // the tile after the ones the ring can hold goes to L2 now, so its later load does not wait on DRAM
-          for (int c = 0; c < D / 64; ++c) tma_prefetch_rows_l2(&tmK, c * 64, (j + ST) * BN, h, b, p.ok);
-          for (int c = 0; c < DV / 64; ++c) tma_prefetch_rows_l2(&tmV, c * 64, (j + ST) * BN, h, b, p.ov);
-        }
         if (!mbar_wait(&k_empty[st], ph ^ 1, ab, kSiteKEmpty)) break;
         mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
         for (int c = 0; c < D / 64; ++c)
