@@ -34,7 +34,8 @@ namespace b200 {
 
 constexpr int kLinT = 128;    // tokens per block
 constexpr int kLinDvs = 128;  // dim_v columns per CTA
-constexpr int kLinThreads = 256;
+constexpr int kLinRowThreads = 256;              // eight warps: one TMEM lane each, two column halves
+constexpr int kLinThreads = kLinRowThreads + 32;   // plus the warp that issues TMA copies and MMAs
 
 struct LinearParams {
   void* o;                 // [B,H,S,DV] 16-bit
@@ -48,7 +49,8 @@ struct LinearParams {
 
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
-enum LinearWaitSite { kLinQFull = 41, kLinKvFull, kLinMma };
+enum LinearWaitSite { kLinQFull = 41, kLinKvFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone };
+enum LinearBarrier { kBarQFull = 0, kBarKvFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarOStaged, kBarStageFree, kBarConvDone, kNumLinBarriers };
 
 template <int DK>
 struct LinearSmem {
@@ -62,7 +64,7 @@ struct LinearSmem {
   static constexpr int kOffH = kOffV + kVBytes;
   static constexpr int kOffG = kOffH + kHBytes;          // float g2[2][128] + float wsum[8]
   static constexpr int kOffBar = kOffG + 2 * kLinT * 4 + 32;
-  static constexpr int kOffMisc = kOffBar + 8 * 3;
+  static constexpr int kOffMisc = kOffBar + 8 * kNumLinBarriers;
   static constexpr int kBytes = kOffMisc + 16 + 1024;
 };
 
@@ -85,15 +87,23 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   float* g2 = reinterpret_cast<float*>(smem + L::kOffG);  // [2][T] cumulative log2-decay inside a block
   float* wsum = g2 + 2 * T;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
-  uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* mma_bar = bars + 2;
+  uint64_t* q_full = bars + kBarQFull;
+  uint64_t* kv_full = bars + kBarKvFull;
+  uint64_t* s_bar = bars + kBarScore;
+  uint64_t* qh_bar = bars + kBarQh;
+  uint64_t* pv_bar = bars + kBarPv;
+  uint64_t* st_bar = bars + kBarState;
+  uint64_t* p_ready = bars + kBarPReady;
+  uint64_t* v_ready = bars + kBarVReady;
+  uint64_t* o_staged = bars + kBarOStaged;
+  uint64_t* stage_free = bars + kBarStageFree;
+  uint64_t* conv_done = bars + kBarConvDone;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wg = warp >> 2;                 // 0: row work on S / O, 1: V rescale; both convert the state
-  const int row = (warp & 3) * 32 + lane;   // TMEM lane owned by this thread
+  const int wg = (warp >> 2) & 1;           // row warps: column half owned in the row phases
+  const int row = (warp & 3) * 32 + lane;   // TMEM lane owned by a row thread
   const AbortState ab{abort_flag, p.status};
   const int slice = blockIdx.x;
   const int bh = blockIdx.y;
@@ -104,7 +114,15 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_init(q_full, 1);
     mbar_init(kv_full, 1);
-    mbar_init(mma_bar, 1);
+    mbar_init(s_bar, 1);
+    mbar_init(qh_bar, 1);
+    mbar_init(pv_bar, 1);
+    mbar_init(st_bar, 1);
+    mbar_init(p_ready, kLinRowThreads);
+    mbar_init(v_ready, kLinRowThreads);
+    mbar_init(o_staged, kLinRowThreads);
+    mbar_init(stage_free, 1);
+    mbar_init(conv_done, kLinRowThreads);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -119,129 +137,177 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  const uint32_t tH = tmem_base + lane_base + kColH;
-  const uint32_t tS = tmem_base + lane_base + kColS;
-  const uint32_t tO = tmem_base + lane_base + kColO;
+  const bool start_ok = !*abort_flag;
 
-  auto load_q = [&](int t) {
-    mbar_arrive_expect_tx(q_full, L::kQBytes);
-    for (int c = 0; c < KC; ++c) tma_load_3d(sQ + c * (T * 128), &tmQ, q_full, c * 64, t * T, bh);
-  };
-  auto load_kv = [&](int t) {
-    mbar_arrive_expect_tx(kv_full, L::kQBytes + L::kVBytes);
-    for (int c = 0; c < KC; ++c) tma_load_3d(sK + c * (T * 128), &tmK, kv_full, c * 64, t * T, bh);
-    for (int c = 0; c < DVS / 64; ++c) tma_load_3d(sV + c * (T * 128), &tmV, kv_full, slice * DVS + c * 64, t * T, bh);
-  };
-  // inclusive scan of the block's log2-decays into g2[buf][0..T); two CTA barriers inside
-  auto scan_block = [&](int t, int buf) {
-    float x = 0.0f;
-    if (tid < T) {
-      const int tok = t * T + tid;
-      x = (tok < p.seq) ? ld_row[tok] * kLog2e : 0.0f;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const float y = __shfl_up_sync(0xffffffffu, x, d);
-        if (lane >= d) x += y;
-      }
-      if (lane == 31) wsum[warp] = x;
-    }
-    __syncthreads();
-    if (tid < T) {
-      float pre = 0.0f;
-      for (int w = 0; w < warp; ++w) pre += wsum[w];
-      g2[buf * T + tid] = x + pre;
-    }
-    __syncthreads();
-  };
+  if (warp == kLinRowThreads / 32) {
+    // ======================= issuing warp: every TMA copy and every MMA =======================
+    if (lane == 0 && start_ok) {
+      auto load_q = [&](int t) {
+        mbar_arrive_expect_tx(q_full, L::kQBytes);
+        for (int c = 0; c < KC; ++c) tma_load_3d(sQ + c * (T * 128), &tmQ, q_full, c * 64, t * T, bh);
+      };
+      auto load_kv = [&](int t) {
+        mbar_arrive_expect_tx(kv_full, L::kQBytes + L::kVBytes);
+        for (int c = 0; c < KC; ++c) tma_load_3d(sK + c * (T * 128), &tmK, kv_full, c * 64, t * T, bh);
+        for (int c = 0; c < DVS / 64; ++c) tma_load_3d(sV + c * (T * 128), &tmV, kv_full, slice * DVS + c * 64, t * T, bh);
+      };
+      // kind::f16 takes one 16-bit format for both operands: a variant with fp16 intermediates next to
+      // bf16 inputs (A and B formats differing) raised a CUDA fault on B200 and is not offered.
+      constexpr uint32_t idesc_s = make_idesc_f16(T, T, kBf16, false, false);       // S = Q K^T
+      constexpr uint32_t idesc_qh = make_idesc_f16(T, DVS, kBf16, false, false);    // O = Q hT^T (B = hT copy, K-major)
+      constexpr uint32_t idesc_pv = make_idesc_f16(T, DVS, kBf16, false, true);     // O += P V   (B = V, MN-major)
+      constexpr uint32_t idesc_h = make_idesc_f16(DVS, DK, kBf16, true, true);      // hT += V'^T K (A M-major, B MN-major)
+      // descriptors are built once; the issue loops only move the start-address field (units of 16 bytes)
+      const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024), k_desc0 = make_smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t h_desc0 = make_smem_desc(smem_u32(sH), 16, 1024);
+      const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024), k_mn_desc0 = make_smem_desc(smem_u32(sK), T * 128, 1024);
+      constexpr uint64_t kChunk = (T * 128) >> 4;
 
-  bool ok = !*abort_flag;
-  uint32_t mma_n = 0;
-  if (ok && tid == 0) {
-    load_q(0);
-    load_kv(0);
-  }
-  scan_block(0, 0);
-
-  // kind::f16 takes one 16-bit format for both operands: a variant with fp16 intermediates next to
-  // bf16 inputs (A and B formats differing) raised a CUDA fault on B200 and is not offered.
-  constexpr uint32_t idesc_s = make_idesc_f16(T, T, kBf16, false, false);       // S = Q K^T
-  constexpr uint32_t idesc_qh = make_idesc_f16(T, DVS, kBf16, false, false);    // O = Q hT^T (B = hT copy, K-major)
-  constexpr uint32_t idesc_pv = make_idesc_f16(T, DVS, kBf16, false, true);     // O += P V   (B = V, MN-major)
-  constexpr uint32_t idesc_h = make_idesc_f16(DVS, DK, kBf16, true, true);      // hT += V'^T K (A M-major, B MN-major)
-  // descriptors are built once; the issue loops only move the start-address field (units of 16 bytes)
-  const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024), k_desc0 = make_smem_desc(smem_u32(sK), 16, 1024);
-  const uint64_t h_desc0 = make_smem_desc(smem_u32(sH), 16, 1024);
-  const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024), k_mn_desc0 = make_smem_desc(smem_u32(sK), T * 128, 1024);
-  constexpr uint64_t kChunk = (T * 128) >> 4;
-
-  for (int t = 0; t < nblk; ++t) {
-    const int buf = t & 1;
-    const bool last = (t + 1 == nblk);
-    if (!last) scan_block(t + 1, buf ^ 1);
-    // ---- phase 1: S = Q K^T and (t > 0) O = Q h ----
-    ok = mbar_wait(q_full, t & 1, ab, kLinQFull) && mbar_wait(kv_full, t & 1, ab, kLinKvFull);
-    if (!__syncthreads_and(ok)) break;
-    if (tid == 0) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int ch = 0; ch < KC; ++ch)
-        umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + ch * kChunk, k_desc0 + ch * kChunk, idesc_s, ch > 0 ? 1u : 0u);
-      if (t > 0) {
+      load_q(0);
+      load_kv(0);
+      for (int t = 0; t < nblk; ++t) {
+        const bool last = (t + 1 == nblk);
+        const uint32_t par = t & 1, par_prev = (t - 1) & 1;
+        // S = Q K^T needs only the loads: it runs while the row threads still convert the previous state
+        if (!(mbar_wait(q_full, par, ab, kLinQFull) && mbar_wait(kv_full, par, ab, kLinKvFull))) break;
+        tc_fence_after_sync();
 #pragma unroll
         for (int ch = 0; ch < KC; ++ch)
-          umma_ss_x4<2, 2>(tmem_base + kColO, q_desc0 + ch * kChunk, h_desc0 + ch * kChunk, idesc_qh, ch > 0 ? 1u : 0u);
+          umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + ch * kChunk, k_desc0 + ch * kChunk, idesc_s, ch > 0 ? 1u : 0u);
+        umma_commit(s_bar);
+        if (t > 0) {
+          // O = Q h needs the 16-bit copy of the state written by the conversion pass of the previous block
+          if (!mbar_wait(conv_done, par_prev, ab, kLinConvDone)) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int ch = 0; ch < KC; ++ch)
+            umma_ss_x4<2, 2>(tmem_base + kColO, q_desc0 + ch * kChunk, h_desc0 + ch * kChunk, idesc_qh, ch > 0 ? 1u : 0u);
+          umma_commit(qh_bar);
+          if (!mbar_wait(qh_bar, par_prev, ab, kLinQh)) break;
+        } else {
+          if (!mbar_wait(s_bar, par, ab, kLinScore)) break;
+        }
+        if (!last) load_q(t + 1);  // Q is no longer read by any MMA of this block
+        // O (+)= P V
+        if (!mbar_wait(p_ready, par, ab, kLinPReady)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int g = 0; g < T / 64; ++g)
+          umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + g * 32, v_mn_desc0 + g * 512, idesc_pv, (t > 0 || g > 0) ? 1u : 0u);
+        if (p.split_p) {
+#pragma unroll
+          for (int g = 0; g < T / 64; ++g)
+            umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + 64 + g * 32, v_mn_desc0 + g * 512, idesc_pv, 1u);
+        }
+        umma_commit(pv_bar);
+        if (!last) {
+          // hT (+)= V'^T K once the rows of V carry their decay factors
+          if (!mbar_wait(v_ready, par, ab, kLinVReady)) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int g = 0; g < T / 64; ++g)   // both operands are MN-major over tokens: 16 tokens = 2048 B per K step
+            umma_ss_x4<128, 128>(tmem_base + kColH, v_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
+          umma_commit(st_bar);
+        }
+        // output rows staged in the state-copy buffer: full swizzled lines, rows past the end clipped by the map
+        if (!mbar_wait(o_staged, par, ab, kLinOStaged)) break;
+        for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
+        tma_store_commit();
+        if (last) break;
+        tma_store_wait_read();   // the conversion pass overwrites the staging buffer
+        mbar_arrive(stage_free);
+        if (!mbar_wait(st_bar, par, ab, kLinState)) break;
+        load_kv(t + 1);  // K and V' are no longer read
       }
-      umma_commit(mma_bar);
+      tma_store_wait_all();
     }
-    ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
-    ++mma_n;
-    tc_fence_after_sync();
-    if (tid == 0 && ok && !last) load_q(t + 1);  // Q is no longer read by any MMA of this block
-    // ---- phase 2: rows of S -> P, rows of O scaled by scale * exp(g_i) ----
-    // Both warp groups work on every row: group `wg` owns columns [64*wg, 64*wg+64) of S and of O (a single
-    // warp per scheduler running dependent arithmetic is latency-bound; two interleave).
-    {
+  } else {
+    // ======================= row threads: one TMEM lane (token / state row) each =======================
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tH = tmem_base + lane_base + kColH;
+    const uint32_t tS = tmem_base + lane_base + kColS;
+    const uint32_t tO = tmem_base + lane_base + kColO;
+    auto load_decay = [&](int t) -> float {
+      const int tok = t * T + tid;
+      return (tid < T && tok < p.seq) ? ld_row[tok] * kLog2e : 0.0f;
+    };
+    // inclusive scan of a block's log2-decays (one per thread of the first four warps) into g2[buf][0..T);
+    // two barriers of the row threads inside, the second one reducing `ok`
+    auto scan_block = [&](float x, int buf, bool ok_in) -> bool {
+      if (tid < T) {
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const float y = __shfl_up_sync(0xffffffffu, x, d);
+          if (lane >= d) x += y;
+        }
+        if (lane == 31) wsum[warp] = x;
+      }
+      named_sync(1, kLinRowThreads);
+      if (tid < T) {
+        float pre = 0.0f;
+        for (int w = 0; w < warp; ++w) pre += wsum[w];
+        g2[buf * T + tid] = x + pre;
+      }
+      return named_sync_and(1, kLinRowThreads, ok_in);
+    };
+
+    bool ok = scan_block(load_decay(0), 0, start_ok);
+    for (int t = 0; ok && t < nblk; ++t) {
+      const int buf = t & 1;
+      const bool last = (t + 1 == nblk);
+      const uint32_t par = t & 1;
+      const float x_next = last ? 0.0f : load_decay(t + 1);  // consumed by the scan further down
+      // ---- rows of S -> P (while Q h still runs) ----
+      // Both warp groups work on every row: group `wg` owns columns [64*wg, 64*wg+64) of S and of O (a single
+      // warp per scheduler running dependent arithmetic is latency-bound; two interleave).
       const float gi = g2[buf * T + row];
       const float qs = p.q_scale;
-      const float* gcol = g2 + buf * T + wg * 64;
-      float s[64];
-      tmem_ld32f(tS + wg * 64, &s[0]);
-      tmem_ld32f(tS + wg * 64 + 32, &s[32]);
-      tmem_wait_ld();
-      uint32_t pk[32], pl[32];
+      {
+        const float* gcol = g2 + buf * T + wg * 64;
+        ok = mbar_wait(s_bar, par, ab, kLinScore);
+        tc_fence_after_sync();
+        float s[64];
+        tmem_ld32f(tS + wg * 64, &s[0]);
+        tmem_ld32f(tS + wg * 64 + 32, &s[32]);
+        tmem_wait_ld();
+        uint32_t pk[32], pl[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int j0 = wg * 64 + 2 * i, j1 = j0 + 1;
-        // computed for every column and selected afterwards: a per-lane branch here diverges in every warp
-        const float e0 = s[2 * i] * qs * fast_exp2(fminf(gi - gcol[2 * i], 0.0f));
-        const float e1 = s[2 * i + 1] * qs * fast_exp2(fminf(gi - gcol[2 * i + 1], 0.0f));
-        const float p0 = (j0 <= row) ? e0 : 0.0f;
-        const float p1 = (j1 <= row) ? e1 : 0.0f;
-        pk[i] = pack2<kBf16>(p0, p1);
-        if (p.split_p) {
-          float h0, h1;
-          if constexpr (kBf16) {
-            const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&pk[i]);
-            h0 = __bfloat162float(h2.x);
-            h1 = __bfloat162float(h2.y);
-          } else {
-            const __half2 h2 = *reinterpret_cast<__half2*>(&pk[i]);
-            h0 = __half2float(h2.x);
-            h1 = __half2float(h2.y);
+        for (int i = 0; i < 32; ++i) {
+          const int j0 = wg * 64 + 2 * i, j1 = j0 + 1;
+          // computed for every column and selected afterwards: a per-lane branch here diverges in every warp
+          const float e0 = s[2 * i] * qs * fast_exp2(fminf(gi - gcol[2 * i], 0.0f));
+          const float e1 = s[2 * i + 1] * qs * fast_exp2(fminf(gi - gcol[2 * i + 1], 0.0f));
+          const float p0 = (j0 <= row) ? e0 : 0.0f;
+          const float p1 = (j1 <= row) ? e1 : 0.0f;
+          pk[i] = pack2<kBf16>(p0, p1);
+          if (p.split_p) {
+            float h0, h1;
+            if constexpr (kBf16) {
+              const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&pk[i]);
+              h0 = __bfloat162float(h2.x);
+              h1 = __bfloat162float(h2.y);
+            } else {
+              const __half2 h2 = *reinterpret_cast<__half2*>(&pk[i]);
+              h0 = __half2float(h2.x);
+              h1 = __half2float(h2.y);
+            }
+            pl[i] = pack2<kBf16>(p0 - h0, p1 - h1);
           }
-          pl[i] = pack2<kBf16>(p0 - h0, p1 - h1);
         }
+        // P overwrites S: 16-bit pairs in columns [0, 64), and with split_p the 16-bit remainder P - round(P) in
+        // columns [64, 128) for a second PV pass.  Those columns belong to the other group's half of S, so
+        // every thread must have its S values in registers first.
+        tc_fence_before_sync();
+        ok = named_sync_and(1, kLinRowThreads, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        tmem_st32(tS + wg * 32, pk);
+        if (p.split_p) tmem_st32(tS + 64 + wg * 32, pl);
       }
-      // P overwrites S: 16-bit pairs in columns [0, 64), and with split_p the 16-bit remainder P - round(P) in
-      // columns [64, 128) for a second PV pass.  Those columns belong to the other group's half of S, so
-      // every thread must have its S values in registers first.
-      tc_fence_before_sync();
-      __syncthreads();
-      tc_fence_after_sync();
-      tmem_st32(tS + wg * 32, pk);
-      if (p.split_p) tmem_st32(tS + 64 + wg * 32, pl);
+      // ---- rows of O = Q h scaled by scale * exp(g_i) ----
       if (t > 0) {
+        ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh) && ok;
+        tc_fence_after_sync();
         const float f = qs * fast_exp2(gi);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -254,82 +320,23 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       tmem_wait_st();
-    }
-    tc_fence_before_sync();
-    if (!__syncthreads_and(ok)) break;
-    // ---- phase 3: O (+)= P V ----
-    if (tid == 0) {
+      tc_fence_before_sync();
+      mbar_arrive(p_ready);
+      // ---- the next block's decay scan runs under the P V MMAs ----
+      if (!last) ok = scan_block(x_next, buf ^ 1, ok);
+      ok = mbar_wait(pv_bar, par, ab, kLinPv) && ok;
       tc_fence_after_sync();
-#pragma unroll
-      for (int g = 0; g < T / 64; ++g)
-        umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + g * 32, v_mn_desc0 + g * 512, idesc_pv, (t > 0 || g > 0) ? 1u : 0u);
-      if (p.split_p) {
-#pragma unroll
-        for (int g = 0; g < T / 64; ++g)
-          umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + 64 + g * 32, v_mn_desc0 + g * 512, idesc_pv, 1u);
-      }
-      umma_commit(mma_bar);
-    }
-    ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
-    ++mma_n;
-    tc_fence_after_sync();
-    // ---- phase 4: store O rows; rescale V rows for the state update ----
-    {
-      // The rows go out through shared memory: the buffer of the state's operand copy is idle between the
-      // Q.h MMA of this block and the conversion pass at its end.  Group `wg` writes the 64-column chunk
-      // `wg` of its row as one swizzled 128-byte line (the layout TMA expects); one TMA store per chunk
-      // writes full lines, and rows past the end of the sequence are clipped by the tensor map.
-      const int tok = t * T + row;
-      float sum = 0.f, sq = 0.f;
-      uint8_t* line = sH + wg * (T * 128) + row * 128;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float o[32];
-        tmem_ld32f(tO + wg * 64 + c * 32, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 pk;
-          if (p.stats == nullptr) {
-            pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
-            pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
-            pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
-            pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
-          } else {
-            // normalised by a second pass: staged as fp16 (11 significant bits, clamped to the fp16 range)
-            pk.x = pack2<false>(clamp_h(o[8 * v + 0]), clamp_h(o[8 * v + 1]));
-            pk.y = pack2<false>(clamp_h(o[8 * v + 2]), clamp_h(o[8 * v + 3]));
-            pk.z = pack2<false>(clamp_h(o[8 * v + 4]), clamp_h(o[8 * v + 5]));
-            pk.w = pack2<false>(clamp_h(o[8 * v + 6]), clamp_h(o[8 * v + 7]));
-          }
-          *reinterpret_cast<uint4*>(line + (((c * 4 + v) ^ (row & 7)) << 4)) = pk;
-        }
-        if (p.stats != nullptr) {
-          float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            s0 += o[i];
-            s1 += o[i + 1];
-            q0 = fmaf(o[i], o[i], q0);
-            q1 = fmaf(o[i + 1], o[i + 1], q1);
-          }
-          sum += s0 + s1;
-          sq += q0 + q1;
-        }
-      }
-      if (p.stats != nullptr && tok < p.seq) {
-        float* st = p.stats + (static_cast<long long>(bh) * p.seq + tok) * 2;
-        atomicAdd(st, sum);
-        atomicAdd(st + 1, sq);
-      }
+      // ---- rows of V rescaled for the state update ----
       if (!last) {
-        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row); the 16-byte pieces of a row stay
-        // inside its 128-byte line under the swizzle, so the permutation does not matter here
+        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row).  Every 16-byte piece of the row
+        // gets the same factor, so neither the swizzle nor the order matters: lanes start at different
+        // pieces to stay off each other's banks (rows are 128 bytes apart).
         const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
         uint4* vline = reinterpret_cast<uint4*>(sV + wg * (T * 128) + row * 128);
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
-          uint4 x = vline[q4];
+          const int piece = (q4 + lane) & 7;
+          uint4 x = vline[piece];
           uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -345,66 +352,100 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             xs[e] = pack2<kBf16>(lo * w, hi * w);
           }
-          vline[q4] = x;
+          vline[piece] = x;
         }
+        fence_proxy_async_smem();
+        mbar_arrive(v_ready);
       }
-      fence_proxy_async_smem();
-    }
-    tc_fence_before_sync();
-    if (!__syncthreads_and(ok)) break;
-    if (tid == 0) {
-      for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
-      tma_store_commit();
-    }
-    if (last) break;
-    // ---- phase 5: hT (+)= V'^T K ----
-    if (tid == 0) {
+      // ---- output rows to the staging buffer (while the state update runs) ----
+      {
+        // The rows go out through shared memory: the buffer of the state's operand copy is idle between the
+        // Q.h MMA of this block and the conversion pass at its end.  Group `wg` writes the 64-column chunk
+        // `wg` of its row as one swizzled 128-byte line (the layout TMA expects).
+        const int tok = t * T + row;
+        float sum = 0.f, sq = 0.f;
+        uint8_t* line = sH + wg * (T * 128) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float o[32];
+          tmem_ld32f(tO + wg * 64 + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 pk;
+            if (p.stats == nullptr) {
+              pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
+              pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
+              pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
+              pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
+            } else {
+              // normalised by a second pass: staged as fp16 (11 significant bits, clamped to the fp16 range)
+              pk.x = pack2<false>(clamp_h(o[8 * v + 0]), clamp_h(o[8 * v + 1]));
+              pk.y = pack2<false>(clamp_h(o[8 * v + 2]), clamp_h(o[8 * v + 3]));
+              pk.z = pack2<false>(clamp_h(o[8 * v + 4]), clamp_h(o[8 * v + 5]));
+              pk.w = pack2<false>(clamp_h(o[8 * v + 6]), clamp_h(o[8 * v + 7]));
+            }
+            *reinterpret_cast<uint4*>(line + (((c * 4 + v) ^ (row & 7)) << 4)) = pk;
+          }
+          if (p.stats != nullptr) {
+            float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              s0 += o[i];
+              s1 += o[i + 1];
+              q0 = fmaf(o[i], o[i], q0);
+              q1 = fmaf(o[i + 1], o[i + 1], q1);
+            }
+            sum += s0 + s1;
+            sq += q0 + q1;
+          }
+        }
+        if (p.stats != nullptr && tok < p.seq) {
+          float* st = p.stats + (static_cast<long long>(bh) * p.seq + tok) * 2;
+          atomicAdd(st, sum);
+          atomicAdd(st + 1, sq);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(o_staged);
+      }
+      if (last) break;
+      // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
+      ok = mbar_wait(st_bar, par, ab, kLinState) && ok;
+      ok = mbar_wait(stage_free, par, ab, kLinStageFree) && ok;
       tc_fence_after_sync();
+      {
+        const float decay_next = fast_exp2(g2[(buf ^ 1) * T + T - 1]);
+        constexpr int kColsPerWg = DK / 2;
 #pragma unroll
-      for (int g = 0; g < T / 64; ++g)   // both operands are MN-major over tokens: 16 tokens = 2048 B per K step
-        umma_ss_x4<128, 128>(tmem_base + kColH, v_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
-      // the output stores read the buffer that the conversion pass below overwrites: the barrier that
-      // releases that pass is only committed once they have finished reading
-      tma_store_wait_read();
-      umma_commit(mma_bar);
-    }
-    ok = mbar_wait(mma_bar, mma_n & 1, ab, kLinMma);
-    ++mma_n;
-    tc_fence_after_sync();
-    if (tid == 0 && ok) load_kv(t + 1);  // K and V' are no longer read
-    // ---- phase 6: bf16 copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
-    {
-      const float decay_next = fast_exp2(g2[(buf ^ 1) * T + T - 1]);
-      constexpr int kColsPerWg = DK / 2;
+        for (int c = 0; c < kColsPerWg / 32; ++c) {
+          const int col0 = wg * kColsPerWg + c * 32;
+          float hv[32];
+          tmem_ld32f(tH + col0, hv);
+          tmem_wait_ld();
+          uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
+          const int piece0 = (col0 & 63) >> 3;
 #pragma unroll
-      for (int c = 0; c < kColsPerWg / 32; ++c) {
-        const int col0 = wg * kColsPerWg + c * 32;
-        float hv[32];
-        tmem_ld32f(tH + col0, hv);
-        tmem_wait_ld();
-        uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
-        const int piece0 = (col0 & 63) >> 3;
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 pk;
+            pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
+            pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
+            pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
+            pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
+            *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
+          }
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 pk;
-          pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
-          pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
-          pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
-          pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
-          *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
+          for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+          tmem_st32f(tH + col0, hv);
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
-        tmem_st32f(tH + col0, hv);
+        tmem_wait_st();
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(conv_done);
       }
-      tmem_wait_st();
-      fence_proxy_async_smem();
     }
-    tc_fence_before_sync();
-    if (!__syncthreads_and(ok)) break;
   }
 
-  if (tid == 0) tma_store_wait_all();
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {

@@ -101,6 +101,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return true;
 }
 
+// Named CTA barriers for a subset of the warps (`count` threads, a multiple of 32; id 1..15, 0 is __syncthreads).
+__device__ __forceinline__ void named_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// Same, returning the AND of `pred` over the participating threads.
+__device__ __forceinline__ bool named_sync_and(int id, int count, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\tbar.red.and.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(count), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+
 // ---------------------------------------------------------------------------
 // thread-block clusters: distributed shared memory and cross-CTA barriers
 // ---------------------------------------------------------------------------
