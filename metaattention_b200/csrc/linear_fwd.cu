@@ -49,8 +49,8 @@ struct LinearParams {
 
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
-enum LinearWaitSite { kLinQFull = 41, kLinKvFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone };
-enum LinearBarrier { kBarQFull = 0, kBarKvFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarOStaged, kBarStageFree, kBarConvDone, kNumLinBarriers };
+enum LinearWaitSite { kLinQFull = 41, kLinKFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone, kLinVFull };
+enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarOStaged, kBarStageFree, kBarConvDone, kNumLinBarriers };
 
 template <int DK>
 struct LinearSmem {
@@ -62,8 +62,12 @@ struct LinearSmem {
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + kQBytes;
   static constexpr int kOffH = kOffV + kVBytes;
-  static constexpr int kOffG = kOffH + kHBytes;          // float g2[2][128] + float wsum[8]
-  static constexpr int kOffBar = kOffG + 2 * kLinT * 4 + 32;
+  // rows of V times their decay factors, the A operand of the state update: with dim_qk 256 the upper half of
+  // the state-copy buffer (idle between the Q h MMA and the conversion pass), else a buffer of its own
+  static constexpr bool kScaledVInH = (kHBytes >= 2 * kVBytes);
+  static constexpr int kOffV2 = kScaledVInH ? kOffH + kHBytes - kVBytes : kOffH + kHBytes;
+  static constexpr int kOffG = kOffH + kHBytes + (kScaledVInH ? 0 : kVBytes);  // float g2[2][128] + float gb[128] + float wsum[8]
+  static constexpr int kOffBar = kOffG + 3 * kLinT * 4 + 32;
   static constexpr int kOffMisc = kOffBar + 8 * kNumLinBarriers;
   static constexpr int kBytes = kOffMisc + 16 + 1024;
 };
@@ -84,11 +88,14 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* sK = smem + L::kOffK;
   uint8_t* sV = smem + L::kOffV;
   uint8_t* sH = smem + L::kOffH;
+  uint8_t* sV2 = smem + L::kOffV2;
   float* g2 = reinterpret_cast<float*>(smem + L::kOffG);  // [2][T] cumulative log2-decay inside a block
-  float* wsum = g2 + 2 * T;
+  float* gb = g2 + 2 * T;   // [T] exp2(g at the end of the column's 32-token chunk - g of the column), current block
+  float* wsum = gb + T;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* q_full = bars + kBarQFull;
-  uint64_t* kv_full = bars + kBarKvFull;
+  uint64_t* k_full = bars + kBarKFull;
+  uint64_t* v_full = bars + kBarVFull;
   uint64_t* s_bar = bars + kBarScore;
   uint64_t* qh_bar = bars + kBarQh;
   uint64_t* pv_bar = bars + kBarPv;
@@ -113,7 +120,8 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (tid == 0) {
     *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_init(q_full, 1);
-    mbar_init(kv_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(v_full, 1);
     mbar_init(s_bar, 1);
     mbar_init(qh_bar, 1);
     mbar_init(pv_bar, 1);
@@ -146,10 +154,13 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_arrive_expect_tx(q_full, L::kQBytes);
         for (int c = 0; c < KC; ++c) tma_load_3d(sQ + c * (T * 128), &tmQ, q_full, c * 64, t * T, bh);
       };
-      auto load_kv = [&](int t) {
-        mbar_arrive_expect_tx(kv_full, L::kQBytes + L::kVBytes);
-        for (int c = 0; c < KC; ++c) tma_load_3d(sK + c * (T * 128), &tmK, kv_full, c * 64, t * T, bh);
-        for (int c = 0; c < DVS / 64; ++c) tma_load_3d(sV + c * (T * 128), &tmV, kv_full, slice * DVS + c * 64, t * T, bh);
+      auto load_k = [&](int t) {
+        mbar_arrive_expect_tx(k_full, L::kQBytes);
+        for (int c = 0; c < KC; ++c) tma_load_3d(sK + c * (T * 128), &tmK, k_full, c * 64, t * T, bh);
+      };
+      auto load_v = [&](int t) {
+        mbar_arrive_expect_tx(v_full, L::kVBytes);
+        for (int c = 0; c < DVS / 64; ++c) tma_load_3d(sV + c * (T * 128), &tmV, v_full, slice * DVS + c * 64, t * T, bh);
       };
       // kind::f16 takes one 16-bit format for both operands: a variant with fp16 intermediates next to
       // bf16 inputs (A and B formats differing) raised a CUDA fault on B200 and is not offered.
@@ -161,20 +172,30 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024), k_desc0 = make_smem_desc(smem_u32(sK), 16, 1024);
       const uint64_t h_desc0 = make_smem_desc(smem_u32(sH), 16, 1024);
       const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024), k_mn_desc0 = make_smem_desc(smem_u32(sK), T * 128, 1024);
+      const uint64_t v2_mn_desc0 = make_smem_desc(smem_u32(sV2), T * 128, 1024);
       constexpr uint64_t kChunk = (T * 128) >> 4;
-
-      load_q(0);
-      load_kv(0);
-      for (int t = 0; t < nblk; ++t) {
-        const bool last = (t + 1 == nblk);
-        const uint32_t par = t & 1, par_prev = (t - 1) & 1;
-        // S = Q K^T needs only the loads: it runs while the row threads still convert the previous state
-        if (!(mbar_wait(q_full, par, ab, kLinQFull) && mbar_wait(kv_full, par, ab, kLinKvFull))) break;
-        tc_fence_after_sync();
+      auto issue_scores = [&]() {
 #pragma unroll
         for (int ch = 0; ch < KC; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + ch * kChunk, k_desc0 + ch * kChunk, idesc_s, ch > 0 ? 1u : 0u);
         umma_commit(s_bar);
+      };
+
+      // The tensor pipe executes in issue order and the issuing thread is held back while the pipe is full,
+      // so the order below is the schedule.  Per block: Q h, state update (its A operand V' sits in a buffer
+      // of its own, so it does not wait for P V), K of the next block, P V, V of the next block, output
+      // store, and already the next block's S = Q K^T, which then runs under the conversion pass.
+      load_q(0);
+      load_k(0);
+      load_v(0);
+      bool alive = mbar_wait(q_full, 0, ab, kLinQFull) && mbar_wait(k_full, 0, ab, kLinKFull);
+      if (alive) {
+        tc_fence_after_sync();
+        issue_scores();
+      }
+      for (int t = 0; alive && t < nblk; ++t) {
+        const bool last = (t + 1 == nblk);
+        const uint32_t par = t & 1, par_prev = (t - 1) & 1;
         if (t > 0) {
           // O = Q h needs the 16-bit copy of the state written by the conversion pass of the previous block
           if (!mbar_wait(conv_done, par_prev, ab, kLinConvDone)) break;
@@ -188,8 +209,19 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           if (!mbar_wait(s_bar, par, ab, kLinScore)) break;
         }
         if (!last) load_q(t + 1);  // Q is no longer read by any MMA of this block
+        if (!last) {
+          // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step
+          if (!mbar_wait(v_ready, par, ab, kLinVReady)) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int g = 0; g < T / 64; ++g)
+            umma_ss_x4<128, 128>(tmem_base + kColH, v2_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
+          umma_commit(st_bar);
+          if (!mbar_wait(st_bar, par, ab, kLinState)) break;
+          load_k(t + 1);  // K is no longer read
+        }
         // O (+)= P V
-        if (!mbar_wait(p_ready, par, ab, kLinPReady)) break;
+        if (!(mbar_wait(p_ready, par, ab, kLinPReady) && mbar_wait(v_full, par, ab, kLinVFull))) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int g = 0; g < T / 64; ++g)
@@ -200,24 +232,42 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + 64 + g * 32, v_mn_desc0 + g * 512, idesc_pv, 1u);
         }
         umma_commit(pv_bar);
-        if (!last) {
-          // hT (+)= V'^T K once the rows of V carry their decay factors
-          if (!mbar_wait(v_ready, par, ab, kLinVReady)) break;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int g = 0; g < T / 64; ++g)   // both operands are MN-major over tokens: 16 tokens = 2048 B per K step
-            umma_ss_x4<128, 128>(tmem_base + kColH, v_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
-          umma_commit(st_bar);
+        // Three follow-ups, served as they become possible: V of the next block (after P V), the output store
+        // (after the rows are staged), S of the next block (after its loads; P of this block is consumed by
+        // then because the pipe runs in order).
+        bool need_v = !last, need_s = !last, need_store = true;
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while (need_v || need_s || need_store) {
+          if (need_v && mbar_test(pv_bar, par)) {
+            load_v(t + 1);  // V was read by the row threads (before v_ready) and by P V
+            need_v = false;
+          }
+          if (need_store && mbar_test(o_staged, par)) {
+            // output rows staged in the state-copy buffer: full swizzled lines, rows past the end clipped by the map
+            for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
+            tma_store_commit();
+            if (!last) {
+              tma_store_wait_read();  // the conversion pass overwrites the staging buffer
+              mbar_arrive(stage_free);
+            }
+            need_store = false;
+          }
+          if (need_s && mbar_test(q_full, par ^ 1) && mbar_test(k_full, par ^ 1)) {
+            tc_fence_after_sync();
+            issue_scores();
+            need_s = false;
+          }
+          if ((++spins & 0xff) == 0) {
+            if (*abort_flag) alive = false;
+            else if (clock64() - t0 > kWaitCycleLimit) {
+              *abort_flag = 1;
+              atomicCAS(p.status, 0, kStatusTimeoutBase + kLinOStaged);
+              alive = false;
+            }
+            if (!alive) break;
+          }
         }
-        // output rows staged in the state-copy buffer: full swizzled lines, rows past the end clipped by the map
-        if (!mbar_wait(o_staged, par, ab, kLinOStaged)) break;
-        for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
-        tma_store_commit();
-        if (last) break;
-        tma_store_wait_read();   // the conversion pass overwrites the staging buffer
-        mbar_arrive(stage_free);
-        if (!mbar_wait(st_bar, par, ab, kLinState)) break;
-        load_kv(t + 1);  // K and V' are no longer read
       }
       tma_store_wait_all();
     }
@@ -246,7 +296,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (tid < T) {
         float pre = 0.0f;
         for (int w = 0; w < warp; ++w) pre += wsum[w];
-        g2[buf * T + tid] = x + pre;
+        const float g = x + pre;
+        g2[buf * T + tid] = g;
+        gb[tid] = fast_exp2(__shfl_sync(0xffffffffu, g, 31) - g);
       }
       return named_sync_and(1, kLinRowThreads, ok_in);
     };
@@ -262,36 +314,59 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // warp per scheduler running dependent arithmetic is latency-bound; two interleave).
       const float gi = g2[buf * T + row];
       const float qs = p.q_scale;
+      uint32_t pk[32], pl[32];
       {
-        const float* gcol = g2 + buf * T + wg * 64;
+        // exp(g_i - g_j) costs one MUFU operation per score only in the 32x32 chunk on the diagonal.  Below
+        // it the factor splits into exp(g_i - g_end) * exp(g_end - g_j), g_end the last token of the column
+        // chunk: a per-row and a per-column number, both at most 1.  Chunks above the diagonal are zero and
+        // are not even read.  All three cases are uniform over a warp.
+        const int wq = warp & 3;
         ok = mbar_wait(s_bar, par, ab, kLinScore);
         tc_fence_after_sync();
-        float s[64];
-        tmem_ld32f(tS + wg * 64, &s[0]);
-        tmem_ld32f(tS + wg * 64 + 32, &s[32]);
-        tmem_wait_ld();
-        uint32_t pk[32], pl[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int j0 = wg * 64 + 2 * i, j1 = j0 + 1;
-          // computed for every column and selected afterwards: a per-lane branch here diverges in every warp
-          const float e0 = s[2 * i] * qs * fast_exp2(fminf(gi - gcol[2 * i], 0.0f));
-          const float e1 = s[2 * i + 1] * qs * fast_exp2(fminf(gi - gcol[2 * i + 1], 0.0f));
-          const float p0 = (j0 <= row) ? e0 : 0.0f;
-          const float p1 = (j1 <= row) ? e1 : 0.0f;
-          pk[i] = pack2<kBf16>(p0, p1);
-          if (p.split_p) {
-            float h0, h1;
-            if constexpr (kBf16) {
-              const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&pk[i]);
-              h0 = __bfloat162float(h2.x);
-              h1 = __bfloat162float(h2.y);
-            } else {
-              const __half2 h2 = *reinterpret_cast<__half2*>(&pk[i]);
-              h0 = __half2float(h2.x);
-              h1 = __half2float(h2.y);
+        for (int h = 0; h < 2; ++h) {
+          const int c = 2 * wg + h;  // 32-column chunk of S
+          uint32_t* pkh = pk + 16 * h;
+          uint32_t* plh = pl + 16 * h;
+          if (c > wq) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pkh[i] = plh[i] = 0u;
+            continue;
+          }
+          float s[32];
+          tmem_ld32f(tS + c * 32, s);
+          tmem_wait_ld();
+          const float* gcol = g2 + buf * T + c * 32;
+          const float* bcol = gb + c * 32;
+          if (c < wq) {
+            const float a = qs * fast_exp2(fminf(gi - gcol[31], 0.0f));
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s[i] *= a * bcol[i];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              // computed for every column and selected afterwards: a per-lane branch here diverges in every warp
+              const float e = s[i] * qs * fast_exp2(fminf(gi - gcol[i], 0.0f));
+              s[i] = (i <= lane) ? e : 0.0f;
             }
-            pl[i] = pack2<kBf16>(p0 - h0, p1 - h1);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pkh[i] = pack2<kBf16>(s[2 * i], s[2 * i + 1]);
+          if (p.split_p) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float h0, h1;
+              if constexpr (kBf16) {
+                const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&pkh[i]);
+                h0 = __bfloat162float(h2.x);
+                h1 = __bfloat162float(h2.y);
+              } else {
+                const __half2 h2 = *reinterpret_cast<__half2*>(&pkh[i]);
+                h0 = __half2float(h2.x);
+                h1 = __half2float(h2.y);
+              }
+              plh[i] = pack2<kBf16>(s[2 * i] - h0, s[2 * i + 1] - h1);
+            }
           }
         }
         // P overwrites S: 16-bit pairs in columns [0, 64), and with split_p the 16-bit remainder P - round(P) in
@@ -304,35 +379,20 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_st32(tS + wg * 32, pk);
         if (p.split_p) tmem_st32(tS + 64 + wg * 32, pl);
       }
-      // ---- rows of O = Q h scaled by scale * exp(g_i) ----
       if (t > 0) {
         ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh) && ok;
         tc_fence_after_sync();
-        const float f = qs * fast_exp2(gi);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float o[32];
-          tmem_ld32f(tO + wg * 64 + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= f;
-          tmem_st32f(tO + wg * 64 + c * 32, o);
-        }
       }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(p_ready);
-      // ---- the next block's decay scan runs under the P V MMAs ----
-      if (!last) ok = scan_block(x_next, buf ^ 1, ok);
-      ok = mbar_wait(pv_bar, par, ab, kLinPv) && ok;
-      tc_fence_after_sync();
-      // ---- rows of V rescaled for the state update ----
+      // ---- rows of V times their decay factors, into the buffer the state update reads ----
       if (!last) {
-        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row).  Every 16-byte piece of the row
-        // gets the same factor, so neither the swizzle nor the order matters: lanes start at different
-        // pieces to stay off each other's banks (rows are 128 bytes apart).
+        ok = mbar_wait(v_full, par, ab, kLinVFull) && ok;
+        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row) and written to the same place of the
+        // second buffer (with 256 state columns that is the upper half of the state copy, free once Q h has
+        // run).  Every 16-byte piece of the row gets the same factor, so neither the swizzle nor the order
+        // matters: lanes start at different pieces to stay off each other's banks (rows are 128 bytes apart).
         const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
-        uint4* vline = reinterpret_cast<uint4*>(sV + wg * (T * 128) + row * 128);
+        const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
+        uint4* v2line = reinterpret_cast<uint4*>(sV2 + wg * (T * 128) + row * 128);
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
           const int piece = (q4 + lane) & 7;
@@ -352,11 +412,31 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             xs[e] = pack2<kBf16>(lo * w, hi * w);
           }
-          vline[piece] = x;
+          v2line[piece] = x;
         }
         fence_proxy_async_smem();
         mbar_arrive(v_ready);
       }
+      // ---- rows of O = Q h scaled by scale * exp(g_i) ----
+      if (t > 0) {
+        const float f = qs * fast_exp2(gi);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float o[32];
+          tmem_ld32f(tO + wg * 64 + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= f;
+          tmem_st32f(tO + wg * 64 + c * 32, o);
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(p_ready);
+      // ---- the next block's decay scan runs under the MMAs ----
+      if (!last) ok = scan_block(x_next, buf ^ 1, ok);
+      ok = mbar_wait(pv_bar, par, ab, kLinPv) && ok;
+      tc_fence_after_sync();
       // ---- output rows to the staging buffer (while the state update runs) ----
       {
         // The rows go out through shared memory: the buffer of the state's operand copy is idle between the
@@ -412,31 +492,40 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (last) break;
       // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
       ok = mbar_wait(st_bar, par, ab, kLinState) && ok;
-      ok = mbar_wait(stage_free, par, ab, kLinStageFree) && ok;
       tc_fence_after_sync();
       {
+        // The staged output rows occupy the first 32 KB of the copy's buffer, i.e. its columns [0, 128).  With
+        // 256 columns every group first converts its share of [128, 256) and only then waits for the output
+        // stores to have read their rows.
+        constexpr bool kEarlyPart = (DK == 256);
+        constexpr int kParts = kEarlyPart ? 2 : 1;
+        constexpr int kColsPerPart = DK / 2 / kParts;  // per group
         const float decay_next = fast_exp2(g2[(buf ^ 1) * T + T - 1]);
-        constexpr int kColsPerWg = DK / 2;
 #pragma unroll
-        for (int c = 0; c < kColsPerWg / 32; ++c) {
-          const int col0 = wg * kColsPerWg + c * 32;
-          float hv[32];
-          tmem_ld32f(tH + col0, hv);
-          tmem_wait_ld();
-          uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
-          const int piece0 = (col0 & 63) >> 3;
+        for (int part = 0; part < kParts; ++part) {
+          if (part == kParts - 1) ok = mbar_wait(stage_free, par, ab, kLinStageFree) && ok;
+          const int base = (kEarlyPart && part == 0 ? DK / 2 : 0) + wg * kColsPerPart;
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 pk;
-            pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
-            pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
-            pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
-            pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
-            *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
+          for (int c = 0; c < kColsPerPart / 32; ++c) {
+            const int col0 = base + c * 32;
+            float hv[32];
+            tmem_ld32f(tH + col0, hv);
+            tmem_wait_ld();
+            uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
+            const int piece0 = (col0 & 63) >> 3;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 pk;
+              pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
+              pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
+              pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
+              pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
+              *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+            tmem_st32f(tH + col0, hv);
           }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
-          tmem_st32f(tH + col0, hv);
         }
         tmem_wait_st();
         fence_proxy_async_smem();
