@@ -126,11 +126,11 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(qh_bar, 1);
     mbar_init(pv_bar, 1);
     mbar_init(st_bar, 1);
-    mbar_init(p_ready, kLinRowThreads);
-    mbar_init(v_ready, kLinRowThreads);
-    mbar_init(o_staged, kLinRowThreads);
+    mbar_init(p_ready, kLinRowThreads / 32);
+    mbar_init(v_ready, kLinRowThreads / 32);
+    mbar_init(o_staged, kLinRowThreads / 32);
     mbar_init(stage_free, 1);
-    mbar_init(conv_done, kLinRowThreads);
+    mbar_init(conv_done, kLinRowThreads / 32);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -277,6 +277,11 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tH = tmem_base + lane_base + kColH;
     const uint32_t tS = tmem_base + lane_base + kColS;
     const uint32_t tO = tmem_base + lane_base + kColO;
+    // one arrival per warp: the lanes' writes are ordered before it by the warp barrier
+    auto warp_arrive = [&](uint64_t* bar) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    };
     auto load_decay = [&](int t) -> float {
       const int tok = t * T + tid;
       return (tid < T && tok < p.seq) ? ld_row[tok] * kLog2e : 0.0f;
@@ -309,11 +314,62 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const bool last = (t + 1 == nblk);
       const uint32_t par = t & 1;
       const float x_next = last ? 0.0f : load_decay(t + 1);  // consumed by the scan further down
+      const float gi = g2[buf * T + row];
+      const float qs = p.q_scale;
+      if (t > 0) {
+        ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh);
+        tc_fence_after_sync();
+      }
+      // ---- rows of V times their decay factors, into the buffer the state update reads ----
+      if (!last) {
+        ok = mbar_wait(v_full, par, ab, kLinVFull) && ok;
+        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row) and written to the same place of the
+        // second buffer (with 256 state columns that is the upper half of the state copy, free once Q h has
+        // run).  Every 16-byte piece of the row gets the same factor, so neither the swizzle nor the order
+        // matters: lanes start at different pieces to stay off each other's banks (rows are 128 bytes apart).
+        const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
+        const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
+        uint4* v2line = reinterpret_cast<uint4*>(sV2 + wg * (T * 128) + row * 128);
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          const int piece = (q4 + lane) & 7;
+          uint4 x = vline[piece];
+          uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float lo, hi;
+            if constexpr (kBf16) {
+              const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&xs[e]);
+              lo = __bfloat162float(h2.x);
+              hi = __bfloat162float(h2.y);
+            } else {
+              const __half2 h2 = *reinterpret_cast<__half2*>(&xs[e]);
+              lo = __half2float(h2.x);
+              hi = __half2float(h2.y);
+            }
+            xs[e] = pack2<kBf16>(lo * w, hi * w);
+          }
+          v2line[piece] = x;
+        }
+        fence_proxy_async_smem();
+        warp_arrive(v_ready);
+      }
+      // ---- rows of O = Q h scaled by scale * exp(g_i) ----
+      if (t > 0) {
+        const float f = qs * fast_exp2(gi);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          float o[32];
+          tmem_ld32f(tO + wg * 64 + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= f;
+          tmem_st32f(tO + wg * 64 + c * 32, o);
+        }
+      }
       // ---- rows of S -> P (while Q h still runs) ----
       // Both warp groups work on every row: group `wg` owns columns [64*wg, 64*wg+64) of S and of O (a single
       // warp per scheduler running dependent arithmetic is latency-bound; two interleave).
-      const float gi = g2[buf * T + row];
-      const float qs = p.q_scale;
       uint32_t pk[32], pl[32];
       {
         // exp(g_i - g_j) costs one MUFU operation per score only in the 32x32 chunk on the diagonal.  Below
@@ -321,7 +377,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // chunk: a per-row and a per-column number, both at most 1.  Chunks above the diagonal are zero and
         // are not even read.  All three cases are uniform over a warp.
         const int wq = warp & 3;
-        ok = mbar_wait(s_bar, par, ab, kLinScore);
+        ok = mbar_wait(s_bar, par, ab, kLinScore) && ok;
         tc_fence_after_sync();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -379,60 +435,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_st32(tS + wg * 32, pk);
         if (p.split_p) tmem_st32(tS + 64 + wg * 32, pl);
       }
-      if (t > 0) {
-        ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh) && ok;
-        tc_fence_after_sync();
-      }
-      // ---- rows of V times their decay factors, into the buffer the state update reads ----
-      if (!last) {
-        ok = mbar_wait(v_full, par, ab, kLinVFull) && ok;
-        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row) and written to the same place of the
-        // second buffer (with 256 state columns that is the upper half of the state copy, free once Q h has
-        // run).  Every 16-byte piece of the row gets the same factor, so neither the swizzle nor the order
-        // matters: lanes start at different pieces to stay off each other's banks (rows are 128 bytes apart).
-        const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
-        const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
-        uint4* v2line = reinterpret_cast<uint4*>(sV2 + wg * (T * 128) + row * 128);
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const int piece = (q4 + lane) & 7;
-          uint4 x = vline[piece];
-          uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float lo, hi;
-            if constexpr (kBf16) {
-              const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&xs[e]);
-              lo = __bfloat162float(h2.x);
-              hi = __bfloat162float(h2.y);
-            } else {
-              const __half2 h2 = *reinterpret_cast<__half2*>(&xs[e]);
-              lo = __half2float(h2.x);
-              hi = __half2float(h2.y);
-            }
-            xs[e] = pack2<kBf16>(lo * w, hi * w);
-          }
-          v2line[piece] = x;
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(v_ready);
-      }
-      // ---- rows of O = Q h scaled by scale * exp(g_i) ----
-      if (t > 0) {
-        const float f = qs * fast_exp2(gi);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float o[32];
-          tmem_ld32f(tO + wg * 64 + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= f;
-          tmem_st32f(tO + wg * 64 + c * 32, o);
-        }
-      }
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(p_ready);
+      warp_arrive(p_ready);
       // ---- the next block's decay scan runs under the MMAs ----
       if (!last) ok = scan_block(x_next, buf ^ 1, ok);
       ok = mbar_wait(pv_bar, par, ab, kLinPv) && ok;
@@ -487,7 +492,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(o_staged);
+        warp_arrive(o_staged);
       }
       if (last) break;
       // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
@@ -530,7 +535,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(conv_done);
+        warp_arrive(conv_done);
       }
     }
   }
