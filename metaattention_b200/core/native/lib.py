@@ -150,11 +150,12 @@ def load_library() -> C.CDLL:
     """Load (once) the native library.  Raises if it has not been built."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("ATTN_B200_LIBRARY", LIB_PATH)  # an alternative build of the same ABI
+        if not os.path.exists(path):
             raise NativeError(
-                f"{LIB_PATH} not found: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                f"{path} not found: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
                 "from the repository root (there is no non-native fallback)")
-        _lib = bind(C.CDLL(LIB_PATH))
+        _lib = bind(C.CDLL(path))
     return _lib
 
 
