@@ -21,8 +21,11 @@
 // One CTA per (128-column slice of dim_v, batch*head), walking the sequence in 128-token blocks.
 // The state is held transposed, hT[dv_slice=128][dim_qk], so that its MMAs have M = 128 for any
 // dim_qk: TMEM columns [0, DK) = hT, [256, 384) = S / P, [384, 512) = O.
-// Shared memory: Q, K (DK/64 chunks of 128 rows x 128 B each), V (2 chunks), bf16 hT (DK/64 chunks).
-// Phases of one block are separated by CTA-wide barriers; thread 0 issues TMA and MMAs.
+// Shared memory: Q, K (DK/64 chunks of 128 rows x 128 B each), V (2 chunks), bf16 hT (DK/64 chunks;
+// its lower 32 KB also stage the output rows, with dim_qk 256 its upper 32 KB hold the rescaled V).
+// Eight row warps (thread = TMEM lane x column half) and one issuing warp that launches every TMA copy
+// and MMA; they hand work to each other through mbarriers, and the order in which the issuing warp
+// serves them is the schedule of a block (see the comment at its loop).
 #include <cstring>
 
 #include "../../include/attn_b200.h"
