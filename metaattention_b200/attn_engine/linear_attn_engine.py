@@ -109,6 +109,14 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         raise native.NativeError("q, k, v must share dtype float16 or bfloat16")
     B, H, T, Dk = q.shape
     Dv = v.shape[-1]
+    if Dv % 128 != 0:
+        # the kernel works on 128-column slices of dim_v: a narrower v (Mamba2's head dim 64) is padded with
+        # zero columns, which stay zero in the output and are cut off again
+        if normalize:
+            raise native.NativeError("normalize needs dim_v to be a multiple of 128")
+        pad = 128 - Dv % 128
+        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps)
+        return o[..., :Dv].contiguous()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     log_decay = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
     with torch.cuda.device(q.device):
@@ -151,9 +159,10 @@ class LinearAttentionEngine:
         self.HK = qkv_meta[1].shape[1]
         self.H = qkv_meta[2].shape[1]
         self.Dv = qkv_meta[2].shape[3]
-        if Dk not in (64, 128, 256) or self.Dv % 128 != 0:
-            raise NotImplementedError(f"linear attention kernel covers dim_qk in (64,128,256) and dim_v a multiple of 128 "
-                                      f"(got {Dk}, {self.Dv})")
+        if Dk not in (64, 128, 256):
+            raise NotImplementedError(f"linear attention kernel covers dim_qk in (64,128,256) (got {Dk})")
+        if self.H % HQ != 0 or self.H % self.HK != 0:
+            raise NotImplementedError(f"v heads ({self.H}) must be a multiple of q heads ({HQ}) and k heads ({self.HK})")
         # trace the mods once
         self._leaves = {
             "q": SymbolicArray("q", Var("q"), shape_idx=["B", "H", "T", "D"]),
@@ -196,10 +205,12 @@ class LinearAttentionEngine:
         log_decay = self._apply("decay", decay.float(), cenv)
         B, _, T, _ = q.shape
         H = v.shape[1]
+        # fewer q / k heads than v heads: each group serves H / HQ consecutive heads (the grouping of the
+        # Mamba2 reference, testing/test.py:222,271)
         if q.shape[1] != H:
-            q = q.expand(B, H, T, q.shape[-1])
+            q = q.repeat_interleave(H // q.shape[1], dim=1)
         if k.shape[1] != H:
-            k = k.expand(B, H, T, k.shape[-1])
+            k = k.repeat_interleave(H // k.shape[1], dim=1)
         return linear_attention_forward(q, k, v, log_decay, q_scale=self.q_scale, normalize=self.normalize_output)
 
     def __call__(self, *args, **kargs):

@@ -49,6 +49,32 @@ def mla_inputs(B, H, S, D, Dv, seed, dtype=torch.bfloat16):
     return q, kv
 
 
+def gla_inputs(B, H, S, D, Dv, seed, dtype=torch.bfloat16):
+    """Gated retention / simple GLA (testing/test.py:412-418): q,k [B,H,S,D], v [B,H,S,Dv] N(0,1),
+    g [B,H,S] fp32 = logsigmoid(N(0,1)) clamped at -5 (natural-log decay per token)."""
+    g_ = _gen(seed)
+    q = torch.randn(B, H, S, D, generator=g_).to(dtype)
+    k = torch.randn(B, H, S, D, generator=g_).to(dtype)
+    v = torch.randn(B, H, S, Dv, generator=g_).to(dtype)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, H, S, generator=g_)).clamp_min(-5.0)
+    return q, k, v, g
+
+
+def mamba2_inputs(B, HQ, HK, HV, S, D, Dv, seed, dtype=torch.bfloat16):
+    """Mamba2 SSD (testing/test.py:161-180), in the engine's [B,H,S,*] layout: q (= C) [B,HQ,S,D],
+    k (= B) [B,HK,S,D] scaled 0.5, v (= x) [B,HV,S,Dv], dt [B,HV,S] fp32 = softplus(0.7 U(0,1) + bias_h),
+    A [1,HV] = 1.5 U(0,1) - 4."""
+    g_ = _gen(seed)
+    q = torch.randn(B, HQ, S, D, generator=g_).to(dtype)
+    k = (0.5 * torch.randn(B, HK, S, D, generator=g_)).to(dtype)
+    v = torch.randn(B, HV, S, Dv, generator=g_).to(dtype)
+    A = (1.5 * torch.rand(HV, generator=g_) - 4.0).to(dtype).float().view(1, HV)
+    dt0 = torch.exp(torch.rand(HV, generator=g_) * (math.log(0.1) - math.log(0.001)) + math.log(0.001)).clamp(min=1e-4)
+    bias = dt0 + torch.log(-torch.expm1(-dt0))
+    dt = torch.nn.functional.softplus(0.7 * torch.rand(B, HV, S, generator=g_) + bias.view(1, HV, 1))
+    return q, k, v, dt, A
+
+
 # The five benchmark configurations (shapes, seeds, constants).
 CONFIGS = {
     "C1": dict(kind="softmax", B=1, H=4, S=512, D=64, Dv=64, causal=False, seed=1001),

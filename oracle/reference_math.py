@@ -101,6 +101,28 @@ def retention_recurrent(q, k, v):
     return o
 
 
+def decayed_linear_attention(q, k, v, log_decay, scale: float = 1.0):
+    """o[i] = sum_{j<=i} exp(G_i - G_j) (scale q_i . k_j) v_j with G the inclusive cumulative sum of the
+    per-token natural-log decay: the function computed chunk by chunk by naive_chunk_simple_gla
+    (testing/test.py:436-481, gated retention, scale = 1/sqrt(D)) and by ssd_chunk_scan_combined_ref
+    (testing/test.py:305-343, Mamba2 SSD with q = C, k = B, v = x dt, log_decay = dt A, scale = 1).
+    q [B,HQ,S,D] and k [B,HK,S,D] may have fewer heads than v [B,H,S,Dv]: head h of v uses group
+    h // (H / HQ) (the SSD reference repeats each group consecutively, testing/test.py:222,271).
+    Evaluated as a plain token recurrence over the state in fp64; returns fp32 [B,H,S,Dv]."""
+    q, k, v, log_decay = q.double(), k.double(), v.double(), log_decay.double()
+    B, H, S, Dv = v.shape
+    if q.shape[1] != H:
+        q = q.repeat_interleave(H // q.shape[1], dim=1)
+    if k.shape[1] != H:
+        k = k.repeat_interleave(H // k.shape[1], dim=1)
+    state = torch.zeros(B, H, q.shape[-1], Dv, dtype=torch.float64)
+    o = torch.empty(B, H, S, Dv, dtype=torch.float64)
+    for i in range(S):
+        state = state * torch.exp(log_decay[:, :, i])[..., None, None] + k[:, :, i, :, None] * v[:, :, i, None, :]
+        o[:, :, i] = torch.einsum("bhd,bhde->bhe", q[:, :, i] * scale, state)
+    return o.float()
+
+
 def group_norm_heads(o, eps: float = 1e-5):
     """Normalisation of each (batch, head, token) vector over Dv to zero mean and unit
     variance, no affine parameters (GroupNorm with one group per head).  The reference

@@ -89,6 +89,23 @@ def main():
     o = ref(q[..., :Dv].float(), q[..., Dv:].float(), kv[..., :Dv].float(), kv[..., Dv:].float())
     out["mla"] = dict(shape=(B, H, S, D, Dv), seed=51, o=o.contiguous())
 
+    # gated retention / simple GLA (testing/test.py:436-481), chunk size 64 as the reference test calls it
+    ref = extract(tree, source, "test_gated_retention", "naive_chunk_simple_gla", {"Optional": __import__("typing").Optional})
+    B, H, S, D, Dv = 1, 4, 200, 64, 128
+    q, k, v, g = inputs.gla_inputs(B, H, S, D, Dv, 61)
+    out["gla"] = dict(shape=(B, H, S, D, Dv), seed=61, o=ref(q, k, v, g, chunk_size=64)[0].contiguous())
+
+    # Mamba2 SSD (testing/test.py:206-343): the combined reference and the three closures it calls
+    helpers = {}
+    for name in ("chunk_state_ref", "state_passing_ref", "chunk_scan_ref"):
+        helpers[name] = extract(tree, source, "test_mamba2", name, helpers)
+    ref = extract(tree, source, "test_mamba2", "ssd_chunk_scan_combined_ref", helpers)
+    B, HQ, HK, HV, S, D, Dv = 1, 2, 2, 4, 192, 64, 64
+    q, k, v, dt, A = inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, 71)
+    # the reference layout is [B,S,H,*]: x = v, B = k, C = q
+    o = ref(v.float().transpose(1, 2), dt.transpose(1, 2), A[0], k.float().transpose(1, 2), q.float().transpose(1, 2), chunk_size=64)
+    out["mamba2"] = dict(shape=(B, HQ, HK, HV, S, D, Dv), seed=71, o=o.transpose(1, 2).contiguous())
+
     for name, rec in out.items():
         rec["o"] = rec["o"].to(torch.float32)
         torch.save(rec, os.path.join(HERE, f"{name}.pt"))

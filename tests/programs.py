@@ -139,3 +139,32 @@ def retnet_engine(B, H, S, Dk, Dv, dtype=torch.bfloat16):
         return q * scale
     meta = (meta_tensor(B, H, S, Dk, dtype=dtype), meta_tensor(B, H, S, Dk, dtype=dtype), meta_tensor(B, H, S, Dv, dtype=dtype))
     return LinearAttentionEngine(meta, q_mod=q_mod, decay_mod=decay_mod, custom_io=CustomIO({}))
+
+
+def gla_engine(B, H, S, D, Dv, dtype=torch.bfloat16):
+    """Gated retention / simple GLA as examples/gated_retention.py builds it: q scaled by 1/sqrt(D),
+    the decay input already holds the per-token natural-log decay."""
+    scale = 1 / D ** 0.5
+
+    def q_mod(q, custom_io):
+        return q * scale
+    meta = (meta_tensor(B, H, S, D, dtype=dtype), meta_tensor(B, H, S, D, dtype=dtype), meta_tensor(B, H, S, Dv, dtype=dtype))
+    return LinearAttentionEngine(meta, q_mod=q_mod, custom_io=CustomIO({}))
+
+
+def mamba2_engine(B, HQ, S, D, Dv, HK=None, HV=None, dtype=torch.bfloat16):
+    """Mamba2 SSD as examples/mamba2.py builds it: decay_mod = decay * A, v_mod = v * dt;
+    called as mod(q, k, v, dt, A, dt)."""
+    HK = HQ if HK is None else HK
+    HV = HQ if HV is None else HV
+
+    def decay_mod(decay, custom_io):
+        A = custom_io.input_tensors["A"]
+        return (decay * A)
+
+    def v_mod(v, custom_io):
+        dt = custom_io.input_tensors["dt"]
+        return v * dt
+    meta = (meta_tensor(B, HQ, S, D, dtype=dtype), meta_tensor(B, HK, S, D, dtype=dtype), meta_tensor(B, HV, S, Dv, dtype=dtype))
+    custom_io = CustomIO({"A": (1, "heads"), "dt": ("batch", "heads", "seq_len")})
+    return LinearAttentionEngine(meta, decay_mod=decay_mod, v_mod=v_mod, custom_io=custom_io)

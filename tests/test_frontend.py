@@ -138,5 +138,12 @@ def test_reference_examples_construct_unchanged():
         assert sg2.sigmoid_attention(1, 4, 512, 128, 128).functor_kind == "lowered"
         relu = importlib.import_module("examples.reluattn")
         assert relu.relu_attention(1, 6, 512, 64, 64).mask_kind == 0
+        ret = importlib.import_module("examples.retnet_recurrent")
+        assert ret.retnet_recurrent(1, 8, 512, 256, 512).q_scale == 256 ** -0.5
+        gla = importlib.import_module("examples.gated_retention")
+        assert gla.gated_retention(1, 4, 512, 256, 256).q_scale == 1 / 256 ** 0.5
+        mb = importlib.import_module("examples.mamba2")
+        e = mb.mamba2(1, 1, 512, 128, 64, HK=1, HV=8)
+        assert e.custom_names == ["A", "dt"] and e.H == 8 and e.HK == 1
     finally:
         sys.path.remove("/root/reference")

@@ -105,10 +105,59 @@ def test_config4_normalised_output_sampled_heads():
             assert d[~small].max().item() <= 1.3 * 0.03125 * (want[~small].abs().max().item() // 4), d[~small].max().item()
 
 
+def test_gated_retention_against_reference_golden():
+    """examples/gated_retention.py (simple GLA) on the same kernel; golden from naive_chunk_simple_gla
+    (testing/test.py:436-481).  Strong per-token decays (down to e^-5) exercise the factorised mask."""
+    g = torch.load(os.path.join(GOLD, "gla.pt"))
+    B, H, S, D, Dv = g["shape"]
+    q, k, v, gl = inputs.gla_inputs(B, H, S, D, Dv, g["seed"])
+    e = programs.gla_engine(B, H, S, D, Dv)
+    o = e(q.cuda(), k.cuda(), v.cuda(), gl.cuda())
+    assert o.shape == (B, H, S, Dv)
+    check_raw(o, g["o"])
+
+
+def test_gated_retention_reference_dims():
+    """dims of the reference's own functional test (testing/test.py:58: D = DV = 256), shorter sequence"""
+    B, H, S, D, Dv = 2, 4, 640, 256, 256
+    q, k, v, gl = inputs.gla_inputs(B, H, S, D, Dv, 62)
+    e = programs.gla_engine(B, H, S, D, Dv)
+    o = e(q.cuda(), k.cuda(), v.cuda(), gl.cuda())
+    check_raw(o, rm.decayed_linear_attention(q, k, v, gl, scale=D ** -0.5))
+
+
+def test_mamba2_against_reference_golden():
+    """examples/mamba2.py: decay_mod = dt * A, v_mod = v * dt, two q/k groups for four v heads, head dim 64
+    (padded to the kernel's 128-column slice); golden from ssd_chunk_scan_combined_ref (testing/test.py:305-343)."""
+    g = torch.load(os.path.join(GOLD, "mamba2.pt"))
+    B, HQ, HK, HV, S, D, Dv = g["shape"]
+    q, k, v, dt, A = inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, g["seed"])
+    e = programs.mamba2_engine(B, HQ, S, D, Dv, HK=HK, HV=HV)
+    o = e(q.cuda(), k.cuda(), v.cuda(), dt.cuda(), A.cuda(), dt.to(torch.bfloat16).cuda())
+    assert o.shape == (B, HV, S, Dv)
+    check_raw(o, g["o"])
+
+
+def test_mamba2_reference_dims():
+    """head layout of the reference's functional test (testing/test.py:57: one q/k group, D = 128, DV = 64),
+    fewer v heads and a shorter sequence"""
+    B, HQ, HK, HV, S, D, Dv = 1, 1, 1, 8, 700, 128, 64
+    q, k, v, dt, A = inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, 72)
+    e = programs.mamba2_engine(B, HQ, S, D, Dv, HK=HK, HV=HV)
+    o = e(q.cuda(), k.cuda(), v.cuda(), dt.cuda(), A.cuda(), dt.to(torch.bfloat16).cuda())
+    dtb = dt.to(torch.bfloat16).float()  # v_mod sees the 16-bit dt the reference test passes
+    want = rm.decayed_linear_attention(q, k, (v.float() * dtb[..., None]).to(torch.bfloat16), dt * A.view(1, HV, 1), scale=1.0)
+    check_raw(o, want)
+
+
 def test_bad_arguments():
     import ctypes as C
     a = lib.LinearArgs()
     assert lib.load_library().attn_b200_linear_fwd(C.byref(a), None) == -1
     q, k, v, decay = [t.cuda() for t in inputs.retention_bhsd(1, 1, 128, 64, 128, 1)]
-    with pytest.raises(lib.NativeError, match="unsupported"):
-        linear_attention_forward(q, k, v[..., :96].contiguous(), decay.log())
+    with pytest.raises(lib.NativeError, match="unsupported"):   # dim_qk must be 64, 128 or 256
+        linear_attention_forward(q[..., :32].contiguous(), k[..., :32].contiguous(), v, decay.log())
+    # a dim_v that is not a multiple of the kernel's 128-column slice is padded, not refused
+    o = linear_attention_forward(q, k, v[..., :96].contiguous(), decay.log(), q_scale=0.125)
+    full = linear_attention_forward(q, k, v, decay.log(), q_scale=0.125)
+    assert o.shape[-1] == 96 and torch.equal(o, full[..., :96])

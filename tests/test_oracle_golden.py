@@ -89,3 +89,18 @@ def test_gqa_head_grouping():
     for h in range(4):
         single = rm.softmax_attention(q[:, :, h:h + 1], k[:, :, h // 2:h // 2 + 1], v[:, :, h // 2:h // 2 + 1], causal=False)
         close(o[:, :, h:h + 1], single, tol=1e-6)
+
+
+def test_gated_retention():
+    g = load("gla")
+    B, H, S, D, Dv = g["shape"]
+    q, k, v, gl = inputs.gla_inputs(B, H, S, D, Dv, g["seed"])
+    close(rm.decayed_linear_attention(q, k, v, gl, scale=D ** -0.5), g["o"], tol=1e-4)
+
+
+def test_mamba2_ssd():
+    g = load("mamba2")
+    B, HQ, HK, HV, S, D, Dv = g["shape"]
+    q, k, v, dt, A = inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, g["seed"])
+    o = rm.decayed_linear_attention(q, k, v.float() * dt[..., None], dt * A.view(1, HV, 1), scale=1.0)
+    close(o, g["o"], tol=1e-4)
