@@ -217,7 +217,17 @@ def extras_mla(steps, warmup):
         out["C5_mla_decode"] = {"ms": ms, "gbs": bytes_alg / ms / 1e6, "tflops": flops / ms / 1e9, "num_splits": splits,
                                 "frac_of_hbm_peak": bytes_alg / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
                                 "algorithmic_bytes": bytes_alg}
-        del q, kv
+        # the same cache seen as a pool of 64-token pages through a block table with the pages of every
+        # sequence in scrambled order, and full-length cache_seqlens (the reference's native call)
+        pages = S // 64
+        perm = torch.stack([torch.randperm(pages, generator=g, device="cuda") + b * pages for b in range(B)]).to(torch.int32)
+        pool = torch.empty(B * pages, 64, D, device="cuda", dtype=torch.bfloat16)
+        pool[perm.view(-1).long()] = kv.view(B * pages, 64, D)
+        lens = torch.full((B,), S, dtype=torch.int32, device="cuda")
+        ms_p = time_device(lambda: mla_decode_forward(q, pool, Dv, D ** -0.5, num_splits=splits, cache_seqlens=lens,
+                                                      block_table=perm), steps, warmup, lambda: None) / steps
+        out["C5_mla_decode_paged64"] = {"ms": ms_p, "gbs": bytes_alg / ms_p / 1e6}
+        del q, kv, pool
     except Exception as exc:
         out["C5_mla_decode"] = {"error": repr(exc)[:200]}
     torch.cuda.empty_cache()

@@ -139,6 +139,19 @@ typedef struct AttnB200MlaArgs {
   int32_t num_splits;
   int32_t dtype;
   float scale;          /* softmax scale, e.g. 1/sqrt(dim_qk) */
+  /* Ragged and paged caches (cache_seqlens / block_table of mha_fwd_kvcache_mla,
+   * core/template/cute_template_kvshared/flash_api.cpp:61-72).  All-zero fields = one dense
+   * [batch, seq_kv, *] cache in which every sequence has seq_kv tokens. */
+  const int32_t* seq_lens;     /* device, [batch]: tokens of each sequence, 1 <= n <= shape.seq_kv; NULL = seq_kv   */
+  const int32_t* block_table;  /* device, [batch, block_table_stride]: pool page holding tokens
+                                  [i*page_size, (i+1)*page_size) of the sequence; NULL = dense cache.  With a
+                                  table, kv (and kv_rope) point at a page pool [num_pages, page_size, *]:
+                                  kv_stride[0] is the page stride, kv_stride[1] the token stride.  Entries are
+                                  read up to the page of the sequence's last token; tokens of that page past the
+                                  sequence end are read but carry no weight and must be finite numbers. */
+  int64_t block_table_stride;  /* elements between the tables of two sequences */
+  int32_t page_size;           /* tokens per page: a multiple of 64 */
+  int32_t num_pages;           /* pages in the pool */
 } AttnB200MlaArgs;
 
 /* Split-KV decode + combine.  Replaces flash_fwd_splitkv_mla_kernel and

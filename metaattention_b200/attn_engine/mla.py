@@ -60,15 +60,35 @@ def _rows(t: torch.Tensor, what: str):
 
 
 def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=None, num_splits: int | None = None,
-                       workspace: torch.Tensor | None = None):
+                       workspace: torch.Tensor | None = None, cache_seqlens: torch.Tensor | None = None,
+                       block_table: torch.Tensor | None = None, max_seqlen: int | None = None):
     """q: [B,H,D] (or [B,1,H,D]); kv: [B,S,D] (or [B,S,1,D]).  With ``q_rope`` /
     ``kv_rope`` given, q and kv hold only the first ``dim_v`` columns.
+    ``cache_seqlens`` (int32 [B], CUDA): tokens of each sequence (1..S); default all S.
+    ``block_table`` (int32 [B, max_blocks], CUDA): kv is then a page pool [num_pages, page_size, D] (or
+    [num_pages, page_size, 1, D]), page_size a multiple of 64, and entry i of a sequence's row names the
+    page with its tokens [i*page_size, (i+1)*page_size); ``max_seqlen`` (default max_blocks*page_size)
+    bounds the sequence lengths.
     Returns (o [B,H,dim_v] in the input dtype, lse [B,H] fp32)."""
     q3, kv3 = _rows(q, "q"), _rows(kv, "kv")
     if not q3.is_cuda:
         raise native.NativeError("MLA decode needs CUDA tensors")
     B, H, dq = q3.shape
     S = kv3.shape[1]
+    page_size = num_pages = 0
+    if block_table is not None:
+        if block_table.dtype != torch.int32 or not block_table.is_cuda or block_table.dim() != 2 or block_table.shape[0] != B:
+            raise ValueError("block_table must be a CUDA int32 tensor [batch, max_blocks]")
+        if block_table.stride(1) != 1:
+            block_table = block_table.contiguous()
+        num_pages, page_size = kv3.shape[0], kv3.shape[1]
+        S = block_table.shape[1] * page_size if max_seqlen is None else int(max_seqlen)
+        if S > block_table.shape[1] * page_size:
+            raise ValueError("max_seqlen exceeds the block table")
+    if cache_seqlens is not None:
+        if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_cuda or cache_seqlens.numel() != B:
+            raise ValueError("cache_seqlens must be a CUDA int32 tensor [batch]")
+        cache_seqlens = cache_seqlens.contiguous()
     rope_dim = 0
     qr3 = kr3 = None
     if (q_rope is None) != (kv_rope is None):
@@ -104,6 +124,12 @@ def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=Non
         a.num_splits = num_splits
         a.dtype = native.DTYPE_CODES[q3.dtype]
         a.scale = float(scale)
+        if cache_seqlens is not None:
+            a.seq_lens = cache_seqlens.data_ptr()
+        if block_table is not None:
+            a.block_table = block_table.data_ptr()
+            a.block_table_stride = block_table.stride(0)
+            a.page_size, a.num_pages = page_size, num_pages
         native.check(native.load_library().attn_b200_mla_decode(C.byref(a), native.current_stream_ptr()),
                      "attn_b200_mla_decode")
     return o, lse
@@ -130,3 +156,30 @@ def build_mla_decode(engine, B, H, Hkv, Skv, D, Dv, dtype, backend):
         engine.last_final_rowscales = {"lse": lse}
         return o.view(Bq, 1, o.shape[1], o.shape[2]), lse.view(Bq, lse.shape[1], 1)
     return attention_paged
+
+
+def get_mla_metadata(cache_seqlens: torch.Tensor, num_heads_per_head_k: int, num_heads_k: int = 1):
+    """Same call as the reference's scheduler query (cute_template_kvshared/flash_mla_interface.py:57-72).
+    The native kernel takes one split count per call instead of per-SM tile lists: returns
+    (None, num_splits) with num_splits an int chosen by attn_b200_mla_plan for the longest sequence the
+    table can hold; pass both on to flash_mla_with_kvcache."""
+    if num_heads_k != 1:
+        raise NotImplementedError("MLA decode expects a single shared latent KV head")
+    return None, None   # the plan needs the page geometry: flash_mla_with_kvcache makes it when given None
+
+
+def flash_mla_with_kvcache(q, k_cache, block_table, cache_seqlens, head_dim_v, tile_scheduler_metadata=None,
+                           num_splits=None, softmax_scale=None, causal=False):
+    """Drop-in for the reference's paged MLA decode call
+    (cute_template_kvshared/flash_mla_interface.py:74-115): q [B,1,Hq,D], k_cache [num_blocks,
+    page_block_size, 1, D], block_table int32 [B, max_blocks], cache_seqlens int32 [B].
+    Returns (out [B,1,Hq,head_dim_v], softmax_lse [B,Hq,1] fp32).  ``causal`` has no effect with one
+    query token per sequence."""
+    if q.shape[1] != 1:
+        raise NotImplementedError("one query token per sequence")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    splits = num_splits if isinstance(num_splits, int) else None
+    o, lse = mla_decode_forward(q, k_cache, head_dim_v, softmax_scale, num_splits=splits,
+                                cache_seqlens=cache_seqlens, block_table=block_table)
+    return o.view(o.shape[0], 1, o.shape[1], o.shape[2]), lse.view(lse.shape[0], lse.shape[1], 1)

@@ -82,6 +82,8 @@ class MlaArgs(C.Structure):
         ("o", C.c_void_p), ("lse", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("shape", MlaShape), ("num_splits", C.c_int32), ("dtype", C.c_int32), ("scale", C.c_float),
+        ("seq_lens", C.c_void_p), ("block_table", C.c_void_p), ("block_table_stride", C.c_int64),
+        ("page_size", C.c_int32), ("num_pages", C.c_int32),
     ]
 
 

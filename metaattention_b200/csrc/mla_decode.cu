@@ -43,9 +43,6 @@
 #include "parallel_launch.cuh"  // tensor_map_encoder()
 #include "sm100.cuh"
 
-#ifndef MLA_ST_ASYNC
-#define MLA_ST_ASYNC 1
-#endif
 namespace b200 {
 
 constexpr int kMlaHeads = 128;     // heads per cluster (MMA M)
@@ -61,6 +58,10 @@ struct MlaParams {
   float* part_o;        // [B, splits, H, DV] fp32 (num_splits > 1)
   float* part_lse;      // [B, splits, H]
   int batch, heads, seq_kv, num_splits, tiles_per_split, head_blocks;
+  const int* seq_lens;     // [B] tokens per sequence, or null (= seq_kv)
+  const int* block_table;  // [B, bt_stride] pool page of every page_rows-token block, or null (dense cache)
+  long long bt_stride;
+  int page_rows;
   float scale_log2;     // scale * log2(e)
   float scale;
   int* status;
@@ -145,7 +146,18 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
   const int hb = blockIdx.y / p.num_splits;
   const int b = blockIdx.z;
   const int head0 = hb * M;
-  const int total_tiles = (p.seq_kv + N - 1) / N;
+  // tokens of this sequence (uniform over the cluster), and with a paged cache the table of its pages
+  const int seq_len = p.seq_lens != nullptr ? max(1, min(p.seq_lens[b], p.seq_kv)) : p.seq_kv;
+  const int* pages = p.block_table != nullptr ? p.block_table + static_cast<long long>(b) * p.bt_stride : nullptr;
+  // pool coordinates of logical token row `r` (rows past the end are redirected to the last token's
+  // 64-row block: they are masked, but must be read from mapped memory)
+  auto locate = [&](int r, int& row_in_page, int& page) {
+    r = min(r, ((seq_len - 1) >> 6) << 6 | (r & 63));
+    const int blk = r / p.page_rows;
+    page = pages[blk];
+    row_in_page = r - blk * p.page_rows;
+  };
+  const int total_tiles = (seq_len + N - 1) / N;
   const int tile_begin = split * p.tiles_per_split;
   const int n = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);  // 128-row tiles of this split
   constexpr uint32_t kPTxEven = L::kPBytes + M * 4;   // half 0 of a tile also carries the rescale factors
@@ -170,7 +182,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
       mbar_init(&bars[L::kRowMax + i], 256);
     }
     for (int i = 0; i < 4; ++i) {
-      mbar_init(&bars[L::kPFull + i], MLA_ST_ASYNC ? 1 : 128);
+      mbar_init(&bars[L::kPFull + i], 1);
       mbar_init(&bars[L::kPFree + i], 1);
       mbar_init(&bars[L::kPvGo + i], 128);
       mbar_init(&bars[L::kPvDone + i], 1);
@@ -183,7 +195,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
     fence_barrier_init();
     if (rank == 1) {
       // every P slot expects its first half tile before the score CTA can send anything
-      if (MLA_ST_ASYNC) for (int i = 0; i < 4; ++i) mbar_arrive_expect_tx(&bars[L::kPFull + i], (i & 1) ? kPTxOdd : kPTxEven);
+      for (int i = 0; i < 4; ++i) mbar_arrive_expect_tx(&bars[L::kPFull + i], (i & 1) ? kPTxOdd : kPTxEven);
     }
   }
   if (warp == 9) {
@@ -213,9 +225,20 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           const int j = g / 3, c0 = (g - j * 3) * 3, slot = g % L::kScoreSlots;
           if (!mbar_wait(&bars[L::kSlotEmpty + slot], ((g / L::kScoreSlots) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
           mbar_arrive_expect_tx(&bars[L::kSlotFull + slot], L::kSlotBytes);
-          for (int c = c0; c < c0 + 3; ++c)
-            tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot],
-                        c < 8 ? c * 64 : 0, (tile_begin + j) * N, b);
+          if (pages == nullptr) {
+            for (int c = c0; c < c0 + 3; ++c)
+              tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot],
+                          c < 8 ? c * 64 : 0, (tile_begin + j) * N, b);
+          } else {
+            // paged cache: the maps have 64-row boxes over [pool page][row in page]; a tile is two boxes
+            for (int hf = 0; hf < 2; ++hf) {
+              int rin, pg;
+              locate((tile_begin + j) * N + hf * 64, rin, pg);
+              for (int c = c0; c < c0 + 3; ++c)
+                tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes + hf * (64 * 128), c < 8 ? &tmKV : &tmKVr,
+                            &bars[L::kSlotFull + slot], c < 8 ? c * 64 : 0, rin, pg);
+            }
+          }
         }
       }
     } else if (warp == 9) {
@@ -297,9 +320,9 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           tc_fence_before_sync();
           mbar_arrive(&bars[L::kSFree + buf]);  // this half is in registers
           const int kv0 = (tile_begin + j) * N + wg * 64;
-          if (kv0 + 64 > p.seq_kv) {
+          if (kv0 + 64 > seq_len) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) s[i] = (kv0 + i < p.seq_kv) ? s[i] : -INFINITY;
+            for (int i = 0; i < 64; ++i) s[i] = (kv0 + i < seq_len) ? s[i] : -INFINITY;
           }
           float mx0 = s[0], mx1 = s[1];
 #pragma unroll
@@ -337,18 +360,10 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           if (!ok) break;
           const uint32_t dst = peer_p + pslot * L::kPBytes;
           const uint32_t bar = peer_pfull + pslot * 8;
-#if MLA_ST_ASYNC
 #pragma unroll
           for (int q4 = 0; q4 < 8; ++q4)
             st_async_v4(dst + ((q4 ^ (row & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]), bar);
           if (wg == 0) st_async_f32(peer_scale + (j & 1) * (M * 4), o_scale, bar);
-#else
-#pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            st_cluster_v4(dst + ((q4 ^ (row & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]));
-          if (wg == 0) st_cluster_f32(peer_scale + (j & 1) * (M * 4), o_scale);
-          mbar_arrive_cluster(bar);
-#endif
         }
         // ---- final row statistics: sum of both halves ----
         if (ok) {
@@ -378,8 +393,10 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           if (!mbar_wait(&bars[L::kSlotEmpty + st], ((g / L::kVStages) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
           mbar_arrive_expect_tx(&bars[L::kSlotFull + st], L::kVStageBytes);
           uint8_t* dst = sV + st * L::kVStageBytes;
+          int vrow = tile_begin * N + g * L::kVStageRows, vz = b;
+          if (pages != nullptr) locate(vrow, vrow, vz);
           for (int c = 0; c < 8; ++c)
-            tma_load_3d(dst + c * (L::kVStageRows * 128), &tmV, &bars[L::kSlotFull + st], c * 64, tile_begin * N + g * L::kVStageRows, b);
+            tma_load_3d(dst + c * (L::kVStageRows * 128), &tmV, &bars[L::kSlotFull + st], c * 64, vrow, vz);
         }
       }
     } else if (warp == 5) {
@@ -415,7 +432,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           const int pslot = h & 3;
           if (!mbar_wait(&bars[L::kPvDone + pslot], (h >> 2) & 1, ab, kMlaPvDone)) break;
           // arm the slot for its next half tile BEFORE the score CTA learns that it is free
-          if (MLA_ST_ASYNC && h + 4 < n_half) mbar_arrive_expect_tx(&bars[L::kPFull + pslot], (pslot & 1) ? kPTxOdd : kPTxEven);
+          if (h + 4 < n_half) mbar_arrive_expect_tx(&bars[L::kPFull + pslot], (pslot & 1) ? kPTxOdd : kPTxEven);
           mbar_arrive_cluster(peer_pfree + pslot * 8);
         }
       }
@@ -605,11 +622,19 @@ int launch_mla(const AttnB200MlaArgs* a, cudaStream_t stream, int* status) {
   if ((reinterpret_cast<uintptr_t>(a->q) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
   for (int i = 0; i < 2; ++i)
     if (a->q_stride[i] % 8 != 0) return ATTN_B200_E_UNSUPPORTED;
-  int rc = encode_3d(&tmKV, a->kv, a->dtype, DV, s.seq_kv, s.batch, a->kv_stride[0], a->kv_stride[1], kMlaTileN);
+  // dense cache: maps over [batch][token]; paged cache: maps over [pool page][row in page], score-side boxes of 64 rows
+  const bool paged = a->block_table != nullptr;
+  if (paged) {
+    if (a->page_size <= 0 || a->page_size % 64 != 0 || a->num_pages <= 0) return ATTN_B200_E_INVALID_ARG;
+    if (a->block_table_stride < (s.seq_kv + a->page_size - 1) / a->page_size) return ATTN_B200_E_INVALID_ARG;
+  }
+  const uint64_t map_rows = paged ? a->page_size : s.seq_kv, map_outer = paged ? a->num_pages : s.batch;
+  const uint32_t score_box = paged ? 64 : kMlaTileN;
+  int rc = encode_3d(&tmKV, a->kv, a->dtype, DV, map_rows, map_outer, a->kv_stride[0], a->kv_stride[1], score_box);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_3d(&tmKVr, kv_rope, a->dtype, D - DV, s.seq_kv, s.batch, kr_st[0], kr_st[1], kMlaTileN);
+  rc = encode_3d(&tmKVr, kv_rope, a->dtype, D - DV, map_rows, map_outer, kr_st[0], kr_st[1], score_box);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_3d(&tmV, a->kv, a->dtype, DV, s.seq_kv, s.batch, a->kv_stride[0], a->kv_stride[1], MlaSmem::kVStageRows);
+  rc = encode_3d(&tmV, a->kv, a->dtype, DV, map_rows, map_outer, a->kv_stride[0], a->kv_stride[1], MlaSmem::kVStageRows);
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_3d(&tmQr, q_rope, a->dtype, D - DV, s.heads_q, s.batch, qr_st[0], qr_st[1], kMlaHeads);
   if (rc != ATTN_B200_OK) return rc;
@@ -625,6 +650,10 @@ int launch_mla(const AttnB200MlaArgs* a, cudaStream_t stream, int* status) {
   p.batch = s.batch;
   p.heads = s.heads_q;
   p.seq_kv = s.seq_kv;
+  p.seq_lens = a->seq_lens;
+  p.block_table = a->block_table;
+  p.bt_stride = a->block_table_stride;
+  p.page_rows = paged ? a->page_size : 0;
   p.num_splits = a->num_splits;
   p.tiles_per_split = (total_tiles + a->num_splits - 1) / a->num_splits;
   p.scale = a->scale;

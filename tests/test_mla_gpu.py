@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import programs
-from attn_engine.mla import mla_decode_forward, plan_splits
+from attn_engine.mla import flash_mla_with_kvcache, mla_decode_forward, plan_splits
 from core.native import lib
 from oracle import inputs, reference_math as rm
 
@@ -108,3 +108,57 @@ def test_plan_and_workspace_errors():
     assert lib.load_library().attn_b200_mla_decode(C.byref(a), None) == -5      # no workspace
     a.shape = lib.MlaShape(1, 128, 256, 512, 512)
     assert lib.load_library().attn_b200_mla_decode(C.byref(a), None) == -2      # unsupported dims
+
+
+def ragged_oracle(q, kv, lens, Dv):
+    """per sequence: attention over its first lens[b] cache rows"""
+    outs, lses = [], []
+    for b, n in enumerate(lens):
+        qb, kb = q[b:b + 1], kv[b:b + 1, :n]
+        outs.append(rm.mla_decode(qb[..., :Dv], qb[..., Dv:], kb[..., :Dv], kb[..., Dv:]))
+        lses.append(rm.mla_decode_lse(qb[..., :Dv], qb[..., Dv:], kb[..., :Dv], kb[..., Dv:]))
+    return torch.cat(outs), torch.cat(lses)
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_ragged_sequence_lengths(splits):
+    """cache_seqlens of flash_api.cpp:61-72: every sequence stops at its own length; the rows behind it
+    hold large numbers that must not leak into the result."""
+    B, H, S, D, Dv = 5, 128, 700, 576, 512
+    lens = [700, 1, 129, 64, 333]
+    q, kv = inputs.mla_inputs(B, H, S, D, Dv, 4001)
+    kv_dirty = kv.clone()
+    for b, n in enumerate(lens):
+        kv_dirty[b, n:] = 1000.0
+    o, lse = mla_decode_forward(q.cuda(), kv_dirty.cuda(), Dv, D ** -0.5, num_splits=splits,
+                                cache_seqlens=torch.tensor(lens, dtype=torch.int32, device="cuda"))
+    want, want_lse = ragged_oracle(q, kv, lens, Dv)
+    check(o, want)
+    assert (lse.cpu().reshape(-1) - want_lse.reshape(-1)).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("page,splits", [(64, 1), (64, 4), (128, 2)])
+def test_paged_cache_with_block_table(page, splits):
+    """block_table of flash_api.cpp:61-72 / flash_mla_interface.py:74-115: the cache is a pool of pages in
+    arbitrary order, with unrelated pages (large numbers) in between."""
+    B, H, S, D, Dv = 3, 128, 1024, 576, 512
+    lens = [1024, 450, 65]
+    q, kv = inputs.mla_inputs(B, H, S, D, Dv, 4002)
+    blocks = S // page
+    gen = torch.Generator().manual_seed(7)
+    num_pages = B * blocks + 5
+    perm = torch.randperm(num_pages, generator=gen)[: B * blocks].view(B, blocks)
+    pool = torch.full((num_pages, page, 1, D), 1000.0, dtype=kv.dtype)
+    for b in range(B):
+        for i in range(blocks):
+            pool[perm[b, i], :, 0] = kv[b, i * page:(i + 1) * page, 0]
+    table = perm.to(torch.int32)
+    # entries behind a sequence's last page are never read: make them invalid
+    for b, n in enumerate(lens):
+        table[b, (n + page - 1) // page:] = -1
+    out, lse = flash_mla_with_kvcache(q.cuda(), pool.cuda(), table.cuda(),
+                                      torch.tensor(lens, dtype=torch.int32, device="cuda"), Dv, None, splits)
+    assert out.shape == (B, 1, H, Dv) and lse.shape == (B, H, 1)
+    want, want_lse = ragged_oracle(q, kv, lens, Dv)
+    check(out, want)
+    assert (lse.cpu().reshape(-1) - want_lse.reshape(-1)).abs().max().item() <= 2e-3
