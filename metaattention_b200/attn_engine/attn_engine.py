@@ -129,10 +129,16 @@ class AttentionEngine:
             self.attention = build_mla_decode(self, B, H, Hkv, Skv, D, Dv, dtype, backend)
         elif self.pattern == "parallel":
             self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value)
+        elif self.pattern == "mha_decode":
+            # A few query rows against a long KV (examples/mha_decode.py; the reference lowers it to a split-KV
+            # kernel plus OnlineFunc.combine, lower_decode.py:375-449).  The forward kernel takes any
+            # q_len != kv_len, streams K/V once per (batch, head) and needs no combine step; with few
+            # (batch, head) pairs it leaves SMs idle.
+            self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=Skv)
         else:
             raise NotImplementedError(
                 f"pattern {self.pattern!r} (q_len={Sq}, kv_len={Skv}, heads={H}, kv_heads={Hkv}) is not covered by the "
-                "native backend yet: it implements the parallel MHA forward, chunked linear attention and MLA decode")
+                "native backend yet: it implements the parallel MHA forward, MHA decode, chunked linear attention and MLA decode")
 
     # pattern selection by shape, as attn_engine.py:227-343 of the reference
     @staticmethod
@@ -148,11 +154,13 @@ class AttentionEngine:
         return "gqa"
 
     # ------------------------------------------------------------------
-    def _build_parallel(self, B, H, S, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value):
+    def _build_parallel(self, B, H, S, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=None):
         if (D, Dv) not in ((64, 64), (128, 128)):
             raise NotImplementedError(f"head dims (qk={D}, v={Dv}) are not covered by the forward kernel yet "
                                       "(supported: 64/64 and 128/128)")
-        self.mask_kind = classify_mask(mask_mod, B, H, S, S)
+        self.mask_kind = classify_mask(mask_mod, B, H, S, S if kv_len is None else kv_len)
+        if kv_len is not None and kv_len != S and self.mask_kind != native.MASK_NONE:
+            raise NotImplementedError("decode (q_len != kv_len) supports mask_mod=None or an all-true mask")
         neg_inf_mask = str(mask_value).strip() in ("-inf", "-float('inf')")
         self.traced = trace_parallel(score_mod, online_func, self.custom_fwd_inputs)
         tr = self.traced

@@ -168,3 +168,15 @@ def mamba2_engine(B, HQ, S, D, Dv, HK=None, HV=None, dtype=torch.bfloat16):
     meta = (meta_tensor(B, HQ, S, D, dtype=dtype), meta_tensor(B, HK, S, D, dtype=dtype), meta_tensor(B, HV, S, Dv, dtype=dtype))
     custom_io = CustomIO({"A": (1, "heads"), "dt": ("batch", "heads", "seq_len")})
     return LinearAttentionEngine(meta, decay_mod=decay_mod, v_mod=v_mod, custom_io=custom_io)
+
+
+def softmax_decode_engine(B, H, Sq, Skv, D, Dv, dtype=torch.bfloat16):
+    """A few query rows against a long KV, built like examples/mha_decode.py: the q meta tensor is padded to
+    a multiple of 128 rows, no mask."""
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    meta = (meta_tensor(B, H, ((Sq + 127) // 128) * 128, D, dtype=dtype), meta_tensor(B, H, Skv, D, dtype=dtype),
+            meta_tensor(B, H, Skv, Dv, dtype=dtype))
+    return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=NaturalSoftmax())

@@ -61,9 +61,9 @@ def test_pattern_selection_follows_reference_rules():
 
 
 def test_unsupported_patterns_raise_clearly():
-    meta = (meta_tensor(1, 16, 1, 128, dtype=torch.float16), meta_tensor(1, 16, 4096, 128, dtype=torch.float16),
-            meta_tensor(1, 16, 4096, 128, dtype=torch.float16))
-    with pytest.raises(NotImplementedError, match="mha_decode"):
+    meta = (meta_tensor(1, 16, 1, 128, dtype=torch.float16), meta_tensor(1, 4, 4096, 128, dtype=torch.float16),
+            meta_tensor(1, 4, 4096, 128, dtype=torch.float16))
+    with pytest.raises(NotImplementedError, match="gqa_decode"):
         AttentionEngine(meta, CustomIO({}), None, None, None)
     with pytest.raises(TypeError):
         AttentionEngine(programs._meta(1, 2, 128, 64, 64, torch.float32), CustomIO({}), None, None, None)
@@ -142,6 +142,8 @@ def test_reference_examples_construct_unchanged():
         assert ret.retnet_recurrent(1, 8, 512, 256, 512).q_scale == 256 ** -0.5
         gla = importlib.import_module("examples.gated_retention")
         assert gla.gated_retention(1, 4, 512, 256, 256).q_scale == 1 / 256 ** 0.5
+        dec = importlib.import_module("examples.mha_decode")
+        assert dec.softmax_attention_decode(2, 8, 1, 4096, 128, 128).pattern == "mha_decode"
         mb = importlib.import_module("examples.mamba2")
         e = mb.mamba2(1, 1, 512, 128, 64, HK=1, HV=8)
         assert e.custom_names == ["A", "dt"] and e.H == 8 and e.HK == 1

@@ -202,3 +202,18 @@ def test_bad_arguments_return_error_codes():
     a = lib.fill_parallel_args(q[..., 1:33], k[..., 1:33], v[..., 1:33], o[..., 1:33], mask_kind=0, fparams=[0.1])
     with pytest.raises(lib.NativeError):
         lib.parallel_fwd(a)   # misaligned base pointers are rejected before launch
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv,D", [(2, 8, 1, 1000, 128), (1, 4, 5, 4096, 128), (3, 2, 130, 333, 64)])
+def test_mha_decode_pattern(B, H, Sq, Skv, D):
+    """q_len != kv_len, equal head counts (examples/mha_decode.py): full attention of every query row over
+    the whole KV, on the forward kernel."""
+    g = torch.Generator().manual_seed(900 + Skv)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Skv, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Skv, H, D, generator=g).to(torch.bfloat16)
+    e = programs.softmax_decode_engine(B, H, Sq, Skv, D, D)
+    assert e.pattern == "mha_decode"
+    o = e(q.cuda(), k.cuda(), v.cuda())
+    assert o.shape == (B, Sq, H, D)
+    check(o, rm.softmax_attention(q, k, v, causal=False, softmax_scale=D ** -0.5))
