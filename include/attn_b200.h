@@ -40,6 +40,8 @@ extern "C" {
 
 #define ATTN_B200_MASK_NONE 0
 #define ATTN_B200_MASK_CAUSAL 1        /* keep q_idx >= kv_idx (top-left aligned)           */
+#define ATTN_B200_MASK_BAND 2          /* keep q_idx - mask_left <= kv_idx <= q_idx + mask_right (sliding windows) */
+#define ATTN_B200_MASK_OPEN 0x3fffffff /* value of mask_left / mask_right for a side without a bound */
 
 /* Built-in functors of the parallel pattern (score_mod + online_func pairs
  * recognised by the front-end).  Anything else is compiled from the traced
@@ -67,10 +69,13 @@ typedef struct AttnB200ParallelArgs {
   int32_t dtype;         /* ATTN_B200_DTYPE_*  */
   int32_t mask_kind;     /* ATTN_B200_MASK_*   */
   int32_t functor;       /* ATTN_B200_FUNCTOR_* (ignored by *_jit libraries) */
-  int32_t reserved;
+  int32_t heads_kv;      /* heads of k and v: 0 or `heads` = one per query head; a divisor of `heads` = grouped
+                            (query head h reads KV head h / (heads / heads_kv), attn_gqa_tl.py of the reference) */
   float fparams[8];      /* functor scalars */
   const void* custom[ATTN_B200_MAX_CUSTOM];          /* custom_fwd_inputs tensors */
   int64_t custom_stride[ATTN_B200_MAX_CUSTOM][4];    /* element strides of (batch, heads, seq_len, seq_len_kv); 0 = broadcast */
+  int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only: tokens kept before / after the diagonal, >= 0 or
+                                      ATTN_B200_MASK_OPEN; KV tiles outside the band are skipped */
 } AttnB200ParallelArgs;
 
 /* Replaces the generated TileLang forward kernel and its launcher

@@ -84,22 +84,42 @@ class _ForwardOnly(torch.autograd.Function):
         raise NotImplementedError("the B200-native backend implements the forward pass only")
 
 
-def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int) -> int:
-    """MASK_NONE / MASK_CAUSAL for a ``mask_mod(b, h, q_idx, kv_idx)``.  The mask is
-    evaluated on CPU for one (b, h) over the [q_len, kv_len] grid (never the
-    B*H*S*S tensor the reference materialises at core/lower/lower.py:729)."""
+def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int):
+    """(mask kind, (left, right)) for a ``mask_mod(b, h, q_idx, kv_idx)``: MASK_NONE, MASK_CAUSAL, or
+    MASK_BAND = keep q_idx - left <= kv_idx <= q_idx + right (sliding windows; MASK_OPEN = no bound on
+    that side).  The mask is evaluated on CPU for one (b, h) over the [q_len, kv_len] grid (never the
+    B*H*S*S tensor the reference materialises at core/lower/lower.py:729) and compared with the band it
+    suggests; the kernel then skips the KV tiles outside the band, which is what the reference's block
+    mask does for it (core/transform/core.py:492-506)."""
+    open_band = (native.MASK_OPEN, native.MASK_OPEN)
     if mask_mod is None:
-        return native.MASK_NONE
+        return native.MASK_NONE, open_band
     if mask_depends_on_batch_head(mask_mod, B, H, q_len, kv_len, "cpu"):
         raise NotImplementedError("mask_mod depending on batch or head index is not supported by the native backend yet")
     dense = _eval_mask_2d(mask_mod, 0, 0, q_len, kv_len, "cpu")
     if bool(dense.all()):
-        return native.MASK_NONE
-    causal = torch.ones(q_len, kv_len, dtype=torch.bool).tril()
-    if torch.equal(dense, causal):
-        return native.MASK_CAUSAL
-    raise NotImplementedError("only mask_mod=None, all-true and causal (q_idx >= kv_idx) masks are supported by the "
-                              "native backend yet")
+        return native.MASK_NONE, open_band
+    q = torch.arange(q_len).view(-1, 1)
+    kv = torch.arange(kv_len).view(1, -1)
+    if torch.equal(dense, kv <= q):
+        return native.MASK_CAUSAL, open_band
+    if bool(dense.any(dim=1).all()):
+        # widest reach of any row to either side of its diagonal; a side that always runs to the edge is open
+        first = dense.float().argmax(dim=1)
+        last = kv_len - 1 - dense.flip(1).float().argmax(dim=1)
+        rows = torch.arange(q_len)
+        left = int((rows - first).max())
+        right = int((last - rows).max())
+        if left >= 0 and right >= 0:
+            if bool((first == 0).all()):
+                left = native.MASK_OPEN
+            if bool((last == kv_len - 1).all()):
+                right = native.MASK_OPEN
+            if torch.equal(dense, (kv >= q - left) & (kv <= q + right)):
+                return native.MASK_BAND, (left, right)
+    raise NotImplementedError("only mask_mod=None, all-true, causal (q_idx >= kv_idx) and band masks "
+                              "(q_idx - left <= kv_idx <= q_idx + right, e.g. sliding windows) are supported by the native "
+                              "backend yet")
 
 
 class AttentionEngine:
@@ -129,6 +149,15 @@ class AttentionEngine:
             self.attention = build_mla_decode(self, B, H, Hkv, Skv, D, Dv, dtype, backend)
         elif self.pattern == "parallel":
             self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value)
+        elif self.pattern in ("gqa", "gqa_decode"):
+            # grouped KV heads (the reference's lower_gqa.py / attn_gqa_tl.py and the dense case of its GQA decode):
+            # the same forward kernel, query head h reading KV head h / (H / Hkv); K/V of a group are fetched
+            # once per query head and mostly hit L2.  Block-sparse / varlen GQA decode is not covered.
+            if H % Hkv != 0:
+                raise NotImplementedError(f"query heads ({H}) must be a multiple of KV heads ({Hkv})")
+            if use_varlen or extern_block_mask:
+                raise NotImplementedError("block-sparse / variable-length GQA decode is not covered by the native backend yet")
+            self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=Skv)
         elif self.pattern == "mha_decode":
             # A few query rows against a long KV (examples/mha_decode.py; the reference lowers it to a split-KV
             # kernel plus OnlineFunc.combine, lower_decode.py:375-449).  The forward kernel takes any
@@ -138,7 +167,8 @@ class AttentionEngine:
         else:
             raise NotImplementedError(
                 f"pattern {self.pattern!r} (q_len={Sq}, kv_len={Skv}, heads={H}, kv_heads={Hkv}) is not covered by the "
-                "native backend yet: it implements the parallel MHA forward, MHA decode, chunked linear attention and MLA decode")
+                "native backend yet: it implements the parallel MHA / GQA forward, dense MHA / GQA decode, chunked linear "
+                "attention and MLA decode")
 
     # pattern selection by shape, as attn_engine.py:227-343 of the reference
     @staticmethod
@@ -158,7 +188,7 @@ class AttentionEngine:
         if (D, Dv) not in ((64, 64), (128, 128)):
             raise NotImplementedError(f"head dims (qk={D}, v={Dv}) are not covered by the forward kernel yet "
                                       "(supported: 64/64 and 128/128)")
-        self.mask_kind = classify_mask(mask_mod, B, H, S, S if kv_len is None else kv_len)
+        self.mask_kind, self.mask_band = classify_mask(mask_mod, B, H, S, S if kv_len is None else kv_len)
         if kv_len is not None and kv_len != S and self.mask_kind != native.MASK_NONE:
             raise NotImplementedError("decode (q_len != kv_len) supports mask_mod=None or an all-true mask")
         neg_inf_mask = str(mask_value).strip() in ("-inf", "-float('inf')")
@@ -214,7 +244,8 @@ class AttentionEngine:
                     st[ax] = t.stride(dim)
             tensors.append(t)
             strides.append(st)
-        args = native.fill_parallel_args(q, k, v, o, mask_kind=self.mask_kind, functor=native.FUNCTOR_SOFTMAX,
+        args = native.fill_parallel_args(q, k, v, o, mask_kind=self.mask_kind, mask_band=self.mask_band,
+                                         functor=native.FUNCTOR_SOFTMAX,
                                          fparams=self._fparams, final_rowscales=finals, custom=tensors,
                                          custom_strides=strides)
         if self.functor_kind == "builtin_softmax":

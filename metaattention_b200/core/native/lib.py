@@ -37,7 +37,8 @@ ERRORS = {
 }
 
 DTYPE_CODES = {torch.float16: 0, torch.bfloat16: 1}
-MASK_NONE, MASK_CAUSAL = 0, 1
+MASK_NONE, MASK_CAUSAL, MASK_BAND = 0, 1, 2
+MASK_OPEN = 0x3fffffff   # mask_left / mask_right of a band side without a bound
 FUNCTOR_SOFTMAX = 0
 
 
@@ -53,10 +54,11 @@ class ParallelArgs(C.Structure):
         ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3),
         ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
-        ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("functor", C.c_int32), ("reserved", C.c_int32),
+        ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("functor", C.c_int32), ("heads_kv", C.c_int32),
         ("fparams", C.c_float * 8),
         ("custom", C.c_void_p * MAX_CUSTOM),
         ("custom_stride", (C.c_int64 * 4) * MAX_CUSTOM),
+        ("mask_left", C.c_int32), ("mask_right", C.c_int32),
     ]
 
 
@@ -192,7 +194,7 @@ def _strides_bsh(t: torch.Tensor):
 
 
 def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=(), final_rowscales=(),
-                       custom=(), custom_strides=()) -> ParallelArgs:
+                       custom=(), custom_strides=(), mask_band=(MASK_OPEN, MASK_OPEN)) -> ParallelArgs:
     """q,k: [B,S,H,D]; v,o: [B,S,H,Dv] CUDA tensors (any strides with a contiguous last dim)."""
     for t in (q, k, v, o):
         if not t.is_cuda:
@@ -207,12 +209,16 @@ def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=
         a.final_rowscales[i] = t.data_ptr() if t is not None else None
     B, Sq, H, D = q.shape
     a.batch, a.heads, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, Sq, k.shape[1], D, v.shape[3]
+    if k.shape[2] != v.shape[2] or H % k.shape[2] != 0:
+        raise NativeError(f"k and v need the same number of heads, a divisor of the query heads (got {H}, {k.shape[2]}, {v.shape[2]})")
+    a.heads_kv = k.shape[2]
     a.q_stride[:] = _strides_bsh(q)
     a.k_stride[:] = _strides_bsh(k)
     a.v_stride[:] = _strides_bsh(v)
     a.o_stride[:] = _strides_bsh(o)
     a.dtype = DTYPE_CODES[q.dtype]
     a.mask_kind = mask_kind
+    a.mask_left, a.mask_right = int(mask_band[0]), int(mask_band[1])
     a.functor = functor
     for i, f in enumerate(fparams):
         a.fparams[i] = float(f)

@@ -26,6 +26,7 @@
 namespace b200 {
 
 constexpr int kMaxCustom = 4;
+constexpr int kNoBound = 0x3fffffff;   // an open side of the mask band
 constexpr int kMaxRowScales = 4;
 
 struct FunctorArgs {
@@ -53,8 +54,10 @@ struct ParallelParams {
   void* o;
   float* final_out[kMaxRowScales];
   int batch, heads, seq_q, seq_kv;
+  int kv_group;                // query heads per KV head (1 = one KV head per query head)
   long long o_sb, o_ss, o_sh;  // element strides of o
-  int mask_kind;               // 0 none, 1 causal (keep q_idx >= kv_idx)
+  int mask_kind;               // 0 none, 1 causal (keep q_idx >= kv_idx), 2 band
+  int win_left, win_right;     // band: keep kv_idx in [q_idx - win_left, q_idx + win_right]; kNoBound = open side
   CoordOrder oq, ok, ov;
   int* status;
   FunctorArgs fa;
@@ -119,25 +122,35 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int lane = threadIdx.x & 31;
   const AbortState ab{abort_flag, p.status};
 
+  // Every mask is a band kv_idx in [q_idx - left, q_idx + right]: none = open on both sides, causal = open
+  // to the left with right = 0, sliding windows bound the left side as well.
   const bool causal = p.mask_kind == 1;
+  const int left = p.mask_kind == 2 ? p.win_left : kNoBound;
+  const int right = p.mask_kind == 0 ? kNoBound : (p.mask_kind == 1 ? 0 : p.win_right);
+  const bool banded = p.mask_kind != 0;
   // heaviest query tiles (largest KV range under a causal mask) are launched first
   const int m_pair = causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int m0 = m_pair * 2 * BM;
   const int n_kv_tiles = (p.seq_kv + BN - 1) / BN;
-  int n_t[2];
+  // KV tiles [j_lo, j_hi) of each query tile; the CTA walks the union [j_min, j_max)
+  int j_lo[2], j_hi[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int row0 = m0 + t * BM;
-    int n = 0;
+    j_lo[t] = j_hi[t] = 0;
     if (row0 < p.seq_q) {
-      n = n_kv_tiles;
-      if (causal) n = min(n, (row0 + BM + BN - 1) / BN);
+      j_lo[t] = (left >= kNoBound || row0 <= left) ? 0 : (row0 - left) / BN;
+      j_hi[t] = right >= kNoBound ? n_kv_tiles : min(n_kv_tiles, (row0 + BM - 1 + right) / BN + 1);
+      if (j_hi[t] < j_lo[t]) j_hi[t] = j_lo[t];
     }
-    n_t[t] = n;
   }
-  const int n_max = max(n_t[0], n_t[1]);
+  const bool act0 = j_hi[0] > j_lo[0], act1 = j_hi[1] > j_lo[1];
+  const int j_min = act0 ? (act1 ? min(j_lo[0], j_lo[1]) : j_lo[0]) : j_lo[1];
+  const int j_max = max(act0 ? j_hi[0] : 0, act1 ? j_hi[1] : 0);
+  const int n_max = (act0 || act1) ? j_max - j_min : 0;
+  auto active = [&](int t, int j) { return j >= j_lo[t] && j < j_hi[t]; };
 
   // ---------------- setup ----------------
   if (threadIdx.x == 0) {
@@ -173,22 +186,23 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 8) {
     // =============== TMA producer ===============
     if (lane == 0 && n_max > 0 && !*abort_flag) {
-      const int nq = (n_t[1] > 0) ? 2 : 1;
+      const int nq = act1 ? 2 : 1;
       mbar_arrive_expect_tx(q_full, nq * L::kQBytes);
       for (int t = 0; t < nq; ++t)
         for (int c = 0; c < D / 64; ++c)
           tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, q_full, c * 64, m0 + t * BM, h, b, p.oq);
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j % ST;
-        const uint32_t ph = (j / ST) & 1;
+      for (int i = 0; i < n_max; ++i) {
+        const int j = j_min + i;
+        const int st = i % ST;
+        const uint32_t ph = (i / ST) & 1;
         if (!mbar_wait(&k_empty[st], ph ^ 1, ab, kSiteKEmpty)) break;
         mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
         for (int c = 0; c < D / 64; ++c)
-          tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, j * BN, h, b, p.ok);
+          tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, j * BN, h / p.kv_group, b, p.ok);
         if (!mbar_wait(&v_empty[st], ph ^ 1, ab, kSiteVEmpty)) break;
         mbar_arrive_expect_tx(&v_full[st], L::kVBytes);
         for (int c = 0; c < DV / 64; ++c)
-          tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, j * BN, h, b, p.ov);
+          tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, j * BN, h / p.kv_group, b, p.ov);
       }
     }
   } else if (warp == 9) {
@@ -222,26 +236,28 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (ok) {
         tc_fence_after_sync();
         for (int t = 0; t < 2; ++t)
-          if (n_t[t] > 0) issue_qk(t, 0);
+          if (active(t, j_min)) issue_qk(t, 0);
         umma_commit(&k_empty[0]);
-        for (int j = 0; j < n_max && ok; ++j) {
-          const int st = j % ST;
-          const int stn = (j + 1) % ST;
-          ok = mbar_wait(&v_full[st], (j / ST) & 1, ab, kSiteVFull);
-          if (ok && j + 1 < n_max) ok = mbar_wait(&k_full[stn], ((j + 1) / ST) & 1, ab, kSiteKFull);
+        for (int i = 0; i < n_max && ok; ++i) {
+          const int j = j_min + i;
+          const int st = i % ST;
+          const int stn = (i + 1) % ST;
+          ok = mbar_wait(&v_full[st], (i / ST) & 1, ab, kSiteVFull);
+          if (ok && i + 1 < n_max) ok = mbar_wait(&k_full[stn], ((i + 1) / ST) & 1, ab, kSiteKFull);
           if (!ok) break;
           for (int t = 0; t < 2; ++t) {
-            if (j < n_t[t]) {
-              ok = mbar_wait(&p_ready[t], j & 1, ab, kSitePReady);
+            if (active(t, j)) {
+              ok = mbar_wait(&p_ready[t], (j - j_lo[t]) & 1, ab, kSitePReady);
               if (!ok) break;
               tc_fence_after_sync();
-              issue_pv(t, st, j == 0);
-              if (j + 1 < n_t[t]) issue_qk(t, stn);
+              issue_pv(t, st, j == j_lo[t]);
             }
+            // the tile's next scores; also its first ones when its KV range starts later than the other tile's
+            if (active(t, j + 1)) issue_qk(t, stn);
           }
           if (!ok) break;
           umma_commit(&v_empty[st]);
-          if (j + 1 < n_max) umma_commit(&k_empty[stn]);
+          if (i + 1 < n_max) umma_commit(&k_empty[stn]);
         }
       }
     }
@@ -253,12 +269,13 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + kColS + t * BN;
     const uint32_t tO = tmem_base + lane_base + kColO + t * DV;
-    const int n = n_t[t];
+    const int n = j_hi[t] - j_lo[t];
+    const int row0 = m0 + t * BM;
     float rs[F::kRowScales > 0 ? F::kRowScales : 1];
     RowCtx ctx{b, h, q_idx, 0, p.seq_q, p.seq_kv, &p.fa};
     F::init(rs, ctx);
     bool ok = (n > 0) && !*abort_flag;
-    for (int j = 0; j < n && ok; ++j) {
+    for (int j = 0; j < n && ok; ++j) {   // j counts this query tile's own KV tiles
       ok = mbar_wait(&s_full[t], j & 1, ab, kSiteSFull);
       if (!ok) break;
       tc_fence_after_sync();
@@ -266,16 +283,19 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld32f(tS + c * 32, &s[c * 32]);
       tmem_wait_ld();
-      const int kv0 = j * BN;
+      const int kv0 = (j_lo[t] + j) * BN;
       ctx.kv0 = kv0;
-      // a tile needs element masking when it crosses the causal diagonal or the end of the KV sequence
-      const bool crosses = (causal && (kv0 + BN - 1 > m0 + t * BM)) || (kv0 + BN > p.seq_kv);
+      // a tile needs element masking when it crosses an edge of the mask band or the end of the KV sequence
+      const bool crosses = (banded && ((right < kNoBound && kv0 + BN - 1 > row0 + right) ||
+                                       (left < kNoBound && kv0 < row0 + BM - 1 - left))) || (kv0 + BN > p.seq_kv);
       if (crosses) {
         if (F::kNegInfMask) {
+          const int kv_first = left < kNoBound ? q_idx - left : -kNoBound;
+          const int kv_last = right < kNoBound ? min(q_idx + right, p.seq_kv - 1) : p.seq_kv - 1;
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
             const int kv = kv0 + i;
-            const bool keep = (kv < p.seq_kv) && (!causal || kv <= q_idx);
+            const bool keep = (kv >= kv_first) && (kv <= kv_last);
             s[i] = keep ? s[i] : -INFINITY;
           }
         }

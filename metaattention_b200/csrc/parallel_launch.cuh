@@ -75,11 +75,14 @@ inline int validate_parallel_args(const AttnB200ParallelArgs* a) {
   if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr) return ATTN_B200_E_INVALID_ARG;
   if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0) return ATTN_B200_E_INVALID_ARG;
   if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
-  if (a->mask_kind != ATTN_B200_MASK_NONE && a->mask_kind != ATTN_B200_MASK_CAUSAL) return ATTN_B200_E_INVALID_ARG;
+  if (a->mask_kind != ATTN_B200_MASK_NONE && a->mask_kind != ATTN_B200_MASK_CAUSAL && a->mask_kind != ATTN_B200_MASK_BAND)
+    return ATTN_B200_E_INVALID_ARG;
+  if (a->mask_kind == ATTN_B200_MASK_BAND && (a->mask_left < 0 || a->mask_right < 0)) return ATTN_B200_E_INVALID_ARG;
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
   for (int i = 0; i < 3; ++i)
     if (a->o_stride[i] % 8 != 0) return ATTN_B200_E_UNSUPPORTED;
   if (a->heads > 65535 || a->batch > 65535) return ATTN_B200_E_UNSUPPORTED;
+  if (a->heads_kv < 0 || (a->heads_kv > 0 && a->heads % a->heads_kv != 0)) return ATTN_B200_E_INVALID_ARG;
   return ATTN_B200_OK;
 }
 
@@ -93,20 +96,24 @@ int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* dev
   std::memset(&p, 0, sizeof(p));
   int rc = encode_rows_map(&tmQ, &p.oq, a->q, a->dtype, D, a->batch, a->seq_q, a->heads, a->q_stride, L::kBM);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_rows_map(&tmK, &p.ok, a->k, a->dtype, D, a->batch, a->seq_kv, a->heads, a->k_stride, L::kBN);
+  const int heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;
+  rc = encode_rows_map(&tmK, &p.ok, a->k, a->dtype, D, a->batch, a->seq_kv, heads_kv, a->k_stride, L::kBN);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_rows_map(&tmV, &p.ov, a->v, a->dtype, DV, a->batch, a->seq_kv, a->heads, a->v_stride, L::kBN);
+  rc = encode_rows_map(&tmV, &p.ov, a->v, a->dtype, DV, a->batch, a->seq_kv, heads_kv, a->v_stride, L::kBN);
   if (rc != ATTN_B200_OK) return rc;
   p.o = a->o;
   for (int i = 0; i < kMaxRowScales; ++i) p.final_out[i] = a->final_rowscales[i];
   p.batch = a->batch;
   p.heads = a->heads;
+  p.kv_group = a->heads / heads_kv;
   p.seq_q = a->seq_q;
   p.seq_kv = a->seq_kv;
   p.o_sb = a->o_stride[0];
   p.o_ss = a->o_stride[1];
   p.o_sh = a->o_stride[2];
   p.mask_kind = a->mask_kind;
+  p.win_left = a->mask_left > kNoBound ? kNoBound : a->mask_left;
+  p.win_right = a->mask_right > kNoBound ? kNoBound : a->mask_right;
   p.status = device_status;
   for (int i = 0; i < 8; ++i) p.fa.f[i] = a->fparams[i];
   for (int i = 0; i < kMaxCustom; ++i) {

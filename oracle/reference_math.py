@@ -26,9 +26,11 @@ def _causal_keep(q_len: int, kv_len: int) -> torch.Tensor:
     return torch.ones(q_len, kv_len, dtype=torch.bool).tril()
 
 
-def softmax_attention(q, k, v, causal: bool = True, softmax_scale: float | None = None):
+def softmax_attention(q, k, v, causal: bool = True, softmax_scale: float | None = None, keep=None):
     """testing/test.py:79-104.  q,k: [B,S,H,D], v: [B,S,Hkv,Dv] with H a multiple of
-    Hkv; returns [B,S,H,Dv] fp32.  The mask is applied before the scale."""
+    Hkv; returns [B,S,H,Dv] fp32.  The mask is applied before the scale.  ``keep`` (bool
+    [q_len, kv_len]) replaces the causal mask by an arbitrary one (the reference closure masks with
+    -inf the same way, testing/test.py:93-97)."""
     q, k, v = q.float(), k.float(), v.float()
     B, Sq, H, D = q.shape
     Hkv = k.shape[2]
@@ -37,7 +39,9 @@ def softmax_attention(q, k, v, causal: bool = True, softmax_scale: float | None 
     # query head (h*g + j) uses kv head h
     qg = q.view(B, Sq, Hkv, g, D)
     s = torch.einsum("bshgd,bthd->bhgst", qg, k)
-    if causal:
+    if keep is not None:
+        s = s.masked_fill(~keep, float("-inf"))
+    elif causal:
         s = s.masked_fill(~_causal_keep(Sq, k.shape[1]), float("-inf"))
     p = torch.softmax(s * scale, dim=-1)
     o = torch.einsum("bhgst,bthd->bshgd", p, v)

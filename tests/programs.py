@@ -180,3 +180,28 @@ def softmax_decode_engine(B, H, Sq, Skv, D, Dv, dtype=torch.bfloat16):
     meta = (meta_tensor(B, H, ((Sq + 127) // 128) * 128, D, dtype=dtype), meta_tensor(B, H, Skv, D, dtype=dtype),
             meta_tensor(B, H, Skv, Dv, dtype=dtype))
     return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=NaturalSoftmax())
+
+
+def gqa_engine(B, H, Hkv, Sq, Skv, D, Dv, dtype=torch.bfloat16, is_causal=False):
+    """Grouped KV heads: H query heads share Hkv KV heads (prefill when Sq == Skv, dense decode otherwise)."""
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    meta = (meta_tensor(B, H, Sq, D, dtype=dtype), meta_tensor(B, Hkv, Skv, D, dtype=dtype), meta_tensor(B, Hkv, Skv, Dv, dtype=dtype))
+    return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=causal if is_causal else None,
+                           online_func=NaturalSoftmax())
+
+
+def sliding_window_mask(b, h, q_idx, kv_idx):
+    """the mask of the reference's tracing test (attention_engine/tests/test_torchtrace.py:5-6)"""
+    return torch.logical_and(q_idx >= kv_idx, q_idx < kv_idx + 128)
+
+
+def masked_softmax_engine(B, H, S, D, Dv, mask_mod, dtype=torch.bfloat16):
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({}), score_mod=score_mod, mask_mod=mask_mod,
+                           online_func=NaturalSoftmax())

@@ -28,10 +28,31 @@ def test_binding_covers_header():
     assert set(declared_functions()) <= set(lib.SIGNATURES), "ctypes binding misses a declared entry point"
 
 
-def test_struct_sizes_match_header(native_lib):
-    # layout cross-check of the ctypes mirrors against sizeof() computed from the field list
-    assert ctypes.sizeof(lib.ParallelArgs) == 8 * 4 + 8 * 4 + 4 * 6 + 8 * 12 + 4 * 4 + 4 * 8 + 8 * 4 + 8 * 16
-    assert ctypes.sizeof(lib.MlaShape) == 20
+def test_struct_layouts_match_header(tmp_path):
+    """sizeof / offsetof of every argument struct as the C compiler sees the header, against the ctypes mirrors"""
+    import subprocess
+    probes = {
+        "AttnB200ParallelArgs": (lib.ParallelArgs, ["o", "seq_kv", "o_stride", "heads_kv", "fparams", "custom_stride", "mask_left", "mask_right"]),
+        "AttnB200LinearArgs": (lib.LinearArgs, ["log_decay", "dim_v", "normalize", "q_scale", "workspace", "workspace_bytes"]),
+        "AttnB200MlaShape": (lib.MlaShape, ["dim_v"]),
+        "AttnB200MlaArgs": (lib.MlaArgs, ["kv_rope", "o", "workspace_bytes", "shape", "scale", "seq_lens", "block_table",
+                                          "block_table_stride", "page_size", "num_pages"]),
+    }
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "attn_b200.h"', "int main(void) {"]
+    for name, (_, fields) in probes.items():
+        lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
+        for f in fields:
+            lines.append(f'  printf("{name}.{f} %zu\\n", offsetof({name}, {f}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "probe.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "probe"
+    subprocess.run(["gcc", "-I", os.path.dirname(HEADER), "-o", str(exe), str(src)], check=True)
+    seen = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for name, (mirror, fields) in probes.items():
+        assert int(seen[name]) == ctypes.sizeof(mirror), name
+        for f in fields:
+            assert int(seen[f"{name}.{f}"]) == getattr(mirror, f).offset, f"{name}.{f}"
 
 
 def test_version(native_lib):

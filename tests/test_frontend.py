@@ -61,10 +61,14 @@ def test_pattern_selection_follows_reference_rules():
 
 
 def test_unsupported_patterns_raise_clearly():
+    meta = (meta_tensor(1, 6, 1, 128, dtype=torch.float16), meta_tensor(1, 4, 4096, 128, dtype=torch.float16),
+            meta_tensor(1, 4, 4096, 128, dtype=torch.float16))
+    with pytest.raises(NotImplementedError, match="multiple of KV heads"):
+        AttentionEngine(meta, CustomIO({}), None, None, None)
     meta = (meta_tensor(1, 16, 1, 128, dtype=torch.float16), meta_tensor(1, 4, 4096, 128, dtype=torch.float16),
             meta_tensor(1, 4, 4096, 128, dtype=torch.float16))
-    with pytest.raises(NotImplementedError, match="gqa_decode"):
-        AttentionEngine(meta, CustomIO({}), None, None, None)
+    with pytest.raises(NotImplementedError, match="variable-length"):
+        AttentionEngine(meta, CustomIO({}), None, None, None, use_varlen=True)
     with pytest.raises(TypeError):
         AttentionEngine(programs._meta(1, 2, 128, 64, 64, torch.float32), CustomIO({}), None, None, None)
 
@@ -149,3 +153,17 @@ def test_reference_examples_construct_unchanged():
         assert e.custom_names == ["A", "dt"] and e.H == 8 and e.HK == 1
     finally:
         sys.path.remove("/root/reference")
+
+
+def test_band_masks_are_recognised():
+    from attn_engine.attn_engine import classify_mask
+    from core.native import lib as native
+    assert classify_mask(programs.sliding_window_mask, 1, 2, 512, 512) == (native.MASK_BAND, (127, 0))
+    assert classify_mask(lambda b, h, q, kv: (kv - q <= 40) & (q - kv <= 70), 1, 1, 300, 300) == (native.MASK_BAND, (70, 40))
+    assert classify_mask(lambda b, h, q, kv: kv <= q + 5, 1, 1, 200, 200) == (native.MASK_BAND, (native.MASK_OPEN, 5))
+    assert classify_mask(programs.causal, 1, 1, 256, 256)[0] == native.MASK_CAUSAL
+    assert classify_mask(lambda b, h, q, kv: q >= 0, 1, 1, 128, 128)[0] == native.MASK_NONE
+    with pytest.raises(NotImplementedError):
+        classify_mask(lambda b, h, q, kv: (q + kv) % 2 == 0, 1, 1, 128, 128)   # not a band
+    with pytest.raises(NotImplementedError):
+        classify_mask(lambda b, h, q, kv: (kv <= q) & (h >= 0) & (b == 0), 2, 1, 128, 128)   # depends on the batch index

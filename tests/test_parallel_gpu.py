@@ -12,6 +12,7 @@ import pytest
 import torch
 
 import programs
+from core.native import lib as native_lib
 from oracle import inputs, reference_math as rm
 
 pytestmark = pytest.mark.gpu
@@ -217,3 +218,47 @@ def test_mha_decode_pattern(B, H, Sq, Skv, D):
     o = e(q.cuda(), k.cuda(), v.cuda())
     assert o.shape == (B, Sq, H, D)
     check(o, rm.softmax_attention(q, k, v, causal=False, softmax_scale=D ** -0.5))
+
+
+@pytest.mark.parametrize("B,H,Hkv,Sq,Skv,D,is_causal", [
+    (1, 8, 2, 512, 512, 128, True),      # GQA prefill, causal
+    (2, 6, 3, 300, 300, 64, False),      # ragged, non-causal
+    (2, 16, 4, 1, 2048, 128, False),     # dense GQA decode
+])
+def test_grouped_kv_heads(B, H, Hkv, Sq, Skv, D, is_causal):
+    """query head h reads KV head h // (H / Hkv) (the reference's GQA templates, attn_gqa_tl.py)"""
+    g = torch.Generator().manual_seed(1300 + Skv + H)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Skv, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Skv, Hkv, D, generator=g).to(torch.bfloat16)
+    e = programs.gqa_engine(B, H, Hkv, Sq, Skv, D, D, is_causal=is_causal)
+    assert e.pattern == ("gqa" if Sq == Skv else "gqa_decode")
+    o = e(q.cuda(), k.cuda(), v.cuda())
+    rep = H // Hkv
+    want = rm.softmax_attention(q, k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2), causal=is_causal,
+                                softmax_scale=D ** -0.5)
+    check(o, want)
+
+
+@pytest.mark.parametrize("name,S,D", [("sliding128", 700, 128), ("two_sided", 1000, 64), ("right_open", 400, 128), ("wide_window", 2048, 128)])
+def test_band_masks(name, S, D):
+    """sliding-window and other band masks: KV tiles outside the band are skipped, tiles crossing an edge
+    are masked element by element"""
+    masks = {
+        "sliding128": programs.sliding_window_mask,
+        "two_sided": lambda b, h, q, kv: (kv - q <= 40) & (q - kv <= 300),
+        "right_open": lambda b, h, q, kv: q - kv <= 17,
+        "wide_window": lambda b, h, q, kv: (q >= kv) & (q - kv < 1000),
+    }
+    B, H = 2, 3
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 1500 + S)
+    e = programs.masked_softmax_engine(B, H, S, D, D, masks[name])
+    assert e.mask_kind == native_lib.MASK_BAND
+    o = e(q.cuda(), k.cuda(), v.cuda())
+    qi, ki = torch.arange(S).view(-1, 1), torch.arange(S).view(1, -1)
+    keep = masks[name](0, 0, qi, ki)
+    check(o, rm.softmax_attention(q, k, v, softmax_scale=D ** -0.5, keep=keep))
+    lse = e.last_final_rowscales["lse"].cpu()
+    s = torch.einsum("bshd,bthd->bhst", q.float(), k.float()) * D ** -0.5
+    want_lse = torch.logsumexp(s.masked_fill(~keep, float("-inf")), dim=-1)
+    assert (lse - want_lse).abs().max().item() <= 2e-3
