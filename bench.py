@@ -191,6 +191,15 @@ def extras_parallel(steps, warmup):
         ms = time_device(lambda: eng(q, k, v, bias), steps, warmup, lambda: None) / steps
         fl = c2_flops(causal=False)
         out["C3_sigmoid_noncausal"] = {"ms": ms, "tflops": fl / ms / 1e9}
+        # the C2 shape under a causal sliding window of 1024 tokens (band mask: KV tiles outside the window are
+        # skipped); FLOPs counted over the kept (q, kv) pairs
+        import programs
+        W = 1024
+        S, B, H, D, Dv = C3["S"], C3["B"], C3["H"], C3["D"], C3["Dv"]
+        eng_w = programs.masked_softmax_engine(B, H, S, D, Dv, lambda b, h, qi, ki: (qi >= ki) & (qi - ki < W))
+        ms_w = time_device(lambda: eng_w(q, k, v), steps, warmup, lambda: None) / steps
+        pairs = sum(min(i + 1, W) for i in range(S))
+        out["C2_shape_sliding_window_1024"] = {"ms": ms_w, "tflops": 2.0 * B * H * pairs * (D + Dv) / ms_w / 1e9}
         del q, k, v
     except Exception as exc:  # a missing extra must not take the headline number down
         out["C3_sigmoid_noncausal"] = {"error": repr(exc)[:200]}
