@@ -15,6 +15,7 @@ is the CPU oracle on a bounded sample; `extras` holds the other BASELINE configs
 """
 
 import argparse
+import datetime
 import json
 import math
 import os
@@ -61,14 +62,17 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi.  The process is started ahead of the warm-up
+    (its first line takes a while); every line carries nvidia-smi's own timestamp and only the lines stamped
+    inside the window [mark_begin, mark_end] are used."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.proc = None
         self.gpu = gpu_index
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
@@ -78,10 +82,16 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = datetime.datetime.now()
+
+    def mark_end(self):
+        self.t1 = datetime.datetime.now()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -92,20 +102,23 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                clock, clock_max = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for n, val in zip(names, parts[2:6]):
+            if self.t0 is not None and not (self.t0 <= stamp <= self.t1):
+                continue
+            sm.append(clock)
+            mx.append(clock_max)
+            for n, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(n)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [x for x in sm if x > 0.5 * max(sm)] or sm
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def build_softmax_engine():
@@ -337,11 +350,12 @@ def main():
 
     # ---- device-resident timing ----
     sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         eng(dq, dk, dv)
     barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.mark_begin()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -349,9 +363,19 @@ def main():
         eng(dq, dk, dv)
     e1.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
-    barrier()
     ms_total = e0.elapsed_time(e1)
+    # A short timed region can fall between two nvidia-smi samples: the same launches keep running (untimed)
+    # until the sampled window is at least 0.3 s long, so that the clocks are those of this kernel under load.
+    hold_launches = 0
+    t_hold = time.time()
+    while ms_total * 1e-3 + (time.time() - t_hold) < 0.3:
+        eng(dq, dk, dv)
+        torch.cuda.synchronize()
+        hold_launches += 1
+    sampler.mark_end()
+    clocks = sampler.stop()
+    clocks["window"] = "timed region" if hold_launches == 0 else f"timed region + {hold_launches} more launches of the same kernel"
+    barrier()
     status = lib.last_device_status()
     if status != 0:
         raise SystemExit(f"device status {status}: a kernel wait timed out")
