@@ -191,26 +191,51 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       load_q(0);
       load_k(0);
       load_v(0);
-      bool alive = mbar_wait(q_full, 0, ab, kLinQFull) && mbar_wait(k_full, 0, ab, kLinKFull);
-      if (alive) {
-        tc_fence_after_sync();
-        issue_scores();
-      }
+      bool alive = true;
+      bool s_pending = true;   // the scores of the coming block have not been issued yet
+      // a bounded poll step shared by the loops that serve several barriers at once
+      auto poll_alive = [&](uint32_t& spins, long long t0, int site) {
+        if ((++spins & 0xff) == 0) {
+          if (*abort_flag) return false;
+          if (clock64() - t0 > kWaitCycleLimit) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, kStatusTimeoutBase + site);
+            return false;
+          }
+        }
+        return true;
+      };
       for (int t = 0; alive && t < nblk; ++t) {
         const bool last = (t + 1 == nblk);
         const uint32_t par = t & 1, par_prev = (t - 1) & 1;
-        if (t > 0) {
-          // O = Q h needs the 16-bit copy of the state written by the conversion pass of the previous block
-          if (!mbar_wait(conv_done, par_prev, ab, kLinConvDone)) break;
-          tc_fence_after_sync();
+        // S = Q K^T (needs the loads) and, after the first block, O = Q h (needs the 16-bit copy of the state
+        // written by the conversion pass of the previous block): whichever can go first goes first
+        {
+          bool need_s = s_pending, need_qh = t > 0;
+          const long long t0 = clock64();
+          uint32_t spins = 0;
+          while (need_s || need_qh) {
+            if (need_s && mbar_test(q_full, par) && mbar_test(k_full, par)) {
+              tc_fence_after_sync();
+              issue_scores();
+              need_s = false;
+            }
+            if (need_qh && mbar_test(conv_done, par_prev)) {
+              tc_fence_after_sync();
 #pragma unroll
-          for (int ch = 0; ch < KC; ++ch)
-            umma_ss_x4<2, 2>(tmem_base + kColO, q_desc0 + ch * kChunk, h_desc0 + ch * kChunk, idesc_qh, ch > 0 ? 1u : 0u);
-          umma_commit(qh_bar);
-          if (!mbar_wait(qh_bar, par_prev, ab, kLinQh)) break;
-        } else {
-          if (!mbar_wait(s_bar, par, ab, kLinScore)) break;
+              for (int ch = 0; ch < KC; ++ch)
+                umma_ss_x4<2, 2>(tmem_base + kColO, q_desc0 + ch * kChunk, h_desc0 + ch * kChunk, idesc_qh, ch > 0 ? 1u : 0u);
+              umma_commit(qh_bar);
+              need_qh = false;
+            }
+            if (!(alive = poll_alive(spins, t0, kLinConvDone))) break;
+          }
+          if (!alive) break;
+          s_pending = true;
         }
+        // Q may be replaced once both have run
+        if (!mbar_wait(s_bar, par, ab, kLinScore)) break;
+        if (t > 0 && !mbar_wait(qh_bar, par_prev, ab, kLinQh)) break;
         if (!last) load_q(t + 1);  // Q is no longer read by any MMA of this block
         if (!last) {
           // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step
@@ -241,7 +266,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         bool need_v = !last, need_s = !last, need_store = true;
         const long long t0 = clock64();
         uint32_t spins = 0;
-        while (need_v || need_s || need_store) {
+        while (need_v || need_store) {   // the scores are issued here only if their loads are already there
           if (need_v && mbar_test(pv_bar, par)) {
             load_v(t + 1);  // V was read by the row threads (before v_ready) and by P V
             need_v = false;
@@ -261,16 +286,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             issue_scores();
             need_s = false;
           }
-          if ((++spins & 0xff) == 0) {
-            if (*abort_flag) alive = false;
-            else if (clock64() - t0 > kWaitCycleLimit) {
-              *abort_flag = 1;
-              atomicCAS(p.status, 0, kStatusTimeoutBase + kLinOStaged);
-              alive = false;
-            }
-            if (!alive) break;
-          }
+          if (!(alive = poll_alive(spins, t0, kLinOStaged))) break;
         }
+        s_pending = need_s;
       }
       tma_store_wait_all();
     }
