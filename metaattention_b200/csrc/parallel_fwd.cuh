@@ -19,6 +19,10 @@
 // The two query tiles ping-pong: while the functor stage of one tile runs on
 // the CUDA cores, the tensor pipe works on the other tile.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+DV) O1 [256+DV,256+2DV).
+// Masks are bands kv_idx in [q_idx - left, q_idx + right] (none / causal / explicit bounds): a query tile
+// walks only the KV tiles its band touches, the CTA loads the union of its two tiles' ranges, and tiles
+// that cross an edge of the band are masked element by element.  K/V heads may be shared by groups of
+// query heads (kv_group).  The same kernel serves q_len != kv_len (decode patterns).
 #pragma once
 
 #include "sm100.cuh"

@@ -1,0 +1,99 @@
+"""Seeded random sweep over shapes, dtypes, masks and head layouts of the three kernel families against
+the CPU oracle (same tolerances as the targeted tests).  Cheap cases only: the whole sweep runs in seconds."""
+
+import random
+
+import pytest
+import torch
+
+import programs
+from attn_engine import AttentionEngine
+from attn_engine.linear_attn_engine import linear_attention_forward
+from attn_engine.mla import mla_decode_forward
+from core import CustomIO, meta_tensor
+from core.native import lib
+from oracle import reference_math as rm
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(kind, cfg, o, want, max_abs=2e-2, mean_abs=2e-3, rel=None):
+    assert lib.last_device_status() == 0, (kind, cfg)
+    o = o.float().cpu()
+    assert torch.isfinite(o).all(), (kind, cfg)
+    if rel is None:
+        d = (o - want.float()).abs()
+        assert d.max().item() <= max_abs and d.mean().item() <= mean_abs, (kind, cfg, d.max().item(), d.mean().item())
+    else:
+        assert ((o - want).norm() / want.norm()).item() <= rel, (kind, cfg)
+
+
+def _attention_case(rnd, g, kind):
+    D = rnd.choice([64, 128])
+    dt = rnd.choice([torch.bfloat16, torch.float16])
+    B, Hkv = rnd.randint(1, 3), rnd.randint(1, 4)
+    H = Hkv * (rnd.choice([1, 1, 2, 4]) if kind in ("gqa", "decode") else 1)
+    Skv = rnd.choice([1, 63, 128, 129, 255, 256, 257, 500, 1000, 1537])
+    Sq = Skv if kind != "decode" else rnd.choice([1, 2, 17, 128, 300])
+    q = torch.randn(B, Sq, H, D, generator=g).to(dt)
+    k = torch.randn(B, Skv, Hkv, D, generator=g).to(dt)
+    v = torch.randn(B, Skv, Hkv, D, generator=g).to(dt)
+    qi, ki = torch.arange(Sq).view(-1, 1), torch.arange(Skv).view(1, -1)
+    if kind == "band":
+        left, right = rnd.choice([0, 1, 5, 64, 127, 128, 200, 10 ** 9]), rnd.choice([0, 0, 3, 100, 10 ** 9])
+        mask_mod = lambda b, h, qq, kk: (qq - kk <= left) & (kk - qq <= right)   # noqa: E731
+        keep = mask_mod(0, 0, qi, ki)
+    elif kind == "decode" or rnd.random() < 0.5:
+        mask_mod, keep = None, torch.ones(Sq, Skv, dtype=torch.bool)
+    else:
+        mask_mod, keep = programs.causal, ki <= qi
+    scale = D ** -0.5
+    meta = (meta_tensor(B, H, Sq, D, dtype=dt), meta_tensor(B, Hkv, Skv, D, dtype=dt), meta_tensor(B, Hkv, Skv, D, dtype=dt))
+    e = AttentionEngine(meta, CustomIO({}), score_mod=lambda s, c, b, h, qq, kk: s * scale, mask_mod=mask_mod,
+                        online_func=programs.NaturalSoftmax())
+    o = e(q.cuda(), k.cuda(), v.cuda())
+    _close(kind, (B, H, Hkv, Sq, Skv, D, dt), o, rm.softmax_attention(q, k, v, softmax_scale=scale, keep=keep))
+
+
+def _mla_case(rnd, g):
+    B, H = rnd.randint(1, 5), rnd.choice([16, 64, 128, 256])
+    S = rnd.choice([1, 64, 129, 500, 1024, 3000])
+    dt = rnd.choice([torch.bfloat16, torch.float16])
+    splits = rnd.choice([None, 1, 2, 3])
+    if splits and splits > 1 and (S + 127) // 128 < 4 * splits:
+        splits = 1
+    q = torch.randn(B, 1, H, 576, generator=g).to(dt)
+    kv = torch.randn(B, S, 1, 576, generator=g).to(dt)
+    lens = [rnd.randint(1, S) for _ in range(B)] if rnd.random() < 0.5 else None
+    o, _ = mla_decode_forward(q.cuda(), kv.cuda(), 512, 576 ** -0.5, num_splits=splits,
+                              cache_seqlens=None if lens is None else torch.tensor(lens, dtype=torch.int32, device="cuda"))
+    want = torch.cat([rm.mla_decode(q[b:b + 1, ..., :512], q[b:b + 1, ..., 512:], kv[b:b + 1, :(S if lens is None else lens[b]), :, :512],
+                                    kv[b:b + 1, :(S if lens is None else lens[b]), :, 512:]) for b in range(B)])
+    _close("mla", (B, H, S, dt, splits, lens), o.reshape(B, 1, H, 512), want)
+
+
+def _linear_case(rnd, g):
+    B, H = rnd.randint(1, 2), rnd.randint(1, 4)
+    S = rnd.choice([1, 100, 128, 129, 400, 1000])
+    Dk, Dv = rnd.choice([64, 128, 256]), rnd.choice([64, 128, 256, 384])
+    dt = rnd.choice([torch.bfloat16, torch.float16])
+    q = torch.randn(B, H, S, Dk, generator=g).to(dt)
+    k = (torch.randn(B, H, S, Dk, generator=g) * Dk ** -0.5).to(dt)
+    v = torch.randn(B, H, S, Dv, generator=g).to(dt)
+    log_decay = -torch.rand(B, H, S, generator=g) * rnd.choice([0.01, 0.1, 1.0, 4.0])
+    o = linear_attention_forward(q.cuda(), k.cuda(), v.cuda(), log_decay.cuda(), q_scale=Dk ** -0.5)
+    _close("linear", (B, H, S, Dk, Dv, dt), o, rm.decayed_linear_attention(q, k, v, log_decay, scale=Dk ** -0.5), rel=1e-2)
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_sweep(seed):
+    rnd = random.Random(seed)
+    for _ in range(25):
+        kind = rnd.choice(["softmax", "softmax", "band", "gqa", "decode", "mla", "linear"])
+        g = torch.Generator().manual_seed(rnd.randrange(1 << 30))
+        if kind == "mla":
+            _mla_case(rnd, g)
+        elif kind == "linear":
+            _linear_case(rnd, g)
+        else:
+            _attention_case(rnd, g, kind)
