@@ -72,7 +72,7 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.proc = None
         self.gpu = gpu_index
-        self.t0 = self.t1 = None
+        self.t0 = self.t1 = self.t_timed = None
 
     def start(self):
         try:
@@ -84,6 +84,9 @@ class ClockSampler:
 
     def mark_begin(self):
         self.t0 = datetime.datetime.now()
+
+    def mark_timed_end(self):
+        self.t_timed = datetime.datetime.now()
 
     def mark_end(self):
         self.t1 = datetime.datetime.now()
@@ -98,7 +101,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, sm_timed = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
@@ -113,12 +116,18 @@ class ClockSampler:
                 continue
             sm.append(clock)
             mx.append(clock_max)
+            if self.t_timed is not None and stamp <= self.t_timed:
+                sm_timed.append(clock)
             for n, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(n)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if sm_timed:   # the samples that fell inside the timed region itself
+            out["sm_mhz_timed_region"] = statistics.median(sm_timed)
+            out["samples_timed_region"] = len(sm_timed)
+        return out
 
 
 def build_softmax_engine():
@@ -363,6 +372,7 @@ def main():
         eng(dq, dk, dv)
     e1.record()
     torch.cuda.synchronize()
+    sampler.mark_timed_end()
     ms_total = e0.elapsed_time(e1)
     # A short timed region can fall between two nvidia-smi samples: the same launches keep running (untimed)
     # until the sampled window is at least 0.3 s long, so that the clocks are those of this kernel under load.
