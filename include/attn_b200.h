@@ -76,12 +76,23 @@ typedef struct AttnB200ParallelArgs {
   int64_t custom_stride[ATTN_B200_MAX_CUSTOM][4];    /* element strides of (batch, heads, seq_len, seq_len_kv); 0 = broadcast */
   int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only: tokens kept before / after the diagonal, >= 0 or
                                       ATTN_B200_MASK_OPEN; KV tiles outside the band are skipped */
+  /* Split-KV (decode with few query rows and heads; the reference's split kernel + OnlineFunc.combine,
+   * core/lower/lower_decode.py:287-302,375-449): 0 or 1 = off.  With num_splits > 1 the KV tiles are divided
+   * among num_splits CTAs per (query tile pair, head, batch) and a second kernel combines their results through
+   * the log-sum-exp; only ATTN_B200_FUNCTOR_SOFTMAX of attn_b200_parallel_fwd supports it. */
+  int32_t num_splits;
+  int32_t reserved;
+  void* workspace;                 /* attn_b200_parallel_workspace_bytes() bytes of device scratch, or NULL */
+  int64_t workspace_bytes;
 } AttnB200ParallelArgs;
 
 /* Replaces the generated TileLang forward kernel and its launcher
  * (attention_engine/core/template/tl_template/attn/attn_tl.py:93-190, :656-667)
  * and the CuTe forward (core/template/cute_template/flash_api.cpp:283-460). */
 int attn_b200_parallel_fwd(const AttnB200ParallelArgs* args, void* cuda_stream);
+
+/* Bytes of scratch attn_b200_parallel_fwd needs for args->num_splits (0 without split-KV; -1 = bad arguments). */
+int64_t attn_b200_parallel_workspace_bytes(const AttnB200ParallelArgs* args);
 
 /* Arguments of the chunked linear-attention / retention forward
  *   h_{c+1} = h_c * exp(g_last) + (K * exp(g_last - g))^T V

@@ -84,6 +84,18 @@ class _ForwardOnly(torch.autograd.Function):
         raise NotImplementedError("the B200-native backend implements the forward pass only")
 
 
+def plan_kv_splits(batch: int, heads: int, q_len: int, kv_len: int, device) -> int:
+    """KV splits for the forward kernel: 1 unless the (query tile pair, head, batch) grid fills less than half of
+    the SMs; then as many as fit, each keeping at least four 128-row KV tiles (a split re-reads Q and adds a
+    combine pass)."""
+    ctas = batch * heads * ((q_len + 255) // 256)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    kv_tiles = (kv_len + 127) // 128
+    if 2 * ctas > sms or kv_tiles < 8:
+        return 1
+    return max(1, min(sms // ctas, kv_tiles // 4, 65535 // max(batch, 1)))
+
+
 def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int):
     """(mask kind, (left, right)) for a ``mask_mod(b, h, q_idx, kv_idx)``: MASK_NONE, MASK_CAUSAL, or
     MASK_BAND = keep q_idx - left <= kv_idx <= q_idx + right (sliding windows; MASK_OPEN = no bound on
@@ -132,6 +144,7 @@ class AttentionEngine:
         self.backend = backend          # accepted for source compatibility; every value runs the native kernels
         self.use_varlen = use_varlen
         self.block_mask = None
+        self.kv_splits = None      # None = planned per call (plan_kv_splits); an int forces the split count
         self.qkv_meta = qkv_meta
         self.custom_fwd_inputs = custom_fwd_inputs if custom_fwd_inputs is not None else CustomIO()
         self.last_final_rowscales: dict[str, torch.Tensor] = {}
@@ -244,8 +257,15 @@ class AttentionEngine:
                     st[ax] = t.stride(dim)
             tensors.append(t)
             strides.append(st)
+        # split-KV when the launch would leave most SMs idle (decode: few query rows and heads against a long KV);
+        # the split results are combined through the log-sum-exp, which only the built-in softmax provides
+        splits, workspace = 1, None
+        if self.functor_kind == "builtin_softmax":
+            splits = self.kv_splits if self.kv_splits is not None else plan_kv_splits(B, H, S, k.shape[1], q.device)
+            if splits > 1:
+                workspace = torch.empty(B * splits * H * S * (Dv + 1) * 4, dtype=torch.uint8, device=q.device)
         args = native.fill_parallel_args(q, k, v, o, mask_kind=self.mask_kind, mask_band=self.mask_band,
-                                         functor=native.FUNCTOR_SOFTMAX,
+                                         num_splits=splits, workspace=workspace, functor=native.FUNCTOR_SOFTMAX,
                                          fparams=self._fparams, final_rowscales=finals, custom=tensors,
                                          custom_strides=strides)
         if self.functor_kind == "builtin_softmax":

@@ -468,6 +468,7 @@ extern "C" int attn_b200_parallel_fwd_jit(const AttnB200ParallelArgs* args, void
   const int rc = b200::validate_parallel_args(args);
   if (rc != ATTN_B200_OK) return rc;
   if (args->dtype != {1 if bf16 else 0}) return ATTN_B200_E_UNSUPPORTED;
+  if (args->num_splits > 1) return ATTN_B200_E_UNSUPPORTED;  // split-KV combines through the built-in softmax's log-sum-exp
   return b200::launch_parallel<{fs.struct_name}, {dim_qk}, {dim_v}, {'true' if bf16 else 'false'}>(
       args, static_cast<cudaStream_t>(cuda_stream), device_status);
 }}

@@ -59,6 +59,7 @@ class ParallelArgs(C.Structure):
         ("custom", C.c_void_p * MAX_CUSTOM),
         ("custom_stride", (C.c_int64 * 4) * MAX_CUSTOM),
         ("mask_left", C.c_int32), ("mask_right", C.c_int32),
+        ("num_splits", C.c_int32), ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -92,6 +93,7 @@ class MlaArgs(C.Structure):
 # symbol name -> (restype, argtypes); must list every function of include/attn_b200.h
 SIGNATURES = {
     "attn_b200_parallel_fwd": (C.c_int, [C.POINTER(ParallelArgs), C.c_void_p]),
+    "attn_b200_parallel_workspace_bytes": (C.c_int64, [C.POINTER(ParallelArgs)]),
     "attn_b200_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "attn_b200_linear_workspace_bytes": (C.c_int64, [C.POINTER(LinearArgs)]),
     "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
@@ -194,7 +196,8 @@ def _strides_bsh(t: torch.Tensor):
 
 
 def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=(), final_rowscales=(),
-                       custom=(), custom_strides=(), mask_band=(MASK_OPEN, MASK_OPEN)) -> ParallelArgs:
+                       custom=(), custom_strides=(), mask_band=(MASK_OPEN, MASK_OPEN), num_splits: int = 1,
+                       workspace=None) -> ParallelArgs:
     """q,k: [B,S,H,D]; v,o: [B,S,H,Dv] CUDA tensors (any strides with a contiguous last dim)."""
     for t in (q, k, v, o):
         if not t.is_cuda:
@@ -219,6 +222,9 @@ def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=
     a.dtype = DTYPE_CODES[q.dtype]
     a.mask_kind = mask_kind
     a.mask_left, a.mask_right = int(mask_band[0]), int(mask_band[1])
+    a.num_splits = int(num_splits)
+    if workspace is not None:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     a.functor = functor
     for i, f in enumerate(fparams):
         a.fparams[i] = float(f)

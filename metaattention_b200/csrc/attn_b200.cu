@@ -65,6 +65,13 @@ int attn_b200_last_device_status(int32_t device, int32_t* status_out) {
   return ATTN_B200_OK;
 }
 
+int64_t attn_b200_parallel_workspace_bytes(const AttnB200ParallelArgs* args) {
+  if (args == nullptr || args->batch <= 0 || args->heads <= 0 || args->seq_q <= 0 || args->dim_v <= 0) return -1;
+  if (args->num_splits <= 1) return 0;
+  // fp32 partial rows plus one log-sum-exp per row and split
+  return static_cast<int64_t>(args->batch) * args->num_splits * args->heads * args->seq_q * (args->dim_v + 1) * 4;
+}
+
 int attn_b200_parallel_fwd(const AttnB200ParallelArgs* args, void* cuda_stream) {
   if (args == nullptr) return ATTN_B200_E_INVALID_ARG;
   int dev = 0;

@@ -59,6 +59,10 @@ struct ParallelParams {
   float* final_out[kMaxRowScales];
   int batch, heads, seq_q, seq_kv;
   int kv_group;                // query heads per KV head (1 = one KV head per query head)
+  int kv_splits;               // > 1: blockIdx.z = batch * kv_splits + split, each split covers tiles_per_split KV tiles
+  int tiles_per_split;
+  float* part_o;               // [batch, kv_splits, heads, seq_q, dim_v] fp32 results of the splits (kv_splits > 1)
+  float* part_lse;             // [batch, kv_splits, heads, seq_q] their final row scale 0 (log-sum-exp)
   long long o_sb, o_ss, o_sh;  // element strides of o
   int mask_kind;               // 0 none, 1 causal (keep q_idx >= kv_idx), 2 band
   int win_left, win_right;     // band: keep kv_idx in [q_idx - win_left, q_idx + win_right]; kNoBound = open side
@@ -135,7 +139,8 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // heaviest query tiles (largest KV range under a causal mask) are launched first
   const int m_pair = causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
   const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  const int b = p.kv_splits > 1 ? blockIdx.z / p.kv_splits : blockIdx.z;
+  const int split = p.kv_splits > 1 ? blockIdx.z % p.kv_splits : 0;
   const int m0 = m_pair * 2 * BM;
   const int n_kv_tiles = (p.seq_kv + BN - 1) / BN;
   // KV tiles [j_lo, j_hi) of each query tile; the CTA walks the union [j_min, j_max)
@@ -147,6 +152,10 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (row0 < p.seq_q) {
       j_lo[t] = (left >= kNoBound || row0 <= left) ? 0 : (row0 - left) / BN;
       j_hi[t] = right >= kNoBound ? n_kv_tiles : min(n_kv_tiles, (row0 + BM - 1 + right) / BN + 1);
+      if (p.kv_splits > 1) {   // this CTA's share of the KV tiles
+        j_lo[t] = max(j_lo[t], split * p.tiles_per_split);
+        j_hi[t] = min(j_hi[t], (split + 1) * p.tiles_per_split);
+      }
       if (j_hi[t] < j_lo[t]) j_hi[t] = j_lo[t];
     }
   }
@@ -348,7 +357,16 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < DV / 32; ++c) tmem_ld32f(tO + c * 32, &o[c * 32]);
         tmem_wait_ld();
         F::template epilogue<DV>(o, rs, ctx);
-        if (in_range) {
+        if (p.kv_splits > 1) {
+          // split-KV: the normalised rows and their log-sum-exp go to the scratch the combine kernel reads
+          if (in_range) {
+            const long long prow = ((static_cast<long long>(b) * p.kv_splits + split) * p.heads + h) * p.seq_q + q_idx;
+            float4* dst = reinterpret_cast<float4*>(p.part_o + prow * DV);
+#pragma unroll
+            for (int v = 0; v < DV / 4; ++v) dst[v] = make_float4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            p.part_lse[prow] = F::final_rowscale(0, rs, ctx);
+          }
+        } else if (in_range) {
 #pragma unroll
           for (int v = 0; v < DV / 8; ++v) {
             uint4 pk;
@@ -359,7 +377,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             *reinterpret_cast<uint4*>(orow + v * 16) = pk;
           }
         }
-        if (in_range) {
+        if (in_range && p.kv_splits <= 1) {
 #pragma unroll
           for (int i = 0; i < F::kFinal; ++i) {
             if (p.final_out[i] != nullptr) {
@@ -369,6 +387,14 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
+  }
+
+  // a split whose share of the KV tiles is empty for a query tile contributes nothing
+  if (p.kv_splits > 1 && warp < 8) {
+    const int t = warp >> 2;
+    const int q_idx = m0 + t * BM + (warp & 3) * 32 + lane;
+    if (j_hi[t] <= j_lo[t] && q_idx < p.seq_q)
+      p.part_lse[((static_cast<long long>(b) * p.kv_splits + split) * p.heads + h) * p.seq_q + q_idx] = -INFINITY;
   }
 
   // ---------------- teardown ----------------
@@ -384,6 +410,45 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+
+// Split-KV combine for softmax-type results: o[b,q,h,:] = sum_i exp(lse_i - lse) part_o[b,i,h,q,:],
+// lse = log sum_i exp(lse_i) (what OnlineFunc.combine of examples/mha_decode.py:69-77 computes with the
+// final row scale lse).  One warp per (batch, head, query row); splits with lse = -inf are skipped.
+template <int DV, bool kBf16>
+__global__ void __launch_bounds__(256) parallel_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                             void* __restrict__ o, float* __restrict__ lse_out, int batch,
+                                                             int heads, int seq_q, int splits, long long o_sb, long long o_ss,
+                                                             long long o_sh) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= static_cast<long long>(batch) * heads * seq_q) return;
+  const int q = static_cast<int>(row % seq_q);
+  const int h = static_cast<int>((row / seq_q) % heads);
+  const int b = static_cast<int>(row / (static_cast<long long>(seq_q) * heads));
+  auto prow = [&](int i) { return ((static_cast<long long>(b) * splits + i) * heads + h) * seq_q + q; };
+  float mx = -INFINITY;
+  for (int i = 0; i < splits; ++i) mx = fmaxf(mx, part_lse[prow(i)]);
+  float den = 0.f;
+  for (int i = 0; i < splits; ++i) den += __expf(part_lse[prow(i)] - mx);
+  const float lse = mx + __logf(den);
+  constexpr int E = DV / 32;   // columns per lane
+  float acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  for (int i = 0; i < splits; ++i) {
+    const float li = part_lse[prow(i)];
+    if (li == -INFINITY) continue;
+    const float w = __expf(li - lse);
+    const float* src = part_o + prow(i) * DV + lane * E;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] += w * src[e];
+  }
+  uint8_t* orow = reinterpret_cast<uint8_t*>(o) + 2 * (b * o_sb + q * o_ss + h * o_sh + lane * E);
+#pragma unroll
+  for (int e = 0; e < E; e += 2) *reinterpret_cast<uint32_t*>(orow + 2 * e) = pack2<kBf16>(acc[e], acc[e + 1]);
+  if (lane == 0 && lse_out != nullptr) lse_out[(static_cast<long long>(b) * heads + h) * seq_q + q] = lse;
 }
 
 }  // namespace b200

@@ -120,14 +120,35 @@ int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* dev
     p.fa.custom[i] = a->custom[i];
     for (int j = 0; j < 4; ++j) p.fa.cstride[i][j] = a->custom_stride[i][j];
   }
+  const int splits = a->num_splits > 1 ? a->num_splits : 1;
+  if (splits > 1) {
+    const int n_kv_tiles = (a->seq_kv + L::kBN - 1) / L::kBN;
+    if (splits > n_kv_tiles || static_cast<long long>(a->batch) * splits > 65535) return ATTN_B200_E_INVALID_ARG;
+    if (F::kFinal < 1) return ATTN_B200_E_UNSUPPORTED;   // the combine needs a log-sum-exp per row
+    const long long rows = static_cast<long long>(a->batch) * splits * a->heads * a->seq_q;
+    const long long need = rows * (DV + 1) * 4;
+    if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0)
+      return ATTN_B200_E_WORKSPACE;
+    p.kv_splits = splits;
+    p.tiles_per_split = (n_kv_tiles + splits - 1) / splits;
+    p.part_o = static_cast<float*>(a->workspace);
+    p.part_lse = p.part_o + rows * DV;
+  }
   auto kernel = parallel_fwd_kernel<F, D, DV, kBf16>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
     cudaGetLastError();
     return ATTN_B200_E_LAUNCH;
   }
-  dim3 grid((a->seq_q + 2 * L::kBM - 1) / (2 * L::kBM), a->heads, a->batch);
+  dim3 grid((a->seq_q + 2 * L::kBM - 1) / (2 * L::kBM), a->heads, a->batch * splits);
   kernel<<<grid, 320, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  if (splits > 1) {
+    const long long rows = static_cast<long long>(a->batch) * a->heads * a->seq_q;
+    const unsigned blocks = static_cast<unsigned>((rows * 32 + 255) / 256);
+    parallel_combine_kernel<DV, kBf16><<<blocks, 256, 0, stream>>>(p.part_o, p.part_lse, a->o, a->final_rowscales[0], a->batch, a->heads,
+                                                                  a->seq_q, splits, p.o_sb, p.o_ss, p.o_sh);
+    if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  }
   return ATTN_B200_OK;
 }
 

@@ -32,7 +32,7 @@ def test_struct_layouts_match_header(tmp_path):
     """sizeof / offsetof of every argument struct as the C compiler sees the header, against the ctypes mirrors"""
     import subprocess
     probes = {
-        "AttnB200ParallelArgs": (lib.ParallelArgs, ["o", "seq_kv", "o_stride", "heads_kv", "fparams", "custom_stride", "mask_left", "mask_right"]),
+        "AttnB200ParallelArgs": (lib.ParallelArgs, ["o", "seq_kv", "o_stride", "heads_kv", "fparams", "custom_stride", "mask_left", "mask_right", "num_splits", "workspace", "workspace_bytes"]),
         "AttnB200LinearArgs": (lib.LinearArgs, ["log_decay", "dim_v", "normalize", "q_scale", "workspace", "workspace_bytes"]),
         "AttnB200MlaShape": (lib.MlaShape, ["dim_v"]),
         "AttnB200MlaArgs": (lib.MlaArgs, ["kv_rope", "o", "workspace_bytes", "shape", "scale", "seq_lens", "block_table",

@@ -262,3 +262,29 @@ def test_band_masks(name, S, D):
     s = torch.einsum("bshd,bthd->bhst", q.float(), k.float()) * D ** -0.5
     want_lse = torch.logsumexp(s.masked_fill(~keep, float("-inf")), dim=-1)
     assert (lse - want_lse).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("B,H,Hkv,Sq,Skv,D,splits,causal", [
+    (1, 8, 8, 1, 8192, 128, None, False),     # decode, split count planned from the SM count
+    (2, 4, 2, 3, 3000, 64, 5, False),         # grouped heads, forced split count, ragged KV
+    (1, 2, 2, 1024, 1024, 128, 3, True),      # split invariance under a causal mask (empty splits for early rows)
+    (1, 3, 3, 200, 700, 128, 2, False),
+])
+def test_split_kv(B, H, Hkv, Sq, Skv, D, splits, causal):
+    """KV range divided among several CTAs per (tile pair, head, batch) and combined through the log-sum-exp
+    (the reference's split-KV decode kernels with OnlineFunc.combine, lower_decode.py:287-302,375-449)"""
+    g = torch.Generator().manual_seed(1700 + Skv + H)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Skv, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Skv, Hkv, D, generator=g).to(torch.bfloat16)
+    e = programs.gqa_engine(B, H, Hkv, Sq, Skv, D, D, is_causal=causal)
+    e.kv_splits = splits
+    o = e(q.cuda(), k.cuda(), v.cuda())
+    keep = (torch.arange(Skv).view(1, -1) <= torch.arange(Sq).view(-1, 1)) if causal else torch.ones(Sq, Skv, dtype=torch.bool)
+    check(o, rm.softmax_attention(q, k, v, softmax_scale=D ** -0.5, keep=keep))
+    s = torch.einsum("bshgd,bthd->bhgst", q.float().view(B, Sq, Hkv, H // Hkv, D), k.float()).reshape(B, H, Sq, Skv) * D ** -0.5
+    want_lse = torch.logsumexp(s.masked_fill(~keep, float("-inf")), dim=-1)
+    assert (e.last_final_rowscales["lse"].cpu() - want_lse).abs().max().item() <= 2e-3
+    if splits is None:
+        from attn_engine.attn_engine import plan_kv_splits
+        assert plan_kv_splits(B, H, Sq, Skv, torch.device("cuda")) > 1
