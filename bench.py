@@ -281,6 +281,22 @@ def extras_retention(steps, warmup):
                              steps, warmup, lambda: None) / steps
             out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "gbs_min_io": io_bytes / ms / 1e6}
         del q, k, v
+        # the two other users of the chunked kernel, at the shapes of the reference's functional tests
+        # (testing/test.py:57-58), through the engine as the reference examples build it
+        import programs
+        B, H, S, D, Dv = 8, 32, 2048, 256, 256
+        q, k, v, g = [t.cuda() for t in oracle_inputs.gla_inputs(B, H, S, D, Dv, 61)]
+        eng = programs.gla_engine(B, H, S, D, Dv)
+        ms = time_device(lambda: eng(q, k, v, g), steps, warmup, lambda: None) / steps
+        out["gated_retention_8x32x2048_256_256"] = {"ms": ms, "tflops": float(B * H * S) * (2 * 64 * (D + Dv) + 4 * D * Dv) / ms / 1e9,
+                                                    "gbs_min_io": (2 * B * H * S * D + 2 * B * H * S * Dv) * 2 / ms / 1e6}
+        del q, k, v, g
+        B, HQ, HK, HV, S, D, Dv = 1, 1, 1, 80, 2048, 128, 64
+        q, k, v, dt, A = [t.cuda() for t in oracle_inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, 71)]
+        eng = programs.mamba2_engine(B, HQ, S, D, Dv, HK=HK, HV=HV)
+        dtb = dt.to(torch.bfloat16)
+        ms = time_device(lambda: eng(q, k, v, dt, A, dtb), steps, warmup, lambda: None) / steps
+        out["mamba2_1x80x2048_128_64"] = {"ms": ms, "note": "includes the whole-tensor decay_mod / v_mod statements, head broadcast and dim_v padding"}
     except Exception as exc:
         out["C4_retention"] = {"error": repr(exc)[:200]}
     torch.cuda.empty_cache()
