@@ -198,9 +198,9 @@ class AttentionEngine:
 
     # ------------------------------------------------------------------
     def _build_parallel(self, B, H, S, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=None):
-        if (D, Dv) not in ((64, 64), (128, 128)):
+        if (D, Dv) not in ((64, 64), (128, 128)) and not (D == 256 and Dv % 128 == 0):
             raise NotImplementedError(f"head dims (qk={D}, v={Dv}) are not covered by the forward kernel yet "
-                                      "(supported: 64/64 and 128/128)")
+                                      "(supported: 64/64, 128/128 and 256/(a multiple of 128))")
         self.mask_kind, self.mask_band = classify_mask(mask_mod, B, H, S, S if kv_len is None else kv_len)
         if kv_len is not None and kv_len != S and self.mask_kind != native.MASK_NONE:
             raise NotImplementedError("decode (q_len != kv_len) supports mask_mod=None or an all-true mask")
@@ -260,7 +260,7 @@ class AttentionEngine:
         # split-KV when the launch would leave most SMs idle (decode: few query rows and heads against a long KV);
         # the split results are combined through the log-sum-exp, which only the built-in softmax provides
         splits, workspace = 1, None
-        if self.functor_kind == "builtin_softmax":
+        if self.functor_kind == "builtin_softmax" and q.shape[-1] <= 128:
             splits = self.kv_splits if self.kv_splits is not None else plan_kv_splits(B, H, S, k.shape[1], q.device)
             if splits > 1:
                 workspace = torch.empty(B * splits * H * S * (Dv + 1) * 4, dtype=torch.uint8, device=q.device)

@@ -460,6 +460,11 @@ def emit_functor(tr: TracedParallel, *, neg_inf_mask: bool, input_ctype: str, st
 def translation_unit(fs: FunctorSource, dim_qk: int, dim_v: int, bf16: bool) -> str:
     """Source of a library exporting ``attn_b200_parallel_fwd_jit`` for one functor and one
     (dim_qk, dim_v, dtype) instantiation of the forward kernel."""
+    b = "true" if bf16 else "false"
+    if dim_qk == 256:   # one launch per 128-column slice of dim_v (parallel_launch.cuh)
+        launch = f"b200::launch_parallel_sliced<{fs.struct_name}, {b}>"
+    else:
+        launch = f"b200::launch_parallel<{fs.struct_name}, {dim_qk}, {dim_v}, {b}>"
     return f"""// generated by core/lower/functor.py -- do not edit
 #include "parallel_launch.cuh"
 
@@ -469,7 +474,7 @@ extern "C" int attn_b200_parallel_fwd_jit(const AttnB200ParallelArgs* args, void
   if (rc != ATTN_B200_OK) return rc;
   if (args->dtype != {1 if bf16 else 0}) return ATTN_B200_E_UNSUPPORTED;
   if (args->num_splits > 1) return ATTN_B200_E_UNSUPPORTED;  // split-KV combines through the built-in softmax's log-sum-exp
-  return b200::launch_parallel<{fs.struct_name}, {dim_qk}, {dim_v}, {'true' if bf16 else 'false'}>(
+  return {launch}(
       args, static_cast<cudaStream_t>(cuda_stream), device_status);
 }}
 """

@@ -84,14 +84,16 @@ enum ParallelWaitSite {
   kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePReady, kSiteODone, kSiteOFinal
 };
 
-template <int D, int DV>
+// NT = query tiles per CTA: 2 (K/V in two stages, shared by both tiles) or 1 (single-staged K/V; the layout that
+// fits dim_qk = 256: one 64 KB query tile, 64 KB of K, 32 KB of V)
+template <int D, int DV, int NT = 2>
 struct ParallelSmem {
-  static constexpr int kBM = 128, kBN = 128, kStages = 2;
+  static constexpr int kBM = 128, kBN = 128, kStages = NT == 2 ? 2 : 1;
   static constexpr int kQBytes = kBM * D * 2;
   static constexpr int kKBytes = kBN * D * 2;
   static constexpr int kVBytes = kBN * DV * 2;
   static constexpr int kOffQ = 0;
-  static constexpr int kOffK = kOffQ + 2 * kQBytes;
+  static constexpr int kOffK = kOffQ + NT * kQBytes;
   static constexpr int kOffV = kOffK + kStages * kKBytes;
   static constexpr int kOffBar = kOffV + kStages * kVBytes;
   static constexpr int kNumBars = 1 + 4 * kStages + 6;
@@ -99,15 +101,17 @@ struct ParallelSmem {
   static constexpr int kBytes = kOffMisc + 16 + 1024;  // + slack for manual 1024-byte alignment
 };
 
-template <class F, int D, int DV, bool kBf16>
-__global__ void __launch_bounds__(320, 1)
+template <class F, int D, int DV, bool kBf16, int NT = 2>
+__global__ void __launch_bounds__((4 * NT + 2) * 32, 1)
 parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const ParallelParams p) {
-  using L = ParallelSmem<D, DV>;
+  using L = ParallelSmem<D, DV, NT>;
   constexpr int BM = L::kBM, BN = L::kBN, ST = L::kStages;
-  static_assert(D % 64 == 0 && DV % 64 == 0 && D <= 128 && DV <= 128, "unsupported head dims");
-  constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColO = 256;
+  static_assert(D % 64 == 0 && DV % 64 == 0 && DV <= 128 && (D <= 128 || (D == 256 && NT == 1)), "unsupported head dims");
+  static_assert(L::kBytes <= 232448, "shared memory layout exceeds an SM");
+  constexpr uint32_t kTmemCols = NT == 2 ? 512 : 256;
+  constexpr uint32_t kColS = 0, kColO = NT * 128;
+  constexpr int kTmaWarp = 4 * NT, kMmaWarp = 4 * NT + 1;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -141,7 +145,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int h = blockIdx.y;
   const int b = p.kv_splits > 1 ? blockIdx.z / p.kv_splits : blockIdx.z;
   const int split = p.kv_splits > 1 ? blockIdx.z % p.kv_splits : 0;
-  const int m0 = m_pair * 2 * BM;
+  const int m0 = m_pair * NT * BM;
   const int n_kv_tiles = (p.seq_kv + BN - 1) / BN;
   // KV tiles [j_lo, j_hi) of each query tile; the CTA walks the union [j_min, j_max)
   int j_lo[2], j_hi[2];
@@ -149,7 +153,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   for (int t = 0; t < 2; ++t) {
     const int row0 = m0 + t * BM;
     j_lo[t] = j_hi[t] = 0;
-    if (row0 < p.seq_q) {
+    if (t < NT && row0 < p.seq_q) {
       j_lo[t] = (left >= kNoBound || row0 <= left) ? 0 : (row0 - left) / BN;
       j_hi[t] = right >= kNoBound ? n_kv_tiles : min(n_kv_tiles, (row0 + BM - 1 + right) / BN + 1);
       if (p.kv_splits > 1) {   // this CTA's share of the KV tiles
@@ -182,11 +186,11 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -196,7 +200,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // =============== TMA producer ===============
     if (lane == 0 && n_max > 0 && !*abort_flag) {
       const int nq = act1 ? 2 : 1;
@@ -218,7 +222,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, j * BN, h / p.kv_group, b, p.ov);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // =============== MMA issuer ===============
     if (lane == 0 && n_max > 0 && !*abort_flag) {
       constexpr uint32_t idesc_qk = make_idesc_f16(BM, BN, kBf16, false, false);
@@ -248,7 +252,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = ok && mbar_wait(&k_full[0], 0, ab, kSiteKFull);
       if (ok) {
         tc_fence_after_sync();
-        for (int t = 0; t < 2; ++t)
+        for (int t = 0; t < NT; ++t)
           if (active(t, j_min)) issue_qk(t, 0);
         umma_commit(&k_empty[0]);
         for (int i = 0; i < n_max && ok; ++i) {
@@ -258,7 +262,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           ok = mbar_wait(&v_full[st], (i / ST) & 1, ab, kSiteVFull);
           if (ok && i + 1 < n_max) ok = mbar_wait(&k_full[stn], ((i + 1) / ST) & 1, ab, kSiteKFull);
           if (!ok) break;
-          for (int t = 0; t < 2; ++t) {
+          for (int t = 0; t < NT; ++t) {
             if (active(t, j)) {
               ok = mbar_wait(&p_ready[t], (j - j_lo[t]) & 1, ab, kSitePReady);
               if (!ok) break;
@@ -390,7 +394,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 
   // a split whose share of the KV tiles is empty for a query tile contributes nothing
-  if (p.kv_splits > 1 && warp < 8) {
+  if (p.kv_splits > 1 && warp < 4 * NT) {
     const int t = warp >> 2;
     const int q_idx = m0 + t * BM + (warp & 3) * 32 + lane;
     if (j_hi[t] <= j_lo[t] && q_idx < p.seq_q)
@@ -406,7 +410,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }

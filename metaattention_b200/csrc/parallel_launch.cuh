@@ -86,10 +86,13 @@ inline int validate_parallel_args(const AttnB200ParallelArgs* a) {
   return ATTN_B200_OK;
 }
 
-template <class F, int D, int DV, bool kBf16>
-int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
-  using L = ParallelSmem<D, DV>;
-  if (a->dim_qk != D || a->dim_v != DV) return ATTN_B200_E_UNSUPPORTED;
+// `dv0` selects a DV-column slice of v and o when dim_v is wider than the kernel's DV (see launch_parallel_sliced)
+template <class F, int D, int DV, bool kBf16, int NT = 2>
+int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status, int dv0 = -1) {
+  using L = ParallelSmem<D, DV, NT>;
+  if (a->dim_qk != D || (dv0 < 0 ? a->dim_v != DV : (a->dim_v % DV != 0 || dv0 + DV > a->dim_v))) return ATTN_B200_E_UNSUPPORTED;
+  const void* v_base = dv0 > 0 ? static_cast<const uint8_t*>(a->v) + 2 * dv0 : a->v;
+  void* o_base = dv0 > 0 ? static_cast<uint8_t*>(a->o) + 2 * dv0 : a->o;
   if (device_status == nullptr) return ATTN_B200_E_INVALID_ARG;
   CUtensorMap tmQ, tmK, tmV;
   ParallelParams p;
@@ -99,10 +102,10 @@ int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* dev
   const int heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;
   rc = encode_rows_map(&tmK, &p.ok, a->k, a->dtype, D, a->batch, a->seq_kv, heads_kv, a->k_stride, L::kBN);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_rows_map(&tmV, &p.ov, a->v, a->dtype, DV, a->batch, a->seq_kv, heads_kv, a->v_stride, L::kBN);
+  rc = encode_rows_map(&tmV, &p.ov, v_base, a->dtype, DV, a->batch, a->seq_kv, heads_kv, a->v_stride, L::kBN);
   if (rc != ATTN_B200_OK) return rc;
-  p.o = a->o;
-  for (int i = 0; i < kMaxRowScales; ++i) p.final_out[i] = a->final_rowscales[i];
+  p.o = o_base;
+  for (int i = 0; i < kMaxRowScales; ++i) p.final_out[i] = dv0 > 0 ? nullptr : a->final_rowscales[i];   // the first slice writes them
   p.batch = a->batch;
   p.heads = a->heads;
   p.kv_group = a->heads / heads_kv;
@@ -134,13 +137,13 @@ int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* dev
     p.part_o = static_cast<float*>(a->workspace);
     p.part_lse = p.part_o + rows * DV;
   }
-  auto kernel = parallel_fwd_kernel<F, D, DV, kBf16>;
+  auto kernel = parallel_fwd_kernel<F, D, DV, kBf16, NT>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
     cudaGetLastError();
     return ATTN_B200_E_LAUNCH;
   }
-  dim3 grid((a->seq_q + 2 * L::kBM - 1) / (2 * L::kBM), a->heads, a->batch * splits);
-  kernel<<<grid, 320, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
+  dim3 grid((a->seq_q + NT * L::kBM - 1) / (NT * L::kBM), a->heads, a->batch * splits);
+  kernel<<<grid, (4 * NT + 2) * 32, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (splits > 1) {
     const long long rows = static_cast<long long>(a->batch) * a->heads * a->seq_q;
@@ -148,6 +151,19 @@ int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* dev
     parallel_combine_kernel<DV, kBf16><<<blocks, 256, 0, stream>>>(p.part_o, p.part_lse, a->o, a->final_rowscales[0], a->batch, a->heads,
                                                                   a->seq_q, splits, p.o_sb, p.o_ss, p.o_sh);
     if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+  }
+  return ATTN_B200_OK;
+}
+
+// Head dims 256 / (a multiple of 128), e.g. the 256 / 512 of examples/retention_parallel.py: one query tile per CTA
+// (a 256-wide query tile and K tile fill the shared memory) and one launch per 128-column slice of v and o, each
+// recomputing the scores; the accumulator of a slice is the widest the tensor memory holds beside the scores.
+template <class F, bool kBf16>
+int launch_parallel_sliced(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
+  if (a->num_splits > 1) return ATTN_B200_E_UNSUPPORTED;
+  for (int dv0 = 0; dv0 < a->dim_v; dv0 += 128) {
+    const int rc = launch_parallel<F, 256, 128, kBf16, 1>(a, stream, device_status, dv0);
+    if (rc != ATTN_B200_OK) return rc;
   }
   return ATTN_B200_OK;
 }
@@ -164,6 +180,8 @@ int dispatch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* d
   if (a->dim_qk == 64 && a->dim_v == 64)
     return bf16 ? launch_parallel<F, 64, 64, true>(a, stream, device_status)
                 : launch_parallel<F, 64, 64, false>(a, stream, device_status);
+  if (a->dim_qk == 256 && a->dim_v % 128 == 0)
+    return bf16 ? launch_parallel_sliced<F, true>(a, stream, device_status) : launch_parallel_sliced<F, false>(a, stream, device_status);
   return ATTN_B200_E_UNSUPPORTED;
 }
 

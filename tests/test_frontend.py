@@ -146,6 +146,8 @@ def test_reference_examples_construct_unchanged():
         assert ret.retnet_recurrent(1, 8, 512, 256, 512).q_scale == 256 ** -0.5
         gla = importlib.import_module("examples.gated_retention")
         assert gla.gated_retention(1, 4, 512, 256, 256).q_scale == 1 / 256 ** 0.5
+        rp = importlib.import_module("examples.retention_parallel")
+        assert rp.retention_parallel(1, 32, 2048, 256, 512).functor_kind == "lowered"   # the README's smoke run
         dec = importlib.import_module("examples.mha_decode")
         assert dec.softmax_attention_decode(2, 8, 1, 4096, 128, 128).pattern == "mha_decode"
         mb = importlib.import_module("examples.mamba2")

@@ -288,3 +288,29 @@ def test_split_kv(B, H, Hkv, Sq, Skv, D, splits, causal):
     if splits is None:
         from attn_engine.attn_engine import plan_kv_splits
         assert plan_kv_splits(B, H, Sq, Skv, torch.device("cuda")) > 1
+
+
+@pytest.mark.parametrize("B,H,S,D,Dv", [(1, 2, 384, 256, 512), (1, 3, 200, 256, 128)])
+def test_wide_heads_retention_parallel(B, H, S, D, Dv):
+    """dims of examples/retention_parallel.py's own run (256 / 512): one query tile per CTA, one launch per
+    128-column slice of v and o"""
+    g = torch.Generator().manual_seed(77 + S)
+    q = (torch.randn(B, S, H, D, generator=g) * D ** -0.25).to(torch.bfloat16)
+    k = (torch.randn(B, S, H, D, generator=g) * D ** -0.25).to(torch.bfloat16)
+    v = torch.randn(B, S, H, Dv, generator=g).to(torch.bfloat16)
+    mask = torch.rand(1, H, S, S, generator=g).tril().to(torch.bfloat16)
+    e = programs.retention_parallel_engine(B, H, S, D, Dv)
+    o = e(*cuda(q, k, v, mask))
+    assert o.shape == (B, S, H, Dv)
+    check(o, rm.retention_parallel(q, k, v, mask))
+
+
+def test_wide_heads_softmax():
+    B, H, S, D, Dv = 2, 2, 300, 256, 256
+    g = torch.Generator().manual_seed(79)
+    q = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, H, Dv, generator=g).to(torch.bfloat16)
+    e = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)
+    o = e(*cuda(q, k, v))
+    check(o, rm.softmax_attention(q, k, v, causal=True, softmax_scale=D ** -0.5))
