@@ -144,6 +144,7 @@ class AttentionEngine:
         self.backend = backend          # accepted for source compatibility; every value runs the native kernels
         self.use_varlen = use_varlen
         self.block_mask = None
+        self._kv_bias_block = None
         self.kv_splits = None      # None = planned per call (plan_kv_splits); an int forces the split count
         self.qkv_meta = qkv_meta
         self.custom_fwd_inputs = custom_fwd_inputs if custom_fwd_inputs is not None else CustomIO()
@@ -169,19 +170,53 @@ class AttentionEngine:
             if H % Hkv != 0:
                 raise NotImplementedError(f"query heads ({H}) must be a multiple of KV heads ({Hkv})")
             if use_varlen or extern_block_mask:
-                raise NotImplementedError("block-sparse / variable-length GQA decode is not covered by the native backend yet")
+                score_mod = self._with_kv_bias(score_mod, Hkv, infer_mask_block_N)
             self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=Skv)
         elif self.pattern == "mha_decode":
             # A few query rows against a long KV (examples/mha_decode.py; the reference lowers it to a split-KV
             # kernel plus OnlineFunc.combine, lower_decode.py:375-449).  The forward kernel takes any
             # q_len != kv_len, streams K/V once per (batch, head) and needs no combine step; with few
             # (batch, head) pairs it leaves SMs idle.
+            if use_varlen or extern_block_mask:
+                score_mod = self._with_kv_bias(score_mod, Hkv, infer_mask_block_N)
             self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=Skv)
         else:
             raise NotImplementedError(
                 f"pattern {self.pattern!r} (q_len={Sq}, kv_len={Skv}, heads={H}, kv_heads={Hkv}) is not covered by the "
                 "native backend yet: it implements the parallel MHA / GQA forward, dense MHA / GQA decode, chunked linear "
                 "attention and MLA decode")
+
+    # ------------------------------------------------------------------
+    _KV_BIAS = "__kv_bias"
+
+    def _with_kv_bias(self, score_mod, heads_kv, block):
+        """Block-sparse and variable-length decode (``block_mask`` [B, Hkv, blocks] bool and ``cache_seqlens`` [B]
+        at call time; examples/sparse_gqa_decode.py, blockattn_decode_varlen_tl.py of the reference): the kept KV
+        positions enter the user's score function as one more custom input, an additive bias [B, H, 1, kv_len]
+        that is 0 where a position is kept and -inf elsewhere.  Functionally the reference's kernel; masked
+        blocks are computed and discarded here, not skipped."""
+        self.custom_fwd_inputs(self._KV_BIAS, ("batch", "heads", 1, "seq_len_kv"))
+        self._kv_bias_block = int(block)
+        self._kv_bias_heads_kv = heads_kv
+        user = score_mod
+        name = self._KV_BIAS
+
+        def with_bias(score, custom, b, h, q_idx, kv_idx):
+            out = user(score, custom, b, h, q_idx, kv_idx) if user is not None else score
+            return out + custom.input_tensors[name]
+        return with_bias
+
+    def _kv_bias(self, q, k, block_mask, cache_seqlens):
+        B, H, Skv = q.shape[0], q.shape[2], k.shape[1]
+        keep = torch.ones((B, self._kv_bias_heads_kv, Skv), dtype=torch.bool, device=q.device)
+        if block_mask is not None:
+            keep = block_mask.to(q.device).bool().repeat_interleave(self._kv_bias_block, dim=-1)[..., :Skv]
+            if keep.shape[-1] < Skv:   # blocks past the table are not kept
+                keep = torch.nn.functional.pad(keep, (0, Skv - keep.shape[-1]))
+        if cache_seqlens is not None:
+            keep = keep & (torch.arange(Skv, device=q.device).view(1, 1, -1) < cache_seqlens.to(q.device).view(-1, 1, 1))
+        bias = torch.zeros(keep.shape, dtype=q.dtype, device=q.device).masked_fill_(~keep, float("-inf"))
+        return bias.repeat_interleave(H // self._kv_bias_heads_kv, dim=1).unsqueeze(2)   # [B, H, 1, Skv]
 
     # pattern selection by shape, as attn_engine.py:227-343 of the reference
     @staticmethod
@@ -280,6 +315,11 @@ class AttentionEngine:
 
     # ------------------------------------------------------------------
     def __call__(self, *args, **kargs):
+        if getattr(self, "_kv_bias_block", None) is not None:
+            # (q, k, v, *user custom tensors, block_mask=..., cache_seqlens=...): the kept positions become the
+            # bias input appended by _with_kv_bias
+            q, k = args[0], args[1]
+            return self.attention(*args, self._kv_bias(q, k, kargs.get("block_mask"), kargs.get("cache_seqlens")))
         if kargs.get("block_mask") is not None:
             args = args + (kargs["block_mask"],)
         elif self.block_mask is not None:

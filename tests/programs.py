@@ -205,3 +205,15 @@ def masked_softmax_engine(B, H, S, D, Dv, mask_mod, dtype=torch.bfloat16):
         return score * scale
     return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({}), score_mod=score_mod, mask_mod=mask_mod,
                            online_func=NaturalSoftmax())
+
+
+def sparse_decode_engine(B, H, Hkv, Skv, D, Dv, block=32, dtype=torch.bfloat16):
+    """Block-sparse, variable-length GQA decode built like examples/sparse_gqa_decode.py: no mask_mod, the kept
+    blocks and the sequence lengths arrive with each call (block_mask=, cache_seqlens=)."""
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    meta = (meta_tensor(B, H, 1, D, dtype=dtype), meta_tensor(B, Hkv, Skv, D, dtype=dtype), meta_tensor(B, Hkv, Skv, Dv, dtype=dtype))
+    return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=NaturalSoftmax(),
+                           extern_block_mask=True, use_varlen=True, infer_mask_block_N=block)

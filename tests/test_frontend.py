@@ -67,8 +67,8 @@ def test_unsupported_patterns_raise_clearly():
         AttentionEngine(meta, CustomIO({}), None, None, None)
     meta = (meta_tensor(1, 16, 1, 128, dtype=torch.float16), meta_tensor(1, 4, 4096, 128, dtype=torch.float16),
             meta_tensor(1, 4, 4096, 128, dtype=torch.float16))
-    with pytest.raises(NotImplementedError, match="variable-length"):
-        AttentionEngine(meta, CustomIO({}), None, None, None, use_varlen=True)
+    e = AttentionEngine(meta, CustomIO({}), None, None, None, use_varlen=True, extern_block_mask=True, infer_mask_block_N=32)
+    assert e.pattern == "gqa_decode" and e.custom_names == ["__kv_bias"]   # block mask / lengths enter as a bias input
     with pytest.raises(TypeError):
         AttentionEngine(programs._meta(1, 2, 128, 64, 64, torch.float32), CustomIO({}), None, None, None)
 
@@ -148,6 +148,8 @@ def test_reference_examples_construct_unchanged():
         assert gla.gated_retention(1, 4, 512, 256, 256).q_scale == 1 / 256 ** 0.5
         rp = importlib.import_module("examples.retention_parallel")
         assert rp.retention_parallel(1, 32, 2048, 256, 512).functor_kind == "lowered"   # the README's smoke run
+        sp = importlib.import_module("examples.sparse_gqa_decode")
+        assert sp.sparse_gqa_decode(2, 32, 8, 4096, 128, 128).pattern == "gqa_decode"
         dec = importlib.import_module("examples.mha_decode")
         assert dec.softmax_attention_decode(2, 8, 1, 4096, 128, 128).pattern == "mha_decode"
         mb = importlib.import_module("examples.mamba2")

@@ -314,3 +314,29 @@ def test_wide_heads_softmax():
     e = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)
     o = e(*cuda(q, k, v))
     check(o, rm.softmax_attention(q, k, v, causal=True, softmax_scale=D ** -0.5))
+
+
+def test_block_sparse_varlen_gqa_decode():
+    """examples/sparse_gqa_decode.py: one query token, per-KV-head block mask (32-token blocks) and per-sequence
+    cache lengths given at call time"""
+    B, H, Hkv, Skv, D, block = 3, 16, 4, 1000, 128, 32
+    g = torch.Generator().manual_seed(2100)
+    q = torch.randn(B, 1, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Skv, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Skv, Hkv, D, generator=g).to(torch.bfloat16)
+    lens = torch.tensor([1000, 517, 64], dtype=torch.int32)
+    nblk = (Skv + block - 1) // block
+    block_mask = torch.rand(B, Hkv, nblk, generator=g) < 0.3
+    block_mask[:, :, 0] = True                       # every row keeps something
+    e = programs.sparse_decode_engine(B, H, Hkv, Skv, D, D, block=block)
+    o = e(q.cuda(), k.cuda(), v.cuda(), block_mask=block_mask.cuda(), cache_seqlens=lens.cuda())
+    assert o.shape == (B, 1, H, D)
+    keep = block_mask.repeat_interleave(block, dim=-1)[..., :Skv] & (torch.arange(Skv).view(1, 1, -1) < lens.view(-1, 1, 1))
+    rep = H // Hkv
+    want = torch.empty(B, 1, H, D)
+    for b in range(B):
+        for h in range(H):
+            kk = keep[b, h // rep].view(1, Skv)
+            want[b, :, h] = rm.softmax_attention(q[b:b + 1, :, h:h + 1], k[b:b + 1, :, h // rep:h // rep + 1],
+                                                 v[b:b + 1, :, h // rep:h // rep + 1], softmax_scale=D ** -0.5, keep=kk)[0, :, 0]
+    check(o, want)
