@@ -234,22 +234,22 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           s_pending = true;
         }
         // Q may be replaced once both have run
-        if (!mbar_wait(s_bar, par, ab, kLinScore)) break;
-        if (t > 0 && !mbar_wait(qh_bar, par_prev, ab, kLinQh)) break;
+        if (!mbar_wait_poll(s_bar, par, ab, kLinScore)) break;
+        if (t > 0 && !mbar_wait_poll(qh_bar, par_prev, ab, kLinQh)) break;
         if (!last) load_q(t + 1);  // Q is no longer read by any MMA of this block
         if (!last) {
           // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step
-          if (!mbar_wait(v_ready, par, ab, kLinVReady)) break;
+          if (!mbar_wait_poll(v_ready, par, ab, kLinVReady)) break;
           tc_fence_after_sync();
 #pragma unroll
           for (int g = 0; g < T / 64; ++g)
             umma_ss_x4<128, 128>(tmem_base + kColH, v2_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
           umma_commit(st_bar);
-          if (!mbar_wait(st_bar, par, ab, kLinState)) break;
+          if (!mbar_wait_poll(st_bar, par, ab, kLinState)) break;
           load_k(t + 1);  // K is no longer read
         }
         // O (+)= P V
-        if (!(mbar_wait(p_ready, par, ab, kLinPReady) && mbar_wait(v_full, par, ab, kLinVFull))) break;
+        if (!(mbar_wait_poll(p_ready, par, ab, kLinPReady) && mbar_wait_poll(v_full, par, ab, kLinVFull))) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int g = 0; g < T / 64; ++g)

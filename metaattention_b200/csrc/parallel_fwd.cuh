@@ -264,7 +264,8 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (!ok) break;
           for (int t = 0; t < NT; ++t) {
             if (active(t, j)) {
-              ok = mbar_wait(&p_ready[t], (j - j_lo[t]) & 1, ab, kSitePReady);
+              // on the serial chain of the tile: polled, a suspended wait wakes up ~150 cycles late
+              ok = mbar_wait_poll(&p_ready[t], (j - j_lo[t]) & 1, ab, kSitePReady);
               if (!ok) break;
               tc_fence_after_sync();
               issue_pv(t, st, j == j_lo[t]);

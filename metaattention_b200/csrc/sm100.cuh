@@ -114,6 +114,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   return true;
 }
 
+// The same bounded wait as a tight poll (test_wait, no suspend): the waiter sees the phase flip a few cycles
+// after it happens instead of after a wake-up, at the price of issue slots.  For waits on a kernel's serial chain.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity, const AbortState& ab, int site) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_test(bar, parity)) {
+    if ((++spins & 0xfff) == 0) {
+      if (*ab.cta_flag) return false;
+      if (*reinterpret_cast<volatile int*>(ab.device_status) != 0) {
+        *ab.cta_flag = 1;
+        return false;
+      }
+      if (clock64() - t0 > kWaitCycleLimit) {
+        *ab.cta_flag = 1;
+        atomicCAS(ab.device_status, 0, kStatusTimeoutBase + site);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // Named CTA barriers for a subset of the warps (`count` threads, a multiple of 32; id 1..15, 0 is __syncthreads).
 __device__ __forceinline__ void named_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
