@@ -104,6 +104,7 @@ struct MlaSmem {
   static constexpr int kQrBytes = kMlaHeads * 128;              // 16384: Q[:, 512:576]
   static constexpr int kSlotBytes = 3 * kChunkBytes;            // 49152
   static constexpr int kScoreTileBytes = kQrBytes + kScoreSlots * kSlotBytes;    // 212992
+  static constexpr int kPStageBytes = 8 * 8 * 128;                 // score: per softmax warp 8 rows x 128 B of P on their way out
   static constexpr int kVStageRows = 32;
   static constexpr int kVStages = 5;
   static constexpr int kVStageBytes = kVStageRows * 512 * 2;    // 32768: 8 chunks of 32 rows x 128 B
@@ -136,6 +137,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
   // score CTA: [Q rope tile][12 KV chunks];  value CTA: [5 V stages][4 P slots]
   uint8_t* sQr = tiles;
   uint8_t* sChunk = tiles + L::kQrBytes;
+  uint8_t* sPStage = tiles + L::kScoreTileBytes;
   uint8_t* sV = tiles;
   uint8_t* sP = tiles + L::kVStages * L::kVStageBytes;
 
@@ -166,7 +168,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
   if (threadIdx.x == 0) {
     int bad = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     // the operand tiles must end inside the dynamic shared memory that was requested
-    const size_t used = static_cast<size_t>(tiles - smem_raw) + (rank == 0 ? L::kScoreTileBytes : L::kValueTileBytes);
+    const size_t used = static_cast<size_t>(tiles - smem_raw) + (rank == 0 ? L::kScoreTileBytes + L::kPStageBytes : L::kValueTileBytes);
     if (used > static_cast<size_t>(kMlaSmemBytes)) {
       atomicCAS(p.status, 0, kStatusTimeoutBase + kMlaSmemLayout);
       bad = 1;
@@ -311,7 +313,12 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         // ---- online softmax, one 128-row tile at a time; this thread produces half tile `wg` ----
         float m_ref = -1.0e30f, r_sum = 0.0f;
         const float c2 = p.scale_log2;
-        const uint32_t peer_p = map_to_cta(smem_u32(sP), 1) + row * 128;
+        // P leaves through an 1 KB staging area per warp: the rows of eight lanes at a time are written there in the
+        // (128-byte swizzled) image of the value CTA's tile and sent on as whole 512-byte runs per warp instruction.
+        // Sixteen-byte pieces sent row by row (32 rows per instruction) held the tensor pipe of this SM back for
+        // about half of every tile.
+        const uint32_t stage_w = smem_u32(sPStage) + warp * 1024;
+        const uint32_t peer_p = map_to_cta(smem_u32(sP), 1) + (warp & 3) * (32 * 128) + lane * 16;
         const uint32_t peer_scale = map_to_cta(smem_u32(s_scale), 1) + row * 4;
         const uint32_t peer_pfull = map_to_cta(smem_u32(&bars[L::kPFull]), 1);
         bool ok = true;
@@ -369,8 +376,19 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           const uint32_t dst = peer_p + pslot * L::kPBytes;
           const uint32_t bar = peer_pfull + pslot * 8;
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            st_async_v4(dst + ((q4 ^ (row & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]), bar);
+          for (int pass = 0; pass < 4; ++pass) {
+            if ((lane >> 3) == pass) {
+              const uint32_t mine = stage_w + (lane & 7) * 128;
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4)
+                st_shared_v4(mine + ((q4 ^ (lane & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+              st_async_v4(dst + pass * 1024 + k * 512, ld_shared_v4(stage_w + k * 512 + lane * 16), bar);
+            __syncwarp();
+          }
           if (wg == 0) st_async_f32(peer_scale + (j & 1) * (M * 4), o_scale, bar);
         }
         // ---- final row statistics: sum of both halves ----

@@ -178,6 +178,15 @@ __device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint4 v, uint
   asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
                ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(cluster_mbar) : "memory");
 }
+// 16-byte accesses to this CTA's shared memory by 32-bit shared-window address
+__device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_async_f32(uint32_t cluster_addr, float v, uint32_t cluster_mbar) {
   asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
                ::"r"(cluster_addr), "r"(__float_as_uint(v)), "r"(cluster_mbar) : "memory");
@@ -196,6 +205,38 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
       : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Polled form of mbar_wait_cluster (see mbar_wait_poll).
+__device__ __forceinline__ bool mbar_wait_cluster_poll(uint64_t* bar, uint32_t parity, const AbortState& ab, int site) {
+  if (mbar_test_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_test_cluster(bar, parity)) {
+    if ((++spins & 0xfff) == 0) {
+      if (*ab.cta_flag) return false;
+      if (*reinterpret_cast<volatile int*>(ab.device_status) != 0) {
+        *ab.cta_flag = 1;
+        return false;
+      }
+      if (clock64() - t0 > kWaitCycleLimit) {
+        *ab.cta_flag = 1;
+        atomicCAS(ab.device_status, 0, kStatusTimeoutBase + site);
+        return false;
+      }
+    }
+  }
+  return true;
 }
 // Bounded wait on a local barrier whose arrivals come from the peer CTA (acquire at cluster scope).
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, const AbortState& ab, int site) {
