@@ -327,3 +327,65 @@ class AttentionEngine:
         if self.use_varlen:
             args = args + (kargs.get("cache_seqlens"),)
         return self.attention(*args)
+
+    # ------------------------------------------------------------------
+    def forward_host(self, q, k, v, *custom, out=None, finals_out=None, batch_chunk=1):
+        """Forward pass for q, k, v that live in (pinned) HOST memory: [batch, seq, heads, dim] each.
+
+        The batch is cut into slices of ``batch_chunk`` sequences that travel through three streams — host to
+        device, kernel, device to host — so that the copies of neighbouring slices overlap each other (PCIe is full
+        duplex) and the kernel.  Returns the output as a pinned host tensor (``out`` if given) and leaves the
+        per-row outputs (e.g. ``lse``) in ``finals_out`` / ``self.last_final_rowscales`` as host tensors.  All work is
+        ordered after the caller's current stream, and that stream waits for the last copy, so CUDA events recorded
+        around the call see all of it.  Custom input tensors are device tensors; one whose leading dimension equals
+        the batch is sliced with it.  The reference has no host-side entry; this is the call for a host that keeps
+        activations outside the device.
+        """
+        if q.is_cuda or k.is_cuda or v.is_cuda:
+            raise ValueError("forward_host takes host tensors; call the engine itself for device tensors")
+        B, S, H, _ = q.shape
+        Dv = v.shape[3]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        if out is None:
+            out = torch.empty((B, S, H, Dv), dtype=q.dtype).pin_memory()
+        finals_host = {} if finals_out is None else finals_out
+        for name in self.final_names:
+            if name not in finals_host:
+                finals_host[name] = torch.empty((B, H, S), dtype=torch.float32).pin_memory()
+        st = getattr(self, "_host_streams", None)
+        if st is None or st[0].device != dev:
+            st = self._host_streams = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
+        s_in, s_run, s_out = st
+        cur = torch.cuda.current_stream(dev)
+        for s_ in st:
+            s_.wait_stream(cur)
+        step = max(1, int(batch_chunk))
+        for b0 in range(0, B, step):
+            b1 = min(B, b0 + step)
+            with torch.cuda.stream(s_in):
+                dq = q[b0:b1].to(dev, non_blocking=True)
+                dk = k[b0:b1].to(dev, non_blocking=True)
+                dv = v[b0:b1].to(dev, non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(arrived)
+                for t in (dq, dk, dv):
+                    t.record_stream(s_run)
+                cs = [c[b0:b1] if (c.dim() > 0 and c.shape[0] == B and B > 1) else c for c in custom]
+                o = self(dq, dk, dv, *cs)
+                finals = dict(self.last_final_rowscales)
+                done = torch.cuda.Event()
+                done.record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                o.record_stream(s_out)
+                out[b0:b1].copy_(o, non_blocking=True)
+                for name, t in finals.items():
+                    t.record_stream(s_out)
+                    finals_host[name][b0:b1].copy_(t, non_blocking=True)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_run)
+        cur.wait_stream(s_in)
+        self.last_final_rowscales = finals_host
+        return out

@@ -340,3 +340,21 @@ def test_block_sparse_varlen_gqa_decode():
             want[b, :, h] = rm.softmax_attention(q[b:b + 1, :, h:h + 1], k[b:b + 1, :, h // rep:h // rep + 1],
                                                  v[b:b + 1, :, h // rep:h // rep + 1], softmax_scale=D ** -0.5, keep=kk)[0, :, 0]
     check(o, want)
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 5])
+def test_forward_host_streams_batch_slices(chunk):
+    """The host-buffer call (batch slices on three streams) returns what the device call returns, bit for bit."""
+    B, H, S, D = 5, 3, 384, 128
+    torch.manual_seed(11)
+    hq, hk, hv = (torch.randn(B, S, H, D).to(torch.bfloat16).pin_memory() for _ in range(3))
+    eng = programs.softmax_engine(B, H, S, D, D, is_causal=True)
+    want = eng(hq.cuda(), hk.cuda(), hv.cuda())
+    want_lse = eng.last_final_rowscales["lse"].clone()
+    got = eng.forward_host(hq, hk, hv, batch_chunk=chunk)
+    torch.cuda.synchronize()
+    assert not got.is_cuda and got.is_pinned()
+    assert torch.equal(got, want.cpu())
+    assert torch.equal(eng.last_final_rowscales["lse"], want_lse.cpu())
+    with pytest.raises(ValueError):
+        eng.forward_host(hq.cuda(), hk, hv)
