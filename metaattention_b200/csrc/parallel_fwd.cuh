@@ -170,8 +170,27 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   auto active = [&](int t, int j) { return j >= j_lo[t] && j < j_hi[t]; };
 
   // ---------------- setup ----------------
-  if (threadIdx.x == 0) {
-    *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+  // The producer lane initialises the barriers and sends off the query tiles and the first K and V tiles at once:
+  // their ~2800 cycles of latency start before the tensor-memory allocation and the CTA-wide sync, not after.
+  auto load_k = [&](int i) {
+    const int st = i % ST;
+    mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, (j_min + i) * BN, h / p.kv_group, b, p.ok);
+  };
+  auto load_v = [&](int i) {
+    const int st = i % ST;
+    mbar_arrive_expect_tx(&v_full[st], L::kVBytes);
+    for (int c = 0; c < DV / 64; ++c)
+      tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, (j_min + i) * BN, h / p.kv_group, b, p.ov);
+  };
+  bool early_loads = false;
+  if (warp == kTmaWarp && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    const int bad = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    *abort_flag = bad;
     mbar_init(q_full, 1);
     for (int i = 0; i < ST; ++i) {
       mbar_init(&k_full[i], 1);
@@ -185,15 +204,20 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&o_done[t], 1);
     }
     fence_barrier_init();
+    if (n_max > 0 && !bad) {
+      const int nq = act1 ? 2 : 1;
+      mbar_arrive_expect_tx(q_full, nq * L::kQBytes);
+      for (int t = 0; t < nq; ++t)
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, q_full, c * 64, m0 + t * BM, h, b, p.oq);
+      load_k(0);
+      load_v(0);
+      early_loads = true;
+    }
   }
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
-  }
-  if (warp == kTmaWarp && lane == 0) {
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmK);
-    tma_prefetch_desc(&tmV);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -202,24 +226,14 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (warp == kTmaWarp) {
     // =============== TMA producer ===============
-    if (lane == 0 && n_max > 0 && !*abort_flag) {
-      const int nq = act1 ? 2 : 1;
-      mbar_arrive_expect_tx(q_full, nq * L::kQBytes);
-      for (int t = 0; t < nq; ++t)
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, q_full, c * 64, m0 + t * BM, h, b, p.oq);
-      for (int i = 0; i < n_max; ++i) {
-        const int j = j_min + i;
+    if (lane == 0 && early_loads && !*abort_flag) {
+      for (int i = 1; i < n_max; ++i) {
         const int st = i % ST;
         const uint32_t ph = (i / ST) & 1;
         if (!mbar_wait(&k_empty[st], ph ^ 1, ab, kSiteKEmpty)) break;
-        mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, j * BN, h / p.kv_group, b, p.ok);
+        load_k(i);
         if (!mbar_wait(&v_empty[st], ph ^ 1, ab, kSiteVEmpty)) break;
-        mbar_arrive_expect_tx(&v_full[st], L::kVBytes);
-        for (int c = 0; c < DV / 64; ++c)
-          tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, j * BN, h / p.kv_group, b, p.ov);
+        load_v(i);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -354,9 +368,6 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (ok) {
         tc_fence_after_sync();
         const bool in_range = q_idx < p.seq_q;
-        uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) +
-                        2 * (static_cast<long long>(b) * p.o_sb + static_cast<long long>(q_idx) * p.o_ss +
-                             static_cast<long long>(h) * p.o_sh);
         float o[DV];
 #pragma unroll
         for (int c = 0; c < DV / 32; ++c) tmem_ld32f(tO + c * 32, &o[c * 32]);
@@ -371,15 +382,37 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int v = 0; v < DV / 4; ++v) dst[v] = make_float4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
             p.part_lse[prow] = F::final_rowscale(0, rs, ctx);
           }
-        } else if (in_range) {
+        } else {
+          // Output rows leave through the tile's own Q buffer (free: its last Q.K^T ran before the P.V that o_done
+          // reports).  Each warp owns the 32 rows it computed, so a warp-level sync is enough: every lane writes its
+          // row in 16-byte pieces (piece index xor row: conflict-free), then the warp stores whole rows, DV*2
+          // contiguous bytes per row and 512 bytes per instruction.  A thread storing its own row put 32 pieces
+          // into 32 different rows with every instruction, and the tile's last output took ~3100 cycles.
+          static_assert(DV <= D, "the output tile is staged in the query tile's buffer");
+          constexpr int PR = DV / 8;     // 16-byte pieces per row
+          constexpr int RPI = 32 / PR;   // rows per warp instruction
+          const uint32_t stage = smem_u32(sQ + t * L::kQBytes) + (warp & 3) * (32 * DV * 2);
+          const uint32_t mine = stage + lane * (DV * 2);
 #pragma unroll
-          for (int v = 0; v < DV / 8; ++v) {
+          for (int v = 0; v < PR; ++v) {
             uint4 pk;
             pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
             pk.y = pack2<kBf16>(o[8 * v + 2], o[8 * v + 3]);
             pk.z = pack2<kBf16>(o[8 * v + 4], o[8 * v + 5]);
             pk.w = pack2<kBf16>(o[8 * v + 6], o[8 * v + 7]);
-            *reinterpret_cast<uint4*>(orow + v * 16) = pk;
+            st_shared_v4(mine + ((v ^ (lane & (PR - 1))) << 4), pk);
+          }
+          __syncwarp();
+          const int c = lane & (PR - 1), rsub = lane / PR;
+          const int row_first = row0 + (warp & 3) * 32;
+          uint8_t* obase = reinterpret_cast<uint8_t*>(p.o) +
+                           2 * (static_cast<long long>(b) * p.o_sb + static_cast<long long>(h) * p.o_sh) + c * 16;
+#pragma unroll
+          for (int i = 0; i < PR; ++i) {
+            const int r = i * RPI + rsub;
+            const uint4 val = ld_shared_v4(stage + r * (DV * 2) + ((c ^ (r & (PR - 1))) << 4));
+            if (row_first + r < p.seq_q)
+              *reinterpret_cast<uint4*>(obase + 2 * static_cast<long long>(row_first + r) * p.o_ss) = val;
           }
         }
         if (in_range && p.kv_splits <= 1) {
