@@ -407,12 +407,17 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const int row_first = row0 + (warp & 3) * 32;
           uint8_t* obase = reinterpret_cast<uint8_t*>(p.o) +
                            2 * (static_cast<long long>(b) * p.o_sb + static_cast<long long>(h) * p.o_sh) + c * 16;
+          uint4 val[PR];   // all loads first, then all stores: one after the other each pair costs a shared-memory round trip
 #pragma unroll
           for (int i = 0; i < PR; ++i) {
             const int r = i * RPI + rsub;
-            const uint4 val = ld_shared_v4(stage + r * (DV * 2) + ((c ^ (r & (PR - 1))) << 4));
+            val[i] = ld_shared_v4(stage + r * (DV * 2) + ((c ^ (r & (PR - 1))) << 4));
+          }
+#pragma unroll
+          for (int i = 0; i < PR; ++i) {
+            const int r = i * RPI + rsub;
             if (row_first + r < p.seq_q)
-              *reinterpret_cast<uint4*>(obase + 2 * static_cast<long long>(row_first + r) * p.o_ss) = val;
+              *reinterpret_cast<uint4*>(obase + 2 * static_cast<long long>(row_first + r) * p.o_ss) = val[i];
           }
         }
         if (in_range && p.kv_splits <= 1) {
