@@ -505,22 +505,43 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           const float inv = s_final[row * 2];
           const float lse = s_final[row * 2 + 1];
           if (p.num_splits == 1) {
-            uint8_t* orow = reinterpret_cast<uint8_t*>(p.o) + 2 * ((static_cast<long long>(b) * p.heads + head) * DV);
+            // Output rows leave through the V stages (all consumed by now): each warp stages the 32 rows it holds
+            // (16-byte pieces, piece index xor row: conflict-free) and then stores them as 512 contiguous bytes per
+            // instruction; a thread storing its own 1 KB row scatters every warp instruction over 32 rows.
+            static_assert(4 * 32 * DV * 2 <= L::kVStages * L::kVStageBytes, "output staging does not fit the V stages");
+            const uint32_t stage = smem_u32(sV) + warp * (32 * DV * 2);
+            const uint32_t mine = stage + lane * (DV * 2);
 #pragma unroll 2
             for (int c = 0; c < DV / 32; ++c) {
               float o[32];
               tmem_ld32f(tO + c * 32, o);
               tmem_wait_ld();
-              if (in_range) {
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                  uint4 pk;
-                  pk.x = pack2<kBf16>(o[8 * v + 0] * inv, o[8 * v + 1] * inv);
-                  pk.y = pack2<kBf16>(o[8 * v + 2] * inv, o[8 * v + 3] * inv);
-                  pk.z = pack2<kBf16>(o[8 * v + 4] * inv, o[8 * v + 5] * inv);
-                  pk.w = pack2<kBf16>(o[8 * v + 6] * inv, o[8 * v + 7] * inv);
-                  *reinterpret_cast<uint4*>(orow + c * 64 + v * 16) = pk;
-                }
+              for (int v = 0; v < 4; ++v) {
+                uint4 pk;
+                pk.x = pack2<kBf16>(o[8 * v + 0] * inv, o[8 * v + 1] * inv);
+                pk.y = pack2<kBf16>(o[8 * v + 2] * inv, o[8 * v + 3] * inv);
+                pk.z = pack2<kBf16>(o[8 * v + 4] * inv, o[8 * v + 5] * inv);
+                pk.w = pack2<kBf16>(o[8 * v + 6] * inv, o[8 * v + 7] * inv);
+                st_shared_v4(mine + (((c * 4 + v) ^ (lane & 7)) << 4), pk);
+              }
+            }
+            __syncwarp();
+            uint8_t* obase = reinterpret_cast<uint8_t*>(p.o) + 2 * ((static_cast<long long>(b) * p.heads + head0 + warp * 32) * DV) + lane * 16;
+            constexpr int kHalves = DV * 2 / 512;   // 512-byte runs per row
+#pragma unroll 1
+            for (int r0 = 0; r0 < 32; r0 += 8) {
+              uint4 val[8 * kHalves];
+#pragma unroll
+              for (int i = 0; i < 8 * kHalves; ++i) {
+                const int r = r0 + i / kHalves, piece = (i % kHalves) * 32 + lane;
+                val[i] = ld_shared_v4(stage + r * (DV * 2) + ((piece ^ (r & 7)) << 4));
+              }
+#pragma unroll
+              for (int i = 0; i < 8 * kHalves; ++i) {
+                const int r = r0 + i / kHalves;
+                if (head0 + warp * 32 + r < p.heads)
+                  *reinterpret_cast<uint4*>(obase + static_cast<long long>(r) * (DV * 2) + (i % kHalves) * 512) = val[i];
               }
             }
             if (in_range && p.lse != nullptr) p.lse[static_cast<long long>(b) * p.heads + head] = lse;
