@@ -189,8 +189,6 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    const int bad = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
-    *abort_flag = bad;
     mbar_init(q_full, 1);
     for (int i = 0; i < ST; ++i) {
       mbar_init(&k_full[i], 1);
@@ -204,7 +202,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&o_done[t], 1);
     }
     fence_barrier_init();
-    if (n_max > 0 && !bad) {
+    if (n_max > 0) {
       const int nq = act1 ? 2 : 1;
       mbar_arrive_expect_tx(q_full, nq * L::kQBytes);
       for (int t = 0; t < nq; ++t)
@@ -215,6 +213,10 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       early_loads = true;
     }
   }
+  // The device status word (set by a CTA whose wait ran out) is read by another thread meanwhile: a global-memory
+  // round trip that the first loads do not wait for.  If it is set, nobody consumes those loads and the teardown
+  // below gives them time to land.
+  if (threadIdx.x == 0) *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
