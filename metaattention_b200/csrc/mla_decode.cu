@@ -384,9 +384,10 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
                 st_shared_v4(mine + ((q4 ^ (lane & 7)) << 4), make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]));
             }
             __syncwarp();
-#pragma unroll
-            for (int k = 0; k < 2; ++k)
-              st_async_v4(dst + pass * 1024 + k * 512, ld_shared_v4(stage_w + k * 512 + lane * 16), bar);
+            const uint4 run0 = ld_shared_v4(stage_w + lane * 16);
+            const uint4 run1 = ld_shared_v4(stage_w + 512 + lane * 16);
+            st_async_v4(dst + pass * 1024, run0, bar);
+            st_async_v4(dst + pass * 1024 + 512, run1, bar);
             __syncwarp();
           }
           if (wg == 0) st_async_f32(peer_scale + (j & 1) * (M * 4), o_scale, bar);
