@@ -27,9 +27,11 @@
 //           take the two 64-column halves of a tile:               the score CTA when the slot is free
 //           online softmax in the exp2 domain with lazy
 //           rescale; P (16-bit) and the rescale factor go
-//           straight into the VALUE CTA's shared memory
-//           with asynchronous stores that are counted on
-//           its mbarrier (no release fence, no waiting)
+//           into the VALUE CTA's shared memory with
+//           asynchronous stores that are counted on its
+//           mbarrier (no release fence, no waiting); P is
+//           staged per warp so that every store
+//           instruction covers 512 contiguous bytes
 //
 // FLOP balance 576 : 512, no recomputation.  Each latent row is fetched by both CTAs (the second
 // fetch is an L2 hit); no multicast is used.  Split-KV partials are fp32; the combine kernel does

@@ -23,6 +23,9 @@
 // walks only the KV tiles its band touches, the CTA loads the union of its two tiles' ranges, and tiles
 // that cross an edge of the band are masked element by element.  K/V heads may be shared by groups of
 // query heads (kv_group).  The same kernel serves q_len != kv_len (decode patterns).
+// Start and end of a CTA: the producer lane initialises the barriers and issues the query tiles and the first K/V
+// tiles before the tensor-memory allocation and the CTA-wide sync; the output rows of a tile are staged in its
+// query buffer and stored as whole rows.
 #pragma once
 
 #include "sm100.cuh"
