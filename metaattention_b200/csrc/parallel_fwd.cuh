@@ -99,7 +99,7 @@ struct ParallelSmem {
   static constexpr int kOffK = kOffQ + NT * kQBytes;
   static constexpr int kOffV = kOffK + kStages * kKBytes;
   static constexpr int kOffBar = kOffV + kStages * kVBytes;
-  static constexpr int kNumBars = 1 + 4 * kStages + 6;
+  static constexpr int kNumBars = 2 + 4 * kStages + 6;
   static constexpr int kOffMisc = kOffBar + 8 * kNumBars;
   static constexpr int kBytes = kOffMisc + 16 + 1024;  // + slack for manual 1024-byte alignment
 };
@@ -122,8 +122,8 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* sK = smem + L::kOffK;
   uint8_t* sV = smem + L::kOffV;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
-  uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
+  uint64_t* q_full = bars;          // [2] one per query tile
+  uint64_t* k_full = bars + 2;
   uint64_t* k_empty = k_full + ST;
   uint64_t* v_full = k_empty + ST;
   uint64_t* v_empty = v_full + ST;
@@ -192,7 +192,8 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    mbar_init(q_full, 1);
+    mbar_init(&q_full[0], 1);
+    mbar_init(&q_full[1], 1);
     for (int i = 0; i < ST; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -206,12 +207,16 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     fence_barrier_init();
     if (n_max > 0) {
+      // in the order of first use: query tile 0 and K so that its scores can start, then query tile 1, then V
       const int nq = act1 ? 2 : 1;
-      mbar_arrive_expect_tx(q_full, nq * L::kQBytes);
-      for (int t = 0; t < nq; ++t)
+      auto load_q = [&](int t) {
+        mbar_arrive_expect_tx(&q_full[t], L::kQBytes);
         for (int c = 0; c < D / 64; ++c)
-          tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, q_full, c * 64, m0 + t * BM, h, b, p.oq);
+          tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, &q_full[t], c * 64, m0 + t * BM, h, b, p.oq);
+      };
+      load_q(0);
       load_k(0);
+      if (nq > 1) load_q(1);
       load_v(0);
       early_loads = true;
     }
@@ -267,12 +272,16 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                              (!first || g > 0) ? 1u : 0u);
         umma_commit(&o_done[t]);
       };
-      bool ok = mbar_wait(q_full, 0, ab, kSiteQFull);
+      bool ok = mbar_wait(&q_full[0], 0, ab, kSiteQFull);
       ok = ok && mbar_wait(&k_full[0], 0, ab, kSiteKFull);
       if (ok) {
         tc_fence_after_sync();
-        for (int t = 0; t < NT; ++t)
-          if (active(t, j_min)) issue_qk(t, 0);
+        if (active(0, j_min)) issue_qk(0, 0);
+        if (NT > 1 && act1) {
+          ok = mbar_wait(&q_full[1], 0, ab, kSiteQFull);
+          tc_fence_after_sync();
+          if (ok && active(1, j_min)) issue_qk(1, 0);
+        }
         umma_commit(&k_empty[0]);
         for (int i = 0; i < n_max && ok; ++i) {
           const int j = j_min + i;
