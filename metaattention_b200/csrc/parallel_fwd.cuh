@@ -28,6 +28,8 @@
 // query buffer and stored as whole rows.
 #pragma once
 
+#include <type_traits>
+
 #include "sm100.cuh"
 
 namespace b200 {
@@ -43,6 +45,12 @@ struct FunctorArgs {
 };
 
 // What a functor knows about the row it is working on.
+// A functor may offer tile_halves<N>() (see SoftmaxFunctor) beside tile<N>().
+template <class F, class = void>
+struct functor_half_store : std::false_type {};
+template <class F>
+struct functor_half_store<F, std::void_t<decltype(F::kHalfStore)>> : std::integral_constant<bool, F::kHalfStore> {};
+
 struct RowCtx {
   int b, h, q_idx;   // batch, head, query position of this thread's row
   int kv0;           // first KV position of the current tile
@@ -346,14 +354,20 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       }
-      const float o_scale = F::template tile<BN>(s, rs, ctx);
       // P (16-bit, two per column) overwrites the first BN/2 columns of S
-#pragma unroll
-      for (int c = 0; c < BN / 64; ++c) {
+      auto store_half = [&](int c) {
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) pk[i] = pack2<kBf16>(s[c * 64 + 2 * i], s[c * 64 + 2 * i + 1]);
         tmem_st32(tS + c * 32, pk);
+      };
+      float o_scale;
+      if constexpr (functor_half_store<F>::value && BN == 128) {
+        o_scale = F::template tile_halves<BN>(s, rs, ctx, store_half);
+      } else {
+        o_scale = F::template tile<BN>(s, rs, ctx);
+#pragma unroll
+        for (int c = 0; c < BN / 64; ++c) store_half(c);
       }
       if (!F::kUnitOScale && j > 0) {
         const bool need = (o_scale != 1.0f);
