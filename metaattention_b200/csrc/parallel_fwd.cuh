@@ -363,7 +363,17 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       float o_scale;
       if constexpr (functor_half_store<F>::value && BN == 128) {
-        o_scale = F::template tile_halves<BN>(s, rs, ctx, store_half);
+        // the functor hands over a piece of the row (BN / kPieces columns) as soon as its probabilities are final: the
+        // piece is on its way to tensor memory while the exponentials of the next one run
+        o_scale = F::template tile_pieces<BN>(s, rs, ctx, [&](int c) {
+          constexpr int W = BN / F::kPieces / 2;   // packed columns per piece
+          uint32_t pk[W];
+#pragma unroll
+          for (int i = 0; i < W; ++i) pk[i] = pack2<kBf16>(s[c * 2 * W + 2 * i], s[c * 2 * W + 2 * i + 1]);
+          if constexpr (W == 32) tmem_st32(tS + c * W, reinterpret_cast<const uint32_t(&)[32]>(pk));
+          else if constexpr (W == 16) tmem_st16(tS + c * W, pk);
+          else tmem_st8(tS + c * W, pk);
+        });
       } else {
         o_scale = F::template tile<BN>(s, rs, ctx);
 #pragma unroll
