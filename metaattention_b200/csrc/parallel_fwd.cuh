@@ -374,6 +374,19 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           else if constexpr (W == 16) tmem_st16(tS + c * W, pk);
           else tmem_st8(tS + c * W, pk);
         });
+      } else if constexpr (F::kUnitOScale && BN == 128) {
+        // no rescale: the row can be handed to the functor as four narrower tiles, each stored as soon as it is done
+        o_scale = 1.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          ctx.kv0 = kv0 + c * 32;
+          F::template tile<32>(reinterpret_cast<float(&)[32]>(s[c * 32]), rs, ctx);
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack2<kBf16>(s[c * 32 + 2 * i], s[c * 32 + 2 * i + 1]);
+          tmem_st16(tS + c * 16, pk);
+        }
+        ctx.kv0 = kv0;
       } else {
         o_scale = F::template tile<BN>(s, rs, ctx);
 #pragma unroll
