@@ -25,7 +25,7 @@ import sys
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-for p in (ROOT, os.path.join(ROOT, "metaattention_b200"), os.path.join(ROOT, "tests")):
+for p in (ROOT, os.path.join(ROOT, "metaattention_b200")):
     if p not in sys.path:
         sys.path.insert(0, p)
 
@@ -131,12 +131,12 @@ class ClockSampler:
 
 
 def build_softmax_engine():
-    import programs
+    from examples_b200 import programs
     return programs.softmax_engine(C2["B"], C2["H"], C2["S"], C2["D"], C2["Dv"], dtype=torch.bfloat16, is_causal=True)
 
 
 def build_sigmoid_engine():
-    import programs
+    from examples_b200 import programs
     return programs.sigmoid_engine(C3["B"], C3["H"], C3["S"], C3["D"], C3["Dv"], dtype=torch.bfloat16, is_causal=False,
                                    scale=C3["D"] ** -0.5)
 
@@ -215,7 +215,7 @@ def extras_parallel(steps, warmup):
         out["C3_sigmoid_noncausal"] = {"ms": ms, "tflops": fl / ms / 1e9}
         # the C2 shape under a causal sliding window of 1024 tokens (band mask: KV tiles outside the window are
         # skipped); FLOPs counted over the kept (q, kv) pairs
-        import programs
+        from examples_b200 import programs
         W = 1024
         S, B, H, D, Dv = C3["S"], C3["B"], C3["H"], C3["D"], C3["Dv"]
         eng_w = programs.masked_softmax_engine(B, H, S, D, Dv, lambda b, h, qi, ki: (qi >= ki) & (qi - ki < W))
@@ -283,7 +283,7 @@ def extras_retention(steps, warmup):
         del q, k, v
         # the two other users of the chunked kernel, at the shapes of the reference's functional tests
         # (testing/test.py:57-58), through the engine as the reference examples build it
-        import programs
+        from examples_b200 import programs
         B, H, S, D, Dv = 8, 32, 2048, 256, 256
         q, k, v, g = [t.cuda() for t in oracle_inputs.gla_inputs(B, H, S, D, Dv, 61)]
         eng = programs.gla_engine(B, H, S, D, Dv)

@@ -188,9 +188,12 @@ int attn_b200_mla_decode(const AttnB200MlaArgs* args, void* cuda_stream);
  *   - status_word is a caller-owned 4-byte DEVICE word: cleared by the call, non-zero after the
  *     stream has been synchronised iff a device-side wait ran out (100 + id of the wait);
  *   - no cudaMalloc / cudaFree / allocating library routine is called.
- * The first call made on a device looks up the array's address (once per device); make it before
- * any stream capture on that device.  All calls on a device share the array and it keeps the
- * previous call's contents (no part of it needs clearing); calls that overlap on the GPU race. */
+ * The first call made on a device looks up the array's address (once per device).  With CUDA's lazy
+ * module loading that look-up, or the first launch, is also the moment the driver loads the library's
+ * device code on that device and reserves the 32 MiB of the array: make this first call at start-up,
+ * before any stream capture on the device and before the host's own arena claims what is left of the
+ * device memory.  All calls on a device share the array and it keeps the previous call's contents
+ * (no part of it needs clearing); calls that overlap on the GPU race. */
 int attn_b200_mla_decode_static(const AttnB200MlaArgs* args, int32_t* status_word, void* cuda_stream);
 
 /* Reads and clears the device-side status word of device `device`

@@ -274,24 +274,67 @@ class AttentionEngine:
             return _ForwardOnly.apply(self._run_parallel_impl, q, k, v, *custom)
         return self._run_parallel_impl(q, k, v, *custom)
 
+    def _custom_operands(self, custom, B, H, Sq, Skv, device):
+        """Checks the custom input tensors against their declared shapes and returns (tensors, element strides over
+        (batch, heads, seq_len, seq_len_kv)).  A named axis must have extent 1 (broadcast) or exactly the extent of
+        this call, a literal axis its declared extent: the kernel addresses the tensor by strides alone, so anything
+        smaller would be read out of bounds."""
+        extent = {0: B, 1: H, 2: Sq, 3: Skv}
+        names = {0: "batch", 1: "heads", 2: "seq_len", 3: "seq_len_kv"}
+        tensors, strides = [], []
+        for name, sym, t, want in zip(self.custom_names, self._custom_syms, custom, self._custom_dtypes):
+            if not isinstance(t, torch.Tensor):
+                raise TypeError(f"custom input {name!r} must be a tensor")
+            axes = custom_axes(sym)
+            if t.dim() != len(axes):
+                raise ValueError(f"custom input {name!r}: declared with {len(axes)} axes {tuple(sym.shape_idx)}, got a "
+                                 f"tensor of shape {tuple(t.shape)}")
+            st = [0, 0, 0, 0]
+            for dim, ax in enumerate(axes):
+                size = t.shape[dim]
+                if ax is None:
+                    declared = sym.shape_idx[dim]
+                    if declared.isdigit() and size != int(declared):
+                        raise ValueError(f"custom input {name!r}: axis {dim} is declared as {declared}, got {size}")
+                    if size != 1:
+                        raise ValueError(f"custom input {name!r}: axis {dim} ({declared!r}, extent {size}) is not an axis "
+                                         "the forward kernel can index; use batch / heads / seq_len / seq_len_kv or 1")
+                    continue
+                if size != 1 and size != extent[ax]:
+                    raise ValueError(f"custom input {name!r}: axis {dim} ({names[ax]}) must have extent 1 or {extent[ax]}, "
+                                     f"got {size}")
+                if size > 1:
+                    st[ax] = t.stride(dim)
+            if t.is_cuda and t.device != device:
+                raise ValueError(f"custom input {name!r} is on {t.device}, q is on {device}")
+            t = t.to(device=device, dtype=want)
+            for dim, ax in enumerate(axes):   # strides of the converted tensor
+                if ax is not None and t.shape[dim] > 1:
+                    st[ax] = t.stride(dim)
+            tensors.append(t)
+            strides.append(st)
+        return tensors, strides
+
     def _run_parallel_impl(self, q, k, v, *custom):
         if len(custom) != len(self.custom_names):
             raise TypeError(f"expected {len(self.custom_names)} custom input tensor(s) {self.custom_names}, got {len(custom)}")
         if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
             raise ValueError("q, k, v must be [batch, seq, heads, dim]")
+        if k.device != q.device or v.device != q.device:
+            raise ValueError(f"q, k, v must be on one device (got {q.device}, {k.device}, {v.device})")
+        if not q.is_cuda:
+            raise native.NativeError("the forward kernel needs CUDA tensors: there is no CPU path")
+        B, S, H, _ = q.shape
+        tensors, strides = self._custom_operands(custom, B, H, S, k.shape[1], q.device)
+        # the entry points launch on the CURRENT device and stream: make q's device current for the whole call
+        with torch.cuda.device(q.device):
+            return self._launch_parallel(q, k, v, tensors, strides)
+
+    def _launch_parallel(self, q, k, v, tensors, strides):
         B, S, H, _ = q.shape
         Dv = v.shape[3]
         o = torch.empty((B, S, H, Dv), dtype=q.dtype, device=q.device)
         finals = [torch.empty((B, H, S), dtype=torch.float32, device=q.device) for _ in self.final_names]
-        tensors, strides = [], []
-        for sym, t, want in zip(self._custom_syms, custom, self._custom_dtypes):
-            t = t.to(device=q.device, dtype=want)
-            st = [0, 0, 0, 0]
-            for dim, ax in enumerate(custom_axes(sym)):
-                if ax is not None and t.shape[dim] > 1:
-                    st[ax] = t.stride(dim)
-            tensors.append(t)
-            strides.append(st)
         # split-KV when the launch would leave most SMs idle (decode: few query rows and heads against a long KV);
         # the split results are combined through the log-sum-exp, which only the built-in softmax provides
         splits, workspace = 1, None
@@ -308,7 +351,7 @@ class AttentionEngine:
         else:
             if self._jit_fn is None:
                 self._jit_fn = native_jit.load(self.functor_source)
-            status = native.device_status_word(q.device.index if q.device.index is not None else torch.cuda.current_device())
+            status = native.device_status_word(q.device.index)
             native.check(self._jit_fn(C.byref(args), native.current_stream_ptr(), status), "attn_b200_parallel_fwd_jit")
         self.last_final_rowscales = dict(zip(self.final_names, finals))
         return o

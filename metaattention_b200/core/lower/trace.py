@@ -266,33 +266,144 @@ def run_traced_attention(tr: TracedParallel, q, k, v, custom_tensors=(), causal=
     return o, finals
 
 
+class _NotSoftmaxShaped(Exception):
+    pass
+
+
+def softmax_shaped(tr: TracedParallel) -> bool:
+    """Structural half of the recognition of online softmax: True when the traced DAG can only be
+    an analytic function of the scores of the form the built-in functor implements.
+
+    Required: no index leaf (b, h, q_idx, kv_idx) and no custom tensor is reachable from any output;
+    every tile value is ``a * scores + (per-row value)`` with a constant ``a > 0``, or the
+    exponential (natural or base 2) of such a value; the new scores are such an exponential; tiles
+    are reduced only by a row maximum of the affine form and a row sum of the exponential; per-row
+    values combine through Add, Sub, Mul, Div, Exp, Exp2, Log, Log2 and exactly one Max, which is
+    ``max(running row scale, row maximum)``; the output is the accumulator divided by a per-row
+    value.  Within this class the functor is an analytic function of its inputs apart from that one
+    maximum, so agreement with softmax on random probes (``probe_softmax_scale``) identifies it;
+    score functions that saturate (tanh soft-capping), depend on positions (relative biases,
+    however far from the diagonal they start) or read custom inputs are outside the class and go
+    to the lowered functor."""
+    forbidden = {id(s) for s in tr.index_leaves.values()} | {id(s) for s in tr.custom.values()}
+    row_leaves = {id(s) for s in tr.rowscale_in.values()}
+    memo: dict[int, tuple] = {}
+    max_nodes: list = []
+
+    def kind_of(sym):
+        key = id(sym)
+        if key in memo:
+            return memo[key]
+        memo[key] = k = classify(sym)
+        return k
+
+    def classify(sym):
+        key = id(sym)
+        if key in forbidden:
+            raise _NotSoftmaxShaped
+        if key == id(tr.scores_in):
+            return ("aff",)
+        if key == id(tr.o_in):
+            return ("acc",)
+        if key in row_leaves:
+            return ("row",)
+        t = sym.code.type
+        if t == "Const":
+            return ("const", float(sym.code.value))
+        if t == "Var":
+            try:
+                return ("const", init_value(sym.code.name))
+            except ValueError:
+                raise _NotSoftmaxShaped
+        a = [kind_of(p) for p in sym.prev]
+        tags = [x[0] for x in a]
+        scalar = all(g in ("const", "row") for g in tags)
+        if t in ("Add", "Sub", "Mul", "Div") and scalar:
+            if tags == ["const", "const"]:
+                x, y = a[0][1], a[1][1]
+                try:
+                    return ("const", {"Add": x + y, "Sub": x - y, "Mul": x * y, "Div": x / y}[t])
+                except ZeroDivisionError:
+                    raise _NotSoftmaxShaped
+            return ("row",)
+        if t in ("Add", "Sub") and "aff" in tags and len(tags) == 2:
+            other = tags[1 - tags.index("aff")]
+            if other in ("const", "row") and not (t == "Sub" and tags[1] == "aff"):
+                return ("aff",)
+        if t == "Mul" and sorted(tags) == ["aff", "const"]:
+            if a[tags.index("const")][1] > 0:
+                return ("aff",)
+        if t == "Div" and tags == ["aff", "const"] and a[1][1] > 0:
+            return ("aff",)
+        if t == "Div" and tags == ["acc", "row"]:
+            return ("acc",)
+        if t in ("Exp", "Exp2"):
+            if tags == ["aff"]:
+                return ("exp",)
+            if scalar:
+                return ("row",)
+        if t in ("Log", "Log2") and scalar:
+            return ("row",)
+        if t == "ReduceMax" and tags == ["aff"]:
+            return ("rowmax",)
+        if t == "ReduceSum" and tags == ["exp"]:
+            return ("row",)
+        if t == "Max" and sorted(tags) == ["row", "rowmax"]:
+            leaf = sym.prev[tags.index("row")]
+            if id(leaf) in row_leaves:
+                max_nodes.append(sym)
+                return ("row",)
+        raise _NotSoftmaxShaped
+
+    try:
+        if kind_of(tr.scores_out)[0] != "exp" or kind_of(tr.o_out)[0] != "acc":
+            return False
+        for sym in [tr.o_scale, *tr.rowscale_out.values(), *tr.final.values()]:
+            if sym is not None and kind_of(sym)[0] not in ("row", "const"):
+                return False
+    except _NotSoftmaxShaped:
+        return False
+    return len({id(s) for s in max_nodes}) == 1
+
+
 def probe_softmax_scale(tr: TracedParallel) -> float | None:
     """If the traced functor computes online softmax of ``scale * score`` (any
     algebraically equivalent form, natural or base-2 exponentials) with outputs
     o / rowsum and a single final row scale equal to the log-sum-exp, return
-    ``scale``; else None.  Decided by running the trace on a small random
-    problem and comparing with the closed form."""
+    ``scale``; else None.  The DAG must have the shape ``softmax_shaped`` describes;
+    the scale and the remaining freedom (how the row scales are updated, what the
+    epilogue returns) are then settled by running the trace on small random problems
+    at two logit magnitudes and comparing with the closed form."""
     if tr.custom or len(tr.final) != 1 or tr.o_scale is None or len(tr.rowscale_in) != 2:
         return None
-    g = torch.Generator().manual_seed(7)
-    q = torch.randn(1, 48, 2, 16, generator=g)
-    k = torch.randn(1, 48, 2, 16, generator=g)
-    v = torch.randn(1, 48, 2, 8, generator=g)
-    try:
-        o, finals = run_traced_attention(tr, q, k, v, causal=True, block_n=16)
-    except Exception:
+    if not softmax_shaped(tr):
         return None
-    lse = next(iter(finals.values()))
-    s = torch.einsum("bshd,bthd->bhst", q, k)
-    causal = torch.ones(48, 48, dtype=torch.bool).tril()
-    # the scale is identified from the lse of rows with two unmasked entries
-    for scale in _candidate_scales(s, lse):
-        sm = (s * scale).masked_fill(~causal, float("-inf"))
-        want_lse = torch.logsumexp(sm, -1)
-        want_o = torch.einsum("bhst,bthd->bshd", torch.softmax(sm, -1), v)
-        if torch.allclose(lse, want_lse, atol=1e-4, rtol=1e-4) and torch.allclose(o, want_o, atol=1e-4, rtol=1e-4):
-            return float(scale)
-    return None
+    g = torch.Generator().manual_seed(7)
+    found = None
+    for magnitude in (1.0, 5.0):
+        q = torch.randn(1, 48, 2, 16, generator=g) * magnitude
+        k = torch.randn(1, 48, 2, 16, generator=g)
+        v = torch.randn(1, 48, 2, 8, generator=g)
+        try:
+            o, finals = run_traced_attention(tr, q, k, v, causal=True, block_n=16)
+        except Exception:
+            return None
+        lse = next(iter(finals.values()))
+        s = torch.einsum("bshd,bthd->bhst", q, k)
+        causal = torch.ones(48, 48, dtype=torch.bool).tril()
+        # row 0 attends to one key, so its lse is scale * score
+        scales = _candidate_scales(s, lse) if found is None else [found]
+        matched = None
+        for scale in scales:
+            sm = (s * scale).masked_fill(~causal, float("-inf"))
+            want_lse = torch.logsumexp(sm, -1)
+            want_o = torch.einsum("bhst,bthd->bshd", torch.softmax(sm, -1), v)
+            if torch.allclose(lse, want_lse, atol=1e-4, rtol=1e-4) and torch.allclose(o, want_o, atol=1e-4, rtol=1e-4):
+                matched = float(scale)
+        if matched is None:
+            return None
+        found = matched
+    return found
 
 
 def _candidate_scales(s, lse):

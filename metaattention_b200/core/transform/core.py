@@ -286,24 +286,51 @@ def _eval_mask_2d(mod_fn, b: int, h: int, q_len: int, kv_len: int, device) -> Te
         return fn(bi, hi, q.view(-1), kv.view(-1)).to(torch.bool)
 
 
+class _Watched(torch.Tensor):
+    """A tensor that remembers whether any torch operation was applied to it."""
+
+    touched = False
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        _Watched.touched = True
+        plain = lambda x: x.as_subclass(torch.Tensor) if isinstance(x, _Watched) else x  # noqa: E731
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*torch.utils._pytree.tree_map(plain, args), **torch.utils._pytree.tree_map(plain, kwargs or {}))
+
+
 def mask_depends_on_batch_head(mod_fn, B: int, H: int, q_len: int, kv_len: int, device="cpu") -> bool:
-    """True when the mask differs between (0,0) and the other corners of the
-    (batch, head) range, probed on a strided sub-grid of positions."""
-    sq = max(1, q_len // 64)
-    sk = max(1, kv_len // 64)
+    """True when ``mask_mod`` may give different masks for different (batch, head) pairs.
+
+    Decided by use, not by sampling: the mask function is called once with batch and head indices that record
+    any operation applied to them.  A function that never touches them cannot depend on them; one that does is
+    treated as dependent (the general per-(batch, head) path is always correct).  If the function cannot be
+    called on such indices, every (batch, head) pair is compared with the first on a strided sub-grid of positions
+    and on the rows and columns next to the diagonal."""
+    if B * H <= 1:
+        return False
+    q = torch.arange(0, q_len, max(1, q_len // 64), device=device).view(-1, 1)
+    kv = torch.arange(0, kv_len, max(1, kv_len // 64), device=device).view(1, -1)
+    try:
+        _Watched.touched = False
+        bi = torch.tensor(0, device=device).as_subclass(_Watched)
+        hi = torch.tensor(0, device=device).as_subclass(_Watched)
+        mod_fn(bi, hi, q, kv)
+        return _Watched.touched
+    except Exception:
+        pass
 
     def sample(b, h):
         bi = torch.tensor(b, device=device)
         hi = torch.tensor(h, device=device)
-        q = torch.arange(0, q_len, sq, device=device).view(-1, 1)
-        kv = torch.arange(0, kv_len, sk, device=device).view(1, -1)
-        return torch.as_tensor(mod_fn(bi, hi, q, kv)).to(torch.bool).expand(q.numel(), kv.numel())
+        out = torch.as_tensor(mod_fn(bi, hi, q, kv)).to(torch.bool).expand(q.numel(), kv.numel())
+        n = min(q_len, kv_len)
+        d = torch.arange(n, device=device)
+        near = [torch.as_tensor(mod_fn(bi, hi, d, (d + off).clamp(0, kv_len - 1))).to(torch.bool).expand(n) for off in (-1, 0, 1)]
+        return torch.cat([out.reshape(-1), *near])
 
     base = sample(0, 0)
-    for b, h in {(B - 1, 0), (0, H - 1), (B - 1, H - 1), (B // 2, H // 2)}:
-        if not torch.equal(base, sample(b, h)):
-            return True
-    return False
+    return any(not torch.equal(base, sample(b, h)) for b in range(B) for h in range(H) if (b, h) != (0, 0))
 
 
 def create_mask(mod_fn, B: Optional[int], H: Optional[int], Q_LEN: int, KV_LEN: int,

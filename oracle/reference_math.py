@@ -9,10 +9,12 @@ pinning: the reference stores no golden vectors (its tests draw unseeded
 random inputs), so the oracle is pinned against outputs of the reference's
 own closures, extracted from testing/test.py and executed on seeded inputs by
 tests/golden/make_golden.py; the resulting fixtures are committed under
-tests/golden/ and checked by tests/test_oracle_golden.py.  Two items have no
-reference closure and are therefore "parity unpinned": the log-sum-exp output
-of softmax attention (defined only by examples/mha.py:64-71) and the
-per-head group normalisation of the retention output.
+tests/golden/ and checked by tests/test_oracle_golden.py (softmax, sigmoid,
+relu, retention, MLA, gated retention, Mamba2, MHA decode, block-sparse GQA
+decode).  Two items have no reference closure and are therefore "parity
+unpinned": the log-sum-exp output of softmax attention (defined only by
+examples/mha.py:64-71) and the per-head group normalisation of the retention
+output.
 """
 
 from __future__ import annotations
@@ -174,3 +176,22 @@ def mla_decode_lse(q, q_pe, kv, k_pe):
     key = torch.cat([kv, k_pe], dim=-1)
     s = torch.einsum("bhgd,bshd->bhgs", query, key) / math.sqrt(query.shape[-1])
     return torch.logsumexp(s, dim=-1).reshape(B, H)
+
+
+def sparse_gqa_decode(q, k, v, block_mask, cache_seqlens, block_size: int):
+    """testing/test.py:654-694 (``ref_program_torch``): one query token per sequence, grouped KV heads, only
+    the KV blocks flagged in ``block_mask`` [B, Hkv, blocks] and the first ``cache_seqlens[b]`` positions take
+    part in the softmax; scale 1/sqrt(D).  q: [B,1,H,D], k: [B,S,Hkv,D], v: [B,S,Hkv,Dv]; query head
+    (h*g + j) uses KV head h.  Returns [B,H,Dv] fp32."""
+    q, k, v = q.float(), k.float(), v.float()
+    B, _, H, D = q.shape
+    S, Hkv = k.shape[1], k.shape[2]
+    g = H // Hkv
+    keep = block_mask.bool().repeat_interleave(block_size, dim=-1)[..., :S]            # [B, Hkv, S]
+    if keep.shape[-1] < S:
+        keep = torch.nn.functional.pad(keep, (0, S - keep.shape[-1]))
+    keep = keep & (torch.arange(S).view(1, 1, S) < cache_seqlens.view(B, 1, 1))
+    s = torch.einsum("bhgd,bshd->bhgs", q[:, 0].view(B, Hkv, g, D), k) / math.sqrt(D)
+    s = s.masked_fill(~keep[:, :, None, :], float("-inf"))
+    o = torch.einsum("bhgs,bshd->bhgd", torch.softmax(s, dim=-1), v)
+    return o.reshape(B, H, v.shape[-1])

@@ -3,6 +3,8 @@ closures on seeded inputs.  Run in a container that has the reference checkout:
 
     python tests/golden/make_golden.py [/path/to/reference]
 
+(default: $ATTN_B200_REFERENCE, then baseline/_ref/ of this repository, then /root/reference)
+
 The reference's functional suite (testing/test.py) cannot be imported as a
 module (it needs termcolor, matplotlib and a GPU at import time), so the
 closures -- plain functions nested inside the test functions -- are located
@@ -25,7 +27,44 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import inputs  # noqa: E402
 
 
-def extract(tree, source, outer: str, inner: str, extra_globals=None):
+# mask functions whose block masks are pinned (name -> mask_mod); tests/test_oracle_golden.py imports this table
+MASK_CASES = {
+    "causal": lambda b, h, q, kv: q >= kv,
+    "full": lambda b, h, q, kv: q >= 0,
+    "sliding_window_100": lambda b, h, q, kv: (q >= kv) & (q - kv < 100),
+    "band_70_40": lambda b, h, q, kv: (kv - q <= 40) & (q - kv <= 70),
+    "per_head_offset": lambda b, h, q, kv: q >= kv + 64 * h,
+    "per_batch_prefix": lambda b, h, q, kv: (kv <= q) | (kv < 32 * (b + 1)),
+    "checker": lambda b, h, q, kv: ((q // 64) + (kv // 64)) % 2 == 0,
+    "document": lambda b, h, q, kv: (q // 192 == kv // 192) & (q >= kv),
+}
+# (batch, heads, q_len, kv_len, q block, kv block)
+MASK_SHAPES = [(2, 3, 512, 512, 128, 128), (1, 2, 384, 384, 64, 64), (2, 2, 256, 256, 128, 64)]
+
+
+def block_mask_goldens(ref_root):
+    """int8 block masks, index lists and the two causal predicates from the reference's own helpers
+    (attention_engine/core/transform/core.py:455-506), imported from its checkout."""
+    sys.path.insert(0, os.path.join(ref_root, "attention_engine"))
+    for name in [m for m in sys.modules if m == "core" or m.startswith("core.")]:
+        del sys.modules[name]   # our own top-level ``core`` package may be loaded already
+    import importlib
+    ref = importlib.import_module("core.transform.core")
+    out = {}
+    for mname, fn in MASK_CASES.items():
+        for shape in MASK_SHAPES:
+            B, H, Q, KV, bq, bk = shape
+            bm = ref.create_block_mask(fn, B, H, Q, KV, "cpu", bq, bk)
+            out[(mname, shape)] = dict(block_mask=bm.clone(), is_causal=bool(ref.is_causal_mask(bm, bq, bk)),
+                                       is_less_causal=bool(ref.is_less_causal_mask(bm, bq, bk)),
+                                       block_idx=ref.create_block_idx(fn, B, H, Q, KV, "cpu", bq, bk).clone())
+    sys.path.pop(0)
+    for name in [m for m in sys.modules if m == "core" or m.startswith("core.")]:
+        del sys.modules[name]
+    return out
+
+
+def extract(tree, source, outer: str, inner: str, extra_globals=None, edit=None):
     for node in ast.walk(tree):
         if isinstance(node, ast.FunctionDef) and node.name == outer:
             for sub in ast.walk(node):
@@ -35,13 +74,19 @@ def extract(tree, source, outer: str, inner: str, extra_globals=None):
                     ns = {"torch": torch, "F": F, "rearrange": rearrange, "einsum": einsum, "repeat": repeat,
                           "math": math}
                     ns.update(extra_globals or {})
+                    if edit is not None:
+                        seg = edit(seg)
                     exec(textwrap.dedent(seg), ns)
                     return ns[inner]
     raise KeyError(f"{outer}.{inner} not found")
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, os.path.dirname(HERE))
+    from conftest import reference_root
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else reference_root()
+    if ref_root is None:
+        raise SystemExit("no checkout of the reference found: pass its path")
     path = os.path.join(ref_root, "testing", "test.py")
     source = open(path).read()
     tree = ast.parse(source)
@@ -105,6 +150,34 @@ def main():
     # the reference layout is [B,S,H,*]: x = v, B = k, C = q
     o = ref(v.float().transpose(1, 2), dt.transpose(1, 2), A[0], k.float().transpose(1, 2), q.float().transpose(1, 2), chunk_size=64)
     out["mamba2"] = dict(shape=(B, HQ, HK, HV, S, D, Dv), seed=71, o=o.transpose(1, 2).contiguous())
+
+    # MHA decode (testing/test.py:131-148): a few query rows against a longer KV, no mask
+    ref = extract(tree, source, "test_softmaxattention_decode", "ref")
+    B, H, Sq, KV, D = 2, 4, 3, 320, 64
+    g = torch.Generator().manual_seed(81)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, KV, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, KV, H, D, generator=g).to(torch.bfloat16)
+    out["mha_decode"] = dict(shape=(B, H, Sq, KV, D, D), seed=81, o=ref(q.float(), k.float(), v.float()).contiguous())
+
+    # block-sparse, variable-length GQA decode (testing/test.py:654-694).  The closure builds two index tensors on
+    # device 'cuda'; that literal is replaced by 'cpu', nothing else is touched.
+    ref = extract(tree, source, "test_sparse_gqa_decode", "ref_program_torch", edit=lambda seg: seg.replace("'cuda'", "'cpu'"))
+    B, H, G, S, D, block = 2, 8, 2, 512, 64, 32
+    g = torch.Generator().manual_seed(91)
+    q = torch.randn(B, 1, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, G, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, G, D, generator=g).to(torch.bfloat16)
+    lens = torch.tensor([S, 300], dtype=torch.int32)
+    nblk = S // block
+    bmask = torch.rand(B, G, nblk, generator=g) < 0.4
+    bmask[:, :, 0] = True   # every (batch, kv head) keeps at least its first block
+    o = ref(q.float(), k.float(), v.float(), bmask, lens, S, nblk, block)
+    out["sparse_gqa_decode"] = dict(shape=(B, H, G, S, D, D), seed=91, block=block, cache_seqlens=lens, block_mask=bmask,
+                                    o=o.contiguous())
+
+    torch.save(block_mask_goldens(ref_root), os.path.join(HERE, "block_masks.pt"))
+    print("block_masks", len(MASK_CASES) * len(MASK_SHAPES), "cases")
 
     for name, rec in out.items():
         rec["o"] = rec["o"].to(torch.float32)

@@ -8,7 +8,8 @@ import os
 import pytest
 import torch
 
-import programs
+from conftest import reference_root
+from examples_b200 import programs
 from attn_engine import AttentionEngine, OnlineFunc
 from core import CustomIO, SymbolicArray, SymbolScalar, Var, meta_tensor
 from core.lower import functor as fl
@@ -125,12 +126,13 @@ def test_engine_needs_cuda_tensors():
         e(q, k, v)   # CPU tensors: there is no CPU fallback
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/examples"), reason="reference checkout not present")
+@pytest.mark.skipif(reference_root() is None, reason="reference checkout not present")
 def test_reference_examples_construct_unchanged():
     """The reference's own example programs run unchanged on top of this package."""
     import importlib
     import sys
-    sys.path.insert(0, "/root/reference")
+    ref = reference_root()
+    sys.path.insert(0, ref)
     try:
         mha = importlib.import_module("examples.mha")
         assert mha.causal_softmax_attention(1, 4, 512, 128, 128, dtype=torch.bfloat16).functor_kind == "builtin_softmax"
@@ -156,7 +158,7 @@ def test_reference_examples_construct_unchanged():
         e = mb.mamba2(1, 1, 512, 128, 64, HK=1, HV=8)
         assert e.custom_names == ["A", "dt"] and e.H == 8 and e.HK == 1
     finally:
-        sys.path.remove("/root/reference")
+        sys.path.remove(ref)
 
 
 def test_band_masks_are_recognised():
@@ -171,3 +173,53 @@ def test_band_masks_are_recognised():
         classify_mask(lambda b, h, q, kv: (q + kv) % 2 == 0, 1, 1, 128, 128)   # not a band
     with pytest.raises(NotImplementedError):
         classify_mask(lambda b, h, q, kv: (kv <= q) & (h >= 0) & (b == 0), 2, 1, 128, 128)   # depends on the batch index
+
+
+def _softmax_with_score_mod(score_mod, S=256, D=64):
+    return AttentionEngine(programs._meta(1, 2, S, D, D, torch.bfloat16), CustomIO({}), score_mod=score_mod,
+                           mask_mod=programs.causal, online_func=programs.NaturalSoftmax())
+
+
+def test_look_alikes_of_softmax_are_lowered_not_recognised():
+    """Only DAGs that can be nothing but online softmax reach the built-in functor: a soft cap (tanh saturates only for
+    large logits), a relative bias that starts far from the diagonal, a per-head slope or a custom bias all look like
+    softmax on a small random probe and must be lowered."""
+    for cap in (50.0, 100.0):
+        e = _softmax_with_score_mod(lambda s, c, b, h, q, kv, cap=cap: (s * 0.125 / cap).tanh() * cap)
+        assert e.functor_kind == "lowered"
+    far = _softmax_with_score_mod(lambda s, c, b, h, q, kv: s * 0.125 - ((q - kv) - 64.0).max(0.0) * 0.5)
+    assert far.functor_kind == "lowered"
+    slope = _softmax_with_score_mod(lambda s, c, b, h, q, kv: s * 0.125 + h * 0.0)
+    assert slope.functor_kind == "lowered"
+    plain = _softmax_with_score_mod(lambda s, c, b, h, q, kv: s / 8.0)
+    assert plain.functor_kind == "builtin_softmax" and abs(plain._fparams[0] - 0.125) < 1e-6
+
+
+def test_mask_dependence_on_batch_or_head_is_decided_by_use():
+    from core.transform.core import mask_depends_on_batch_head
+    assert not mask_depends_on_batch_head(programs.causal, 4, 9, 512, 512)
+    assert not mask_depends_on_batch_head(programs.sliding_window_mask, 4, 9, 512, 512)
+    # differs only at one head in the middle of the range: corner sampling would miss it
+    assert mask_depends_on_batch_head(lambda b, h, q, kv: (q >= kv) | (h == 4), 4, 9, 512, 512)
+    assert mask_depends_on_batch_head(lambda b, h, q, kv: (q >= kv) & (b >= 0), 4, 9, 512, 512)
+
+
+def test_custom_input_shapes_are_checked_before_launch():
+    e = programs.retention_parallel_engine(1, 2, 256, 64, 64)          # mask declared (1, heads, seq_len, seq_len_kv)
+    ok = torch.zeros(1, 2, 256, 256)
+    tensors, strides = e._custom_operands((ok,), 1, 2, 256, 256, torch.device("cpu"))
+    assert strides[0] == [0, 256 * 256, 256, 1]
+    e._custom_operands((torch.zeros(1, 1, 256, 256),), 1, 2, 256, 256, torch.device("cpu"))   # broadcast over heads
+    for bad in (torch.zeros(1, 2, 256, 255), torch.zeros(1, 2, 200, 256), torch.zeros(2, 256, 256), torch.zeros(2, 2, 256, 256)):
+        with pytest.raises(ValueError):
+            e._custom_operands((bad,), 1, 2, 256, 256, torch.device("cpu"))
+    s = programs.sigmoid_engine(1, 2, 256, 64, 64)
+    with pytest.raises(ValueError):
+        s._custom_operands((torch.zeros(3),), 1, 2, 256, 256, torch.device("cpu"))
+
+
+def test_operands_on_different_devices_are_refused():
+    e = programs.softmax_engine(1, 2, 128, 64, 64)
+    q, k, v = inputs.attention_bshd(1, 2, 128, 64, 64, 1)
+    with pytest.raises(ValueError, match="one device"):
+        e._run_parallel_impl(q, k.to("meta"), v)

@@ -13,7 +13,7 @@ import os
 import pytest
 import torch
 
-import programs
+from examples_b200 import programs
 from attn_engine.linear_attn_engine import linear_attention_forward
 from core.native import lib
 from oracle import inputs, reference_math as rm

@@ -7,7 +7,7 @@ import os
 import pytest
 import torch
 
-import programs
+from examples_b200 import programs
 from attn_engine.mla import flash_mla_with_kvcache, mla_decode_forward, plan_splits
 from core.native import lib
 from oracle import inputs, reference_math as rm

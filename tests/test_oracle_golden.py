@@ -104,3 +104,30 @@ def test_mamba2_ssd():
     q, k, v, dt, A = inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, g["seed"])
     o = rm.decayed_linear_attention(q, k, v.float() * dt[..., None], dt * A.view(1, HV, 1), scale=1.0)
     close(o, g["o"], tol=1e-4)
+
+
+def test_mha_decode():
+    """testing/test.py:131-148: a few query rows against a longer KV, no mask"""
+    g = load("mha_decode")
+    B, H, Sq, KV, D, Dv = g["shape"]
+    gen = torch.Generator().manual_seed(g["seed"])
+    q = torch.randn(B, Sq, H, D, generator=gen).to(torch.bfloat16)
+    k = torch.randn(B, KV, H, D, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, KV, H, Dv, generator=gen).to(torch.bfloat16)
+    close(rm.softmax_attention(q, k, v, causal=False), g["o"])
+
+
+def sparse_decode_inputs(g):
+    B, H, G, S, D, Dv = g["shape"]
+    gen = torch.Generator().manual_seed(g["seed"])
+    q = torch.randn(B, 1, H, D, generator=gen).to(torch.bfloat16)
+    k = torch.randn(B, S, G, D, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, S, G, Dv, generator=gen).to(torch.bfloat16)
+    return q, k, v
+
+
+def test_sparse_gqa_decode():
+    """testing/test.py:654-694: block mask per (batch, kv head) and ragged cache lengths"""
+    g = load("sparse_gqa_decode")
+    q, k, v = sparse_decode_inputs(g)
+    close(rm.sparse_gqa_decode(q, k, v, g["block_mask"], g["cache_seqlens"], g["block"]), g["o"])

@@ -11,7 +11,7 @@ import os
 import pytest
 import torch
 
-import programs
+from examples_b200 import programs
 from core.native import lib as native_lib
 from oracle import inputs, reference_math as rm
 

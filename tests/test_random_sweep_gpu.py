@@ -6,7 +6,7 @@ import random
 import pytest
 import torch
 
-import programs
+from examples_b200 import programs
 from attn_engine import AttentionEngine
 from attn_engine.linear_attn_engine import linear_attention_forward
 from attn_engine.mla import mla_decode_forward
