@@ -3,15 +3,24 @@
     python bench.py --gpus N --steps K --warmup W            # our arm
     python bench.py --impl reference --gpus N --steps K ...   # the reference's PyTorch math on the host cores
 
-Headline workload (N=1): BASELINE config 2 -- causal softmax MHA forward, bf16, B=8 H=32 S=4096 D=128,
-output bf16 + per-row log-sum-exp fp32.  A step is one forward over one batch of synthetic inputs.
-With N>1 every rank runs the same workload on its own batch shard (batch x head sharding, no
+Headline workload (N=1): causal softmax MHA forward, bf16, B=8 H=32 S=4096 D=128, output bf16 + per-row
+log-sum-exp fp32 (the configuration the reference's metric is quoted on).  A step is one forward over one batch of
+synthetic inputs.  With N>1 every rank runs the same workload on its own batch shard (batch x head sharding, no
 collective on the data path): weak scaling, value = total FLOPs of all ranks / max-over-ranks time.
 
-Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` is the same
-forward through AttentionEngine.__call__ with pinned HOST buffers, host<->device copies inside the
-timed region; `roofline` is the forward kernel against the measured bf16 tensor peak; `cpu_baseline`
-is the CPU oracle on a bounded sample; `extras` holds the other BASELINE configs (device-timed).
+Prints ONE JSON line (rank 0).
+  value      K steps timed with CUDA events after the warm-up steps AND a heat-up of at least one second of the same
+             launches, so that the GPU is in the power-capped state a long-running job sees: a sustained number.
+  roofline   that kernel against the measured SUSTAINED bf16 tensor peak; `roofline.sustained_leg` is the heat-up
+             itself (>= 1 s, timed as one region), `roofline.burst` the same K steps after an idle pause against the
+             measured BURST peak.
+  e2e        the same forward through AttentionEngine.forward_host with pinned HOST buffers, host<->device copies
+             inside the timed region, next to the time the same copies take alone (`copy_ceiling_ms`).
+  cpu_baseline  the CPU oracle on a bounded sample.
+  extras     the other workloads of the metric, device-timed launch by launch, each with its own roofline block and
+             clock samples: sigmoid attention (tensor-bound), chunked RetNet retention (tensor-bound), MLA decode
+             (HBM-bound, L2 flushed between launches); with N>1 also retention and MLA decode on a 1/N batch shard of
+             the SAME global problem (strong scaling).
 """
 
 import argparse
@@ -33,22 +42,42 @@ import torch  # noqa: E402
 
 from oracle import inputs as oracle_inputs  # noqa: E402  (input factory shared with the parity tests)
 
-WORKLOAD = "C2: softmax MHA fwd causal bf16 B=8 H=32 S=4096 D=128 (+lse)"
+WORKLOAD = "softmax MHA fwd causal bf16 B=8 H=32 S=4096 D=128 (+lse)"
 C2 = oracle_inputs.CONFIGS["C2"]
 C3 = oracle_inputs.CONFIGS["C3"]
+C4 = oracle_inputs.CONFIGS["C4"]
+C5 = oracle_inputs.CONFIGS["C5"]
 METRIC = "fwd_attention_tflops"
 UNIT = "TFLOP/s"
 
-# DRAM bytes (read+write) of one forward-kernel launch at the C2 shape from an ncu capture
-# (profiles/parallel_fwd_softmax_c2.md).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 1.017e9  # 254.2 MB measured at batch 2, scaled x4 to batch 8
+# DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/, scaled to the full workload
+# by the units processed (traffic grows in proportion to the batch): see each profile for the captured case.
+NCU_TRAFFIC = {
+    "softmax": 1.017e9,     # profiles/parallel_fwd_softmax_c2.md: 254.2 MB at batch 2, x4
+    "retention": 7.16e8,    # profiles/linear_fwd_kernel_b2_s4096.md: 179 MB at batch 2, x4
+    "mla": 1.296e9,         # profiles/mla_split_kernel_b74_s4096.md: 374.2 MB at 74 x 4096 tokens, x (128 x 8192)/(74 x 4096)
+}
 
 
-def c2_flops(B=C2["B"], H=C2["H"], S=C2["S"], D=C2["D"], Dv=C2["Dv"], causal=True):
+def attention_flops(B, H, S, D, Dv, causal):
     """Algorithmic FLOPs: 2*B*H*S^2*(D+Dv), halved for a causal mask (reference convention,
     attention_engine/benchmark/bench_utils.py:770-771)."""
     f = 2.0 * B * H * S * S * (D + Dv)
     return f * (0.5 if causal else 1.0)
+
+
+def c2_flops(B=C2["B"], H=C2["H"]):
+    return attention_flops(B, H, C2["S"], C2["D"], C2["Dv"], True)
+
+
+def retention_flops(B, H, S, Dk, Dv, chunk=64):
+    """Chunked count with the reference's chunk of 64: B*H*S*[2*C*(Dk+Dv) + 4*Dk*Dv]."""
+    return float(B * H * S) * (2 * chunk * (Dk + Dv) + 4 * Dk * Dv)
+
+
+def mla_bytes(B, H, S, D, Dv):
+    """Algorithmic bytes: latent KV + Q + O (16-bit)."""
+    return (B * S * D + B * H * D + B * H * Dv) * 2
 
 
 def measured_peaks():
@@ -62,17 +91,19 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi.  The process is started ahead of the warm-up
-    (its first line takes a while); every line carries nvidia-smi's own timestamp and only the lines stamped
-    inside the window [mark_begin, mark_end] are used."""
+    """Samples SM clock and throttle reasons with nvidia-smi for the whole run (its first line takes a while); every
+    line carries nvidia-smi's own timestamp, and each measurement marks its window and reads back the lines stamped
+    inside it."""
 
     FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index: int):
         self.proc = None
         self.gpu = gpu_index
-        self.t0 = self.t1 = self.t_timed = None
+        self.windows = {}
+        self.rows = None
 
     def start(self):
         try:
@@ -82,18 +113,16 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def mark_begin(self):
-        self.t0 = datetime.datetime.now()
+    def begin(self, name):
+        self.windows[name] = [datetime.datetime.now(), None]
 
-    def mark_timed_end(self):
-        self.t_timed = datetime.datetime.now()
-
-    def mark_end(self):
-        self.t1 = datetime.datetime.now()
+    def end(self, name):
+        self.windows[name][1] = datetime.datetime.now()
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            self.rows = []
+            return
         time.sleep(0.1)
         self.proc.terminate()
         try:
@@ -101,33 +130,30 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons, sm_timed = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        self.rows = []
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
             try:
                 stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
-                clock, clock_max = float(parts[1]), float(parts[2])
+                self.rows.append((stamp, float(parts[1]), float(parts[2]), [v.lower().startswith("active") for v in parts[3:7]]))
             except ValueError:
                 continue
-            if self.t0 is not None and not (self.t0 <= stamp <= self.t1):
-                continue
-            sm.append(clock)
-            mx.append(clock_max)
-            if self.t_timed is not None and stamp <= self.t_timed:
-                sm_timed.append(clock)
-            for n, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
-        if sm_timed:   # the samples that fell inside the timed region itself
-            out["sm_mhz_timed_region"] = statistics.median(sm_timed)
-            out["samples_timed_region"] = len(sm_timed)
-        return out
+
+    def summary(self, name):
+        """{"sm_mhz": median inside the window, "sm_max_mhz", "reasons", "samples"}"""
+        if self.rows is None:
+            self.stop()
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        t0, t1 = self.windows.get(name, (None, None))
+        rows = [r for r in self.rows if t0 is not None and t1 is not None and t0 <= r[0] <= t1]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"], "samples": 0}
+        reasons = sorted({n for r in rows for n, on in zip(self.NAMES, r[3]) if on})
+        return {"sm_mhz": statistics.median(r[1] for r in rows), "sm_max_mhz": max(r[2] for r in rows), "reasons": reasons,
+                "samples": len(rows)}
 
 
 def build_softmax_engine():
@@ -148,32 +174,74 @@ def prebuild_functors():
     build_sigmoid_engine()
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline
+# ---------------------------------------------------------------------------------------------------------------
+
+def reference_root():
+    """A checkout of the reference project (holding testing/test.py), or None: $ATTN_B200_REFERENCE, then baseline/_ref/
+    of this repository, then /root/reference."""
+    for cand in (os.environ.get("ATTN_B200_REFERENCE"), os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
+        if cand and os.path.isfile(os.path.join(cand, "testing", "test.py")):
+            return cand
+    return None
+
+
+def reference_softmax_closure():
+    """(callable, kind): the reference's own PyTorch closure for softmax attention (testing/test.py:79-104), located
+    with `ast` in a checkout of the reference and executed unchanged (kind "_ref"); where no checkout is present, the
+    restatement of the same math in oracle/reference_math.py (kind "port")."""
+    root = reference_root()
+    if root is not None:
+        try:
+            import ast
+            import textwrap
+            import torch.nn.functional as F
+            from einops import einsum, rearrange, repeat
+            source = open(os.path.join(root, "testing", "test.py")).read()
+            for node in ast.walk(ast.parse(source)):
+                if isinstance(node, ast.FunctionDef) and node.name == "test_softmaxattention":
+                    for sub in ast.walk(node):
+                        if isinstance(sub, ast.FunctionDef) and sub.name == "ref":
+                            ns = {"torch": torch, "F": F, "rearrange": rearrange, "einsum": einsum, "repeat": repeat, "math": math}
+                            exec(textwrap.dedent(ast.get_source_segment(source, sub)), ns)
+                            fn = ns["ref"]
+                            return (lambda q, k, v: fn(q.float(), k.float(), v.float(), causal=True, softmax_scale=C2["D"] ** -0.5)), "_ref"
+        except Exception:
+            pass
+    from oracle import reference_math as rm
+    return (lambda q, k, v: rm.softmax_attention(q, k, v, True)), "port"
+
+
 def cpu_softmax_sample(n_heads: int, threads: int):
-    """Seconds for the CPU oracle on `n_heads` (batch, head) slices of the C2 problem."""
+    """(seconds, kind) for the CPU reference on `n_heads` (batch, head) slices of the headline problem: attention
+    output plus the per-row log-sum-exp."""
     from oracle import reference_math as rm
     torch.set_num_threads(threads)
+    fn, kind = reference_softmax_closure()
     S, D = C2["S"], C2["D"]
     q, k, v = oracle_inputs.attention_bshd(1, n_heads, S, D, D, C2["seed"], dtype=torch.bfloat16)
-    rm.softmax_attention(q[:, :, :1], k[:, :, :1], v[:, :, :1], True)  # warm-up
+    fn(q[:, :, :1], k[:, :, :1], v[:, :, :1])  # warm-up
     t0 = time.perf_counter()
     for h in range(n_heads):
-        rm.softmax_attention(q[:, :, h:h + 1], k[:, :, h:h + 1], v[:, :, h:h + 1], True)
-        rm.softmax_lse(q[:, :, h:h + 1], k[:, :, h:h + 1], True)
-    return time.perf_counter() - t0
+        fn(q[:, :, h:h + 1], k[:, :, h:h + 1], v[:, :, h:h + 1])
+        rm.softmax_lse(q[:, :, h:h + 1], k[:, :, h:h + 1], True)   # no reference closure returns the lse
+    return time.perf_counter() - t0, kind
 
 
 def run_reference(args, rank):
-    """The reference's PyTorch reference math (restated in oracle/) on the host cores."""
+    """The reference's own CPU implementation of the path (its PyTorch reference math) on the host cores."""
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     heads_per_step = 4
     flops_per_step = c2_flops(B=1, H=heads_per_step)
+    kind = "port"
     for _ in range(args.warmup):
         cpu_softmax_sample(1, threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_softmax_sample(heads_per_step, threads)
+        _, kind = cpu_softmax_sample(heads_per_step, threads)
     dt = time.perf_counter() - t0
     value = flops_per_step * args.steps / dt / 1e12
     sample = f"{heads_per_step} of {C2['B'] * C2['H']} (batch, head) slices per step, fp32 PyTorch, softmax + lse"
@@ -181,15 +249,18 @@ def run_reference(args, rank):
             "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "sample": sample},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def time_device(fn, steps, warmup, barrier):
-    for _ in range(warmup):
-        fn()
+# ---------------------------------------------------------------------------------------------------------------
+# timing helpers
+# ---------------------------------------------------------------------------------------------------------------
+
+def time_region(fn, steps, barrier=lambda: None):
+    """ms for `steps` back-to-back calls, one CUDA-event pair around all of them, a synchronize on both sides."""
     barrier()
     torch.cuda.synchronize()
     e0 = torch.cuda.Event(enable_timing=True)
@@ -200,86 +271,205 @@ def time_device(fn, steps, warmup, barrier):
     e1.record()
     torch.cuda.synchronize()
     barrier()
-    return e0.elapsed_time(e1)  # ms for all steps
+    return e0.elapsed_time(e1)
 
 
-def extras_parallel(steps, warmup):
-    """Device-timed numbers for BASELINE config 3 (sigmoid attention)."""
+def time_launches(fn, launches, warmup, flush=None):
+    """Per-launch ms (list): one CUDA-event pair around every launch; `flush` (if given) runs between launches, outside
+    the pairs."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    pairs = []
+    for _ in range(launches):
+        if flush is not None:
+            flush()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        pairs.append((e0, e1))
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in pairs]
+
+
+def heat_up(fn, seconds):
+    """Runs fn back to back for at least `seconds`; returns (launches, ms of the region by CUDA events)."""
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    n = 0
+    t0 = time.time()
+    e0.record()
+    while True:
+        for _ in range(20):
+            fn()
+        n += 20
+        torch.cuda.synchronize()
+        if time.time() - t0 >= seconds:
+            break
+    e1.record()
+    torch.cuda.synchronize()
+    return n, e0.elapsed_time(e1)
+
+
+def tensor_roofline(flops, ms, peaks, sustained, traffic=None):
+    achieved = flops / ms / 1e9
+    peak = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"]
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
+            "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'} cuBLAS bf16)"}
+
+
+def hbm_roofline(nbytes, ms, peaks, traffic=None):
+    achieved = nbytes / ms / 1e6
+    return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+            "traffic": traffic, "peak_source": f"{peaks['source']} (copy bandwidth)"}
+
+
+def launch_stats(times):
+    return {"ms": statistics.median(times), "ms_mean": statistics.fmean(times), "ms_min": min(times), "launches": len(times)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the other workloads of the metric
+# ---------------------------------------------------------------------------------------------------------------
+
+def extras_parallel(sampler, peaks, launches):
+    """Sigmoid attention via score_mod (non-causal, bf16, B=8 H=32 S=4096 D=128, scalar bias -ln 4096): tensor-bound."""
     out = {}
     try:
         eng = build_sigmoid_engine()
         q, k, v = [t.cuda() for t in oracle_inputs.attention_bshd(C3["B"], C3["H"], C3["S"], C3["D"], C3["Dv"], C3["seed"])]
         bias = torch.tensor([C3["bias"]], device="cuda")
-        ms = time_device(lambda: eng(q, k, v, bias), steps, warmup, lambda: None) / steps
-        fl = c2_flops(causal=False)
-        out["C3_sigmoid_noncausal"] = {"ms": ms, "tflops": fl / ms / 1e9}
-        # the C2 shape under a causal sliding window of 1024 tokens (band mask: KV tiles outside the window are
+        fl = attention_flops(C3["B"], C3["H"], C3["S"], C3["D"], C3["Dv"], False)
+        fn = lambda: eng(q, k, v, bias)  # noqa: E731
+        sampler.begin("sigmoid")
+        n, ms_heat = heat_up(fn, 1.0)
+        times = time_launches(fn, launches, 0)
+        sampler.end("sigmoid")
+        rec = launch_stats(times)
+        rec["tflops"] = fl / rec["ms"] / 1e9
+        rec["roofline"] = tensor_roofline(fl, rec["ms"], peaks, sustained=True)
+        rec["sustained_leg"] = {"launches": n, "seconds": ms_heat / 1e3, "ms_per_launch": ms_heat / n,
+                                "frac_of_sustained_peak": fl / (ms_heat / n) / 1e9 / peaks["bf16_tflops_sustained"]}
+        rec["l2"] = "inputs (805 MB) larger than L2"
+        out["sigmoid_noncausal_8x32x4096x128"] = rec
+        # the headline shape under a causal sliding window of 1024 tokens (band mask: KV tiles outside the window are
         # skipped); FLOPs counted over the kept (q, kv) pairs
         from examples_b200 import programs
         W = 1024
         S, B, H, D, Dv = C3["S"], C3["B"], C3["H"], C3["D"], C3["Dv"]
         eng_w = programs.masked_softmax_engine(B, H, S, D, Dv, lambda b, h, qi, ki: (qi >= ki) & (qi - ki < W))
-        ms_w = time_device(lambda: eng_w(q, k, v), steps, warmup, lambda: None) / steps
+        ms_w = statistics.median(time_launches(lambda: eng_w(q, k, v), 20, 3))
         pairs = sum(min(i + 1, W) for i in range(S))
-        out["C2_shape_sliding_window_1024"] = {"ms": ms_w, "tflops": 2.0 * B * H * pairs * (D + Dv) / ms_w / 1e9}
+        out["softmax_sliding_window_1024"] = {"ms": ms_w, "tflops": 2.0 * B * H * pairs * (D + Dv) / ms_w / 1e9}
+        # a mask that is not a band: causal inside documents of 1024 tokens, run as a block-sparse walk
+        eng_d = programs.masked_softmax_engine(B, H, S, D, Dv, lambda b, h, qi, ki: (qi // 1024 == ki // 1024) & (qi >= ki))
+        ms_d = statistics.median(time_launches(lambda: eng_d(q, k, v), 20, 3))
+        pairs = (S // 1024) * (1024 * 1025 // 2)
+        out["softmax_document_mask_1024_block_sparse"] = {"ms": ms_d, "tflops": 2.0 * B * H * pairs * (D + Dv) / ms_d / 1e9,
+                                                          "kept_tiles": eng_d._sparse_host["kept_tiles"], "all_tiles": eng_d._sparse_host["all_tiles"]}
         del q, k, v
+        # head dims of the reference's own suite and sweep (testing/test.py:55, testing/benchmark_h100.py:60-63)
+        for (D, Dv) in ((128, 256), (192, 128)):
+            B, H, S = 1, 16, 2048
+            g = torch.Generator(device="cuda").manual_seed(D)
+            q = torch.randn(B, S, H, D, generator=g, device="cuda").to(torch.bfloat16)
+            k = torch.randn(B, S, H, D, generator=g, device="cuda").to(torch.bfloat16)
+            v = torch.randn(B, S, H, Dv, generator=g, device="cuda").to(torch.bfloat16)
+            e = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)
+            ms = statistics.median(time_launches(lambda: e(q, k, v), 20, 3))
+            out[f"softmax_causal_1x16x2048_{D}_{Dv}"] = {"ms": ms, "tflops": attention_flops(B, H, S, D, Dv, True) / ms / 1e9}
     except Exception as exc:  # a missing extra must not take the headline number down
-        out["C3_sigmoid_noncausal"] = {"error": repr(exc)[:200]}
+        out["sigmoid_noncausal_8x32x4096x128_error"] = repr(exc)[:300]
+    torch.cuda.empty_cache()
     return out
 
 
-def extras_mla(steps, warmup):
-    """Device-timed numbers for BASELINE config 5 (MLA decode): algorithmic bytes = latent KV + Q + O."""
-    c = oracle_inputs.CONFIGS["C5"]
+def mla_case(B, H, S, D, Dv, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(B, H, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    kv = torch.empty(B, S, D, device="cuda", dtype=torch.bfloat16)
+    for b0 in range(0, B, 16):  # drawn in slices to bound the fp32 staging buffer
+        b1 = min(B, b0 + 16)
+        kv[b0:b1] = torch.randn(b1 - b0, S, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    return q, kv
+
+
+def l2_flusher():
+    buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")   # larger than the 126 MB L2
+    return buf.zero_
+
+
+def extras_mla(sampler, peaks, launches):
+    """MLA decode, bf16, 128 sequences x 8192 latent rows of 576, 128 heads: HBM-bound; algorithmic bytes = latent KV +
+    Q + O.  Q and O fit in L2, so L2 is flushed between launches."""
     out = {}
     try:
-        from attn_engine.mla import mla_decode_forward, plan_splits
-        B, H, S, D, Dv = c["B"], c["H"], c["S"], c["D"], c["Dv"]
-        g = torch.Generator(device="cuda").manual_seed(c["seed"])
-        q = torch.randn(B, H, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
-        kv = torch.empty(B, S, D, device="cuda", dtype=torch.bfloat16)
-        for b0 in range(0, B, 16):  # drawn in slices to bound the fp32 staging buffer
-            kv[b0:b0 + 16] = torch.randn(16, S, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
-        splits = plan_splits(B, H, S, D, Dv, torch.cuda.get_device_properties(0).multi_processor_count)
-        ms = time_device(lambda: mla_decode_forward(q, kv, Dv, D ** -0.5, num_splits=splits), steps, warmup, lambda: None) / steps
-        bytes_alg = (B * S * D + B * H * D + B * H * Dv) * 2
-        flops = 2.0 * B * H * S * (D + Dv)
-        peaks = measured_peaks()
-        out["C5_mla_decode"] = {"ms": ms, "gbs": bytes_alg / ms / 1e6, "tflops": flops / ms / 1e9, "num_splits": splits,
-                                "frac_of_hbm_peak": bytes_alg / ms / 1e6 / peaks["hbm_gbs"], "hbm_peak_gbs": peaks["hbm_gbs"],
-                                "algorithmic_bytes": bytes_alg}
+        from attn_engine import mla
+        B, H, S, D, Dv = C5["B"], C5["H"], C5["S"], C5["D"], C5["Dv"]
+        q, kv = mla_case(B, H, S, D, Dv, C5["seed"])
+        flush = l2_flusher()
+        fn = lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5)  # noqa: E731
+        sampler.begin("mla")
+        heat_up(fn, 0.5)
+        times = time_launches(fn, launches, 0, flush=flush)
+        sampler.end("mla")
+        nbytes = mla_bytes(B, H, S, D, Dv)
+        rec = launch_stats(times)
+        rec.update({"gbs": nbytes / rec["ms"] / 1e6, "tflops": 2.0 * B * H * S * (D + Dv) / rec["ms"] / 1e9, "algorithmic_bytes": nbytes,
+                    "roofline": hbm_roofline(nbytes, rec["ms"], peaks, NCU_TRAFFIC["mla"]), "l2": "flushed between launches (256 MB write)",
+                    "schedule": getattr(mla, "last_plan", None)})
+        out["mla_decode_128x8192x576"] = rec
         # the same cache seen as a pool of 64-token pages through a block table with the pages of every
         # sequence in scrambled order, and full-length cache_seqlens (the reference's native call)
+        g = torch.Generator(device="cuda").manual_seed(1)
         pages = S // 64
         perm = torch.stack([torch.randperm(pages, generator=g, device="cuda") + b * pages for b in range(B)]).to(torch.int32)
         pool = torch.empty(B * pages, 64, D, device="cuda", dtype=torch.bfloat16)
         pool[perm.view(-1).long()] = kv.view(B * pages, 64, D)
         lens = torch.full((B,), S, dtype=torch.int32, device="cuda")
-        ms_p = time_device(lambda: mla_decode_forward(q, pool, Dv, D ** -0.5, num_splits=splits, cache_seqlens=lens,
-                                                      block_table=perm), steps, warmup, lambda: None) / steps
-        out["C5_mla_decode_paged64"] = {"ms": ms_p, "gbs": bytes_alg / ms_p / 1e6}
-        del q, kv, pool
+        ms_p = statistics.median(time_launches(lambda: mla.mla_decode_forward(q, pool, Dv, D ** -0.5, cache_seqlens=lens, block_table=perm),
+                                               20, 3, flush=flush))
+        out["mla_decode_paged64"] = {"ms": ms_p, "gbs": nbytes / ms_p / 1e6}
+        del pool
+        # ragged lengths (uniform in [S/8, S]): bytes counted over the rows that exist
+        gl = torch.Generator().manual_seed(2)
+        lens_r = torch.randint(S // 8, S + 1, (B,), generator=gl).to(torch.int32).cuda()
+        ms_r = statistics.median(time_launches(lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5, cache_seqlens=lens_r), 20, 3, flush=flush))
+        nb_r = (int(lens_r.sum()) * D + B * H * D + B * H * Dv) * 2
+        out["mla_decode_ragged"] = {"ms": ms_r, "gbs": nb_r / ms_r / 1e6, "frac_of_hbm_peak": nb_r / ms_r / 1e6 / peaks["hbm_gbs"]}
+        del q, kv
     except Exception as exc:
-        out["C5_mla_decode"] = {"error": repr(exc)[:200]}
+        out["mla_decode_error"] = repr(exc)[:300]
     torch.cuda.empty_cache()
     return out
 
 
-def extras_retention(steps, warmup):
-    """Device-timed numbers for BASELINE config 4 (chunked RetNet retention, group-normalised output)."""
-    c = oracle_inputs.CONFIGS["C4"]
+def extras_retention(sampler, peaks, launches):
+    """Chunked RetNet retention, bf16, B=8 H=8 S=4096 Dk=256 Dv=512, gamma_h = 1 - 2^(-5-h): raw output and the
+    group-normalised output."""
     out = {}
     try:
         from attn_engine.linear_attn_engine import linear_attention_forward
-        B, H, S, Dk, Dv, C = c["B"], c["H"], c["S"], c["D"], c["Dv"], c["chunk"]
-        q, k, v, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(B, H, S, Dk, Dv, c["seed"])]
+        B, H, S, Dk, Dv = C4["B"], C4["H"], C4["S"], C4["D"], C4["Dv"]
+        q, k, v, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(B, H, S, Dk, Dv, C4["seed"])]
         ld = decay.log()
-        flops = float(B * H * S) * (2 * C * (Dk + Dv) + 4 * Dk * Dv)   # chunked count with the reference's chunk of 64
+        flops = retention_flops(B, H, S, Dk, Dv, C4["chunk"])
         io_bytes = (2 * B * H * S * Dk + 2 * B * H * S * Dv) * 2
-        for name, norm in (("C4_retention_normalised", True), ("C4_retention_raw", False)):
-            ms = time_device(lambda: linear_attention_forward(q, k, v, ld, q_scale=Dk ** -0.5, normalize=norm),
-                             steps, warmup, lambda: None) / steps
-            out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "gbs_min_io": io_bytes / ms / 1e6}
+        for name, norm in (("retention_raw_8x8x4096_256_512", False), ("retention_normalised_8x8x4096_256_512", True)):
+            fn = lambda: linear_attention_forward(q, k, v, ld, q_scale=Dk ** -0.5, normalize=norm)  # noqa: E731
+            sampler.begin(name)
+            heat_up(fn, 0.5)
+            times = time_launches(fn, launches, 0)
+            sampler.end(name)
+            rec = launch_stats(times)
+            rec.update({"tflops": flops / rec["ms"] / 1e9, "gbs_min_io": io_bytes / rec["ms"] / 1e6,
+                        "roofline": tensor_roofline(flops, rec["ms"], peaks, sustained=False, traffic=NCU_TRAFFIC["retention"]),
+                        "frac_of_sustained_peak": flops / rec["ms"] / 1e9 / peaks["bf16_tflops_sustained"],
+                        "l2": "q, k, v, o (805 MB) larger than L2"})
+            out[name] = rec
         del q, k, v
         # the two other users of the chunked kernel, at the shapes of the reference's functional tests
         # (testing/test.py:57-58), through the engine as the reference examples build it
@@ -287,20 +477,110 @@ def extras_retention(steps, warmup):
         B, H, S, D, Dv = 8, 32, 2048, 256, 256
         q, k, v, g = [t.cuda() for t in oracle_inputs.gla_inputs(B, H, S, D, Dv, 61)]
         eng = programs.gla_engine(B, H, S, D, Dv)
-        ms = time_device(lambda: eng(q, k, v, g), steps, warmup, lambda: None) / steps
-        out["gated_retention_8x32x2048_256_256"] = {"ms": ms, "tflops": float(B * H * S) * (2 * 64 * (D + Dv) + 4 * D * Dv) / ms / 1e9,
+        ms = statistics.median(time_launches(lambda: eng(q, k, v, g), 20, 3))
+        out["gated_retention_8x32x2048_256_256"] = {"ms": ms, "tflops": retention_flops(B, H, S, D, Dv) / ms / 1e9,
                                                     "gbs_min_io": (2 * B * H * S * D + 2 * B * H * S * Dv) * 2 / ms / 1e6}
         del q, k, v, g
         B, HQ, HK, HV, S, D, Dv = 1, 1, 1, 80, 2048, 128, 64
         q, k, v, dt, A = [t.cuda() for t in oracle_inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, 71)]
         eng = programs.mamba2_engine(B, HQ, S, D, Dv, HK=HK, HV=HV)
         dtb = dt.to(torch.bfloat16)
-        ms = time_device(lambda: eng(q, k, v, dt, A, dtb), steps, warmup, lambda: None) / steps
+        ms = statistics.median(time_launches(lambda: eng(q, k, v, dt, A, dtb), 20, 3))
         out["mamba2_1x80x2048_128_64"] = {"ms": ms, "note": "includes the whole-tensor decay_mod / v_mod statements, head broadcast and dim_v padding"}
     except Exception as exc:
-        out["C4_retention"] = {"error": repr(exc)[:200]}
+        out["retention_error"] = repr(exc)[:300]
     torch.cuda.empty_cache()
     return out
+
+
+def extras_decode(launches=20):
+    """Block-sparse, variable-length GQA decode (the reference's examples/sparse_gqa_decode.py shape: 32 query heads on 8
+    KV heads, 8192 cached tokens, 32-token blocks) with all blocks kept and with 30 % kept: the kept KV tiles are the
+    only ones visited, so the time follows the kept share."""
+    out = {}
+    try:
+        from examples_b200 import programs
+        B, H, Hkv, S, D, block = 8, 32, 8, 8192, 128, 32
+        g = torch.Generator(device="cuda").manual_seed(3)
+        q = torch.randn(B, 1, H, D, generator=g, device="cuda").to(torch.bfloat16)
+        k = torch.randn(B, S, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+        v = torch.randn(B, S, Hkv, D, generator=g, device="cuda").to(torch.bfloat16)
+        lens = torch.full((B,), S, dtype=torch.int32, device="cuda")
+        eng = programs.sparse_decode_engine(B, H, Hkv, S, D, D, block=block)
+        nblk = S // block
+        for share in (1.0, 0.3):
+            # whole 128-token tiles are kept or dropped (four neighbouring 32-token blocks share their fate), so that
+            # the kept share of blocks is also the kept share of tiles
+            tile_keep = torch.rand(B, Hkv, nblk // 4, generator=g, device="cuda") < share
+            tile_keep[..., 0] = True
+            bm = tile_keep.repeat_interleave(4, dim=-1)
+            ms = statistics.median(time_launches(lambda: eng(q, k, v, block_mask=bm, cache_seqlens=lens), launches, 3))
+            out[f"sparse_gqa_decode_kept_{int(share * 100)}pct"] = {"ms": ms, "kept_share": float(bm.float().mean()),
+                                                                   "gbs_kept_kv": float(bm.float().mean()) * 2 * B * S * Hkv * D * 2 / ms / 1e6}
+    except Exception as exc:
+        out["sparse_gqa_decode_error"] = repr(exc)[:300]
+    torch.cuda.empty_cache()
+    return out
+
+
+def strong_scaling_shards(rank, world, peaks, dist, launches=20):
+    """Retention and MLA decode on a 1/N batch shard of the SAME global problem on every rank (N = world): the times of
+    all ranks are reduced to their maximum; figures are whole-job (total work / max time)."""
+    out = {}
+    try:
+        from attn_engine import mla
+        from attn_engine.linear_attn_engine import linear_attention_forward
+        B, H, S, Dk, Dv = C4["B"], C4["H"], C4["S"], C4["D"], C4["Dv"]
+        b = max(1, B // world)
+        q, k, v, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(b, H, S, Dk, Dv, C4["seed"] + rank)]
+        ld = decay.log()
+        t_ret = statistics.median(time_launches(lambda: linear_attention_forward(q, k, v, ld, q_scale=Dk ** -0.5), launches, 3))
+        del q, k, v
+        B5, H5, S5, D5, Dv5 = C5["B"], C5["H"], C5["S"], C5["D"], C5["Dv"]
+        b5 = max(1, B5 // world)
+        q5, kv5 = mla_case(b5, H5, S5, D5, Dv5, C5["seed"] + rank)
+        flush = l2_flusher()
+        t_mla = statistics.median(time_launches(lambda: mla.mla_decode_forward(q5, kv5, Dv5, D5 ** -0.5), launches, 3, flush=flush))
+        plan = getattr(mla, "last_plan", None)
+        t = torch.tensor([t_ret, t_mla], device="cuda", dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_ret, t_mla = t.tolist()
+        fl = retention_flops(b * world, H, S, Dk, Dv, C4["chunk"])
+        nb = mla_bytes(b5 * world, H5, S5, D5, Dv5)
+        out["retention_strong_scaling"] = {"global_batch": b * world, "batch_per_gpu": b, "ms": t_ret, "tflops_total": fl / t_ret / 1e9,
+                                           "frac_of_burst_peak_per_gpu": fl / t_ret / 1e9 / world / peaks["bf16_tflops"],
+                                           "ctas_per_gpu": b * H * (Dv // 128)}
+        out["mla_decode_strong_scaling"] = {"global_batch": b5 * world, "batch_per_gpu": b5, "ms": t_mla, "gbs_total": nb / t_mla / 1e6,
+                                            "frac_of_hbm_peak_per_gpu": nb / t_mla / 1e6 / world / peaks["hbm_gbs"], "schedule": plan}
+    except Exception as exc:
+        out["strong_scaling_error"] = repr(exc)[:300]
+    torch.cuda.empty_cache()
+    return out
+
+
+def copy_ceiling_ms(hq, hk, hv, ho, hl, steps, barrier):
+    """ms per step of the plain pinned copies of one end-to-end step (q, k, v in; o, lse out) with no kernel between
+    them: input and output copies on two streams, as PCIe moves both directions at once."""
+    dq, dk, dv = [torch.empty_like(t, device="cuda") for t in (hq, hk, hv)]
+    do, dl = torch.empty_like(ho, device="cuda"), torch.empty_like(hl, device="cuda")
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def step():
+        cur = torch.cuda.current_stream()
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            ho.copy_(do, non_blocking=True)
+            hl.copy_(dl, non_blocking=True)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+    step()
+    return time_region(step, steps, barrier) / steps
 
 
 def run_profile_case(kind, steps, warmup):
@@ -310,31 +590,33 @@ def run_profile_case(kind, steps, warmup):
     torch.cuda.set_device(0)
     if kind == "mla":
         from attn_engine.mla import mla_decode_forward
-        B, H, S, D, Dv = 74, 128, 4096, 576, 512     # one cluster per sequence: a single full wave; KV = 349 MB
+        B, H, S, D, Dv = 74, 128, 4096, 576, 512     # KV = 349 MB
         q, kv = [t.cuda() for t in oracle_inputs.mla_inputs(B, H, S, D, Dv, 5)]
-        fn = lambda: mla_decode_forward(q, kv, Dv, D ** -0.5, num_splits=1)  # noqa: E731
-        work = {"bytes": (B * S * D + B * H * D + B * H * Dv) * 2}
+        fn = lambda: mla_decode_forward(q, kv, Dv, D ** -0.5)  # noqa: E731
+        work = {"bytes": mla_bytes(B, H, S, D, Dv)}
     else:
         from attn_engine.linear_attn_engine import linear_attention_forward
-        B, H, S, Dk, Dv = 2, 8, 4096, 256, 512       # q,k,v,o = 201 MB
+        B, H, S, Dk, Dv = (5, 8, 2048, 256, 512) if kind == "linear_full_wave" else (2, 8, 4096, 256, 512)   # 252 / 201 MB
         q, k, v, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(B, H, S, Dk, Dv, 4)]
         ld = decay.log()
         fn = lambda: linear_attention_forward(q, k, v, ld, q_scale=Dk ** -0.5)  # noqa: E731
-        work = {"flops": float(B * H * S) * (2 * 64 * (Dk + Dv) + 4 * Dk * Dv)}
-    ms = time_device(fn, steps, warmup, lambda: None) / steps
+        work = {"flops": retention_flops(B, H, S, Dk, Dv)}
+    for _ in range(warmup):
+        fn()
+    ms = time_region(fn, steps) / steps
     print(json.dumps({"profile_case": kind, "ms": ms, **work}), flush=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    # 40 steps (~45 ms) keep the timed region inside the burst window in which the roofline peak was measured;
-    # --steps 100 and more show the power-capped rate, to be read against the sustained peak
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--profile-kernel", choices=["mla", "linear"], default=None,
+    ap.add_argument("--heat-seconds", type=float, default=1.0,
+                    help="length of the heat-up (and sustained leg) in front of the timed steps; 0 turns it off (profiler captures)")
+    ap.add_argument("--profile-kernel", choices=["mla", "linear", "linear_full_wave"], default=None,
                     help="run a few launches of one of the other kernel families on a small case and exit (for ncu captures)")
     ap.add_argument("--batch", type=int, default=None,
                     help="shrink the batch of the headline workload (for small profiler captures; not a headline number)")
@@ -366,6 +648,7 @@ def main():
             dist.barrier()
 
     lib.load_library()
+    peaks = measured_peaks()
     eng = build_softmax_engine()
     B, H, S, D = C2["B"] if args.batch is None else args.batch, C2["H"], C2["S"], C2["D"]
     # every rank draws its own shard of the global batch (seed offset by rank): weak scaling
@@ -374,36 +657,23 @@ def main():
     dq, dk, dv = hq.cuda(non_blocking=True), hk.cuda(non_blocking=True), hv.cuda(non_blocking=True)
     torch.cuda.synchronize()
     flops = c2_flops(B=B)
+    step = lambda: eng(dq, dk, dv)  # noqa: E731
 
-    # ---- device-resident timing ----
     sampler = ClockSampler(local_rank)
     sampler.start()
+    # ---- burst leg: K steps after an idle pause, against the burst peak ----
     for _ in range(args.warmup):
-        eng(dq, dk, dv)
-    barrier()
+        step()
     torch.cuda.synchronize()
-    sampler.mark_begin()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        eng(dq, dk, dv)
-    e1.record()
-    torch.cuda.synchronize()
-    sampler.mark_timed_end()
-    ms_total = e0.elapsed_time(e1)
-    # A short timed region can fall between two nvidia-smi samples: the same launches keep running (untimed)
-    # until the sampled window is at least 0.3 s long, so that the clocks are those of this kernel under load.
-    hold_launches = 0
-    t_hold = time.time()
-    while ms_total * 1e-3 + (time.time() - t_hold) < 0.3:
-        eng(dq, dk, dv)
-        torch.cuda.synchronize()
-        hold_launches += 1
-    sampler.mark_end()
-    clocks = sampler.stop()
-    clocks["window"] = "timed region" if hold_launches == 0 else f"timed region + {hold_launches} more launches of the same kernel"
-    barrier()
+    time.sleep(0.5)
+    for _ in range(3):
+        step()
+    ms_burst = time_region(step, min(args.steps, 40), barrier) / min(args.steps, 40)
+    # ---- sustained leg (>= heat-seconds of back-to-back launches) and the K timed steps right behind it ----
+    sampler.begin("headline")
+    heat_n, heat_ms = heat_up(step, args.heat_seconds) if args.heat_seconds > 0 else (0, 0.0)
+    ms_total = time_region(step, args.steps, barrier)
+    sampler.end("headline")
     status = lib.last_device_status()
     if status != 0:
         raise SystemExit(f"device status {status}: a kernel wait timed out")
@@ -416,48 +686,70 @@ def main():
     def e2e_step():
         # the package's host-buffer call: batch slices streamed host -> device -> kernel -> host on three streams
         eng.forward_host(hq, hk, hv, out=ho, finals_out={"lse": hl})
-    e2e_ms = time_device(e2e_step, e2e_steps, 1, barrier) / e2e_steps
+    e2e_step()
+    e2e_ms = time_region(e2e_step, e2e_steps, barrier) / e2e_steps
+    copy_ms = copy_ceiling_ms(hq, hk, hv, ho, hl, e2e_steps, barrier)
 
-    t = torch.tensor([ms_total, e2e_ms], device="cuda", dtype=torch.float64)
+    t = torch.tensor([ms_total, e2e_ms, ms_burst, copy_ms, heat_ms / max(heat_n, 1)], device="cuda", dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = t.tolist()
+    ms_total, e2e_ms, ms_burst, copy_ms, heat_ms_per = t.tolist()
     ms_step = ms_total / args.steps
     value = flops * world / ms_step / 1e9
     e2e_value = flops * world / e2e_ms / 1e9
 
+    extras = {}
+    if not args.no_extras and args.batch is None:
+        del dq, dk, dv
+        torch.cuda.empty_cache()
+        if world > 1:
+            extras.update(strong_scaling_shards(rank, world, peaks, dist))
+        elif rank == 0:
+            extras.update(extras_parallel(sampler, peaks, 40))
+            extras.update(extras_mla(sampler, peaks, 40))
+            extras.update(extras_retention(sampler, peaks, 40))
+            extras.update(extras_decode())
+    sampler.stop()
+
     if rank == 0:
-        peaks = measured_peaks()
-        achieved = flops / ms_step / 1e9
+        clocks = sampler.summary("headline")
+        clocks["window"] = f"heat-up ({heat_n} launches) + the {args.steps} timed steps"
+        roof = tensor_roofline(flops, ms_step, peaks, sustained=args.heat_seconds > 0, traffic=NCU_TRAFFIC["softmax"] * B / C2["B"])
+        roof["frac_of_nominal_2250"] = roof["achieved"] / 2250.0
+        if heat_n:
+            roof["sustained_leg"] = {"launches": heat_n, "seconds": heat_ms_per * heat_n / 1e3, "ms_per_step": heat_ms_per,
+                                     "achieved": flops / heat_ms_per / 1e9, "frac": flops / heat_ms_per / 1e9 / peaks["bf16_tflops_sustained"]}
+        roof["burst"] = {"ms_per_step": ms_burst, "steps": min(args.steps, 40), "achieved": flops / ms_burst / 1e9, "peak": peaks["bf16_tflops"],
+                         "frac": flops / ms_burst / 1e9 / peaks["bf16_tflops"], "note": "after a 0.5 s idle pause, against the burst peak"}
+        for name in ("sigmoid", "mla", "retention_raw_8x8x4096_256_512", "retention_normalised_8x8x4096_256_512"):
+            if name in sampler.windows:
+                key = {"sigmoid": "sigmoid_noncausal_8x32x4096x128", "mla": "mla_decode_128x8192x576"}.get(name, name)
+                if key in extras:
+                    extras[key]["clocks"] = sampler.summary(name)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if args.batch is None else WORKLOAD + f" [batch overridden to {B}]", "global_batch": B * world, "seq_len": S, "heads": H, "head_dim": D,
-                       "parallelism": f"batch-shard x{world}, no collective",
-                       "l2": "inputs (805 MB) larger than L2, no flush needed"},
+            "config": {"workload": WORKLOAD if args.batch is None else WORKLOAD + f" [batch overridden to {B}]", "global_batch": B * world,
+                       "seq_len": S, "heads": H, "head_dim": D, "parallelism": f"batch-shard x{world}, no collective",
+                       "l2": "inputs (805 MB) larger than L2, no flush needed",
+                       "timed_region": f"{args.steps} steps behind {args.warmup} warm-up steps and a heat-up of {heat_n} launches (>= {args.heat_seconds} s)"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": 3 * hq.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2 + hl.numel() * 4},
+                    "h2d_bytes_per_step": 3 * hq.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2 + hl.numel() * 4,
+                    "copy_ceiling_ms": copy_ms, "frac_of_copy_ceiling": copy_ms / e2e_ms,
+                    "note": "copy_ceiling_ms = the same pinned copies alone (both directions at once), max over ranks"},
             "gpu_launches": args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "peak_source": f"{peaks['source']} (burst cuBLAS bf16)",
-                         "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
-                         "frac_of_nominal_2250": achieved / 2250.0},
+            "roofline": roof,
         }
         if world == 1:
             threads = os.cpu_count() or 1
             n_heads = 8
-            secs = cpu_softmax_sample(n_heads, threads)
+            secs, kind = cpu_softmax_sample(n_heads, threads)
             line["cpu_baseline"] = {"value": c2_flops(B=1, H=n_heads) / secs / 1e12, "unit": UNIT, "cores": threads,
-                                    "kind": "port", "sample": f"{n_heads} of {B * H} (batch, head) slices, fp32 PyTorch"}
-            if not args.no_extras:
-                del dq, dk, dv
-                torch.cuda.empty_cache()
-                line["extras"] = extras_parallel(10, 3)
-                line["extras"].update(extras_mla(10, 3))
-                line["extras"].update(extras_retention(10, 3))
+                                    "kind": kind, "sample": f"{n_heads} of {B * H} (batch, head) slices, fp32 PyTorch"}
+        if extras:
+            line["extras"] = extras
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -37,6 +37,8 @@ extern "C" {
 
 #define ATTN_B200_DTYPE_FP16 0
 #define ATTN_B200_DTYPE_BF16 1
+#define ATTN_B200_DTYPE_SAME 0         /* dtype_out: the output has the dtype of the inputs */
+#define ATTN_B200_DTYPE_FP32 2         /* dtype_out: fp32 output (accumulators stored unrounded) */
 
 #define ATTN_B200_MASK_NONE 0
 #define ATTN_B200_MASK_CAUSAL 1        /* keep q_idx >= kv_idx (top-left aligned)           */
@@ -78,12 +80,31 @@ typedef struct AttnB200ParallelArgs {
                                       ATTN_B200_MASK_OPEN; KV tiles outside the band are skipped */
   /* Split-KV (decode with few query rows and heads; the reference's split kernel + OnlineFunc.combine,
    * core/lower/lower_decode.py:287-302,375-449): 0 or 1 = off.  With num_splits > 1 the KV tiles are divided
-   * among num_splits CTAs per (query tile pair, head, batch) and a second kernel combines their results through
-   * the log-sum-exp; only ATTN_B200_FUNCTOR_SOFTMAX of attn_b200_parallel_fwd supports it. */
+   * among num_splits CTAs per (query tile pair, head, batch); each writes its rows after the functor's epilogue
+   * and its final row scales to the workspace, and a second kernel adds the rows up with the weights the
+   * functor's combine gives (built-in softmax: through the log-sum-exp; *_jit libraries: the lowered
+   * OnlineFunc.combine).  Not together with block sparsity. */
   int32_t num_splits;
   int32_t reserved;
   void* workspace;                 /* attn_b200_parallel_workspace_bytes() bytes of device scratch, or NULL */
   int64_t workspace_bytes;
+  /* Block sparsity (the reference's block-sparse templates, core/template/tl_template/attn/blockattn_tl.py and
+   * blockattn_decode_varlen_tl.py, chosen at core/lower/lower.py:723-738): tile_keep == NULL = off.  Otherwise
+   * mask_kind must be ATTN_B200_MASK_NONE and every 128-row query tile visits exactly the 128-row KV tiles whose
+   * bit is set in its bitmap; tiles whose bit is also set in tile_partial get an element mask (-inf where a bit
+   * is clear; applied only by functors with a -inf mask value).
+   *   tile_keep, tile_partial: uint32 [sparse_batch][sparse_heads][ceil(seq_q/128)][ceil(ceil(seq_kv/128)/32)],
+   *       bit (j & 31) of word j >> 5 = KV tile j; sparse_batch is 1 or batch, sparse_heads is 1, heads_kv or heads.
+   *   elem_mask_rows = 128: elem_mask holds one [128 rows][4 words] slot per partial tile, in the order
+   *       (sparse batch, sparse head, query tile, KV tile); tile_mask_base [sparse_batch][sparse_heads][q tiles] is
+   *       the slot of each query tile's first partial tile.  Bit (c & 31) of word c >> 5 of a row = keep column c.
+   *   elem_mask_rows = 0: one [4 words] column mask per (sparse batch, sparse head, KV tile), shared by all query
+   *       rows (decode: kept blocks and cache length per sequence); tile_mask_base is ignored. */
+  const uint32_t* tile_keep;
+  const uint32_t* tile_partial;
+  const int32_t* tile_mask_base;
+  const uint32_t* elem_mask;
+  int32_t sparse_batch, sparse_heads, elem_mask_rows, reserved2;
 } AttnB200ParallelArgs;
 
 /* Replaces the generated TileLang forward kernel and its launcher
@@ -91,8 +112,25 @@ typedef struct AttnB200ParallelArgs {
  * and the CuTe forward (core/template/cute_template/flash_api.cpp:283-460). */
 int attn_b200_parallel_fwd(const AttnB200ParallelArgs* args, void* cuda_stream);
 
-/* Bytes of scratch attn_b200_parallel_fwd needs for args->num_splits (0 without split-KV; -1 = bad arguments). */
+/* Bytes of scratch the forward needs for args->num_splits (0 without split-KV; -1 = bad arguments): fp32 partial
+ * rows plus ATTN_B200_MAX_ROWSCALES final row scales per row and split.  Valid for *_jit libraries as well. */
 int64_t attn_b200_parallel_workspace_bytes(const AttnB200ParallelArgs* args);
+
+/* Tile bitmaps and column masks of a block-sparse, variable-length decode, built on the device from what the
+ * reference's block-sparse decode kernel takes at call time (block_mask and cache_seqlens of
+ * core/template/tl_template/attn/blockattn_decode_varlen_tl.py:40-75): KV position p of (sequence b, KV head g)
+ * takes part when block_mask[b][g][p / block_size] != 0 and p < cache_seqlens[b].
+ *   block_mask: device uint8 [batch, heads_kv, n_blocks], or NULL = every block; cache_seqlens: device int32
+ *   [batch], or NULL = seq_kv for every sequence.
+ *   out: attn_b200_decode_tiles_bytes() bytes of device memory (16-byte aligned), laid out as
+ *     col_mask uint32 [batch][heads_kv][ceil(seq_kv/128)][4], then tile_keep and tile_partial uint32
+ *     [batch][heads_kv][words], words = ceil(ceil(seq_kv/128)/32):
+ *   the elem_mask (elem_mask_rows = 0), tile_keep and tile_partial of AttnB200ParallelArgs with sparse_batch = batch,
+ *   sparse_heads = heads_kv and one query tile.  Enqueued on the stream; no host synchronisation. */
+int64_t attn_b200_decode_tiles_bytes(int32_t batch, int32_t heads_kv, int32_t seq_kv);
+int attn_b200_decode_tiles(const uint8_t* block_mask, const int32_t* cache_seqlens, int32_t batch, int32_t heads_kv,
+                           int32_t n_blocks, int32_t block_size, int32_t seq_kv, void* out, int64_t out_bytes,
+                           void* cuda_stream);
 
 /* Arguments of the chunked linear-attention / retention forward
  *   h_{c+1} = h_c * exp(g_last) + (K * exp(g_last - g))^T V
@@ -113,6 +151,11 @@ typedef struct AttnB200LinearArgs {
   float norm_eps;
   void* workspace;       /* attn_b200_linear_workspace_bytes() bytes (only needed with normalize = 1) */
   int64_t workspace_bytes;
+  int32_t dtype_out;     /* ATTN_B200_DTYPE_SAME (0): o has the dtype of q, k, v; ATTN_B200_DTYPE_FP32: o is
+                            [batch, heads, seq, dim_v] fp32 -- the accumulators as they are, for callers that
+                            keep the result in fp32 and for judging the kernel apart from the output rounding
+                            (the reference casts its fp32 accumulators to the input dtype, linear_tl.py:398-400) */
+  int32_t reserved;
 } AttnB200LinearArgs;
 
 /* Bytes of scratch the linear forward needs: per-row (sum, sum of squares) fp32 when normalize = 1, else 0. */

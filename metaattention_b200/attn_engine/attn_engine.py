@@ -22,6 +22,7 @@ import math
 import torch
 
 from core.lower import functor as functor_lowering
+from core.lower import sparse as sparse_lowering
 from core.lower.trace import probe_softmax_scale, trace_parallel
 from core.native import jit as native_jit
 from core.native import lib as native
@@ -96,10 +97,14 @@ def plan_kv_splits(batch: int, heads: int, q_len: int, kv_len: int, device) -> i
     return max(1, min(sms // ctas, kv_tiles // 4, 65535 // max(batch, 1)))
 
 
+MASK_GENERAL = -1   # classify_mask: not a band, or different per batch / head: runs as a block-sparse walk
+
+
 def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int):
-    """(mask kind, (left, right)) for a ``mask_mod(b, h, q_idx, kv_idx)``: MASK_NONE, MASK_CAUSAL, or
+    """(mask kind, (left, right)) for a ``mask_mod(b, h, q_idx, kv_idx)``: MASK_NONE, MASK_CAUSAL,
     MASK_BAND = keep q_idx - left <= kv_idx <= q_idx + right (sliding windows; MASK_OPEN = no bound on
-    that side).  The mask is evaluated on CPU for one (b, h) over the [q_len, kv_len] grid (never the
+    that side), or MASK_GENERAL for everything else (any other pattern, and masks that use the batch or head
+    index), which the engine turns into a block-sparse walk (core/lower/sparse.py).  The mask is evaluated on CPU for one (b, h) over the [q_len, kv_len] grid (never the
     B*H*S*S tensor the reference materialises at core/lower/lower.py:729) and compared with the band it
     suggests; the kernel then skips the KV tiles outside the band, which is what the reference's block
     mask does for it (core/transform/core.py:492-506)."""
@@ -107,7 +112,7 @@ def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int):
     if mask_mod is None:
         return native.MASK_NONE, open_band
     if mask_depends_on_batch_head(mask_mod, B, H, q_len, kv_len, "cpu"):
-        raise NotImplementedError("mask_mod depending on batch or head index is not supported by the native backend yet")
+        return MASK_GENERAL, open_band
     dense = _eval_mask_2d(mask_mod, 0, 0, q_len, kv_len, "cpu")
     if bool(dense.all()):
         return native.MASK_NONE, open_band
@@ -129,9 +134,7 @@ def classify_mask(mask_mod, B: int, H: int, q_len: int, kv_len: int):
                 right = native.MASK_OPEN
             if torch.equal(dense, (kv >= q - left) & (kv <= q + right)):
                 return native.MASK_BAND, (left, right)
-    raise NotImplementedError("only mask_mod=None, all-true, causal (q_idx >= kv_idx) and band masks "
-                              "(q_idx - left <= kv_idx <= q_idx + right, e.g. sliding windows) are supported by the native "
-                              "backend yet")
+    return MASK_GENERAL, open_band
 
 
 class AttentionEngine:
@@ -144,7 +147,9 @@ class AttentionEngine:
         self.backend = backend          # accepted for source compatibility; every value runs the native kernels
         self.use_varlen = use_varlen
         self.block_mask = None
-        self._kv_bias_block = None
+        self._decode_block = None  # block size of a call-time block_mask (block-sparse, variable-length decode)
+        self._sparse_host = None   # block-sparse walk of a general mask_mod (built once, on the CPU)
+        self._sparse_dev = {}      # its copies by device
         self.kv_splits = None      # None = planned per call (plan_kv_splits); an int forces the split count
         self.qkv_meta = qkv_meta
         self.custom_fwd_inputs = custom_fwd_inputs if custom_fwd_inputs is not None else CustomIO()
@@ -166,11 +171,12 @@ class AttentionEngine:
         elif self.pattern in ("gqa", "gqa_decode"):
             # grouped KV heads (the reference's lower_gqa.py / attn_gqa_tl.py and the dense case of its GQA decode):
             # the same forward kernel, query head h reading KV head h / (H / Hkv); K/V of a group are fetched
-            # once per query head and mostly hit L2.  Block-sparse / varlen GQA decode is not covered.
+            # once per query head and mostly hit L2.  With extern_block_mask / use_varlen (examples/sparse_gqa_decode.py)
+            # the kept blocks and cache lengths of each call select the KV tiles that are visited.
             if H % Hkv != 0:
                 raise NotImplementedError(f"query heads ({H}) must be a multiple of KV heads ({Hkv})")
             if use_varlen or extern_block_mask:
-                score_mod = self._with_kv_bias(score_mod, Hkv, infer_mask_block_N)
+                self._decode_block = int(infer_mask_block_N)
             self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=Skv)
         elif self.pattern == "mha_decode":
             # A few query rows against a long KV (examples/mha_decode.py; the reference lowers it to a split-KV
@@ -178,7 +184,7 @@ class AttentionEngine:
             # q_len != kv_len, streams K/V once per (batch, head) and needs no combine step; with few
             # (batch, head) pairs it leaves SMs idle.
             if use_varlen or extern_block_mask:
-                score_mod = self._with_kv_bias(score_mod, Hkv, infer_mask_block_N)
+                self._decode_block = int(infer_mask_block_N)
             self._build_parallel(B, H, Sq, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=Skv)
         else:
             raise NotImplementedError(
@@ -187,37 +193,6 @@ class AttentionEngine:
                 "attention and MLA decode")
 
     # ------------------------------------------------------------------
-    _KV_BIAS = "__kv_bias"
-
-    def _with_kv_bias(self, score_mod, heads_kv, block):
-        """Block-sparse and variable-length decode (``block_mask`` [B, Hkv, blocks] bool and ``cache_seqlens`` [B]
-        at call time; examples/sparse_gqa_decode.py, blockattn_decode_varlen_tl.py of the reference): the kept KV
-        positions enter the user's score function as one more custom input, an additive bias [B, H, 1, kv_len]
-        that is 0 where a position is kept and -inf elsewhere.  Functionally the reference's kernel; masked
-        blocks are computed and discarded here, not skipped."""
-        self.custom_fwd_inputs(self._KV_BIAS, ("batch", "heads", 1, "seq_len_kv"))
-        self._kv_bias_block = int(block)
-        self._kv_bias_heads_kv = heads_kv
-        user = score_mod
-        name = self._KV_BIAS
-
-        def with_bias(score, custom, b, h, q_idx, kv_idx):
-            out = user(score, custom, b, h, q_idx, kv_idx) if user is not None else score
-            return out + custom.input_tensors[name]
-        return with_bias
-
-    def _kv_bias(self, q, k, block_mask, cache_seqlens):
-        B, H, Skv = q.shape[0], q.shape[2], k.shape[1]
-        keep = torch.ones((B, self._kv_bias_heads_kv, Skv), dtype=torch.bool, device=q.device)
-        if block_mask is not None:
-            keep = block_mask.to(q.device).bool().repeat_interleave(self._kv_bias_block, dim=-1)[..., :Skv]
-            if keep.shape[-1] < Skv:   # blocks past the table are not kept
-                keep = torch.nn.functional.pad(keep, (0, Skv - keep.shape[-1]))
-        if cache_seqlens is not None:
-            keep = keep & (torch.arange(Skv, device=q.device).view(1, 1, -1) < cache_seqlens.to(q.device).view(-1, 1, 1))
-        bias = torch.zeros(keep.shape, dtype=q.dtype, device=q.device).masked_fill_(~keep, float("-inf"))
-        return bias.repeat_interleave(H // self._kv_bias_heads_kv, dim=1).unsqueeze(2)   # [B, H, 1, Skv]
-
     # pattern selection by shape, as attn_engine.py:227-343 of the reference
     @staticmethod
     def _select_pattern(q_len, kv_len, heads, heads_kv, kv_shared) -> str:
@@ -233,12 +208,19 @@ class AttentionEngine:
 
     # ------------------------------------------------------------------
     def _build_parallel(self, B, H, S, D, Dv, dtype, score_mod, mask_mod, online_func, mask_value, kv_len=None):
-        if (D, Dv) not in ((64, 64), (128, 128)) and not (D == 256 and Dv % 128 == 0):
+        if (D, Dv) not in ((64, 64), (128, 128), (192, 128)) and not (D in (128, 256) and Dv % 128 == 0):
             raise NotImplementedError(f"head dims (qk={D}, v={Dv}) are not covered by the forward kernel yet "
-                                      "(supported: 64/64, 128/128 and 256/(a multiple of 128))")
-        self.mask_kind, self.mask_band = classify_mask(mask_mod, B, H, S, S if kv_len is None else kv_len)
-        if kv_len is not None and kv_len != S and self.mask_kind != native.MASK_NONE:
-            raise NotImplementedError("decode (q_len != kv_len) supports mask_mod=None or an all-true mask")
+                                      "(supported: 64/64, 192/128, and 128 or 256 / a multiple of 128)")
+        Skv = S if kv_len is None else kv_len
+        self.mask_kind, self.mask_band = classify_mask(mask_mod, B, H, S, Skv)
+        if self.mask_kind != native.MASK_NONE and self._decode_block is not None:
+            raise NotImplementedError("a mask_mod together with a call-time block_mask / cache_seqlens is not supported")
+        if self.mask_kind == MASK_GENERAL or (Skv != S and self.mask_kind != native.MASK_NONE):
+            # the reference's choice for anything that is not causal (core/lower/lower.py:723-738): block sparsity.
+            # KV tiles without a kept position are skipped, partially kept ones carry their element mask.
+            self._sparse_host = sparse_lowering.build_block_sparse(mask_mod, B, H, S, Skv)
+            self.mask_kind = native.MASK_NONE
+        self.sparse_walk = self._sparse_host is not None or self._decode_block is not None
         neg_inf_mask = str(mask_value).strip() in ("-inf", "-float('inf')")
         self.traced = trace_parallel(score_mod, online_func, self.custom_fwd_inputs)
         tr = self.traced
@@ -263,16 +245,20 @@ class AttentionEngine:
             self.functor_kind = "lowered"
             self._fparams = []
             fs = functor_lowering.emit_functor(tr, neg_inf_mask=neg_inf_mask, input_ctype=input_ctype)
-            self.functor_source = functor_lowering.translation_unit(fs, D, Dv, dtype == torch.bfloat16)
+            self.functor_source = functor_lowering.translation_unit(fs, D, Dv, dtype == torch.bfloat16, sparse=self.sparse_walk)
             # compile now (works without a GPU); loading is deferred to the first call
             native_jit.build(self.functor_source)
             self._jit_fn = None
         self.attention = self._run_parallel
 
-    def _run_parallel(self, q, k, v, *custom):
+    def _run_parallel(self, q, k, v, *custom, block_mask=None, cache_seqlens=None):
+        if self._decode_block is not None:
+            run = lambda *ts: self._run_parallel_impl(*ts, block_mask=block_mask, cache_seqlens=cache_seqlens)  # noqa: E731
+        else:
+            run = self._run_parallel_impl
         if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
-            return _ForwardOnly.apply(self._run_parallel_impl, q, k, v, *custom)
-        return self._run_parallel_impl(q, k, v, *custom)
+            return _ForwardOnly.apply(run, q, k, v, *custom)
+        return run(q, k, v, *custom)
 
     def _custom_operands(self, custom, B, H, Sq, Skv, device):
         """Checks the custom input tensors against their declared shapes and returns (tensors, element strides over
@@ -315,7 +301,7 @@ class AttentionEngine:
             strides.append(st)
         return tensors, strides
 
-    def _run_parallel_impl(self, q, k, v, *custom):
+    def _run_parallel_impl(self, q, k, v, *custom, block_mask=None, cache_seqlens=None):
         if len(custom) != len(self.custom_names):
             raise TypeError(f"expected {len(self.custom_names)} custom input tensor(s) {self.custom_names}, got {len(custom)}")
         if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
@@ -328,24 +314,41 @@ class AttentionEngine:
         tensors, strides = self._custom_operands(custom, B, H, S, k.shape[1], q.device)
         # the entry points launch on the CURRENT device and stream: make q's device current for the whole call
         with torch.cuda.device(q.device):
-            return self._launch_parallel(q, k, v, tensors, strides)
+            sparse = None
+            if self._decode_block is not None:
+                # block-sparse, variable-length decode (examples/sparse_gqa_decode.py, blockattn_decode_varlen_tl.py):
+                # the call's block_mask [B, Hkv, blocks] and cache_seqlens [B] become, on the device, the bitmaps of
+                # the KV tiles to visit and the column masks of the tiles kept in part
+                sparse = native.decode_tiles(block_mask, cache_seqlens, B, k.shape[2], k.shape[1], self._decode_block, q.device)
+            return self._launch_parallel(q, k, v, tensors, strides, sparse)
 
-    def _launch_parallel(self, q, k, v, tensors, strides):
+    def _launch_parallel(self, q, k, v, tensors, strides, sparse=None):
         B, S, H, _ = q.shape
         Dv = v.shape[3]
         o = torch.empty((B, S, H, Dv), dtype=q.dtype, device=q.device)
         finals = [torch.empty((B, H, S), dtype=torch.float32, device=q.device) for _ in self.final_names]
-        # split-KV when the launch would leave most SMs idle (decode: few query rows and heads against a long KV);
-        # the split results are combined through the log-sum-exp, which only the built-in softmax provides
+        if sparse is None and self._sparse_host is not None:
+            if q.device not in self._sparse_dev:
+                self._sparse_dev[q.device] = sparse_lowering.to_device(self._sparse_host, q.device)
+            sparse = self._sparse_dev[q.device]
+        # split-KV when the launch would leave most SMs idle (decode: few query rows and heads against a long KV): the
+        # split results are added up with the weights of the functor's combine (built-in softmax: through the
+        # log-sum-exp; lowered functors: the user's OnlineFunc.combine, which needs every split to be non-empty,
+        # i.e. no mask)
         splits, workspace = 1, None
-        if self.functor_kind == "builtin_softmax" and q.shape[-1] <= 128:
+        lowered_ok = self.functor_kind == "lowered" and self.mask_kind == native.MASK_NONE
+        if sparse is None and Dv <= 128 and q.shape[-1] <= 128 and (self.functor_kind == "builtin_softmax" or lowered_ok):
             splits = self.kv_splits if self.kv_splits is not None else plan_kv_splits(B, H, S, k.shape[1], q.device)
+            if splits > 1 and self.functor_kind == "lowered":
+                kv_tiles = (k.shape[1] + 127) // 128
+                per = -(-kv_tiles // min(splits, kv_tiles))
+                splits = -(-kv_tiles // per)          # no split without KV tiles
             if splits > 1:
-                workspace = torch.empty(B * splits * H * S * (Dv + 1) * 4, dtype=torch.uint8, device=q.device)
+                workspace = torch.empty(B * splits * H * S * (Dv + native.MAX_ROWSCALES) * 4, dtype=torch.uint8, device=q.device)
         args = native.fill_parallel_args(q, k, v, o, mask_kind=self.mask_kind, mask_band=self.mask_band,
                                          num_splits=splits, workspace=workspace, functor=native.FUNCTOR_SOFTMAX,
                                          fparams=self._fparams, final_rowscales=finals, custom=tensors,
-                                         custom_strides=strides)
+                                         custom_strides=strides, sparse=sparse)
         if self.functor_kind == "builtin_softmax":
             native.parallel_fwd(args)
         else:
@@ -353,16 +356,16 @@ class AttentionEngine:
                 self._jit_fn = native_jit.load(self.functor_source)
             status = native.device_status_word(q.device.index)
             native.check(self._jit_fn(C.byref(args), native.current_stream_ptr(), status), "attn_b200_parallel_fwd_jit")
-        self.last_final_rowscales = dict(zip(self.final_names, finals))
+        # a lowered functor's combine gives output weights only: its splits' final row scales are not merged
+        merged = splits == 1 or self.functor_kind == "builtin_softmax"
+        self.last_final_rowscales = dict(zip(self.final_names, finals)) if merged else {}
         return o
 
     # ------------------------------------------------------------------
     def __call__(self, *args, **kargs):
-        if getattr(self, "_kv_bias_block", None) is not None:
-            # (q, k, v, *user custom tensors, block_mask=..., cache_seqlens=...): the kept positions become the
-            # bias input appended by _with_kv_bias
-            q, k = args[0], args[1]
-            return self.attention(*args, self._kv_bias(q, k, kargs.get("block_mask"), kargs.get("cache_seqlens")))
+        if self._decode_block is not None:
+            # (q, k, v, *custom tensors, block_mask=..., cache_seqlens=...)
+            return self.attention(*args, block_mask=kargs.get("block_mask"), cache_seqlens=kargs.get("cache_seqlens"))
         if kargs.get("block_mask") is not None:
             args = args + (kargs["block_mask"],)
         elif self.block_mask is not None:

@@ -99,10 +99,15 @@ def _constant_multiple(out: SymbolScalar, leaf: SymbolScalar):
     return None
 
 
-def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize: bool = False, eps: float = 1e-5):
+def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize: bool = False, eps: float = 1e-5,
+                             out_dtype=None):
     """q,k: [B,H,T,Dk]; v: [B,H,T,Dv] (fp16/bf16 CUDA); log_decay: [B,H,T] fp32, natural log of the
-    per-token decay.  Returns o [B,H,T,Dv].  ``normalize`` applies a per-(batch, head, token)
-    normalisation over Dv (zero mean, unit variance, no affine) to the output."""
+    per-token decay.  Returns o [B,H,T,Dv] in the input dtype, or in fp32 with ``out_dtype=torch.float32``
+    (the kernel's accumulators without the output rounding).  ``normalize`` applies a per-(batch, head,
+    token) normalisation over Dv (zero mean, unit variance, no affine) to the output."""
+    if out_dtype not in (None, q.dtype, torch.float32):
+        raise native.NativeError("out_dtype must be the input dtype or torch.float32")
+    f32_out = out_dtype == torch.float32
     if not q.is_cuda:
         raise native.NativeError("linear attention needs CUDA tensors")
     if q.dtype not in native.DTYPE_CODES or k.dtype != q.dtype or v.dtype != q.dtype:
@@ -115,13 +120,14 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         if normalize:
             raise native.NativeError("normalize needs dim_v to be a multiple of 128")
         pad = 128 - Dv % 128
-        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps)
+        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps, out_dtype)
         return o[..., :Dv].contiguous()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     log_decay = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
     with torch.cuda.device(q.device):
-        o = torch.empty((B, H, T, Dv), dtype=q.dtype, device=q.device)
+        o = torch.empty((B, H, T, Dv), dtype=torch.float32 if f32_out else q.dtype, device=q.device)
         a = native.LinearArgs()
+        a.dtype_out = native.DTYPE_OUT_FP32 if f32_out else native.DTYPE_OUT_SAME
         a.q, a.k, a.v, a.log_decay, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), log_decay.data_ptr(), o.data_ptr()
         a.batch, a.heads, a.seq, a.dim_qk, a.dim_v = B, H, T, Dk, Dv
         a.dtype = native.DTYPE_CODES[q.dtype]

@@ -107,6 +107,8 @@ class _Body:
             for u, w in ((a, b), (b, a)):
                 if isinstance(u, Const) and u.value == 1.0:
                     return w
+                if isinstance(u, Const) and u.value == 0.0:
+                    return Const(0.0)
         if op == "Add":
             for u, w in ((a, b), (b, a)):
                 if isinstance(u, Const) and u.value == 0.0:
@@ -343,6 +345,57 @@ def _emit_custom_loads(body: _Body, tr: TracedParallel, input_ctype: str, leaves
             leaves[id(sym)] = Tile(v)
 
 
+_COMBINE_BIN = {"Add": "({0} + {1})", "Sub": "({0} - {1})", "Mul": "({0} * {1})", "Div": "({0} / {1})",
+                "Max": "fmaxf({0}, {1})", "Min": "fminf({0}, {1})"}
+_COMBINE_UN = {"Neg": "(-{0})", "Abs": "fabsf({0})", "Exp": f"b200::fast_exp2({{0}} * {_f(LOG2E)})", "Exp2": "b200::fast_exp2({0})",
+               "Log": f"(b200::fast_log2({{0}}) * {_f(LN2)})", "Log2": "b200::fast_log2({0})", "Tanh": "b200::fast_tanh({0})"}
+_COMBINE_RED = {"ColReduceSum": ("0.0f", "{0} + {1}"), "ColReduceMax": ("(-INFINITY)", "fmaxf({0}, {1})"),
+                "ColReduceAbsSum": ("0.0f", "{0} + fabsf({1})")}
+
+
+def emit_combine(tr: TracedParallel) -> str:
+    """Body of ``combine(i, n, fin, split_stride, final_stride)``: the weight of split ``i`` among ``n`` from the
+    final row scales of all splits, fin[final * final_stride + split * split_stride] -- the user's
+    ``OnlineFunc.combine`` (reference: core/lower/lower_decode.py:287-302; column reductions of
+    core/codegen/tl_gen.py:22-33).  A value that varies over the splits is an expression in a split index; a column
+    reduction becomes a loop over the splits in front of its first use, its result one number per row."""
+    if tr.combine_out is None:
+        return "return 1.0f;"
+    finals = list(tr.final.keys())
+    leaf = {id(sym): finals.index(name) for name, sym in tr.combine_in.items()}
+    lines: list[str] = []
+    reduced: dict[int, str] = {}
+
+    def expr(sym, idx: str) -> str:
+        key = id(sym)
+        if key in leaf:
+            return f"fin[{leaf[key]} * final_stride + {idx} * split_stride]"
+        if key in reduced:
+            return reduced[key]
+        t = sym.code.type
+        if t == "Const":
+            return _f(float(sym.code.value))
+        if t == "Var":
+            from core.lower.trace import init_value
+            return _f(init_value(sym.code.name))
+        if t in _COMBINE_RED:
+            init, step = _COMBINE_RED[t]
+            inner = expr(sym.prev[0], "k")     # may emit loops of its own first
+            name = f"c{len(reduced) + 1}"
+            lines.append(f"float {name} = {init};")
+            lines.append(f"for (int k = 0; k < n; ++k) {name} = {step.format(name, inner)};")
+            reduced[key] = name
+            return name
+        if t in _COMBINE_BIN:
+            return _COMBINE_BIN[t].format(expr(sym.prev[0], idx), expr(sym.prev[1], idx))
+        if t in _COMBINE_UN:
+            return _COMBINE_UN[t].format(expr(sym.prev[0], idx))
+        raise NotImplementedError(f"op {t} in OnlineFunc.combine is not supported by the functor emitter")
+
+    result = expr(tr.combine_out, "i")
+    return "\n    ".join(lines + [f"return {result};"])
+
+
 @dataclass
 class FunctorSource:
     struct_name: str
@@ -451,20 +504,22 @@ def emit_functor(tr: TracedParallel, *, neg_inf_mask: bool, input_ctype: str, st
   __device__ static float final_rowscale(int which, const float* rs, const b200::RowCtx& c) {{
     {final_code}
   }}
+  static constexpr bool kCombinedFinal = false;
+  __device__ static float combined_final(int, const float*, long long, long long) {{ return 0.0f; }}
+  __device__ static float combine(int i, int n, const float* fin, long long split_stride, long long final_stride) {{
+    {emit_combine(tr)}
+  }}
 }};
 """
     return FunctorSource(struct_name, code, len(rs_names), len(final_names), final_names,
                          list(tr.custom.keys()), unit)
 
 
-def translation_unit(fs: FunctorSource, dim_qk: int, dim_v: int, bf16: bool) -> str:
+def translation_unit(fs: FunctorSource, dim_qk: int, dim_v: int, bf16: bool, sparse: bool = False) -> str:
     """Source of a library exporting ``attn_b200_parallel_fwd_jit`` for one functor and one
-    (dim_qk, dim_v, dtype) instantiation of the forward kernel."""
+    (dim_qk, dim_v, dtype, dense or block-sparse walk) instantiation of the forward kernel."""
     b = "true" if bf16 else "false"
-    if dim_qk == 256:   # one launch per 128-column slice of dim_v (parallel_launch.cuh)
-        launch = f"b200::launch_parallel_sliced<{fs.struct_name}, {b}>"
-    else:
-        launch = f"b200::launch_parallel<{fs.struct_name}, {dim_qk}, {dim_v}, {b}>"
+    dv = dim_v if dim_v <= 128 else 256    # wider dim_v runs as 128-column slices whatever its multiple
     return f"""// generated by core/lower/functor.py -- do not edit
 #include "parallel_launch.cuh"
 
@@ -473,8 +528,8 @@ extern "C" int attn_b200_parallel_fwd_jit(const AttnB200ParallelArgs* args, void
   const int rc = b200::validate_parallel_args(args);
   if (rc != ATTN_B200_OK) return rc;
   if (args->dtype != {1 if bf16 else 0}) return ATTN_B200_E_UNSUPPORTED;
-  if (args->num_splits > 1) return ATTN_B200_E_UNSUPPORTED;  // split-KV combines through the built-in softmax's log-sum-exp
-  return {launch}(
+  if (args->dim_qk != {dim_qk} || args->dim_v != {dim_v}) return ATTN_B200_E_UNSUPPORTED;
+  return b200::launch_parallel_dims<{fs.struct_name}, {dim_qk}, {dv}, {b}, {'true' if sparse else 'false'}>(
       args, static_cast<cudaStream_t>(cuda_stream), device_status);
 }}
 """

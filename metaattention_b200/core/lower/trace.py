@@ -23,7 +23,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from core.transform.core import (CustomIO, SymbolicArray, SymbolicTensor, SymbolScalar)
+from core.transform.core import (CustomIO, SymbolicArray, SymbolicColReduceArray, SymbolicTensor, SymbolScalar)
 from core.transform.graph import Var
 
 NEG_INF_SENTINEL = -1.0e38  # the reference lowers a "-inf" initial row scale to -1e38 (lower.py:24-30)
@@ -52,6 +52,10 @@ class TracedParallel:
     o_in: SymbolScalar
     o_out: SymbolScalar
     final: dict[str, SymbolScalar] = field(default_factory=dict)
+    # OnlineFunc.combine traced over per-split final row scales (split-KV): leaves and the per-split output weight;
+    # None = weight 1 for every split (the base class's combine: the partial results are added up)
+    combine_in: dict[str, SymbolScalar] = field(default_factory=dict)
+    combine_out: SymbolScalar | None = None
 
 
 def _is_unit(sym) -> bool:
@@ -101,8 +105,19 @@ def trace_parallel(score_mod, online_func, custom_fwd_inputs: CustomIO | None) -
     extra = dict(getattr(online_func, "external_fwd_tensors", CustomIO()).input_tensors)
     custom = dict(custom_fwd_inputs.input_tensors)
     custom.update(extra)
-    return TracedParallel(scores, idx, custom, rs_in, rs_init, s2, dict(rs_out),
-                          None if _is_unit(o_scale) else o_scale, o_in, o_out, dict(final))
+    tr = TracedParallel(scores, idx, custom, rs_in, rs_init, s2, dict(rs_out),
+                        None if _is_unit(o_scale) else o_scale, o_in, o_out, dict(final))
+    # combine is traced the way the reference does (core/lower/lower_decode.py:287-302): every final row scale becomes
+    # a [num_split, rows] array whose get_reduce() runs over the split axis
+    comb_in = {name: SymbolicColReduceArray(v.varname, Var(f"final:{name}"), shape_idx=["num_split", "block_M2"])
+               for name, v in online_func.final_rowscales.items() if name in final}
+    try:
+        w = online_func.combine(comb_in)
+    except Exception as exc:   # a combine written for other row scales than the epilogue returns
+        raise ValueError(f"OnlineFunc.combine could not be traced over the final row scales {sorted(comb_in)}: {exc}") from exc
+    if isinstance(w, SymbolScalar) and not _is_unit(w):
+        tr.combine_in, tr.combine_out = comb_in, w
+    return tr
 
 
 # --------------------------------------------------------------------------
@@ -364,6 +379,16 @@ def softmax_shaped(tr: TracedParallel) -> bool:
     except _NotSoftmaxShaped:
         return False
     return len({id(s) for s in max_nodes}) == 1
+
+
+def run_traced_combine(tr: TracedParallel, finals: dict) -> torch.Tensor:
+    """Per-split output weights of a traced ``OnlineFunc.combine``: ``finals`` maps each final row scale to a
+    [num_split, rows] tensor; returns [num_split, rows] (ones when the functor has no combine of its own)."""
+    n, rows = next(iter(finals.values())).shape if finals else (1, 1)
+    if tr.combine_out is None:
+        return torch.ones(n, rows)
+    env = {id(sym): finals[name].float() for name, sym in tr.combine_in.items()}
+    return torch.as_tensor(evaluate([tr.combine_out], env)[0], dtype=torch.float32).expand(n, rows)
 
 
 def probe_softmax_scale(tr: TracedParallel) -> float | None:

@@ -37,6 +37,7 @@ ERRORS = {
 }
 
 DTYPE_CODES = {torch.float16: 0, torch.bfloat16: 1}
+DTYPE_OUT_SAME, DTYPE_OUT_FP32 = 0, 2
 MASK_NONE, MASK_CAUSAL, MASK_BAND = 0, 1, 2
 MASK_OPEN = 0x3fffffff   # mask_left / mask_right of a band side without a bound
 FUNCTOR_SOFTMAX = 0
@@ -60,6 +61,8 @@ class ParallelArgs(C.Structure):
         ("custom_stride", (C.c_int64 * 4) * MAX_CUSTOM),
         ("mask_left", C.c_int32), ("mask_right", C.c_int32),
         ("num_splits", C.c_int32), ("reserved", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("tile_keep", C.c_void_p), ("tile_partial", C.c_void_p), ("tile_mask_base", C.c_void_p), ("elem_mask", C.c_void_p),
+        ("sparse_batch", C.c_int32), ("sparse_heads", C.c_int32), ("elem_mask_rows", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 
@@ -69,6 +72,7 @@ class LinearArgs(C.Structure):
         ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
         ("dtype", C.c_int32), ("normalize", C.c_int32), ("q_scale", C.c_float), ("norm_eps", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("dtype_out", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -94,6 +98,9 @@ class MlaArgs(C.Structure):
 SIGNATURES = {
     "attn_b200_parallel_fwd": (C.c_int, [C.POINTER(ParallelArgs), C.c_void_p]),
     "attn_b200_parallel_workspace_bytes": (C.c_int64, [C.POINTER(ParallelArgs)]),
+    "attn_b200_decode_tiles_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
+    "attn_b200_decode_tiles": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                         C.c_void_p, C.c_int64, C.c_void_p]),
     "attn_b200_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "attn_b200_linear_workspace_bytes": (C.c_int64, [C.POINTER(LinearArgs)]),
     "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
@@ -197,7 +204,7 @@ def _strides_bsh(t: torch.Tensor):
 
 def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=(), final_rowscales=(),
                        custom=(), custom_strides=(), mask_band=(MASK_OPEN, MASK_OPEN), num_splits: int = 1,
-                       workspace=None) -> ParallelArgs:
+                       workspace=None, sparse=None) -> ParallelArgs:
     """q,k: [B,S,H,D]; v,o: [B,S,H,Dv] CUDA tensors (any strides with a contiguous last dim)."""
     for t in (q, k, v, o):
         if not t.is_cuda:
@@ -225,6 +232,11 @@ def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=
     a.num_splits = int(num_splits)
     if workspace is not None:
         a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    if sparse is not None:   # dict from core.lower.sparse: device tensors + extents
+        a.tile_keep, a.tile_partial = sparse["keep"].data_ptr(), sparse["partial"].data_ptr()
+        a.tile_mask_base = sparse["mask_base"].data_ptr() if sparse.get("mask_base") is not None else None
+        a.elem_mask = sparse["elem_mask"].data_ptr() if sparse.get("elem_mask") is not None else None
+        a.sparse_batch, a.sparse_heads, a.elem_mask_rows = sparse["batch"], sparse["heads"], sparse["mask_rows"]
     a.functor = functor
     for i, f in enumerate(fparams):
         a.fparams[i] = float(f)
@@ -233,6 +245,37 @@ def fill_parallel_args(q, k, v, o, *, mask_kind: int, functor: int = 0, fparams=
         for j, s in enumerate(custom_strides[i]):
             a.custom_stride[i][j] = int(s)
     return a
+
+
+def decode_tiles(block_mask, cache_seqlens, batch: int, heads_kv: int, seq_kv: int, block_size: int, device) -> dict:
+    """Sparse-walk description (see fill_parallel_args ``sparse``) of a block-sparse, variable-length decode, built
+    on the device by attn_b200_decode_tiles.  block_mask: bool/uint8 [batch, heads_kv, blocks] or None;
+    cache_seqlens: int32 [batch] or None."""
+    lib = load_library()
+    tiles = (seq_kv + 127) // 128
+    words = (tiles + 31) // 32
+    bh = batch * heads_kv
+    out = torch.empty(int(lib.attn_b200_decode_tiles_bytes(batch, heads_kv, seq_kv)) // 4, dtype=torch.int32, device=device)
+    n_blocks = 0
+    if block_mask is not None:
+        if block_mask.dim() != 3 or block_mask.shape[0] != batch or block_mask.shape[1] != heads_kv:
+            raise NativeError(f"block_mask must be [batch, kv heads, blocks] = [{batch}, {heads_kv}, *], got {tuple(block_mask.shape)}")
+        block_mask = block_mask.to(device=device).contiguous()
+        block_mask = block_mask.view(torch.uint8) if block_mask.dtype == torch.bool else block_mask.to(torch.uint8)
+        n_blocks = block_mask.shape[2]
+    if cache_seqlens is not None:
+        if cache_seqlens.numel() != batch:
+            raise NativeError(f"cache_seqlens must hold one length per sequence ({batch}), got {cache_seqlens.numel()}")
+        cache_seqlens = cache_seqlens.to(device=device, dtype=torch.int32).contiguous()
+    check(lib.attn_b200_decode_tiles(block_mask.data_ptr() if block_mask is not None else None,
+                                     cache_seqlens.data_ptr() if cache_seqlens is not None else None,
+                                     batch, heads_kv, n_blocks, int(block_size), seq_kv, out.data_ptr(), out.numel() * 4,
+                                     current_stream_ptr()), "attn_b200_decode_tiles")
+    col = out[:bh * tiles * 4]
+    keep = out[bh * tiles * 4:bh * tiles * 4 + bh * words]
+    part = out[bh * tiles * 4 + bh * words:]
+    return {"keep": keep, "partial": part, "mask_base": None, "elem_mask": col, "batch": batch, "heads": heads_kv,
+            "mask_rows": 0, "_owner": (out, block_mask, cache_seqlens)}
 
 
 def parallel_fwd(args: ParallelArgs):

@@ -42,6 +42,7 @@ constexpr int kLinThreads = kLinRowThreads + 32;   // plus the warp that issues 
 
 struct LinearParams {
   void* o;                 // [B,H,S,DV] 16-bit
+  float* o_f32;            // [B,H,S,DV] fp32 output instead (rows are written straight from registers), or null
   const float* log_decay;  // [B,H,S] natural log of the per-token decay
   float* stats;            // [B,H,S,2] (sum, sum of squares) over dim_v, or null
   int seq, dim_v, bh;
@@ -273,7 +274,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           }
           if (need_store && mbar_test(o_staged, par)) {
             // output rows staged in the state-copy buffer: full swizzled lines, rows past the end clipped by the map
-            for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
+            if (p.o_f32 == nullptr) {
+              for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
+            }
             tma_store_commit();
             if (!last) {
               tma_store_wait_read();  // the conversion pass overwrites the staging buffer
@@ -476,8 +479,17 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           float o[32];
           tmem_ld32f(tO + wg * 64 + c * 32, o);
           tmem_wait_ld();
+          if (p.o_f32 != nullptr) {
+            // fp32 output: this thread's 32 columns of its token row, 128 contiguous bytes
+            if (tok < p.seq) {
+              float4* dst = reinterpret_cast<float4*>(p.o_f32 + (static_cast<long long>(bh) * p.seq + tok) * p.dim_v +
+                                                      slice * DVS + wg * 64 + c * 32);
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
+              for (int v = 0; v < 8; ++v) dst[v] = make_float4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            }
+          }
+#pragma unroll
+          for (int v = 0; v < 4 && p.o_f32 == nullptr; ++v) {
             uint4 pk;
             if (p.stats == nullptr) {
               pk.x = pack2<kBf16>(o[8 * v + 0], o[8 * v + 1]);
@@ -576,6 +588,19 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 // In-place normalisation of every (batch, head, token) row of o over dim_v to zero mean and unit
 // variance, from the (sum, sum of squares) the forward kernel accumulated in fp32.  The rows arrive
 // staged as fp16 and leave in the output dtype.  One warp per row.
+// The same normalisation for an fp32 output buffer (rows written in fp32 by the forward kernel), in place.
+__global__ void __launch_bounds__(256) linear_norm_f32_kernel(float* __restrict__ o, const float* __restrict__ stats, long long rows,
+                                                            int dim_v, float eps) {
+  const long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const float mean = stats[2 * r] / dim_v;
+  const float var = fmaxf(stats[2 * r + 1] / dim_v - mean * mean, 0.0f);
+  const float rstd = rsqrtf(var + eps);
+  float* line = o + r * dim_v;
+  for (int i = lane; i < dim_v; i += 32) line[i] = (line[i] - mean) * rstd;
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(256) linear_norm_kernel(void* __restrict__ o, const float* __restrict__ stats, long long rows,
                                                         int dim_v, float eps) {
@@ -619,17 +644,25 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_rows3(&tmO, a->o, a->dtype, a->dim_v, a->seq, bh);
+  const bool f32_out = a->dtype_out == ATTN_B200_DTYPE_FP32;
+  // with an fp32 output the 16-bit store map is not used by the kernel: it is encoded over v so that it stays valid
+  rc = encode_rows3(&tmO, f32_out ? a->v : a->o, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
   LinearParams p;
   std::memset(&p, 0, sizeof(p));
   p.o = a->o;
+  p.o_f32 = f32_out ? static_cast<float*>(a->o) : nullptr;
   p.log_decay = a->log_decay;
   p.seq = a->seq;
   p.dim_v = a->dim_v;
   p.bh = static_cast<int>(bh);
   p.q_scale = a->q_scale;
-  p.split_p = a->normalize ? 1 : 0;  // the normalised output has an absolute tolerance: spend a second PV pass on P
+  // The normalised output has an absolute tolerance whatever the head's scale.  For heads with a fast decay the
+  // output is mostly the intra-block part, where the 16-bit rounding of P is the largest error (a CPU model of the
+  // kernel's arithmetic gives, for gamma = 1 - 2^-5, mean-abs 3.4e-4 on an output of standard deviation 0.25, and
+  // 1.1e-4 with the remainder pass), so a second PV pass over the 16-bit remainder of P is spent there.  For slow
+  // decays the state path's roundings dominate and the pass changes nothing.
+  p.split_p = a->normalize ? 1 : 0;
   p.status = status;
   const long long rows = static_cast<long long>(bh) * a->seq;
   if (a->normalize) {
@@ -646,7 +679,8 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (a->normalize) {
     const int blocks = static_cast<int>((rows * 32 + 255) / 256);
-    linear_norm_kernel<kBf16><<<blocks, 256, 0, stream>>>(a->o, p.stats, rows, a->dim_v, a->norm_eps);
+    if (f32_out) linear_norm_f32_kernel<<<blocks, 256, 0, stream>>>(p.o_f32, p.stats, rows, a->dim_v, a->norm_eps);
+    else linear_norm_kernel<kBf16><<<blocks, 256, 0, stream>>>(a->o, p.stats, rows, a->dim_v, a->norm_eps);
     if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   }
   return ATTN_B200_OK;
@@ -666,6 +700,7 @@ int attn_b200_linear_fwd(const AttnB200LinearArgs* a, void* cuda_stream) {
     return ATTN_B200_E_INVALID_ARG;
   if (a->batch <= 0 || a->heads <= 0 || a->seq <= 0) return ATTN_B200_E_INVALID_ARG;
   if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
+  if (a->dtype_out != ATTN_B200_DTYPE_SAME && a->dtype_out != ATTN_B200_DTYPE_FP32) return ATTN_B200_E_INVALID_ARG;
   if (a->dim_v <= 0 || a->dim_v % b200::kLinDvs != 0) return ATTN_B200_E_UNSUPPORTED;
   if (static_cast<long long>(a->batch) * a->heads > 65535) return ATTN_B200_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;

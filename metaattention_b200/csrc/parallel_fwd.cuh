@@ -73,7 +73,16 @@ struct ParallelParams {
   int kv_splits;               // > 1: blockIdx.z = batch * kv_splits + split, each split covers tiles_per_split KV tiles
   int tiles_per_split;
   float* part_o;               // [batch, kv_splits, heads, seq_q, dim_v] fp32 results of the splits (kv_splits > 1)
-  float* part_lse;             // [batch, kv_splits, heads, seq_q] their final row scale 0 (log-sum-exp)
+  float* part_final;           // [kFinal][batch, kv_splits, heads, seq_q] their final row scales
+  long long part_final_stride; // elements between two final row scales in part_final
+  // Block sparsity (kSparse kernels): per (sparse batch, sparse head, 128-row query tile) a bitmap of the 128-row KV
+  // tiles to visit and one of the tiles among them that need the element mask.
+  const uint32_t* tile_keep;   // [sparse_batch][sparse_heads][q_tiles][tile_words]
+  const uint32_t* tile_partial;
+  const int* tile_mask_base;   // [sparse_batch][sparse_heads][q_tiles] first element-mask slot of the query tile, or null
+  const uint32_t* elem_mask;   // slots of [elem_mask_rows][4] words (bit = keep), or with elem_mask_rows == 0 one
+                               // [4]-word column mask per (sparse batch, sparse head, KV tile)
+  int sparse_batch, sparse_heads, tile_words, elem_mask_rows;
   long long o_sb, o_ss, o_sh;  // element strides of o
   int mask_kind;               // 0 none, 1 causal (keep q_idx >= kv_idx), 2 band
   int win_left, win_right;     // band: keep kv_idx in [q_idx - win_left, q_idx + win_right]; kNoBound = open side
@@ -95,6 +104,26 @@ enum ParallelWaitSite {
   kSiteQFull = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSFull, kSitePReady, kSiteODone, kSiteOFinal
 };
 
+// Walks the set bits of one bitmap, or of the union of two, in increasing order (KV tile indices of a sparse walk).
+struct TileWalk {
+  const uint32_t* a;
+  const uint32_t* b;
+  int words, w;
+  uint32_t bits;
+  __device__ TileWalk(const uint32_t* a_, const uint32_t* b_, int words_) : a(a_), b(b_), words(words_), w(-1), bits(0) {}
+  __device__ int next() {
+    while (bits == 0) {
+      if (++w >= words) return -1;
+      bits = a[w] | (b != nullptr ? b[w] : 0u);
+    }
+    const int j = w * 32 + __ffs(bits) - 1;
+    bits &= bits - 1;
+    return j;
+  }
+};
+
+constexpr int kMaxTileWords = 128;   // sparse walks: at most 4096 KV tiles (512 k tokens)
+
 // NT = query tiles per CTA: 2 (K/V in two stages, shared by both tiles) or 1 (single-staged K/V; the layout that
 // fits dim_qk = 256: one 64 KB query tile, 64 KB of K, 32 KB of V)
 template <int D, int DV, int NT = 2>
@@ -109,17 +138,19 @@ struct ParallelSmem {
   static constexpr int kOffBar = kOffV + kStages * kVBytes;
   static constexpr int kNumBars = 2 + 4 * kStages + 6;
   static constexpr int kOffMisc = kOffBar + 8 * kNumBars;
+  static constexpr int kOffSparse = kOffMisc + 16;     // sparse kernels: keep / partial bitmaps of the two query tiles
   static constexpr int kBytes = kOffMisc + 16 + 1024;  // + slack for manual 1024-byte alignment
+  static constexpr int kBytesSparse = kBytes + 4 * kMaxTileWords * 4;
 };
 
-template <class F, int D, int DV, bool kBf16, int NT = 2>
+template <class F, int D, int DV, bool kBf16, int NT = 2, bool kSparse = false>
 __global__ void __launch_bounds__((4 * NT + 2) * 32, 1)
 parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const ParallelParams p) {
   using L = ParallelSmem<D, DV, NT>;
   constexpr int BM = L::kBM, BN = L::kBN, ST = L::kStages;
-  static_assert(D % 64 == 0 && DV % 64 == 0 && DV <= 128 && (D <= 128 || (D == 256 && NT == 1)), "unsupported head dims");
-  static_assert(L::kBytes <= 232448, "shared memory layout exceeds an SM");
+  static_assert(D % 64 == 0 && DV % 64 == 0 && DV <= 128 && (D <= 128 || (D <= 256 && NT == 1)), "unsupported head dims");
+  static_assert((kSparse ? L::kBytesSparse : L::kBytes) <= 232448, "shared memory layout exceeds an SM");
   constexpr uint32_t kTmemCols = NT == 2 ? 512 : 256;
   constexpr uint32_t kColS = 0, kColO = NT * 128;
   constexpr int kTmaWarp = 4 * NT, kMmaWarp = 4 * NT + 1;
@@ -174,26 +205,65 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (j_hi[t] < j_lo[t]) j_hi[t] = j_lo[t];
     }
   }
-  const bool act0 = j_hi[0] > j_lo[0], act1 = j_hi[1] > j_lo[1];
+  bool act0 = j_hi[0] > j_lo[0], act1 = j_hi[1] > j_lo[1];
   const int j_min = act0 ? (act1 ? min(j_lo[0], j_lo[1]) : j_lo[0]) : j_lo[1];
   const int j_max = max(act0 ? j_hi[0] : 0, act1 ? j_hi[1] : 0);
-  const int n_max = (act0 || act1) ? j_max - j_min : 0;
-  auto active = [&](int t, int j) { return j >= j_lo[t] && j < j_hi[t]; };
+  int n_max = (act0 || act1) ? j_max - j_min : 0;
+  // Sparse walk: the bitmaps of this CTA's two query tiles are copied to shared memory (a query tile past the end of
+  // the sequence gets an empty one); n_tiles[t] = KV tiles of tile t, n_max = tiles of the union.
+  uint32_t* sp_keep = reinterpret_cast<uint32_t*>(smem + L::kOffSparse);      // [2][kMaxTileWords]
+  uint32_t* sp_part = sp_keep + 2 * kMaxTileWords;                           // [2][kMaxTileWords]
+  int n_tiles[2] = {0, 0};
+  int sp_row[2] = {0, 0};       // index of (sparse batch, sparse head, query tile) for each of the two tiles
+  if constexpr (kSparse) {
+    const int sb = p.sparse_batch > 1 ? b : 0;
+    const int sh = p.sparse_heads <= 1 ? 0 : (p.sparse_heads == p.heads ? h : h / (p.heads / p.sparse_heads));
+    const int q_tiles = (p.seq_q + BM - 1) / BM;
+    for (int t = 0; t < 2; ++t) {
+      const int qt = m_pair * NT + t;
+      const bool exists = t < NT && qt < q_tiles;
+      sp_row[t] = (sb * p.sparse_heads + sh) * q_tiles + (exists ? qt : 0);
+      for (int w = threadIdx.x; w < p.tile_words; w += blockDim.x) {
+        sp_keep[t * kMaxTileWords + w] = exists ? p.tile_keep[static_cast<long long>(sp_row[t]) * p.tile_words + w] : 0u;
+        sp_part[t * kMaxTileWords + w] = exists ? p.tile_partial[static_cast<long long>(sp_row[t]) * p.tile_words + w] : 0u;
+      }
+    }
+    __syncthreads();
+    n_max = 0;
+    for (int w = 0; w < p.tile_words; ++w) {
+      n_tiles[0] += __popc(sp_keep[w]);
+      n_tiles[1] += __popc(sp_keep[kMaxTileWords + w]);
+      n_max += __popc(sp_keep[w] | sp_keep[kMaxTileWords + w]);
+    }
+    act0 = n_tiles[0] > 0;
+    act1 = n_tiles[1] > 0;
+  }
+  auto active = [&](int t, int j) {
+    if constexpr (kSparse) return j >= 0 && ((sp_keep[t * kMaxTileWords + (j >> 5)] >> (j & 31)) & 1u) != 0;
+    else return j >= j_lo[t] && j < j_hi[t];
+  };
 
   // ---------------- setup ----------------
   // The producer lane initialises the barriers and sends off the query tiles and the first K and V tiles at once:
   // their ~2800 cycles of latency start before the tensor-memory allocation and the CTA-wide sync, not after.
-  auto load_k = [&](int i) {
+  auto load_k_tile = [&](int i, int j) {   // KV tile j into the stage of step i
     const int st = i % ST;
     mbar_arrive_expect_tx(&k_full[st], L::kKBytes);
     for (int c = 0; c < D / 64; ++c)
-      tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, (j_min + i) * BN, h / p.kv_group, b, p.ok);
+      tma_load_rows(sK + st * L::kKBytes + c * (BN * 128), &tmK, &k_full[st], c * 64, j * BN, h / p.kv_group, b, p.ok);
   };
-  auto load_v = [&](int i) {
+  auto load_v_tile = [&](int i, int j) {
     const int st = i % ST;
     mbar_arrive_expect_tx(&v_full[st], L::kVBytes);
     for (int c = 0; c < DV / 64; ++c)
-      tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, (j_min + i) * BN, h / p.kv_group, b, p.ov);
+      tma_load_rows(sV + st * L::kVBytes + c * (BN * 128), &tmV, &v_full[st], c * 64, j * BN, h / p.kv_group, b, p.ov);
+  };
+  auto load_k = [&](int i) { load_k_tile(i, j_min + i); };
+  auto load_v = [&](int i) { load_v_tile(i, j_min + i); };
+  auto load_q = [&](int t) {
+    mbar_arrive_expect_tx(&q_full[t], L::kQBytes);
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, &q_full[t], c * 64, m0 + t * BM, h, b, p.oq);
   };
   bool early_loads = false;
   if (warp == kTmaWarp && lane == 0) {
@@ -214,14 +284,9 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&o_done[t], 1);
     }
     fence_barrier_init();
-    if (n_max > 0) {
+    if (n_max > 0 && !kSparse) {
       // in the order of first use: query tile 0 and K so that its scores can start, then query tile 1, then V
       const int nq = act1 ? 2 : 1;
-      auto load_q = [&](int t) {
-        mbar_arrive_expect_tx(&q_full[t], L::kQBytes);
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_rows(sQ + t * L::kQBytes + c * (BM * 128), &tmQ, &q_full[t], c * 64, m0 + t * BM, h, b, p.oq);
-      };
       load_q(0);
       load_k(0);
       if (nq > 1) load_q(1);
@@ -244,7 +309,22 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (warp == kTmaWarp) {
     // =============== TMA producer ===============
-    if (lane == 0 && early_loads && !*abort_flag) {
+    if constexpr (kSparse) {
+      if (lane == 0 && n_max > 0 && !*abort_flag) {
+        TileWalk walk(sp_keep, sp_keep + kMaxTileWords, p.tile_words);
+        load_q(0);
+        if (NT > 1 && act1) load_q(1);
+        for (int i = 0; i < n_max; ++i) {
+          const int j = walk.next();
+          const int st = i % ST;
+          const uint32_t ph = (i / ST) & 1;
+          if (i >= ST && !mbar_wait(&k_empty[st], ph ^ 1, ab, kSiteKEmpty)) break;
+          load_k_tile(i, j);
+          if (i >= ST && !mbar_wait(&v_empty[st], ph ^ 1, ab, kSiteVEmpty)) break;
+          load_v_tile(i, j);
+        }
+      }
+    } else if (lane == 0 && early_loads && !*abort_flag) {
       for (int i = 1; i < n_max; ++i) {
         const int st = i % ST;
         const uint32_t ph = (i / ST) & 1;
@@ -282,7 +362,45 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       bool ok = mbar_wait(&q_full[0], 0, ab, kSiteQFull);
       ok = ok && mbar_wait(&k_full[0], 0, ab, kSiteKFull);
-      if (ok) {
+      if constexpr (kSparse) {
+        // the same schedule over the union of the two tiles' KV tile sets; a tile takes part in a step when the
+        // step's KV tile is in its own set, and its barrier phases count its own tiles
+        TileWalk walk(sp_keep, sp_keep + kMaxTileWords, p.tile_words);
+        int j = walk.next();
+        int done[2] = {0, 0};
+        if (ok) {
+          tc_fence_after_sync();
+          if (active(0, j)) issue_qk(0, 0);
+          if (NT > 1 && act1) {
+            ok = mbar_wait(&q_full[1], 0, ab, kSiteQFull);
+            tc_fence_after_sync();
+            if (ok && active(1, j)) issue_qk(1, 0);
+          }
+          umma_commit(&k_empty[0]);
+        }
+        for (int i = 0; i < n_max && ok; ++i) {
+          const int jn = walk.next();
+          const int st = i % ST;
+          const int stn = (i + 1) % ST;
+          ok = mbar_wait(&v_full[st], (i / ST) & 1, ab, kSiteVFull);
+          if (ok && jn >= 0) ok = mbar_wait(&k_full[stn], ((i + 1) / ST) & 1, ab, kSiteKFull);
+          if (!ok) break;
+          for (int t = 0; t < NT; ++t) {
+            if (active(t, j)) {
+              ok = mbar_wait_poll(&p_ready[t], done[t] & 1, ab, kSitePReady);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue_pv(t, st, done[t] == 0);
+              ++done[t];
+            }
+            if (active(t, jn)) issue_qk(t, stn);
+          }
+          if (!ok) break;
+          umma_commit(&v_empty[st]);
+          if (jn >= 0) umma_commit(&k_empty[stn]);
+          j = jn;
+        }
+      } else if (ok) {
         tc_fence_after_sync();
         if (active(0, j_min)) issue_qk(0, 0);
         if (NT > 1 && act1) {
@@ -323,8 +441,10 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + kColS + t * BN;
     const uint32_t tO = tmem_base + lane_base + kColO + t * DV;
-    const int n = j_hi[t] - j_lo[t];
+    const int n = kSparse ? n_tiles[t] : j_hi[t] - j_lo[t];
     const int row0 = m0 + t * BM;
+    TileWalk walk(sp_keep + t * kMaxTileWords, nullptr, kSparse ? p.tile_words : 0);
+    int mask_slot = (kSparse && p.tile_mask_base != nullptr) ? p.tile_mask_base[sp_row[t]] : 0;
     float rs[F::kRowScales > 0 ? F::kRowScales : 1];
     RowCtx ctx{b, h, q_idx, 0, p.seq_q, p.seq_kv, &p.fa};
     F::init(rs, ctx);
@@ -337,8 +457,26 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld32f(tS + c * 32, &s[c * 32]);
       tmem_wait_ld();
-      const int kv0 = (j_lo[t] + j) * BN;
+      const int jt = kSparse ? walk.next() : j_lo[t] + j;   // KV tile of this step
+      const int kv0 = jt * BN;
       ctx.kv0 = kv0;
+      if constexpr (kSparse) {
+        // element mask of a partial tile: 128 keep bits for this thread's row (or one column mask for all rows)
+        if (F::kNegInfMask && ((sp_part[t * kMaxTileWords + (jt >> 5)] >> (jt & 31)) & 1u) != 0) {
+          const uint32_t* mrow;
+          if (p.elem_mask_rows > 0) {
+            mrow = p.elem_mask + (static_cast<long long>(mask_slot) * p.elem_mask_rows + row) * 4;
+            ++mask_slot;
+          } else {
+            const int n_kv = (p.seq_kv + BN - 1) / BN;
+            mrow = p.elem_mask + ((static_cast<long long>(sp_row[t]) / ((p.seq_q + BM - 1) / BM)) * n_kv + jt) * 4;
+          }
+          const uint4 mw = *reinterpret_cast<const uint4*>(mrow);
+          const uint32_t words[4] = {mw.x, mw.y, mw.z, mw.w};
+#pragma unroll
+          for (int i = 0; i < BN; ++i) s[i] = ((words[i >> 5] >> (i & 31)) & 1u) ? s[i] : -INFINITY;
+        }
+      }
       // a tile needs element masking when it crosses an edge of the mask band or the end of the KV sequence
       const bool crosses = (banded && ((right < kNoBound && kv0 + BN - 1 > row0 + right) ||
                                        (left < kNoBound && kv0 < row0 + BM - 1 - left))) || (kv0 + BN > p.seq_kv);
@@ -414,15 +552,23 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before_sync();
       mbar_arrive(&p_ready[t]);
     }
-    if (ok && n > 0) {
-      ok = mbar_wait(&o_done[t], (n - 1) & 1, ab, kSiteOFinal);
+    // a query tile of a sparse walk that visits no KV tile at all still owes its output rows: the epilogue of an
+    // empty accumulator (what the reference's kernel leaves there as well)
+    const bool empty_tile = kSparse && n == 0 && t < NT && row0 < p.seq_q && !*abort_flag;
+    if ((ok && n > 0) || empty_tile) {
+      ok = n > 0 ? mbar_wait(&o_done[t], (n - 1) & 1, ab, kSiteOFinal) : true;
       if (ok) {
         tc_fence_after_sync();
         const bool in_range = q_idx < p.seq_q;
         float o[DV];
+        if (n > 0) {
 #pragma unroll
-        for (int c = 0; c < DV / 32; ++c) tmem_ld32f(tO + c * 32, &o[c * 32]);
-        tmem_wait_ld();
+          for (int c = 0; c < DV / 32; ++c) tmem_ld32f(tO + c * 32, &o[c * 32]);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < DV; ++i) o[i] = 0.0f;
+        }
         F::template epilogue<DV>(o, rs, ctx);
         if (p.kv_splits > 1) {
           // split-KV: the normalised rows and their log-sum-exp go to the scratch the combine kernel reads
@@ -431,7 +577,8 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             float4* dst = reinterpret_cast<float4*>(p.part_o + prow * DV);
 #pragma unroll
             for (int v = 0; v < DV / 4; ++v) dst[v] = make_float4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-            p.part_lse[prow] = F::final_rowscale(0, rs, ctx);
+#pragma unroll
+            for (int i = 0; i < F::kFinal; ++i) p.part_final[i * p.part_final_stride + prow] = F::final_rowscale(i, rs, ctx);
           }
         } else {
           // Output rows leave through the tile's own Q buffer (free: its last Q.K^T ran before the P.V that o_done
@@ -488,7 +635,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int t = warp >> 2;
     const int q_idx = m0 + t * BM + (warp & 3) * 32 + lane;
     if (j_hi[t] <= j_lo[t] && q_idx < p.seq_q)
-      p.part_lse[((static_cast<long long>(b) * p.kv_splits + split) * p.heads + h) * p.seq_q + q_idx] = -INFINITY;
+      p.part_final[((static_cast<long long>(b) * p.kv_splits + split) * p.heads + h) * p.seq_q + q_idx] = -INFINITY;
   }
 
   // ---------------- teardown ----------------
@@ -507,42 +654,42 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }
 
 
-// Split-KV combine for softmax-type results: o[b,q,h,:] = sum_i exp(lse_i - lse) part_o[b,i,h,q,:],
-// lse = log sum_i exp(lse_i) (what OnlineFunc.combine of examples/mha_decode.py:69-77 computes with the
-// final row scale lse).  One warp per (batch, head, query row); splits with lse = -inf are skipped.
-template <int DV, bool kBf16>
-__global__ void __launch_bounds__(256) parallel_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                                             void* __restrict__ o, float* __restrict__ lse_out, int batch,
-                                                             int heads, int seq_q, int splits, long long o_sb, long long o_ss,
-                                                             long long o_sh) {
+// Split-KV combine: o[b,q,h,:] = sum_i w_i part_o[b,i,h,q,:] with w_i = F::combine(i, splits, final row scales of
+// all splits) -- the lowered OnlineFunc.combine of the reference (core/lower/lower_decode.py:287-302, combine kernel
+// of attn_decode_tl.py:158-206).  For the built-in softmax that is exp(lse_i - lse), lse = log sum_i exp(lse_i), and
+// the combined lse is written out as the call's final row scale.  One warp per (batch, head, query row).
+template <class F, int DV, bool kBf16>
+__global__ void __launch_bounds__(256) parallel_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_final,
+                                                             long long part_final_stride, void* __restrict__ o,
+                                                             float* __restrict__ final_out, int batch, int heads, int seq_q,
+                                                             int splits, long long o_sb, long long o_ss, long long o_sh) {
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= static_cast<long long>(batch) * heads * seq_q) return;
   const int q = static_cast<int>(row % seq_q);
   const int h = static_cast<int>((row / seq_q) % heads);
   const int b = static_cast<int>(row / (static_cast<long long>(seq_q) * heads));
-  auto prow = [&](int i) { return ((static_cast<long long>(b) * splits + i) * heads + h) * seq_q + q; };
-  float mx = -INFINITY;
-  for (int i = 0; i < splits; ++i) mx = fmaxf(mx, part_lse[prow(i)]);
-  float den = 0.f;
-  for (int i = 0; i < splits; ++i) den += __expf(part_lse[prow(i)] - mx);
-  const float lse = mx + __logf(den);
+  const long long split_stride = static_cast<long long>(heads) * seq_q;
+  const long long prow0 = (static_cast<long long>(b) * splits * heads + h) * seq_q + q;   // split 0
+  const float* fin = part_final + prow0;
   constexpr int E = DV / 32;   // columns per lane
   float acc[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
   for (int i = 0; i < splits; ++i) {
-    const float li = part_lse[prow(i)];
-    if (li == -INFINITY) continue;
-    const float w = __expf(li - lse);
-    const float* src = part_o + prow(i) * DV + lane * E;
+    const float w = F::combine(i, splits, fin, split_stride, part_final_stride);
+    if (w == 0.0f) continue;   // an empty split (its partial rows were never written)
+    const float* src = part_o + (prow0 + i * split_stride) * DV + lane * E;
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[e] += w * src[e];
   }
   uint8_t* orow = reinterpret_cast<uint8_t*>(o) + 2 * (b * o_sb + q * o_ss + h * o_sh + lane * E);
 #pragma unroll
   for (int e = 0; e < E; e += 2) *reinterpret_cast<uint32_t*>(orow + 2 * e) = pack2<kBf16>(acc[e], acc[e + 1]);
-  if (lane == 0 && lse_out != nullptr) lse_out[(static_cast<long long>(b) * heads + h) * seq_q + q] = lse;
+  if constexpr (F::kCombinedFinal) {
+    if (lane == 0 && final_out != nullptr)
+      final_out[(static_cast<long long>(b) * heads + h) * seq_q + q] = F::combined_final(splits, fin, split_stride, part_final_stride);
+  }
 }
 
 }  // namespace b200

@@ -83,13 +83,25 @@ inline int validate_parallel_args(const AttnB200ParallelArgs* a) {
     if (a->o_stride[i] % 8 != 0) return ATTN_B200_E_UNSUPPORTED;
   if (a->heads > 65535 || a->batch > 65535) return ATTN_B200_E_UNSUPPORTED;
   if (a->heads_kv < 0 || (a->heads_kv > 0 && a->heads % a->heads_kv != 0)) return ATTN_B200_E_INVALID_ARG;
+  if (a->tile_keep != nullptr) {
+    // block sparsity: the bitmaps replace the mask kinds, and the walk is not combined with split-KV
+    if (a->tile_partial == nullptr || a->mask_kind != ATTN_B200_MASK_NONE || a->num_splits > 1) return ATTN_B200_E_INVALID_ARG;
+    if (a->sparse_batch != 1 && a->sparse_batch != a->batch) return ATTN_B200_E_INVALID_ARG;
+    const int hkv = a->heads_kv > 0 ? a->heads_kv : a->heads;
+    if (a->sparse_heads != 1 && a->sparse_heads != a->heads && a->sparse_heads != hkv) return ATTN_B200_E_INVALID_ARG;
+    if (a->elem_mask_rows != 0 && a->elem_mask_rows != 128) return ATTN_B200_E_INVALID_ARG;
+    if (a->elem_mask_rows == 128 && a->elem_mask != nullptr && a->tile_mask_base == nullptr) return ATTN_B200_E_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(a->elem_mask) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+    if ((a->seq_kv + 127) / 128 > 32 * kMaxTileWords) return ATTN_B200_E_UNSUPPORTED;
+  }
   return ATTN_B200_OK;
 }
 
 // `dv0` selects a DV-column slice of v and o when dim_v is wider than the kernel's DV (see launch_parallel_sliced)
-template <class F, int D, int DV, bool kBf16, int NT = 2>
+template <class F, int D, int DV, bool kBf16, int NT = 2, bool kSparse = false>
 int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status, int dv0 = -1) {
   using L = ParallelSmem<D, DV, NT>;
+  if ((a->tile_keep != nullptr) != kSparse) return ATTN_B200_E_UNSUPPORTED;   // this library was not built for that walk
   if (a->dim_qk != D || (dv0 < 0 ? a->dim_v != DV : (a->dim_v % DV != 0 || dv0 + DV > a->dim_v))) return ATTN_B200_E_UNSUPPORTED;
   const void* v_base = dv0 > 0 ? static_cast<const uint8_t*>(a->v) + 2 * dv0 : a->v;
   void* o_base = dv0 > 0 ? static_cast<uint8_t*>(a->o) + 2 * dv0 : a->o;
@@ -127,62 +139,96 @@ int launch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* dev
   if (splits > 1) {
     const int n_kv_tiles = (a->seq_kv + L::kBN - 1) / L::kBN;
     if (splits > n_kv_tiles || static_cast<long long>(a->batch) * splits > 65535) return ATTN_B200_E_INVALID_ARG;
-    if (F::kFinal < 1) return ATTN_B200_E_UNSUPPORTED;   // the combine needs a log-sum-exp per row
     const long long rows = static_cast<long long>(a->batch) * splits * a->heads * a->seq_q;
-    const long long need = rows * (DV + 1) * 4;
+    const int n_final = F::kFinal > 0 ? F::kFinal : 1;
+    const long long need = rows * (DV + n_final) * 4;
     if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0)
       return ATTN_B200_E_WORKSPACE;
     p.kv_splits = splits;
     p.tiles_per_split = (n_kv_tiles + splits - 1) / splits;
+    // a functor other than the built-in softmax has no neutral value for a split without KV tiles: every split
+    // must get some, which holds without a mask when the last split is not empty
+    if (!F::kCombinedFinal && (a->mask_kind != ATTN_B200_MASK_NONE || (splits - 1) * p.tiles_per_split >= n_kv_tiles))
+      return ATTN_B200_E_UNSUPPORTED;
     p.part_o = static_cast<float*>(a->workspace);
-    p.part_lse = p.part_o + rows * DV;
+    p.part_final = p.part_o + rows * DV;
+    p.part_final_stride = rows;
   }
-  auto kernel = parallel_fwd_kernel<F, D, DV, kBf16, NT>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
+  if constexpr (kSparse) {
+    p.tile_keep = a->tile_keep;
+    p.tile_partial = a->tile_partial;
+    p.tile_mask_base = a->elem_mask_rows > 0 ? a->tile_mask_base : nullptr;
+    p.elem_mask = a->elem_mask;
+    p.sparse_batch = a->sparse_batch;
+    p.sparse_heads = a->sparse_heads;
+    p.elem_mask_rows = a->elem_mask_rows;
+    p.tile_words = ((a->seq_kv + L::kBN - 1) / L::kBN + 31) / 32;
+  }
+  auto kernel = parallel_fwd_kernel<F, D, DV, kBf16, NT, kSparse>;
+  constexpr int kSmem = kSparse ? L::kBytesSparse : L::kBytes;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) {
     cudaGetLastError();
     return ATTN_B200_E_LAUNCH;
   }
   dim3 grid((a->seq_q + NT * L::kBM - 1) / (NT * L::kBM), a->heads, a->batch * splits);
-  kernel<<<grid, (4 * NT + 2) * 32, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
+  kernel<<<grid, (4 * NT + 2) * 32, kSmem, stream>>>(tmQ, tmK, tmV, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (splits > 1) {
     const long long rows = static_cast<long long>(a->batch) * a->heads * a->seq_q;
     const unsigned blocks = static_cast<unsigned>((rows * 32 + 255) / 256);
-    parallel_combine_kernel<DV, kBf16><<<blocks, 256, 0, stream>>>(p.part_o, p.part_lse, a->o, a->final_rowscales[0], a->batch, a->heads,
-                                                                  a->seq_q, splits, p.o_sb, p.o_ss, p.o_sh);
+    parallel_combine_kernel<F, DV, kBf16><<<blocks, 256, 0, stream>>>(p.part_o, p.part_final, p.part_final_stride, a->o,
+                                                                     a->final_rowscales[0], a->batch, a->heads, a->seq_q, splits,
+                                                                     p.o_sb, p.o_ss, p.o_sh);
     if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   }
   return ATTN_B200_OK;
 }
 
-// Head dims 256 / (a multiple of 128), e.g. the 256 / 512 of examples/retention_parallel.py: one query tile per CTA
-// (a 256-wide query tile and K tile fill the shared memory) and one launch per 128-column slice of v and o, each
-// recomputing the scores; the accumulator of a slice is the widest the tensor memory holds beside the scores.
-template <class F, bool kBf16>
+// dim_v wider than the 128 accumulator columns a query tile has beside its scores (the 256 / 512 of
+// examples/retention_parallel.py, the 128 / 256 of the reference's functional suite, testing/test.py:55): one launch per
+// 128-column slice of v and o, each recomputing the scores.  With dim_qk 256 a CTA holds one query tile (NT = 1).
+template <class F, int D, bool kBf16, int NT, bool kSparse = false>
 int launch_parallel_sliced(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
   if (a->num_splits > 1) return ATTN_B200_E_UNSUPPORTED;
   for (int dv0 = 0; dv0 < a->dim_v; dv0 += 128) {
-    const int rc = launch_parallel<F, 256, 128, kBf16, 1>(a, stream, device_status, dv0);
+    const int rc = launch_parallel<F, D, 128, kBf16, NT, kSparse>(a, stream, device_status, dv0);
     if (rc != ATTN_B200_OK) return rc;
   }
   return ATTN_B200_OK;
 }
 
+// The instantiation for one pair of head dims: 64/64 and 128/128 with two query tiles per CTA, 192/128 and 256/128 with
+// one (their query and K tiles fill the shared memory), wider dim_v sliced.  A library built for one pair calls this.
+template <class F, int D, int DV, bool kBf16, bool kSparse = false>
+int launch_parallel_dims(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
+  static_assert(D == 64 || D == 128 || D == 192 || D == 256, "dim_qk must be 64, 128, 192 or 256");
+  constexpr int NT = D <= 128 ? 2 : 1;
+  if constexpr (DV > 128) return launch_parallel_sliced<F, D, kBf16, NT, kSparse>(a, stream, device_status);
+  else return launch_parallel<F, D, DV, kBf16, NT, kSparse>(a, stream, device_status);
+}
+
 // Dispatch over the head-dimension / dtype instantiations compiled for functor F.
+template <class F, bool kSparse>
+int dispatch_parallel_dims(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
+  const bool bf16 = a->dtype == ATTN_B200_DTYPE_BF16;
+#define ATTN_B200_DIMS(DQ, DVV)                                                                          \
+  return bf16 ? launch_parallel_dims<F, DQ, DVV, true, kSparse>(a, stream, device_status)                \
+              : launch_parallel_dims<F, DQ, DVV, false, kSparse>(a, stream, device_status)
+  if (a->dim_qk == 128 && a->dim_v == 128) { ATTN_B200_DIMS(128, 128); }
+  if (a->dim_qk == 64 && a->dim_v == 64) { ATTN_B200_DIMS(64, 64); }
+  if (a->dim_qk == 192 && a->dim_v == 128) { ATTN_B200_DIMS(192, 128); }
+  if (a->dim_qk == 128 && a->dim_v > 128 && a->dim_v % 128 == 0) { ATTN_B200_DIMS(128, 256); }   // any multiple: sliced
+  if (a->dim_qk == 256 && a->dim_v % 128 == 0) { ATTN_B200_DIMS(256, 256); }
+#undef ATTN_B200_DIMS
+  return ATTN_B200_E_UNSUPPORTED;
+}
+
 template <class F>
 int dispatch_parallel(const AttnB200ParallelArgs* a, cudaStream_t stream, int* device_status) {
   const int rc = validate_parallel_args(a);
   if (rc != ATTN_B200_OK) return rc;
-  const bool bf16 = a->dtype == ATTN_B200_DTYPE_BF16;
-  if (a->dim_qk == 128 && a->dim_v == 128)
-    return bf16 ? launch_parallel<F, 128, 128, true>(a, stream, device_status)
-                : launch_parallel<F, 128, 128, false>(a, stream, device_status);
-  if (a->dim_qk == 64 && a->dim_v == 64)
-    return bf16 ? launch_parallel<F, 64, 64, true>(a, stream, device_status)
-                : launch_parallel<F, 64, 64, false>(a, stream, device_status);
-  if (a->dim_qk == 256 && a->dim_v % 128 == 0)
-    return bf16 ? launch_parallel_sliced<F, true>(a, stream, device_status) : launch_parallel_sliced<F, false>(a, stream, device_status);
-  return ATTN_B200_E_UNSUPPORTED;
+  return a->tile_keep != nullptr ? dispatch_parallel_dims<F, true>(a, stream, device_status)
+                                 : dispatch_parallel_dims<F, false>(a, stream, device_status);
 }
 
 }  // namespace b200

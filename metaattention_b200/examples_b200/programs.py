@@ -217,3 +217,97 @@ def sparse_decode_engine(B, H, Hkv, Skv, D, Dv, block=32, dtype=torch.bfloat16):
     meta = (meta_tensor(B, H, 1, D, dtype=dtype), meta_tensor(B, Hkv, Skv, D, dtype=dtype), meta_tensor(B, Hkv, Skv, Dv, dtype=dtype))
     return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None, online_func=NaturalSoftmax(),
                            extern_block_mask=True, use_varlen=True, infer_mask_block_N=block)
+
+
+class Base2Softmax(OnlineFunc):
+    """Online softmax written with base-2 exponentials and logarithms on scores that are already scaled."""
+    LOG2E, LN2 = 1.4426950408889634, 0.6931471805599453
+
+    def __init__(self):
+        super().__init__({"m": SymbolScalar("m", Var("-inf")), "r": SymbolScalar("r", Var("0.0"))},
+                         {"lse": SymbolScalar("lse", Var("0.0"))}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        m, r = online_rowscales["m"], online_rowscales["r"]
+        m_new = m.max(scores.get_reduce("max"))
+        shrink = ((m - m_new) * Base2Softmax.LOG2E).exp2()
+        p = ((scores - m_new) * Base2Softmax.LOG2E).exp2()
+        return p, {"m": m_new, "r": r * shrink + p.get_reduce("sum")}, shrink
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        r, m = online_rowscales["r"], online_rowscales["m"]
+        return o / r, {"lse": r.log2() * Base2Softmax.LN2 + m}
+
+
+def capped_distance_bias_engine(B, H, S, D, Dv, cap=2.0, slope=0.02, dtype=torch.bfloat16):
+    """Causal softmax of min(scale * q.k, cap) - slope_h * |q_idx - kv_idx| with slope_h = slope * (h + 1): a logit
+    cap and a per-head linear distance bias.  Drives Min, Abs, Neg, index operands, Exp2, Log2 and a division by a
+    per-row value through the lowered functor."""
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        dist = (q_idx - kv_idx).abs()
+        return (score * scale).min(cap) + (-dist) * ((h + 1) * slope)
+    return AttentionEngine(_meta(B, H, S, D, Dv, dtype), CustomIO({}), score_mod=score_mod, mask_mod=causal,
+                           online_func=Base2Softmax())
+
+
+class SplitSoftmax(NaturalSoftmax):
+    """Online softmax with the split-KV ``combine`` of examples/mha_decode.py, written with natural exponentials so
+    that it matches the natural-log lse of the epilogue: w_i = exp(lse_i - log sum_k exp(lse_k)).  A second final row
+    scale keeps the engine from recognising the built-in softmax, so the combine below is what runs."""
+
+    def __init__(self):
+        OnlineFunc.__init__(self, {"m": SymbolScalar("m", Var("-inf")), "r": SymbolScalar("r", Var("0.0"))},
+                            {"lse": SymbolScalar("lse", Var("0.0")), "rowmax": SymbolScalar("rowmax", Var("0.0"))},
+                            CustomIO())
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        r, m = online_rowscales["r"], online_rowscales["m"]
+        return o / r, {"lse": r.log() + m, "rowmax": m}
+
+    @staticmethod
+    def combine(final_rowscales):
+        lse = final_rowscales["lse"]
+        lse_max = lse.get_reduce("max")
+        total = (lse - lse_max).exp().get_reduce("sum")
+        return (lse - (total.log() + lse_max)).exp()
+
+
+class SplitAbsSum(OnlineFunc):
+    """A normaliser that is not softmax: p = scores / max(running sum of |scores|, 1) like retention's, with a
+    ``combine`` that re-normalises the splits by their denominators: w_i = den_i / max(sum_k acc_k, 1)."""
+
+    def __init__(self):
+        super().__init__({"acc": SymbolScalar("acc", Var("0.0")), "den": SymbolScalar("den", Var("1.0"))},
+                         {"acc": SymbolScalar("acc", Var("0.0")), "den": SymbolScalar("den", Var("1.0"))}, CustomIO())
+
+    @staticmethod
+    def online_fwd(scores, online_rowscales, b, h, q_idx):
+        acc = online_rowscales["acc"] + scores.get_reduce("abssum")
+        den_new = acc.max(1.0)
+        return scores / den_new, {"acc": acc, "den": den_new}, online_rowscales["den"] / den_new
+
+    @staticmethod
+    def online_fwd_epilogue(o, online_rowscales, b, h, q_idx):
+        return o, {"acc": online_rowscales["acc"], "den": online_rowscales["den"]}
+
+    @staticmethod
+    def combine(final_rowscales):
+        acc, den = final_rowscales["acc"], final_rowscales["den"]
+        return den / acc.get_reduce("abssum").max(1.0)
+
+
+def split_decode_engine(B, H, Sq, Skv, D, Dv, online="softmax", dtype=torch.bfloat16):
+    """Decode (a few query rows against a long KV, no mask) through a LOWERED functor with its own combine."""
+    scale = D ** -0.5
+
+    def score_mod(score, custom, b, h, q_idx, kv_idx):
+        return score * scale
+    meta = (meta_tensor(B, H, ((Sq + 127) // 128) * 128, D, dtype=dtype), meta_tensor(B, H, Skv, D, dtype=dtype),
+            meta_tensor(B, H, Skv, Dv, dtype=dtype))
+    return AttentionEngine(meta, CustomIO({}), score_mod=score_mod, mask_mod=None,
+                           online_func=SplitSoftmax() if online == "softmax" else SplitAbsSum())

@@ -69,7 +69,7 @@ def test_unsupported_patterns_raise_clearly():
     meta = (meta_tensor(1, 16, 1, 128, dtype=torch.float16), meta_tensor(1, 4, 4096, 128, dtype=torch.float16),
             meta_tensor(1, 4, 4096, 128, dtype=torch.float16))
     e = AttentionEngine(meta, CustomIO({}), None, None, None, use_varlen=True, extern_block_mask=True, infer_mask_block_N=32)
-    assert e.pattern == "gqa_decode" and e.custom_names == ["__kv_bias"]   # block mask / lengths enter as a bias input
+    assert e.pattern == "gqa_decode" and e.custom_names == [] and e.sparse_walk   # block mask / lengths select KV tiles per call
     with pytest.raises(TypeError):
         AttentionEngine(programs._meta(1, 2, 128, 64, 64, torch.float32), CustomIO({}), None, None, None)
 
@@ -169,10 +169,44 @@ def test_band_masks_are_recognised():
     assert classify_mask(lambda b, h, q, kv: kv <= q + 5, 1, 1, 200, 200) == (native.MASK_BAND, (native.MASK_OPEN, 5))
     assert classify_mask(programs.causal, 1, 1, 256, 256)[0] == native.MASK_CAUSAL
     assert classify_mask(lambda b, h, q, kv: q >= 0, 1, 1, 128, 128)[0] == native.MASK_NONE
-    with pytest.raises(NotImplementedError):
-        classify_mask(lambda b, h, q, kv: (q + kv) % 2 == 0, 1, 1, 128, 128)   # not a band
-    with pytest.raises(NotImplementedError):
-        classify_mask(lambda b, h, q, kv: (kv <= q) & (h >= 0) & (b == 0), 2, 1, 128, 128)   # depends on the batch index
+    from attn_engine.attn_engine import MASK_GENERAL
+    assert classify_mask(lambda b, h, q, kv: (q + kv) % 2 == 0, 1, 1, 128, 128)[0] == MASK_GENERAL   # not a band
+    assert classify_mask(lambda b, h, q, kv: (kv <= q) & (h >= 0) & (b == 0), 2, 1, 128, 128)[0] == MASK_GENERAL   # uses the batch index
+
+
+def test_general_masks_become_block_sparse_walks():
+    """Bitmaps and element masks of a mask that is not a band, against the dense mask they stand for."""
+    from core.lower import sparse
+    import numpy as np
+    doc = lambda b, h, q, kv: (q // 192 == kv // 192) & (q >= kv)      # causal inside documents of 192 tokens
+    S = 600
+    sp = sparse.build_block_sparse(doc, 2, 3, S, S)
+    assert (sp["batch"], sp["heads"], sp["mask_rows"]) == (1, 1, 128) and sp["keep"].shape == (1, 1, 5, 1)
+    dense = doc(0, 0, torch.arange(S).view(-1, 1), torch.arange(S).view(1, -1))
+    rebuilt = torch.zeros(640, 640, dtype=torch.bool)
+    keep = sp["keep"].numpy().view(np.uint32)
+    part = sp["partial"].numpy().view(np.uint32)
+    elem = sp["elem_mask"].numpy().view(np.uint32)
+    for qt in range(5):
+        slot = int(sp["mask_base"][0, 0, qt])
+        for kt in range(5):
+            if not (keep[0, 0, qt, 0] >> kt) & 1:
+                continue
+            if (part[0, 0, qt, 0] >> kt) & 1:
+                bits = (elem[slot][:, :, None] >> np.arange(32, dtype=np.uint32)) & 1      # [128, 4, 32]
+                rebuilt[qt * 128:(qt + 1) * 128, kt * 128:(kt + 1) * 128] = torch.from_numpy(bits.reshape(128, 128).astype(bool))
+                slot += 1
+            else:
+                rebuilt[qt * 128:(qt + 1) * 128, kt * 128:(kt + 1) * 128] = True
+    assert torch.equal(rebuilt[:S, :S], dense)
+    assert sp["kept_tiles"] < sp["all_tiles"]
+    # the kept tiles are those of the reference's block mask
+    assert torch.equal(torch.from_numpy(((keep[0, 0, :, 0, None] >> np.arange(5, dtype=np.uint32)) & 1).astype(np.int8)),
+                       create_block_mask(doc, 1, 1, S, S, "cpu")[0, 0])
+    per_head = sparse.build_block_sparse(lambda b, h, q, kv: q >= kv + 64 * h, 2, 3, 256, 256)
+    assert (per_head["batch"], per_head["heads"]) == (2, 3)
+    e = programs.masked_softmax_engine(1, 2, 384, 64, 64, doc)
+    assert e.sparse_walk and e.functor_kind == "builtin_softmax" and e.mask_kind == 0
 
 
 def _softmax_with_score_mod(score_mod, S=256, D=64):

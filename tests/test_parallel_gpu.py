@@ -358,3 +358,240 @@ def test_forward_host_streams_batch_slices(chunk):
     assert torch.equal(eng.last_final_rowscales["lse"], want_lse.cpu())
     with pytest.raises(ValueError):
         eng.forward_host(hq.cuda(), hk, hv)
+
+
+def test_lowered_functor_op_vocabulary():
+    """Min, Abs, Neg, index operands, Exp2, Log2 and a division by a per-row value, all through the LOWERED functor
+    (nothing here is recognised as a built-in): against the torch interpreter of the same traced DAG and against
+    the closed form softmax(min(scale q.k, cap) - slope_h |i - j|) v."""
+    from core.lower.trace import run_traced_attention
+    B, H, S, D, cap, slope = 1, 3, 320, 64, 2.0, 0.02
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 12)
+    e = programs.capped_distance_bias_engine(B, H, S, D, D, cap=cap, slope=slope)
+    assert e.functor_kind == "lowered"
+    for needle in ("fminf(", "fabsf(", "fast_exp2(", "fast_log2("):
+        assert needle in e.functor_source
+    o = e(*cuda(q, k, v))
+    lse = e.last_final_rowscales["lse"].cpu()
+    pos = torch.arange(S)
+    dist = (pos.view(-1, 1) - pos.view(1, -1)).abs().float()
+    s = torch.einsum("bshd,bthd->bhst", q.float(), k.float()) * D ** -0.5
+    s = s.clamp(max=cap) - dist * (slope * (torch.arange(H).float() + 1)).view(1, H, 1, 1)
+    s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+    want = torch.einsum("bhst,bthd->bshd", torch.softmax(s, -1), v.float())
+    check(o, want)
+    assert (lse - torch.logsumexp(s, -1)).abs().max().item() < 2e-3
+    o_ref, fin = run_traced_attention(e.traced, q, k, v, causal=True)
+    check(o, o_ref)
+    assert (lse - fin["lse"]).abs().max().item() < 2e-3
+
+
+def test_mha_decode_against_reference_golden():
+    """golden from the reference's decode closure (testing/test.py:131-148), its tolerance 1e-2"""
+    g = torch.load(os.path.join(GOLD, "mha_decode.pt"))
+    B, H, Sq, KV, D, Dv = g["shape"]
+    gen = torch.Generator().manual_seed(g["seed"])
+    q = torch.randn(B, Sq, H, D, generator=gen).to(torch.bfloat16)
+    k = torch.randn(B, KV, H, D, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, KV, H, Dv, generator=gen).to(torch.bfloat16)
+    e = programs.softmax_decode_engine(B, H, Sq, KV, D, Dv)
+    for splits in (1, 2):
+        e.kv_splits = splits
+        o = e(*cuda(q, k, v))
+        assert o.shape == (B, Sq, H, Dv)
+        check(o, g["o"], max_abs=1e-2)
+
+
+def test_sparse_gqa_decode_against_reference_golden():
+    """golden from the reference's block-sparse decode closure (testing/test.py:654-694): 32-token blocks per
+    (batch, KV head), ragged cache lengths"""
+    g = torch.load(os.path.join(GOLD, "sparse_gqa_decode.pt"))
+    B, H, G, S, D, Dv = g["shape"]
+    gen = torch.Generator().manual_seed(g["seed"])
+    q = torch.randn(B, 1, H, D, generator=gen).to(torch.bfloat16)
+    k = torch.randn(B, S, G, D, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, S, G, Dv, generator=gen).to(torch.bfloat16)
+    e = programs.sparse_decode_engine(B, H, G, S, D, Dv, block=g["block"])
+    o = e(*cuda(q, k, v), block_mask=g["block_mask"].cuda(), cache_seqlens=g["cache_seqlens"].cuda())
+    check(o[:, 0], g["o"], max_abs=1e-2)
+    check(o[:, 0], rm.sparse_gqa_decode(q, k, v, g["block_mask"], g["cache_seqlens"], g["block"]))
+
+
+def test_reference_examples_called_on_the_gpu():
+    """The reference's own example programs, imported unchanged from a checkout of the reference (skipped where none
+    is present), constructed AND called on seeded inputs, against the oracle."""
+    import importlib
+    import sys
+    from conftest import reference_root
+    ref = reference_root()
+    if ref is None:
+        pytest.skip("no checkout of the reference on this machine")
+    sys.path.insert(0, ref)
+    try:
+        B, H, S, D = 1, 4, 512, 128
+        q, k, v = inputs.attention_bshd(B, H, S, D, D, 301)
+        for mod_name in ("examples.mha", "examples.mha_v2"):
+            eng = importlib.import_module(mod_name).causal_softmax_attention(B, H, S, D, D, dtype=torch.bfloat16)
+            check(eng(*cuda(q, k, v)), rm.softmax_attention(q, k, v, True))
+        bias = torch.tensor([-math.log(S)])
+        for mod_name in ("examples.sigmoid_attn", "examples.sigmoid_attn_v2"):
+            eng = importlib.import_module(mod_name).sigmoid_attention(B, H, S, D, D)   # fp16 engines
+            qs, ks, vs = [(t * D ** -0.5 if i == 0 else t).to(eng.dtype) for i, t in enumerate((q, k, v))]
+            o = eng(*cuda(qs, ks, vs), bias.cuda())
+            check(o, rm.sigmoid_attention(qs, ks, vs, bias, True), max_abs=1e-1, mean_abs=1e-2)
+        q6, k6, v6 = inputs.attention_bshd(1, 6, 512, 64, 64, 302, k_scale=0.5, v_scale=0.5)
+        for mod_name in ("examples.reluattn", "examples.reluattn_v2"):
+            eng = importlib.import_module(mod_name).relu_attention(1, 6, 512, 64, 64, dtype=torch.bfloat16)
+            check(eng(*cuda(q6, k6, v6)), rm.relu_attention(q6, k6, v6), max_abs=1e-1, mean_abs=1e-2)
+        dec = importlib.import_module("examples.mha_decode").softmax_attention_decode(2, 8, 1, 4096, 128, 128, dtype=torch.bfloat16)
+        qd, kd, vd = inputs.randn((2, 1, 8, 128), 303, torch.bfloat16), inputs.randn((2, 4096, 8, 128), 304, torch.bfloat16), \
+            inputs.randn((2, 4096, 8, 128), 305, torch.bfloat16)
+        check(dec(*cuda(qd, kd, vd)), rm.softmax_attention(qd, kd, vd, causal=False))
+        ret = importlib.import_module("examples.retnet_recurrent").retnet_recurrent(1, 8, 512, 256, 512, dtype=torch.bfloat16)
+        qr, kr, vr, decay = inputs.retention_bhsd(1, 8, 512, 256, 512, 306)
+        torch.testing.assert_close(ret(*cuda(qr, kr, vr, decay)).float().cpu(), rm.retention_recurrent(qr, kr, vr), rtol=1e-1, atol=1e-1)
+        gla = importlib.import_module("examples.gated_retention").gated_retention(1, 4, 512, 256, 256, dtype=torch.bfloat16)
+        qg, kg, vg, gg = inputs.gla_inputs(1, 4, 512, 256, 256, 307)
+        torch.testing.assert_close(gla(*cuda(qg, kg, vg, gg)).float().cpu(),
+                                   rm.decayed_linear_attention(qg, kg, vg, gg, scale=256 ** -0.5), rtol=1e-1, atol=1e-1)
+    finally:
+        sys.path.remove(ref)
+
+
+def _masked_oracle(q, k, v, mask_mod, per_head):
+    """softmax attention under an arbitrary mask_mod, head by head when the mask depends on (batch, head)"""
+    B, S, H, _ = q.shape
+    Skv = k.shape[1]
+    qi, ki = torch.arange(S).view(-1, 1), torch.arange(Skv).view(1, -1)
+    if not per_head:
+        return rm.softmax_attention(q, k, v, keep=mask_mod(0, 0, qi, ki).expand(S, Skv))
+    out = torch.empty(B, S, H, v.shape[-1])
+    for b in range(B):
+        for h in range(H):
+            keep = mask_mod(torch.tensor(b), torch.tensor(h), qi, ki).expand(S, Skv)
+            out[b, :, h] = rm.softmax_attention(q[b:b + 1, :, h:h + 1], k[b:b + 1, :, h:h + 1], v[b:b + 1, :, h:h + 1], keep=keep)[0, :, 0]
+    return out
+
+
+GENERAL_MASKS = {
+    # causal inside documents of 192 tokens: partial tiles on and next to the diagonal, everything else skipped
+    "document": (lambda b, h, q, kv: (q // 192 == kv // 192) & (q >= kv), False),
+    # whole KV tiles dropped in a checkerboard, the diagonal kept: full tiles and skipped tiles only
+    "checkerboard": (lambda b, h, q, kv: (((q // 128) + (kv // 128)) % 2 == 0) | (q == kv), False),
+    # a different causal offset for every head, first column always kept
+    "per_head_offset": (lambda b, h, q, kv: (q >= kv + 64 * h) | (kv == 0), True),
+    # a prefix whose length depends on the batch entry, causal behind it
+    "per_batch_prefix": (lambda b, h, q, kv: (kv <= q) | (kv < 100 * (b + 1)), True),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GENERAL_MASKS))
+@pytest.mark.parametrize("S,D", [(600, 64), (1024, 128)])
+def test_general_masks_run_as_block_sparse_walks(name, S, D):
+    """mask_mod that is neither causal nor a band, or that uses the batch / head index: the reference switches to its
+    block-sparse template (core/lower/lower.py:723-738); here the KV tiles without a kept position are skipped and the
+    partially kept ones carry their element mask."""
+    mask_mod, per_head = GENERAL_MASKS[name]
+    B, H = 2, 3
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 500 + S)
+    e = programs.masked_softmax_engine(B, H, S, D, D, mask_mod)
+    assert e.sparse_walk and e.functor_kind == "builtin_softmax"
+    assert (e._sparse_host["batch"], e._sparse_host["heads"]) == ((B, H) if per_head else (1, 1))
+    o = e(*cuda(q, k, v))
+    check(o, _masked_oracle(q, k, v, mask_mod, per_head))
+
+
+def test_general_mask_with_a_lowered_functor_and_empty_query_tiles():
+    """sigmoid attention (lowered, identity online function) under a mask that leaves the second query tile of the first
+    batch entry without any KV tile: those rows are the epilogue of an empty accumulator, i.e. zero"""
+    B, H, S, D = 2, 2, 512, 64
+    mask_mod = lambda b, h, q, kv: (kv <= q) & ((q < 128) | (q >= 256) | (b > 0))   # noqa: E731
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 77)
+    bias = torch.tensor([-math.log(S)])
+    score_mod = lambda s, c, b, h, qi, ki: ((s * D ** -0.5 + c.input_tensors["softmax_bias"]) * 0.5).tanh() * 0.5 + 0.5   # noqa: E731
+    from attn_engine import AttentionEngine
+    from core import CustomIO
+    e = AttentionEngine(programs._meta(B, H, S, D, D, torch.bfloat16), CustomIO({"softmax_bias": (1,)}), score_mod=score_mod,
+                        mask_mod=mask_mod, online_func=None)
+    assert e.sparse_walk and e.functor_kind == "lowered"
+    o = e(*cuda(q, k, v), bias.cuda())
+    qi, ki = torch.arange(S).view(-1, 1), torch.arange(S).view(1, -1)
+    want = torch.empty(B, S, H, D)
+    for b in range(B):
+        s = torch.einsum("shd,thd->hst", q[b].float(), k[b].float()) * D ** -0.5 + bias
+        p = torch.sigmoid(s) * mask_mod(torch.tensor(b), 0, qi, ki)
+        want[b] = torch.einsum("hst,thd->shd", p, v[b].float())
+    check(o, want)
+    assert bool((o[0, 128:256] == 0).all())
+
+
+@pytest.mark.parametrize("online", ["softmax", "abssum"])
+def test_split_kv_with_a_lowered_combine(online):
+    """Split-KV for a LOWERED functor: the user's OnlineFunc.combine (traced over the splits' final row scales, lowered
+    with column reductions) weighs the partial results; forced split counts against the unsplit run and the closed form."""
+    from core.lower.trace import run_traced_combine
+    B, H, Sq, Skv, D = 2, 3, 2, 1152, 128     # 9 KV tiles
+    g = torch.Generator().manual_seed(2200)
+    q = torch.randn(B, Sq, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Skv, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Skv, H, D, generator=g).to(torch.bfloat16)
+    e = programs.split_decode_engine(B, H, Sq, Skv, D, D, online=online)
+    assert e.functor_kind == "lowered" and e.traced.combine_out is not None
+    assert "for (int k = 0; k < n; ++k)" in e.functor_source
+    if online == "softmax":
+        want = rm.softmax_attention(q, k, v, causal=False)
+    else:
+        s = torch.einsum("bshd,bthd->bhst", q.float(), k.float()) * D ** -0.5
+        want = torch.einsum("bhst,bthd->bshd", s / s.abs().sum(-1, keepdim=True).clamp(min=1.0), v.float())
+    outs = {}
+    for splits in (1, 2, 3, 4, 9):      # 4 becomes 3 (no split may be empty)
+        e.kv_splits = splits
+        outs[splits] = e(*cuda(q, k, v))
+        check(outs[splits], want)
+    assert torch.equal(outs[4], outs[3])
+    # the lowered combine means what the traced one means
+    lse = torch.tensor([[1.0, 2.0], [0.5, -1.0], [3.0, 0.0]])
+    fin = {name: (lse if name in ("lse", "den") else lse.abs() + 1) for name in e.traced.final}
+    w = run_traced_combine(e.traced, fin)
+    assert w.shape == (3, 2) and torch.isfinite(w).all()
+    if online == "softmax":
+        assert torch.allclose(w, torch.softmax(lse, 0), atol=1e-6)
+
+
+@pytest.mark.parametrize("B,H,S,D,Dv", [(1, 16, 2048, 128, 256), (1, 16, 2048, 192, 128), (2, 3, 333, 192, 128), (1, 2, 400, 128, 384)])
+def test_head_dims_of_the_reference_suite(B, H, S, D, Dv):
+    """dim_qk 128 / dim_v 256 (the reference's second softmax case, testing/test.py:55) and 192 / 128 (its H100
+    sweep, testing/benchmark_h100.py:60-63): causal softmax against the oracle"""
+    g = torch.Generator().manual_seed(D + Dv)
+    q = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, H, Dv, generator=g).to(torch.bfloat16)
+    e = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)
+    o = e(*cuda(q, k, v))
+    assert o.shape == (B, S, H, Dv)
+    check(o, rm.softmax_attention(q, k, v, causal=True, softmax_scale=D ** -0.5))
+    assert (e.last_final_rowscales["lse"].cpu() - rm.softmax_lse(q, k, True, D ** -0.5)).abs().max().item() < 1e-3
+
+
+def test_decode_tiles_entry_point():
+    """attn_b200_decode_tiles against a torch evaluation of the same rule, bit for bit"""
+    import numpy as np
+    B, Hkv, Skv, block = 3, 2, 1000, 32
+    g = torch.Generator().manual_seed(5)
+    nblk = (Skv + block - 1) // block
+    bm = torch.rand(B, Hkv, nblk, generator=g) < 0.4
+    lens = torch.tensor([1000, 517, 1], dtype=torch.int32)
+    sp = native_lib.decode_tiles(bm.cuda(), lens.cuda(), B, Hkv, Skv, block, torch.device("cuda", 0))
+    torch.cuda.synchronize()
+    keep = bm.repeat_interleave(block, -1)[..., :Skv] & (torch.arange(Skv).view(1, 1, -1) < lens.view(-1, 1, 1))
+    tiles = torch.nn.functional.pad(keep, (0, 1024 - Skv)).view(B, Hkv, 8, 128)
+    col = sp["elem_mask"].cpu().numpy().view(np.uint32).reshape(B, Hkv, 8, 4)
+    bits = ((col[..., None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(B, Hkv, 8, 128).astype(bool)
+    assert np.array_equal(bits, tiles.numpy())
+    kept_words = sp["keep"].cpu().numpy().view(np.uint32).reshape(B, Hkv)
+    part_words = sp["partial"].cpu().numpy().view(np.uint32).reshape(B, Hkv)
+    any_, all_ = tiles.any(-1).numpy(), tiles.all(-1).numpy()
+    for b in range(B):
+        for h in range(Hkv):
+            assert [(int(kept_words[b, h]) >> j) & 1 for j in range(8)] == [int(x) for x in any_[b, h]]
+            assert [(int(part_words[b, h]) >> j) & 1 for j in range(8)] == [int(x and not y) for x, y in zip(any_[b, h], all_[b, h])]
