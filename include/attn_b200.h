@@ -170,14 +170,28 @@ typedef struct AttnB200MlaShape {
   int32_t batch, heads_q, seq_kv, dim_qk, dim_v;
 } AttnB200MlaShape;
 
-/* Split-KV plan.  Replaces get_mla_metadata
- * (core/template/cute_template_kvshared/flash_api.cpp:23-59,
- *  kernels/get_mla_metadata.cu:8-82): chooses how many KV splits each
- * sequence gets so that sm_count SMs are evenly loaded.  Host-side, integer. */
+/* Uniform split-KV plan: one split count for every sequence, from the shape alone, so that sm_count SMs are
+ * evenly loaded when all sequences have seq_kv tokens.  Host-side, integer.  (The scheduler below, which looks at
+ * the actual cache lengths, is the counterpart of the reference's get_mla_metadata.) */
 int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t* num_splits_out);
 
-/* Bytes of scratch (fp32 partial outputs + partial log-sum-exp) the decode
- * needs for a given plan. */
+/* Tile scheduler.  Replaces get_mla_metadata (core/template/cute_template_kvshared/flash_api.cpp:23-59,
+ * kernels/get_mla_metadata.cu:8-82): from the per-sequence cache lengths ON THE DEVICE, cuts the 128-row KV tiles of
+ * all sequences -- every sequence, and every piece of one, charged 4 tiles of fixed overhead -- into num_parts equal
+ * payloads, one per two-SM cluster.  Enqueued on the stream, no host synchronisation.
+ *   cache_seqlens: device int32 [batch], or NULL = seq_kv tokens each;
+ *   num_parts: attn_b200_mla_num_parts(heads_q, SM count) = SM pairs / head blocks of 128 heads;
+ *   tile_scheduler_metadata: device int32 [num_parts][8] = first sequence, first token, last sequence (inclusive),
+ *     end token (exclusive), split index of the part's first piece, KV tiles of the part, 0, 0 (fields 0-4 as in
+ *     the reference's record);
+ *   num_splits: device int32 [batch + 1], cumulative count of pieces (= partial-result rows) per sequence. */
+int32_t attn_b200_mla_num_parts(int32_t heads_q, int32_t sm_count);
+int attn_b200_mla_metadata(const int32_t* cache_seqlens, int32_t batch, int32_t seq_kv, int32_t num_parts,
+                           int32_t* tile_scheduler_metadata, int32_t* num_splits, void* cuda_stream);
+
+/* Bytes of scratch the decode needs: num_splits >= 1: fp32 partial outputs + partial log-sum-exp of a uniform split;
+ * num_splits = 0 (scheduled): scheduler records, split counts and up to batch + num_parts partial rows, for the
+ * current device's SM count. */
 int64_t attn_b200_mla_workspace_bytes(const AttnB200MlaShape* shape, int32_t num_splits);
 
 typedef struct AttnB200MlaArgs {
@@ -195,7 +209,8 @@ typedef struct AttnB200MlaArgs {
   void* workspace;      /* attn_b200_mla_workspace_bytes() bytes */
   int64_t workspace_bytes;
   AttnB200MlaShape shape;
-  int32_t num_splits;
+  int32_t num_splits;   /* 0: scheduled -- every cluster runs the pieces the tile scheduler gives it (computed by the
+                           call from seq_lens, or passed in below); >= 1: that many equal splits per sequence */
   int32_t dtype;
   float scale;          /* softmax scale, e.g. 1/sqrt(dim_qk) */
   /* Ragged and paged caches (cache_seqlens / block_table of mha_fwd_kvcache_mla,
@@ -211,6 +226,12 @@ typedef struct AttnB200MlaArgs {
   int64_t block_table_stride;  /* elements between the tables of two sequences */
   int32_t page_size;           /* tokens per page: a multiple of 64 */
   int32_t num_pages;           /* pages in the pool */
+  /* num_splits = 0 only: the output of attn_b200_mla_metadata for these cache lengths (as the reference passes
+   * tile_scheduler_metadata and num_splits to its decode, flash_api.cpp:61-72), or NULL to let the call compute it. */
+  const int32_t* sched_meta;        /* device, [sched_parts][8] */
+  const int32_t* sched_num_splits;  /* device, [batch + 1] */
+  int32_t sched_parts;
+  int32_t reserved;
 } AttnB200MlaArgs;
 
 /* Split-KV decode + combine.  Replaces flash_fwd_splitkv_mla_kernel and

@@ -59,9 +59,31 @@ def _rows(t: torch.Tensor, what: str):
     return t
 
 
+last_plan = None   # how the most recent mla_decode_forward call was distributed (read by the benchmark)
+
+
+def num_parts(heads_q: int, device) -> int:
+    """Clusters that walk the tile schedule for ``heads_q`` query heads on ``device`` (SM pairs / head blocks)."""
+    return int(native.load_library().attn_b200_mla_num_parts(heads_q, _sm_count(device)))
+
+
+def mla_schedule(cache_seqlens, batch: int, seq_kv: int, heads_q: int, device):
+    """(tile_scheduler_metadata int32 [parts, 8], num_splits int32 [batch + 1]) from attn_b200_mla_metadata: the
+    equal-payload partition of all sequences' KV tiles over the clusters, computed on the device from the actual
+    cache lengths (``cache_seqlens`` None = ``seq_kv`` tokens each).  Enqueued on the current stream."""
+    parts = num_parts(heads_q, device)
+    meta = torch.empty((parts, 8), dtype=torch.int32, device=device)
+    cum = torch.empty((batch + 1,), dtype=torch.int32, device=device)
+    native.check(native.load_library().attn_b200_mla_metadata(
+        cache_seqlens.data_ptr() if cache_seqlens is not None else None, batch, seq_kv, parts, meta.data_ptr(), cum.data_ptr(),
+        native.current_stream_ptr()), "attn_b200_mla_metadata")
+    return meta, cum
+
+
 def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=None, num_splits: int | None = None,
                        workspace: torch.Tensor | None = None, cache_seqlens: torch.Tensor | None = None,
-                       block_table: torch.Tensor | None = None, max_seqlen: int | None = None):
+                       block_table: torch.Tensor | None = None, max_seqlen: int | None = None,
+                       tile_scheduler_metadata: torch.Tensor | None = None, num_splits_cum: torch.Tensor | None = None):
     """q: [B,H,D] (or [B,1,H,D]); kv: [B,S,D] (or [B,S,1,D]).  With ``q_rope`` /
     ``kv_rope`` given, q and kv hold only the first ``dim_v`` columns.
     ``cache_seqlens`` (int32 [B], CUDA): tokens of each sequence (1..S); default all S.
@@ -69,7 +91,12 @@ def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=Non
     [num_pages, page_size, 1, D]), page_size a multiple of 64, and entry i of a sequence's row names the
     page with its tokens [i*page_size, (i+1)*page_size); ``max_seqlen`` (default max_blocks*page_size)
     bounds the sequence lengths.
+    ``num_splits``: None or 0 = scheduled -- one cluster per SM pair walks the pieces of sequences that the tile
+    scheduler gives it (equal payloads from the actual cache lengths; ``tile_scheduler_metadata`` / ``num_splits_cum``
+    from ``mla_schedule`` may be passed to reuse one schedule over many calls); an int >= 1 = that many equal splits
+    per sequence.
     Returns (o [B,H,dim_v] in the input dtype, lse [B,H] fp32)."""
+    global last_plan
     q3, kv3 = _rows(q, "q"), _rows(kv, "kv")
     if not q3.is_cuda:
         raise native.NativeError("MLA decode needs CUDA tensors")
@@ -101,8 +128,9 @@ def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=Non
         raise native.NativeError("q and kv must share dtype float16 or bfloat16")
     with torch.cuda.device(q3.device):
         if num_splits is None:
-            num_splits = plan_splits(B, H, S, dim_qk, dim_v, _sm_count(q3.device))
+            num_splits = 0
         need = workspace_bytes(B, H, S, dim_qk, dim_v, num_splits)
+        last_plan = {"mode": "scheduled", "parts": num_parts(H, q3.device)} if num_splits == 0 else {"mode": "uniform", "num_splits": num_splits}
         if need < 0:
             raise native.NativeError(f"MLA decode does not support dims qk={dim_qk} v={dim_v}")
         if need > 0 and (workspace is None or workspace.numel() * workspace.element_size() < need):
@@ -126,6 +154,13 @@ def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=Non
         a.scale = float(scale)
         if cache_seqlens is not None:
             a.seq_lens = cache_seqlens.data_ptr()
+        if num_splits == 0 and tile_scheduler_metadata is not None:
+            if num_splits_cum is None or tile_scheduler_metadata.dtype != torch.int32 or num_splits_cum.dtype != torch.int32:
+                raise ValueError("tile_scheduler_metadata and num_splits_cum must be the int32 tensors of mla_schedule")
+            if tile_scheduler_metadata.shape[0] != num_parts(H, q3.device) or num_splits_cum.numel() != B + 1:
+                raise ValueError("the schedule was made for another batch or device")
+            a.sched_meta, a.sched_num_splits = tile_scheduler_metadata.data_ptr(), num_splits_cum.data_ptr()
+            a.sched_parts = tile_scheduler_metadata.shape[0]
         if block_table is not None:
             a.block_table = block_table.data_ptr()
             a.block_table_stride = block_table.stride(0)
@@ -159,27 +194,34 @@ def build_mla_decode(engine, B, H, Hkv, Skv, D, Dv, dtype, backend):
 
 
 def get_mla_metadata(cache_seqlens: torch.Tensor, num_heads_per_head_k: int, num_heads_k: int = 1):
-    """Same call as the reference's scheduler query (cute_template_kvshared/flash_mla_interface.py:57-72).
-    The native kernel takes one split count per call instead of per-SM tile lists: returns
-    (None, num_splits) with num_splits an int chosen by attn_b200_mla_plan for the longest sequence the
-    table can hold; pass both on to flash_mla_with_kvcache."""
+    """Same call as the reference's scheduler query (cute_template_kvshared/flash_mla_interface.py:57-72): returns
+    (tile_scheduler_metadata int32 [num_sm_parts, 8], num_splits int32 [batch + 1]) for these cache lengths; pass both
+    on to flash_mla_with_kvcache, for every layer of a decoding step."""
     if num_heads_k != 1:
         raise NotImplementedError("MLA decode expects a single shared latent KV head")
-    return None, None   # the plan needs the page geometry: flash_mla_with_kvcache makes it when given None
+    if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_cuda:
+        raise ValueError("cache_seqlens must be a CUDA int32 tensor [batch]")
+    with torch.cuda.device(cache_seqlens.device):
+        return mla_schedule(cache_seqlens.contiguous(), cache_seqlens.numel(), 0x3fffffff, num_heads_per_head_k, cache_seqlens.device)
 
 
 def flash_mla_with_kvcache(q, k_cache, block_table, cache_seqlens, head_dim_v, tile_scheduler_metadata=None,
                            num_splits=None, softmax_scale=None, causal=False):
     """Drop-in for the reference's paged MLA decode call
     (cute_template_kvshared/flash_mla_interface.py:74-115): q [B,1,Hq,D], k_cache [num_blocks,
-    page_block_size, 1, D], block_table int32 [B, max_blocks], cache_seqlens int32 [B].
+    page_block_size, 1, D], block_table int32 [B, max_blocks], cache_seqlens int32 [B],
+    tile_scheduler_metadata / num_splits as returned by get_mla_metadata (or None: the call makes its own schedule;
+    an int num_splits asks for that many equal splits per sequence instead).
     Returns (out [B,1,Hq,head_dim_v], softmax_lse [B,Hq,1] fp32).  ``causal`` has no effect with one
     query token per sequence."""
     if q.shape[1] != 1:
         raise NotImplementedError("one query token per sequence")
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
-    splits = num_splits if isinstance(num_splits, int) else None
-    o, lse = mla_decode_forward(q, k_cache, head_dim_v, softmax_scale, num_splits=splits,
-                                cache_seqlens=cache_seqlens, block_table=block_table)
+    if isinstance(num_splits, int):
+        o, lse = mla_decode_forward(q, k_cache, head_dim_v, softmax_scale, num_splits=num_splits,
+                                    cache_seqlens=cache_seqlens, block_table=block_table)
+    else:
+        o, lse = mla_decode_forward(q, k_cache, head_dim_v, softmax_scale, cache_seqlens=cache_seqlens, block_table=block_table,
+                                    tile_scheduler_metadata=tile_scheduler_metadata, num_splits_cum=num_splits)
     return o.view(o.shape[0], 1, o.shape[1], o.shape[2]), lse.view(lse.shape[0], lse.shape[1], 1)

@@ -91,6 +91,7 @@ class MlaArgs(C.Structure):
         ("shape", MlaShape), ("num_splits", C.c_int32), ("dtype", C.c_int32), ("scale", C.c_float),
         ("seq_lens", C.c_void_p), ("block_table", C.c_void_p), ("block_table_stride", C.c_int64),
         ("page_size", C.c_int32), ("num_pages", C.c_int32),
+        ("sched_meta", C.c_void_p), ("sched_num_splits", C.c_void_p), ("sched_parts", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -105,6 +106,8 @@ SIGNATURES = {
     "attn_b200_linear_workspace_bytes": (C.c_int64, [C.POINTER(LinearArgs)]),
     "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
     "attn_b200_mla_workspace_bytes": (C.c_int64, [C.POINTER(MlaShape), C.c_int32]),
+    "attn_b200_mla_num_parts": (C.c_int32, [C.c_int32, C.c_int32]),
+    "attn_b200_mla_metadata": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "attn_b200_mla_decode": (C.c_int, [C.POINTER(MlaArgs), C.c_void_p]),
     "attn_b200_mla_decode_static": (C.c_int, [C.POINTER(MlaArgs), C.c_void_p, C.c_void_p]),
     "attn_b200_last_device_status": (C.c_int, [C.c_int32, C.POINTER(C.c_int32)]),

@@ -36,6 +36,15 @@
 // FLOP balance 576 : 512, no recomputation.  Each latent row is fetched by both CTAs (the second
 // fetch is an L2 hit); no multicast is used.  Split-KV partials are fp32; the combine kernel does
 // the log-sum-exp weighted sum.
+//
+// Work distribution.  A cluster runs a LIST of work units (sequence, range of 128-row KV tiles) one after the other,
+// with every ring and barrier phase carried across units, so that the score CTA is already loading and scoring the
+// next unit while the value CTA finishes the current one.  The lists come from a scheduler in the manner of the
+// reference's get_mla_metadata (kernels/get_mla_metadata.cu:8-82): the KV tiles of all sequences, each charged a
+// fixed overhead, are cut into one equal payload per cluster from the ACTUAL cache lengths, on the device, so that
+// ragged batches stay balanced and a batch that does not fill whole waves is split where the payload ends; a
+// sequence cut by a boundary leaves fp32 partial results that the combine kernel merges.  The older mode with a
+// uniform split count per sequence (one unit per cluster) is the same kernel with a one-entry list.
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -67,6 +76,67 @@ struct MlaParams {
   float scale_log2;     // scale * log2(e)
   float scale;
   int* status;
+  // scheduled mode (sched != null): cluster `part` runs the units its 8-int record describes; num_splits_cum[b] is the
+  // number of partial-result rows in front of sequence b (a sequence with exactly one is written directly)
+  const int* sched;
+  const int* num_splits_cum;
+  int num_parts;
+};
+
+constexpr int kMlaSchedInts = 8;      // ints per scheduler record: begin sequence, begin token, end sequence (inclusive),
+                                      // end token (exclusive), split index of the first unit, KV tiles of the part
+constexpr int kMlaSchedOverhead = 4;  // tile-times a work unit costs besides its tiles (fill, drain, Q, final exchange)
+
+struct MlaUnit {
+  int b, t0, n;   // sequence, first KV tile, number of KV tiles
+  int slot;       // row of the partial results, or -1: the unit is its whole sequence and writes the output itself
+  int seq_len;
+};
+
+// The units of one cluster, in order.
+struct MlaWalk {
+  const MlaParams& p;
+  int b, b_end, begin_tile, end_token, split0;
+  bool first, done;
+  __device__ MlaWalk(const MlaParams& p_, int part, int legacy_b, int legacy_split) : p(p_), first(true), done(false) {
+    if (p.sched != nullptr) {
+      const int* m = p.sched + part * kMlaSchedInts;
+      b = m[0];
+      begin_tile = m[1] / kMlaTileN;
+      b_end = m[2];
+      end_token = m[3];
+      split0 = m[4];
+    } else {
+      b = b_end = legacy_b;
+      begin_tile = legacy_split * p.tiles_per_split;
+      split0 = legacy_split;
+      end_token = 0;
+    }
+  }
+  __device__ int len_of(int seq) const { return p.seq_lens != nullptr ? max(1, min(p.seq_lens[seq], p.seq_kv)) : p.seq_kv; }
+  __device__ bool next(MlaUnit& u) {
+    while (!done && b <= b_end && b < p.batch) {
+      u.b = b;
+      u.seq_len = len_of(b);
+      const int total = (u.seq_len + kMlaTileN - 1) / kMlaTileN;
+      if (p.sched != nullptr) {
+        u.t0 = first ? begin_tile : 0;
+        const int t1 = (b == b_end) ? min(total, (end_token + kMlaTileN - 1) / kMlaTileN) : total;
+        u.n = t1 - u.t0;
+        const int first_row = p.num_splits_cum[b], rows = p.num_splits_cum[b + 1] - first_row;
+        u.slot = rows == 1 ? -1 : first_row + (first ? split0 : 0);
+      } else {
+        u.t0 = begin_tile;
+        u.n = max(0, min(total, begin_tile + p.tiles_per_split) - begin_tile);
+        u.slot = p.num_splits == 1 ? -1 : b * p.num_splits + split0;
+        done = true;
+      }
+      first = false;
+      ++b;
+      if (u.n > 0) return true;
+    }
+    return false;
+  }
 };
 
 enum MlaWaitSite {
@@ -86,16 +156,18 @@ struct MlaSmem {
   static constexpr int kPFree = 32;      // [4] score: 1 arrival from the value CTA
   static constexpr int kPvGo = 36;       // [4] value, 128 arrivals
   static constexpr int kPvDone = 40;     // [4] value
-  static constexpr int kODone = 44;      // value
+  static constexpr int kStageFree = 44;   // value, 4 arrivals: the output rows staged in the V stages have been read back
   static constexpr int kFinalFull = 45;  // value, 128 arrivals from the score CTA
   static constexpr int kQReady = 46;     // score, 256 arrivals
   static constexpr int kQrFull = 47;     // score
   static constexpr int kRowMax = 48;     // [2] score, 256 arrivals: both halves of a row's maximum are posted
   static constexpr int kRowSum = 50;     // score, 128 arrivals
-  static constexpr int kNumBars = 51;
+  static constexpr int kFinalFree = 51;  // score, 4 arrivals from the value CTA: the final statistics of a unit have been read
+  static constexpr int kNumBars = 52;
   static constexpr int kOffBars = 0;
   static constexpr int kOffSlot = 416;     // TMEM base address
   static constexpr int kOffAbort = 424;
+  static constexpr int kOffPartTiles = 432;   // int: KV tiles of all units of this cluster
   static constexpr int kOffScale = 512;    // value: float [2][128] rescale factor per tile parity and head
   static constexpr int kOffFinal = 1536;   // value: float [128][2] (1/rowsum, lse)
   static constexpr int kOffRowMax = 512;   // score (same bytes, other CTA): float [2 bufs][2 halves][128]
@@ -146,24 +218,22 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();       // 0 = score CTA, 1 = value CTA
   const AbortState ab{abort_flag, p.status};
-  const int split = blockIdx.y % p.num_splits;
-  const int hb = blockIdx.y / p.num_splits;
-  const int b = blockIdx.z;
+  // scheduled mode: blockIdx.y = head block * parts + part; uniform splits: blockIdx.y = head block * splits + split
+  const int per_hb = p.sched != nullptr ? p.num_parts : p.num_splits;
+  const int part = blockIdx.y % per_hb;
+  const int hb = blockIdx.y / per_hb;
   const int head0 = hb * M;
-  // tokens of this sequence (uniform over the cluster), and with a paged cache the table of its pages
-  const int seq_len = p.seq_lens != nullptr ? max(1, min(p.seq_lens[b], p.seq_kv)) : p.seq_kv;
-  const int* pages = p.block_table != nullptr ? p.block_table + static_cast<long long>(b) * p.bt_stride : nullptr;
-  // pool coordinates of logical token row `r` (rows past the end are redirected to the last token's
-  // 64-row block: they are masked, but must be read from mapped memory)
-  auto locate = [&](int r, int& row_in_page, int& page) {
-    r = min(r, ((seq_len - 1) >> 6) << 6 | (r & 63));
+  volatile int* part_tiles_s = reinterpret_cast<volatile int*>(smem_raw + L::kOffPartTiles);
+  auto make_walk = [&]() { return MlaWalk(p, part, static_cast<int>(blockIdx.z), part); };
+  // pool coordinates of logical token row `r` of a sequence with a paged cache (rows past the end are redirected to
+  // the last token's 64-row block: they are masked, but must be read from mapped memory)
+  auto locate = [&](const MlaUnit& u, int r, int& row_in_page, int& page) {
+    r = min(r, ((u.seq_len - 1) >> 6) << 6 | (r & 63));
     const int blk = r / p.page_rows;
-    page = pages[blk];
+    page = p.block_table[static_cast<long long>(u.b) * p.bt_stride + blk];
     row_in_page = r - blk * p.page_rows;
   };
-  const int total_tiles = (seq_len + N - 1) / N;
-  const int tile_begin = split * p.tiles_per_split;
-  const int n = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);  // 128-row tiles of this split
+  const bool paged = p.block_table != nullptr;
   constexpr uint32_t kPTxEven = L::kPBytes + M * 4;   // half 0 of a tile also carries the rescale factors
   constexpr uint32_t kPTxOdd = L::kPBytes;
 
@@ -176,6 +246,13 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
       bad = 1;
     }
     *abort_flag = bad;
+    {
+      MlaWalk count = make_walk();
+      MlaUnit u;
+      int tiles = 0;
+      while (count.next(u)) tiles += u.n;
+      *part_tiles_s = tiles;
+    }
     for (int i = 0; i < 12; ++i) {
       mbar_init(&bars[L::kSlotFull + i], 1);
       mbar_init(&bars[L::kSlotEmpty + i], 1);
@@ -191,7 +268,8 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
       mbar_init(&bars[L::kPvGo + i], 128);
       mbar_init(&bars[L::kPvDone + i], 1);
     }
-    mbar_init(&bars[L::kODone], 1);
+    mbar_init(&bars[L::kStageFree], 4);
+    mbar_init(&bars[L::kFinalFree], 4);
     mbar_init(&bars[L::kFinalFull], 128);
     mbar_init(&bars[L::kQReady], 256);
     mbar_init(&bars[L::kQrFull], 1);
@@ -217,30 +295,45 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
   cluster_sync_all();  // both CTAs have initialised (and armed) their barriers before any remote traffic
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const bool run = (n > 0) && !*abort_flag && (*reinterpret_cast<volatile int*>(p.status) == 0);
+  const int part_tiles = *part_tiles_s;
+  const bool run = (part_tiles > 0) && !*abort_flag && (*reinterpret_cast<volatile int*>(p.status) == 0);
 
   if (rank == 0) {
     // ===================================== score CTA =====================================
     if (warp == 8) {
       if (lane == 0 && run) {
-        mbar_arrive_expect_tx(&bars[L::kQrFull], L::kQrBytes);
-        tma_load_3d(sQr, &tmQr, &bars[L::kQrFull], 0, head0, b);
-        for (int g = 0; g < n * 3; ++g) {   // slot loads: three 64-column chunks of one 128-row tile each
-          const int j = g / 3, c0 = (g - j * 3) * 3, slot = g % L::kScoreSlots;
-          if (!mbar_wait(&bars[L::kSlotEmpty + slot], ((g / L::kScoreSlots) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
-          mbar_arrive_expect_tx(&bars[L::kSlotFull + slot], L::kSlotBytes);
-          if (pages == nullptr) {
-            for (int c = c0; c < c0 + 3; ++c)
-              tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot],
-                          c < 8 ? c * 64 : 0, (tile_begin + j) * N, b);
-          } else {
-            // paged cache: the maps have 64-row boxes over [pool page][row in page]; a tile is two boxes
-            for (int hf = 0; hf < 2; ++hf) {
-              int rin, pg;
-              locate((tile_begin + j) * N + hf * 64, rin, pg);
+        MlaWalk walk = make_walk();
+        MlaUnit u;
+        int J = 0;     // KV tiles of the units before this one: ring positions and barrier phases run on across units
+        bool ok = true;
+        for (int ui = 0; ok && walk.next(u); ++ui, J += u.n) {
+          if (ui > 0) {
+            // the rope tile of the previous unit is read by the MMAs of its last slot load
+            const int gl = 3 * J - 1;
+            ok = mbar_wait(&bars[L::kSlotEmpty + gl % L::kScoreSlots], (gl / L::kScoreSlots) & 1, ab, kMlaSlotEmpty);
+            if (!ok) break;
+          }
+          mbar_arrive_expect_tx(&bars[L::kQrFull], L::kQrBytes);
+          tma_load_3d(sQr, &tmQr, &bars[L::kQrFull], 0, head0, u.b);
+          for (int g = 0; g < u.n * 3; ++g) {   // slot loads: three 64-column chunks of one 128-row tile each
+            const int gg = 3 * J + g;
+            const int j = g / 3, c0 = (g - j * 3) * 3, slot = gg % L::kScoreSlots;
+            ok = mbar_wait(&bars[L::kSlotEmpty + slot], ((gg / L::kScoreSlots) & 1) ^ 1, ab, kMlaSlotEmpty);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bars[L::kSlotFull + slot], L::kSlotBytes);
+            if (!paged) {
               for (int c = c0; c < c0 + 3; ++c)
-                tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes + hf * (64 * 128), c < 8 ? &tmKV : &tmKVr,
-                            &bars[L::kSlotFull + slot], c < 8 ? c * 64 : 0, rin, pg);
+                tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes, c < 8 ? &tmKV : &tmKVr, &bars[L::kSlotFull + slot],
+                            c < 8 ? c * 64 : 0, (u.t0 + j) * N, u.b);
+            } else {
+              // paged cache: the maps have 64-row boxes over [pool page][row in page]; a tile is two boxes
+              for (int hf = 0; hf < 2; ++hf) {
+                int rin, pg;
+                locate(u, (u.t0 + j) * N + hf * 64, rin, pg);
+                for (int c = c0; c < c0 + 3; ++c)
+                  tma_load_3d(sChunk + slot * L::kSlotBytes + (c - c0) * L::kChunkBytes + hf * (64 * 128), c < 8 ? &tmKV : &tmKVr,
+                              &bars[L::kSlotFull + slot], c < 8 ? c * 64 : 0, rin, pg);
+              }
             }
           }
         }
@@ -250,8 +343,14 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         constexpr uint32_t idesc = make_idesc_f16(M, N, kBf16, false, false);
         const uint64_t chunk_desc0 = make_smem_desc(smem_u32(sChunk), 16, 1024);
         const uint64_t qr_desc0 = make_smem_desc(smem_u32(sQr), 16, 1024);
-        bool ok = mbar_wait(&bars[L::kQReady], 0, ab, kMlaQReady) && mbar_wait(&bars[L::kQrFull], 0, ab, kMlaQrFull);
-        for (int j = 0; j < n && ok; ++j) {
+        MlaWalk walk = make_walk();
+        MlaUnit unit;
+        int J = 0;
+        bool ok = true;
+        for (int ui = 0; ok && walk.next(unit); ++ui, J += unit.n) {
+        ok = mbar_wait(&bars[L::kQReady], ui & 1, ab, kMlaQReady) && mbar_wait(&bars[L::kQrFull], ui & 1, ab, kMlaQrFull);
+        for (int jl = 0; jl < unit.n && ok; ++jl) {
+          const int j = J + jl;
           const int buf = j & 1;
           ok = mbar_wait(&bars[L::kSFree + buf], ((j >> 1) & 1) ^ 1, ab, kMlaSFree);
           for (int u = 0; u < 3 && ok; ++u) {
@@ -275,6 +374,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           }
           if (ok) umma_commit(&bars[L::kSFull + buf]);
         }
+        }
       }
     } else {
       // 256 threads: thread (wg, row) owns columns [64*wg, 64*wg+64) of its head's score row
@@ -282,8 +382,18 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
       const int row = (warp & 3) * 32 + lane;
       const int head = head0 + row;
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      if (run) {
-        // ---- this head's query row, columns [256*wg, 256*wg+256) -> TMEM as 16-bit pairs ----
+      const uint32_t stage_w = smem_u32(sPStage) + warp * 1024;
+      const uint32_t peer_p = map_to_cta(smem_u32(sP), 1) + (warp & 3) * (32 * 128) + lane * 16;
+      const uint32_t peer_scale = map_to_cta(smem_u32(s_scale), 1) + row * 4;
+      const uint32_t peer_pfull = map_to_cta(smem_u32(&bars[L::kPFull]), 1);
+      MlaWalk walk = make_walk();
+      MlaUnit unit;
+      int J = 0;
+      bool ok = run;
+      for (int ui = 0; ok && walk.next(unit); ++ui, J += unit.n) {
+        const int b = unit.b, n = unit.n, seq_len = unit.seq_len, tile_begin = unit.t0;
+        // ---- this head's query row, columns [256*wg, 256*wg+256) -> TMEM as 16-bit pairs (every score MMA of the
+        //      previous unit has completed: this thread has seen its last score tile) ----
         const bool valid = head < p.heads;
         const uint4* qm = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + b * p.q_sb +
                                                          static_cast<long long>(head) * p.q_sh + wg * 256);
@@ -319,12 +429,8 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         // (128-byte swizzled) image of the value CTA's tile and sent on as whole 512-byte runs per warp instruction.
         // Sixteen-byte pieces sent row by row (32 rows per instruction) held the tensor pipe of this SM back for
         // about half of every tile.
-        const uint32_t stage_w = smem_u32(sPStage) + warp * 1024;
-        const uint32_t peer_p = map_to_cta(smem_u32(sP), 1) + (warp & 3) * (32 * 128) + lane * 16;
-        const uint32_t peer_scale = map_to_cta(smem_u32(s_scale), 1) + row * 4;
-        const uint32_t peer_pfull = map_to_cta(smem_u32(&bars[L::kPFull]), 1);
-        bool ok = true;
-        for (int j = 0; j < n && ok; ++j) {
+        for (int jl = 0; jl < n && ok; ++jl) {
+          const int j = J + jl;   // position in the cluster's whole run: rings, buffers and phases
           const int buf = j & 1;
           const int pslot = (2 * j + wg) & 3;
           ok = mbar_wait(&bars[L::kSFull + buf], (j >> 1) & 1, ab, kMlaSFull);
@@ -336,7 +442,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
           tmem_wait_ld();
           tc_fence_before_sync();
           mbar_arrive(&bars[L::kSFree + buf]);  // this half is in registers
-          const int kv0 = (tile_begin + j) * N + wg * 64;
+          const int kv0 = (tile_begin + jl) * N + wg * 64;
           if (kv0 + 64 > seq_len) {
 #pragma unroll
             for (int i = 0; i < 64; ++i) s[i] = (kv0 + i < seq_len) ? s[i] : -INFINITY;
@@ -400,7 +506,9 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
             s_rowsum[row] = r_sum;
             mbar_arrive(&bars[L::kRowSum]);
           } else {
-            ok = mbar_wait(&bars[L::kRowSum], 0, ab, kMlaRowSum);
+            ok = mbar_wait(&bars[L::kRowSum], ui & 1, ab, kMlaRowSum);
+            // the value CTA must have read the previous unit's statistics before they are replaced
+            if (ok && ui > 0) ok = mbar_wait_cluster(&bars[L::kFinalFree], (ui - 1) & 1, ab, kMlaFinal);
             if (ok) {
               const float total = r_sum + s_rowsum[row];
               const uint32_t peer_final = map_to_cta(smem_u32(s_final), 1) + row * 8;
@@ -414,18 +522,28 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
     }
   } else {
     // ===================================== value CTA =====================================
-    const int n_half = 2 * n;   // 64-row half tiles
+    const int part_half = 2 * part_tiles;   // 64-row half tiles of all units
     if (warp == 4) {
       if (lane == 0 && run) {
-        for (int g = 0; g < n * 4; ++g) {   // 32-row stages
-          const int st = g % L::kVStages;
-          if (!mbar_wait(&bars[L::kSlotEmpty + st], ((g / L::kVStages) & 1) ^ 1, ab, kMlaSlotEmpty)) break;
-          mbar_arrive_expect_tx(&bars[L::kSlotFull + st], L::kVStageBytes);
-          uint8_t* dst = sV + st * L::kVStageBytes;
-          int vrow = tile_begin * N + g * L::kVStageRows, vz = b;
-          if (pages != nullptr) locate(vrow, vrow, vz);
-          for (int c = 0; c < 8; ++c)
-            tma_load_3d(dst + c * (L::kVStageRows * 128), &tmV, &bars[L::kSlotFull + st], c * 64, vrow, vz);
+        MlaWalk walk = make_walk();
+        MlaUnit u;
+        int J = 0;
+        bool ok = true;
+        for (int ui = 0; ok && walk.next(u); ++ui, J += u.n) {
+          // the output rows of the previous unit are staged in the V stages: wait until they have been read back
+          if (ui > 0) ok = mbar_wait(&bars[L::kStageFree], (ui - 1) & 1, ab, kMlaOFinal);
+          for (int g = 0; g < u.n * 4 && ok; ++g) {   // 32-row stages
+            const int gg = 4 * J + g;
+            const int st = gg % L::kVStages;
+            ok = mbar_wait(&bars[L::kSlotEmpty + st], ((gg / L::kVStages) & 1) ^ 1, ab, kMlaSlotEmpty);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&bars[L::kSlotFull + st], L::kVStageBytes);
+            uint8_t* dst = sV + st * L::kVStageBytes;
+            int vrow = u.t0 * N + g * L::kVStageRows, vz = u.b;
+            if (paged) locate(u, vrow, vrow, vz);
+            for (int c = 0; c < 8; ++c)
+              tma_load_3d(dst + c * (L::kVStageRows * 128), &tmV, &bars[L::kSlotFull + st], c * 64, vrow, vz);
+          }
         }
       }
     } else if (warp == 5) {
@@ -433,8 +551,13 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         constexpr uint32_t idesc = make_idesc_f16(M, 256, kBf16, false, true);
         const uint64_t v_desc0 = make_smem_desc(smem_u32(sV), L::kVStageRows * 128, 1024);
         const uint64_t p_desc0 = make_smem_desc(smem_u32(sP), 16, 1024);
+        MlaWalk walk = make_walk();
+        MlaUnit u;
+        int J = 0;
         bool ok = true;
-        for (int h = 0; h < n_half && ok; ++h) {
+        for (int ui = 0; ok && walk.next(u); ++ui, J += u.n) {
+        for (int hl = 0; hl < 2 * u.n && ok; ++hl) {
+          const int h = 2 * J + hl;    // position in the cluster's whole run
           const int pslot = h & 3;
           ok = mbar_wait(&bars[L::kPvGo + pslot], (h >> 2) & 1, ab, kMlaPvGo);
           for (int s2 = 0; s2 < 2 && ok; ++s2) {
@@ -447,21 +570,22 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
             const uint64_t adesc = p_desc0 + static_cast<uint64_t>(pslot * (L::kPBytes >> 4) + s2 * 4);
             const uint64_t bdesc = v_desc0 + static_cast<uint64_t>(st * (L::kVStageBytes >> 4));
             constexpr uint64_t kHalf = (4 * L::kVStageRows * 128) >> 4;
-            umma_ss_2d(tmem_base, tmem_base + 256, adesc, bdesc, bdesc + kHalf, idesc, (h > 0 || s2 > 0) ? 1u : 0u);
+            umma_ss_2d(tmem_base, tmem_base + 256, adesc, bdesc, bdesc + kHalf, idesc, (hl > 0 || s2 > 0) ? 1u : 0u);
             umma_ss_2d(tmem_base, tmem_base + 256, adesc + 2, bdesc + 128, bdesc + kHalf + 128, idesc, 1u);
             umma_commit(&bars[L::kSlotEmpty + st]);
           }
           if (ok) umma_commit(&bars[L::kPvDone + pslot]);
         }
+        }
       }
     } else if (warp == 6) {
       if (lane == 0 && run) {
         const uint32_t peer_pfree = map_to_cta(smem_u32(&bars[L::kPFree]), 0);
-        for (int h = 0; h < n_half; ++h) {
+        for (int h = 0; h < part_half; ++h) {
           const int pslot = h & 3;
           if (!mbar_wait(&bars[L::kPvDone + pslot], (h >> 2) & 1, ab, kMlaPvDone)) break;
           // arm the slot for its next half tile BEFORE the score CTA learns that it is free
-          if (h + 4 < n_half) mbar_arrive_expect_tx(&bars[L::kPFull + pslot], (pslot & 1) ? kPTxOdd : kPTxEven);
+          if (h + 4 < part_half) mbar_arrive_expect_tx(&bars[L::kPFull + pslot], (pslot & 1) ? kPTxOdd : kPTxEven);
           mbar_arrive_cluster(peer_pfree + pslot * 8);
         }
       }
@@ -470,13 +594,22 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
       const int head = head0 + row;
       const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
       const uint32_t tO = tmem_base + lane_base;
+      const uint32_t peer_final_free = map_to_cta(smem_u32(&bars[L::kFinalFree]), 0);
+      MlaWalk walk = make_walk();
+      MlaUnit unit;
+      int J = 0;
       bool ok = run;
-      for (int h = 0; h < n_half && ok; ++h) {
+      bool any_unit = false;
+      for (int ui = 0; ok && walk.next(unit); ++ui, J += unit.n) {
+      any_unit = true;
+      const int b = unit.b, n = unit.n, n_half = 2 * unit.n;
+      for (int hl = 0; hl < n_half && ok; ++hl) {
+        const int h = 2 * J + hl;   // position in the cluster's whole run
         const int pslot = h & 3;
         ok = mbar_wait_cluster(&bars[L::kPFull + pslot], (h >> 2) & 1, ab, kMlaPFull);
         if (!ok) break;
         const float o_scale = (h & 1) ? 1.0f : s_scale[((h >> 1) & 1) * M + row];
-        if (h > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
+        if (hl > 0 && __any_sync(0xffffffffu, o_scale != 1.0f)) {
           // O must hold everything up to half tile h-1.  A parity wait is only unambiguous if the barrier
           // cannot be two phases away: these threads run far ahead of the MMAs, so they wait on the ring of
           // per-slot barriers (slot (h-1)&3 was last completed for half tile h-5, which p_full(h) implies).
@@ -499,15 +632,19 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         tc_fence_before_sync();
         mbar_arrive(&bars[L::kPvGo + pslot]);
       }
-      if (ok && n > 0) {
-        ok = mbar_wait_cluster(&bars[L::kFinalFull], 0, ab, kMlaFinal) &&
-             mbar_wait(&bars[L::kPvDone + ((n_half - 1) & 3)], ((n_half - 1) >> 2) & 1, ab, kMlaOFinal);
+      if (ok) {
+        const int h_last = 2 * J + n_half - 1;
+        ok = mbar_wait_cluster(&bars[L::kFinalFull], ui & 1, ab, kMlaFinal) &&
+             mbar_wait(&bars[L::kPvDone + (h_last & 3)], (h_last >> 2) & 1, ab, kMlaOFinal);
         if (ok) {
           tc_fence_after_sync();
           const bool in_range = head < p.heads;
           const float inv = s_final[row * 2];
           const float lse = s_final[row * 2 + 1];
-          if (p.num_splits == 1) {
+          // the statistics are in registers: the score CTA may send the next unit's
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(peer_final_free);
+          if (unit.slot < 0) {
             // Output rows leave through the V stages (all consumed by now): each warp stages the 32 rows it holds
             // (16-byte pieces, piece index xor row: conflict-free) and then stores them as 512 contiguous bytes per
             // instruction; a thread storing its own 1 KB row scatters every warp instruction over 32 rows.
@@ -549,7 +686,7 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
             }
             if (in_range && p.lse != nullptr) p.lse[static_cast<long long>(b) * p.heads + head] = lse;
           } else {
-            float* prow = p.part_o + ((static_cast<long long>(b) * p.num_splits + split) * p.heads + head) * DV;
+            float* prow = p.part_o + (static_cast<long long>(unit.slot) * p.heads + head) * DV;
 #pragma unroll 2
             for (int c = 0; c < DV / 32; ++c) {
               float o[32];
@@ -562,12 +699,17 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
                       make_float4(o[4 * v] * inv, o[4 * v + 1] * inv, o[4 * v + 2] * inv, o[4 * v + 3] * inv);
               }
             }
-            if (in_range) p.part_lse[(static_cast<long long>(b) * p.num_splits + split) * p.heads + head] = lse;
+            if (in_range) p.part_lse[static_cast<long long>(unit.slot) * p.heads + head] = lse;
           }
+          // the staged rows have been read back (or none were staged): the V stages may be refilled
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[L::kStageFree]);
         }
-      } else if (n == 0 && p.num_splits > 1 && head < p.heads) {
-        // a split with no KV rows contributes nothing
-        p.part_lse[(static_cast<long long>(b) * p.num_splits + split) * p.heads + head] = -INFINITY;
+      }
+      }
+      if (!any_unit && p.sched == nullptr && p.num_splits > 1 && head < p.heads && !*abort_flag) {
+        // uniform splits: a split with no KV rows contributes nothing
+        p.part_lse[(static_cast<long long>(blockIdx.z) * p.num_splits + part) * p.heads + head] = -INFINITY;
       }
     }
   }
@@ -587,25 +729,32 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
 
 // o[b,h,:] = sum_i exp(lse_i - lse) * part_o[b,i,h,:],  lse = log sum_i exp(lse_i).
 // One warp per (b, h); each lane owns DV/32 columns spread in float4 groups.
+// The partial rows of sequence b are rows [cum[b], cum[b+1]) of part_o / part_lse (scheduled mode; a sequence with one
+// row was written directly by the decode kernel and is skipped), or rows [b*num_splits, (b+1)*num_splits) (cum == null).
 template <int DV, bool kBf16>
 __global__ void __launch_bounds__(256) mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                                         void* __restrict__ o, float* __restrict__ lse_out, int batch,
-                                                        int heads, int num_splits) {
+                                                        int heads, int uniform_splits, const int* __restrict__ cum) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= batch * heads) return;
   const int b = warp / heads, h = warp % heads;
+  const int row0 = cum != nullptr ? cum[b] : b * uniform_splits;
+  const int num_splits = cum != nullptr ? cum[b + 1] - row0 : uniform_splits;
+  if (cum != nullptr && num_splits <= 1) return;
+  part_o += static_cast<long long>(row0) * heads * DV;
+  part_lse += static_cast<long long>(row0) * heads;
   float mx = -INFINITY;
-  for (int i = 0; i < num_splits; ++i) mx = fmaxf(mx, part_lse[(static_cast<long long>(b) * num_splits + i) * heads + h]);
+  for (int i = 0; i < num_splits; ++i) mx = fmaxf(mx, part_lse[static_cast<long long>(i) * heads + h]);
   float den = 0.f;
-  for (int i = 0; i < num_splits; ++i) den += __expf(part_lse[(static_cast<long long>(b) * num_splits + i) * heads + h] - mx);
+  for (int i = 0; i < num_splits; ++i) den += __expf(part_lse[static_cast<long long>(i) * heads + h] - mx);
   const float lse = mx + __logf(den);
   constexpr int V4 = DV / 128;  // float4 groups per lane
   float4 acc[V4];
 #pragma unroll
   for (int v = 0; v < V4; ++v) acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int i = 0; i < num_splits; ++i) {
-    const long long row = (static_cast<long long>(b) * num_splits + i) * heads + h;
+    const long long row = static_cast<long long>(i) * heads + h;
     const float li = part_lse[row];
     if (li == -INFINITY) continue;
     const float w = __expf(li - lse);
@@ -629,6 +778,87 @@ __global__ void __launch_bounds__(256) mla_combine_kernel(const float* __restric
   }
   if (lane == 0 && lse_out != nullptr) lse_out[static_cast<long long>(b) * heads + h] = lse;
 }
+
+// Scheduler: cuts the KV tiles of all sequences (each sequence, and each part of a sequence, charged
+// kMlaSchedOverhead tiles on top of its own) into `parts` equal payloads, one per cluster.  The greedy of the reference
+// (kernels/get_mla_metadata.cu:8-82) in this kernel's units: a part takes whole sequences while they fit its
+// remaining payload and then as many tiles of the next one as are left beyond the overhead.  Record of a part: first
+// sequence, first token, last sequence (inclusive), end token (exclusive), split index of its first unit, KV tiles.
+// cum[b] = partial-result rows in front of sequence b.  One warp; the walk itself is serial.
+__global__ void __launch_bounds__(32) mla_schedule_kernel(const int* __restrict__ seq_lens, int batch, int seq_kv, int parts,
+                                                        int* __restrict__ sched, int* __restrict__ cum) {
+  auto tiles_of = [&](int b) {
+    const int len = seq_lens != nullptr ? max(1, min(seq_lens[b], seq_kv)) : seq_kv;
+    return (len + kMlaTileN - 1) / kMlaTileN;
+  };
+  auto len_of = [&](int b) { return seq_lens != nullptr ? max(1, min(seq_lens[b], seq_kv)) : seq_kv; };
+  int total = 0;
+  for (int b = threadIdx.x; b < batch; b += 32) total += tiles_of(b) + kMlaSchedOverhead;
+  for (int off = 16; off >= 1; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+  if (threadIdx.x != 0) return;
+  const int payload = max((total + parts - 1) / parts + kMlaSchedOverhead, 2 * kMlaSchedOverhead);
+  int seq = 0, tile = 0, split = 0, rows = 0;
+  cum[0] = 0;
+  for (int part = 0; part < parts; ++part) {
+    int* rec = sched + part * kMlaSchedInts;
+    rec[0] = seq;
+    rec[1] = tile * kMlaTileN;
+    rec[4] = split;
+    int budget = payload, taken = 0;
+    while (seq < batch) {
+      const int rest = tiles_of(seq) - tile;
+      if (budget >= rest + kMlaSchedOverhead) {   // the rest of this sequence fits
+        rows += split + 1;
+        cum[seq + 1] = rows;
+        budget -= rest + kMlaSchedOverhead;
+        taken += rest;
+        ++seq;
+        tile = 0;
+        split = 0;
+      } else {
+        if (budget > kMlaSchedOverhead) {          // a piece of it does
+          tile += budget - kMlaSchedOverhead;
+          taken += budget - kMlaSchedOverhead;
+          ++split;
+        }
+        break;
+      }
+    }
+    rec[2] = tile > 0 ? seq : seq - 1;
+    rec[3] = tile > 0 ? tile * kMlaTileN : (seq > 0 ? len_of(seq - 1) : 0);
+    rec[5] = taken;
+    rec[6] = rec[7] = 0;
+  }
+}
+
+// Clusters that share the KV of all sequences: SM pairs, divided among the head blocks (each head block walks the
+// same schedule on its own clusters).
+inline int mla_num_parts(int heads_q, int sm_count) {
+  const int head_blocks = (heads_q + kMlaHeads - 1) / kMlaHeads;
+  return std::max(1, sm_count / 2 / head_blocks);
+}
+
+inline int current_sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return sms;
+}
+
+// Scheduled mode: layout of the workspace -- scheduler records, cumulative split counts, then the partial rows.
+struct MlaSchedLayout {
+  int parts;
+  long long max_rows, off_cum, off_part_o, off_part_lse, bytes;
+  MlaSchedLayout(const AttnB200MlaShape& s, int parts_) : parts(parts_) {
+    max_rows = static_cast<long long>(s.batch) + parts;   // every part boundary cuts at most one sequence
+    off_cum = static_cast<long long>(parts) * kMlaSchedInts * 4;
+    off_part_o = (off_cum + (static_cast<long long>(s.batch) + 1) * 4 + 255) / 256 * 256;
+    off_part_lse = off_part_o + max_rows * s.heads_q * s.dim_v * 4;
+    bytes = off_part_lse + max_rows * s.heads_q * 4;
+  }
+};
 
 // 3-D map over a 16-bit [batch][rows][cols] tensor view with element strides (batch, row), cols contiguous.
 inline int encode_3d(CUtensorMap* tm, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t batch,
@@ -704,28 +934,53 @@ int launch_mla(const AttnB200MlaArgs* a, cudaStream_t stream, int* status) {
   p.block_table = a->block_table;
   p.bt_stride = a->block_table_stride;
   p.page_rows = paged ? a->page_size : 0;
-  p.num_splits = a->num_splits;
-  p.tiles_per_split = (total_tiles + a->num_splits - 1) / a->num_splits;
+  const bool scheduled = a->num_splits == 0;
+  const int splits = scheduled ? 1 : a->num_splits;
+  p.num_splits = splits;
+  p.tiles_per_split = (total_tiles + splits - 1) / splits;
   p.scale = a->scale;
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.status = status;
-  if (a->num_splits > 1) {
+  dim3 grid(2, splits * p.head_blocks, s.batch);  // x = the two CTAs of a cluster
+  if (scheduled) {
+    // one cluster per SM pair and head block runs the units the scheduler gives it
+    const int parts = a->sched_meta != nullptr ? a->sched_parts : mla_num_parts(s.heads_q, current_sm_count());
+    if (parts <= 0) return ATTN_B200_E_INVALID_ARG;
+    const MlaSchedLayout lay(s, parts);
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    int* sched = reinterpret_cast<int*>(ws);
+    int* cum = reinterpret_cast<int*>(ws + lay.off_cum);
+    if (a->sched_meta != nullptr) {
+      if (a->sched_num_splits == nullptr) return ATTN_B200_E_INVALID_ARG;
+      p.sched = a->sched_meta;
+      p.num_splits_cum = a->sched_num_splits;
+    } else {
+      mla_schedule_kernel<<<1, 32, 0, stream>>>(a->seq_lens, s.batch, s.seq_kv, parts, sched, cum);
+      if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
+      p.sched = sched;
+      p.num_splits_cum = cum;
+    }
+    p.num_parts = parts;
+    p.part_o = reinterpret_cast<float*>(ws + lay.off_part_o);
+    p.part_lse = reinterpret_cast<float*>(ws + lay.off_part_lse);
+    grid = dim3(2, parts * p.head_blocks, 1);
+  } else if (splits > 1) {
     p.part_o = static_cast<float*>(a->workspace);
-    p.part_lse = p.part_o + static_cast<long long>(s.batch) * a->num_splits * s.heads_q * DV;
+    p.part_lse = p.part_o + static_cast<long long>(s.batch) * splits * s.heads_q * DV;
   }
   auto kernel = mla_split_kernel<D, DV, kBf16>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes) != cudaSuccess) {
     cudaGetLastError();
     return ATTN_B200_E_LAUNCH;
   }
-  if (static_cast<long long>(a->num_splits) * p.head_blocks > 65535) return ATTN_B200_E_UNSUPPORTED;
-  dim3 grid(2, a->num_splits * p.head_blocks, s.batch);  // x = the two CTAs of a cluster
+  if (grid.y > 65535) return ATTN_B200_E_UNSUPPORTED;
   kernel<<<grid, kMlaThreads, kMlaSmemBytes, stream>>>(tmKV, tmKVr, tmV, tmQr, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
-  if (a->num_splits > 1) {
+  if (scheduled || splits > 1) {
     const long long warps = static_cast<long long>(s.batch) * s.heads_q;
     const int blocks = static_cast<int>((warps * 32 + 255) / 256);
-    mla_combine_kernel<DV, kBf16><<<blocks, 256, 0, stream>>>(p.part_o, p.part_lse, a->o, a->lse, s.batch, s.heads_q, a->num_splits);
+    mla_combine_kernel<DV, kBf16><<<blocks, 256, 0, stream>>>(p.part_o, p.part_lse, a->o, a->lse, s.batch, s.heads_q, splits,
+                                                             scheduled ? p.num_splits_cum : nullptr);
     if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   }
   return ATTN_B200_OK;
@@ -766,8 +1021,27 @@ int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t*
   return ATTN_B200_OK;
 }
 
+int32_t attn_b200_mla_num_parts(int32_t heads_q, int32_t sm_count) {
+  if (heads_q <= 0 || sm_count <= 0) return -1;
+  return b200::mla_num_parts(heads_q, sm_count);
+}
+
+int attn_b200_mla_metadata(const int32_t* cache_seqlens, int32_t batch, int32_t seq_kv, int32_t num_parts,
+                           int32_t* tile_scheduler_metadata, int32_t* num_splits, void* cuda_stream) {
+  if (tile_scheduler_metadata == nullptr || num_splits == nullptr || batch <= 0 || seq_kv <= 0 || num_parts <= 0)
+    return ATTN_B200_E_INVALID_ARG;
+  b200::mla_schedule_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(cache_seqlens, batch, seq_kv, num_parts,
+                                                                                 tile_scheduler_metadata, num_splits);
+  return cudaGetLastError() == cudaSuccess ? ATTN_B200_OK : ATTN_B200_E_LAUNCH;
+}
+
 int64_t attn_b200_mla_workspace_bytes(const AttnB200MlaShape* shape, int32_t num_splits) {
-  if (b200::validate_mla_shape(shape) != ATTN_B200_OK || num_splits < 1) return -1;
+  if (b200::validate_mla_shape(shape) != ATTN_B200_OK || num_splits < 0) return -1;
+  if (num_splits == 0) {   // scheduled mode on the current device
+    const int sms = b200::current_sm_count();
+    if (sms <= 0) return -1;
+    return b200::MlaSchedLayout(*shape, b200::mla_num_parts(shape->heads_q, sms)).bytes;
+  }
   if (num_splits == 1) return 0;
   const int64_t rows = static_cast<int64_t>(shape->batch) * num_splits * shape->heads_q;
   return rows * shape->dim_v * 4 + rows * 4;
@@ -778,11 +1052,16 @@ int attn_b200_mla_decode(const AttnB200MlaArgs* a, void* cuda_stream) {
   int rc = b200::validate_mla_shape(&a->shape);
   if (rc != ATTN_B200_OK) return rc;
   if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
-  if (a->num_splits < 1 || a->num_splits > 32767) return ATTN_B200_E_INVALID_ARG;
+  if (a->num_splits < 0 || a->num_splits > 32767) return ATTN_B200_E_INVALID_ARG;
   const int total_tiles = (a->shape.seq_kv + b200::kMlaTileN - 1) / b200::kMlaTileN;
   if (a->num_splits > total_tiles) return ATTN_B200_E_INVALID_ARG;
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
-  const int64_t need = attn_b200_mla_workspace_bytes(&a->shape, a->num_splits);
+  int64_t need = attn_b200_mla_workspace_bytes(&a->shape, a->num_splits);
+  if (a->num_splits == 0 && a->sched_meta != nullptr) {
+    if (a->sched_parts <= 0) return ATTN_B200_E_INVALID_ARG;
+    need = b200::MlaSchedLayout(a->shape, a->sched_parts).bytes;
+  }
+  if (need < 0) return ATTN_B200_E_LAUNCH;
   if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need)) return ATTN_B200_E_WORKSPACE;
   if (need > 0 && (reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return ATTN_B200_E_WORKSPACE;
   int dev = 0;
@@ -856,12 +1135,13 @@ extern "C" int attn_b200_mla_decode_static(const AttnB200MlaArgs* a, int32_t* st
   int rc = b200::validate_mla_shape(&a->shape);
   if (rc != ATTN_B200_OK) return rc;
   if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
-  if (a->num_splits < 1 || a->num_splits > 32767) return ATTN_B200_E_INVALID_ARG;
+  if (a->num_splits < 0 || a->num_splits > 32767) return ATTN_B200_E_INVALID_ARG;
   const int total_tiles = (a->shape.seq_kv + b200::kMlaTileN - 1) / b200::kMlaTileN;
   if (a->num_splits > total_tiles) return ATTN_B200_E_INVALID_ARG;
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0 || (reinterpret_cast<uintptr_t>(status_word) & 3) != 0)
     return ATTN_B200_E_UNSUPPORTED;
-  const int64_t need = attn_b200_mla_workspace_bytes(&a->shape, a->num_splits);
+  int64_t need = attn_b200_mla_workspace_bytes(&a->shape, a->num_splits);
+  if (a->num_splits == 0 && a->sched_meta != nullptr && a->sched_parts > 0) need = b200::MlaSchedLayout(a->shape, a->sched_parts).bytes;
   if (need < 0) return ATTN_B200_E_UNSUPPORTED;
   if (static_cast<uint64_t>(need) > b200::kMlaStaticScratchBytes) return ATTN_B200_E_SCRATCH_LIMIT;
   void* scratch = b200::mla_static_scratch_ptr();

@@ -162,3 +162,117 @@ def test_paged_cache_with_block_table(page, splits):
     want, want_lse = ragged_oracle(q, kv, lens, Dv)
     check(out, want)
     assert (lse.cpu().reshape(-1) - want_lse.reshape(-1)).abs().max().item() <= 2e-3
+
+
+def reference_schedule(seqlens, block, overhead, parts):
+    """The equal-payload partition of the reference's scheduler (kernels/get_mla_metadata.cu:22-71) restated on
+    Python ints with its block size and fixed overhead as parameters: returns (records [parts][5] = begin sequence,
+    begin token, end sequence, end token, begin split index; cumulative split counts [batch + 1])."""
+    batch = len(seqlens)
+    blocks = [-(-n // block) for n in seqlens]
+    total = sum(nb + overhead for nb in blocks)
+    payload = max(-(-total // parts) + overhead, 2 * overhead)
+    recs, cum = [], [0] * (batch + 1)
+    idx = blk = split = acc = 0
+    for _ in range(parts):
+        rec = [idx, blk * block, 0, 0, split]
+        remain = payload
+        while idx < batch:
+            rest = blocks[idx] - blk
+            if remain >= rest + overhead:
+                acc += split + 1
+                cum[idx + 1] = acc
+                remain -= rest + overhead
+                idx, blk, split = idx + 1, 0, 0
+            else:
+                if remain - overhead > 0:
+                    blk += remain - overhead
+                    split += 1
+                break
+        rec[2] = idx if blk > 0 else idx - 1
+        rec[3] = blk * block if blk > 0 else seqlens[idx - 1]
+        recs.append(rec)
+    assert idx == batch and blk == 0 and split == 0
+    return recs, cum
+
+
+@pytest.mark.parametrize("batch,max_len,seed", [(128, 8192, 1), (5, 30000, 2), (300, 700, 3), (1, 100000, 4), (74, 4096, 5)])
+def test_tile_scheduler_matches_the_reference_algorithm_bit_for_bit(batch, max_len, seed):
+    """attn_b200_mla_metadata (device) against the restated reference algorithm (integers: exact), and the properties
+    that make it a schedule: every KV tile of every sequence is covered exactly once, in order, and no part carries
+    more than the payload."""
+    from attn_engine.mla import mla_schedule, num_parts
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(1, max_len + 1, (batch,), generator=g).to(torch.int32)
+    if seed == 1:
+        lens[:] = max_len      # the dense benchmark case
+    dev = torch.device("cuda", 0)
+    meta, cum = mla_schedule(lens.cuda(), batch, max_len, 128, dev)
+    torch.cuda.synchronize()
+    parts = num_parts(128, dev)
+    want, want_cum = reference_schedule([int(x) for x in lens], 128, 4, parts)
+    assert meta.shape == (parts, 8)
+    assert meta[:, :5].cpu().tolist() == want
+    assert cum.cpu().tolist() == want_cum
+    # coverage
+    tiles = [-(-int(n) // 128) for n in lens]
+    seen = [0] * batch
+    for rec in meta.cpu().tolist():
+        b0, t0, b1, end_tok = rec[0], rec[1] // 128, rec[2], rec[3]
+        took = 0
+        for b in range(b0, min(b1, batch - 1) + 1):
+            lo = t0 if b == b0 else 0
+            hi = min(tiles[b], -(-end_tok // 128)) if b == b1 else tiles[b]
+            assert lo == seen[b]
+            seen[b] = hi
+            took += hi - lo
+        assert took == rec[5]
+    assert seen == tiles
+    total = sum(t + 4 for t in tiles)
+    assert max(rec[5] for rec in meta.cpu().tolist()) <= max(-(-total // parts) + 4, 8)
+
+
+@pytest.mark.parametrize("B,H,S", [(3, 128, 5000), (1, 128, 20000), (200, 128, 600), (9, 256, 3000), (2, 64, 130)])
+def test_scheduled_decode_ragged_lengths(B, H, S):
+    """The scheduled mode (the default): clusters walk pieces of sequences cut where the equal payload ends; ragged
+    lengths, a single long sequence spread over all clusters, more sequences than clusters, two head blocks."""
+    D, Dv = 576, 512
+    q, kv = inputs.mla_inputs(B, H, S, D, Dv, 3000 + S)
+    g = torch.Generator().manual_seed(S)
+    lens = torch.randint(max(1, S // 10), S + 1, (B,), generator=g).to(torch.int32)
+    lens[0] = S
+    o, lse = mla_decode_forward(q.cuda(), kv.cuda(), Dv, D ** -0.5, cache_seqlens=lens.cuda())
+    want = torch.empty(B, 1, H, Dv)
+    want_lse = torch.empty(B, H)
+    for b in range(B):
+        n = int(lens[b])
+        want[b] = oracle(q[b:b + 1], kv[b:b + 1, :n], Dv)[0]
+        want_lse[b] = rm.mla_decode_lse(q[b:b + 1, ..., :Dv], q[b:b + 1, ..., Dv:], kv[b:b + 1, :n, :, :Dv], kv[b:b + 1, :n, :, Dv:])[0]
+    check(o, want)
+    assert (lse.cpu() - want_lse).abs().max().item() < 2e-3
+    # the same through a schedule made once and passed in, and against a uniform split: identical pieces, identical bits
+    from attn_engine.mla import mla_schedule
+    meta, cum = mla_schedule(lens.cuda(), B, S, H, torch.device("cuda", 0))
+    o2, lse2 = mla_decode_forward(q.cuda(), kv.cuda(), Dv, D ** -0.5, cache_seqlens=lens.cuda(), tile_scheduler_metadata=meta,
+                                  num_splits_cum=cum)
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    o3, _ = mla_decode_forward(q.cuda(), kv.cuda(), Dv, D ** -0.5, cache_seqlens=lens.cuda(), num_splits=1)
+    check(o3, want)
+
+
+def test_reference_call_with_scheduler_metadata():
+    """get_mla_metadata + flash_mla_with_kvcache used the way the reference's benchmark uses them
+    (testing/benchmark_h100.py:1079-1087): metadata once, then the paged decode call"""
+    from attn_engine.mla import get_mla_metadata
+    B, H, S, D, Dv, page = 4, 128, 1024, 576, 512, 64
+    q, kv = inputs.mla_inputs(B, H, S, D, Dv, 44)
+    lens = torch.tensor([1024, 700, 64, 333], dtype=torch.int32)
+    pages = S // page
+    table = torch.arange(B * pages, dtype=torch.int32).view(B, pages)
+    pool = kv.view(B * pages, page, 1, D)
+    meta, nsplits = get_mla_metadata(lens.cuda(), H, 1)
+    assert meta.dtype == torch.int32 and meta.shape[1] == 8 and nsplits.shape == (B + 1,)
+    out, lse = flash_mla_with_kvcache(q.cuda(), pool.cuda(), table.cuda(), lens.cuda(), Dv, meta, nsplits)
+    assert out.shape == (B, 1, H, Dv) and lse.shape == (B, H, 1)
+    want = torch.cat([oracle(q[b:b + 1], kv[b:b + 1, :int(lens[b])], Dv) for b in range(B)])
+    check(out, want)
