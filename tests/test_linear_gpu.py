@@ -199,3 +199,26 @@ def test_bad_arguments():
     o = linear_attention_forward(q, k, v[..., :96].contiguous(), decay.log(), q_scale=0.125)
     full = linear_attention_forward(q, k, v, decay.log(), q_scale=0.125)
     assert o.shape[-1] == 96 and torch.equal(o, full[..., :96])
+
+
+@pytest.mark.parametrize("B,H,S,Dk,Dv,dtype", [
+    (3, 25, 640, 64, 256, torch.bfloat16),      # 150 chains of 5 blocks on 148 SMs
+    (2, 40, 1000, 128, 256, torch.float16),     # 160 chains, ragged last block
+    (5, 8, 2048, 256, 512, torch.bfloat16),     # 160 chains at the dims of the headline retention workload
+])
+def test_more_chains_than_sms(B, H, S, Dk, Dv, dtype):
+    """More (batch, head, slice) chains than SMs, i.e. more than one wave of CTAs: the result of a chain must not
+    depend on what else runs, or ran before it, on its SM."""
+    q, k, v, decay = inputs.retention_bhsd(B, H, S, Dk, Dv, 900 + S, dtype=dtype)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert B * H * (Dv // 128) > sms, "this case is meant to have more chains than SMs"
+    o = linear_attention_forward(q.cuda(), k.cuda(), v.cuda(), decay.log().cuda(), q_scale=Dk ** -0.5)
+    check_raw(o, rm.retention_recurrent(q, k, v))
+    # per-token decays, and the same chains a batch entry at a time give the same bits
+    g = torch.Generator().manual_seed(S)
+    ld = torch.nn.functional.logsigmoid(torch.randn(B, H, S, generator=g) + 2.0)
+    o_all = linear_attention_forward(q.cuda(), k.cuda(), v.cuda(), ld.cuda(), q_scale=0.25)
+    for b in range(0, B, 2):
+        o_one = linear_attention_forward(q[b:b + 1].cuda(), k[b:b + 1].cuda(), v[b:b + 1].cuda(), ld[b:b + 1].cuda(), q_scale=0.25)
+        assert torch.equal(o_all[b:b + 1], o_one)
+    assert lib.last_device_status() == 0
