@@ -170,9 +170,10 @@ typedef struct AttnB200MlaShape {
   int32_t batch, heads_q, seq_kv, dim_qk, dim_v;
 } AttnB200MlaShape;
 
-/* Uniform split-KV plan: one split count for every sequence, from the shape alone, so that sm_count SMs are
- * evenly loaded when all sequences have seq_kv tokens.  Host-side, integer.  (The scheduler below, which looks at
- * the actual cache lengths, is the counterpart of the reference's get_mla_metadata.) */
+/* Plan for a batch in which every sequence has seq_kv tokens, from the shape alone (host-side, integer):
+ * num_splits_out >= 1 = that many equal splits per sequence fill the sm_count SMs well; 0 = they would leave the last
+ * round of clusters far from full, use the scheduled mode.  (For ragged batches always use the scheduled mode: the
+ * scheduler below, which looks at the actual cache lengths, is the counterpart of the reference's get_mla_metadata.) */
 int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t* num_splits_out);
 
 /* Tile scheduler.  Replaces get_mla_metadata (core/template/cute_template_kvshared/flash_api.cpp:23-59,

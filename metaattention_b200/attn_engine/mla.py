@@ -91,10 +91,11 @@ def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=Non
     [num_pages, page_size, 1, D]), page_size a multiple of 64, and entry i of a sequence's row names the
     page with its tokens [i*page_size, (i+1)*page_size); ``max_seqlen`` (default max_blocks*page_size)
     bounds the sequence lengths.
-    ``num_splits``: None or 0 = scheduled -- one cluster per SM pair walks the pieces of sequences that the tile
+    ``num_splits``: 0 = scheduled -- one cluster per SM pair walks the pieces of sequences that the tile
     scheduler gives it (equal payloads from the actual cache lengths; ``tile_scheduler_metadata`` / ``num_splits_cum``
     from ``mla_schedule`` may be passed to reuse one schedule over many calls); an int >= 1 = that many equal splits
-    per sequence.
+    per sequence; None = scheduled when ``cache_seqlens`` or a schedule is given, else what ``plan_splits`` estimates
+    to be faster for equal lengths.
     Returns (o [B,H,dim_v] in the input dtype, lse [B,H] fp32)."""
     global last_plan
     q3, kv3 = _rows(q, "q"), _rows(kv, "kv")
@@ -128,7 +129,9 @@ def mla_decode_forward(q, kv, dim_v: int, scale: float, q_rope=None, kv_rope=Non
         raise native.NativeError("q and kv must share dtype float16 or bfloat16")
     with torch.cuda.device(q3.device):
         if num_splits is None:
-            num_splits = 0
+            # ragged lengths: scheduled; equal lengths: whichever the plan estimates faster (0 = scheduled)
+            num_splits = 0 if (cache_seqlens is not None or tile_scheduler_metadata is not None) else \
+                plan_splits(B, H, S, dim_qk, dim_v, _sm_count(q3.device))
         need = workspace_bytes(B, H, S, dim_qk, dim_v, num_splits)
         last_plan = {"mode": "scheduled", "parts": num_parts(H, q3.device)} if num_splits == 0 else {"mode": "uniform", "num_splits": num_splits}
         if need < 0:
