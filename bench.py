@@ -429,8 +429,18 @@ def extras_mla(sampler, peaks, launches):
         B, H, S, D, Dv = C5["B"], C5["H"], C5["S"], C5["D"], C5["Dv"]
         q, kv = mla_case(B, H, S, D, Dv, C5["seed"])
         flush = l2_flusher()
-        fn = lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5)  # noqa: E731
+        # the tile schedule is made once and passed to every launch, as the reference's benchmark makes its scheduler
+        # metadata once per decoding step and reuses it for every layer (testing/benchmark_h100.py:1079-1087); the call
+        # that makes its own schedule on every launch is timed beside it
+        plan = mla.plan_splits(B, H, S, D, Dv, torch.cuda.get_device_properties(0).multi_processor_count)
+        if plan == 0:
+            meta, cum = mla.mla_schedule(None, B, S, H, q.device)
+            fn = lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5, tile_scheduler_metadata=meta, num_splits_cum=cum)  # noqa: E731
+        else:
+            fn = lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5, num_splits=plan)  # noqa: E731
         burst, times, n, ms_heat = burst_and_sustained(fn, launches, 0.5, sampler, "mla", flush=flush)
+        ms_self = statistics.median(time_launches(lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5), 20, 3, flush=flush))
+        ms_uniform = statistics.median(time_launches(lambda: mla.mla_decode_forward(q, kv, Dv, D ** -0.5, num_splits=1), 20, 3, flush=flush))
         nbytes = mla_bytes(B, H, S, D, Dv)
         rec = launch_stats(burst)
         rec.update({"gbs": nbytes / rec["ms"] / 1e6, "tflops": 2.0 * B * H * S * (D + Dv) / rec["ms"] / 1e9, "algorithmic_bytes": nbytes,
@@ -439,7 +449,8 @@ def extras_mla(sampler, peaks, launches):
                     "timed": "launch by launch after an idle pause (the copy the HBM peak comes from was timed the same way)",
                     "sustained": dict(launch_stats(times), roofline=hbm_roofline(nbytes, statistics.median(times), peaks),
                                       note=f"behind {n} back-to-back launches ({ms_heat / 1e3:.2f} s): power-capped clocks"),
-                    "schedule": getattr(mla, "last_plan", None)})
+                    "schedule": getattr(mla, "last_plan", None), "ms_schedule_made_by_every_call": ms_self,
+                    "ms_one_unit_per_sequence_unsplit": ms_uniform})
         out["mla_decode_128x8192x576"] = rec
         # the same cache seen as a pool of 64-token pages through a block table with the pages of every
         # sequence in scrambled order, and full-length cache_seqlens (the reference's native call)
@@ -608,7 +619,7 @@ def run_profile_case(kind, steps, warmup):
     torch.cuda.set_device(0)
     if kind == "mla":
         from attn_engine.mla import mla_decode_forward
-        B, H, S, D, Dv = 74, 128, 4096, 576, 512     # KV = 349 MB
+        B, H, S, D, Dv = 100, 128, 4096, 576, 512    # KV = 472 MB; 100 sequences on 74 clusters: the scheduled mode
         q, kv = [t.cuda() for t in oracle_inputs.mla_inputs(B, H, S, D, Dv, 5)]
         fn = lambda: mla_decode_forward(q, kv, Dv, D ** -0.5)  # noqa: E731
         work = {"bytes": mla_bytes(B, H, S, D, Dv)}

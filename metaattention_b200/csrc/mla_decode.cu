@@ -1030,16 +1030,25 @@ int attn_b200_mla_plan(const AttnB200MlaShape* shape, int32_t sm_count, int32_t*
       best = s;
     }
   }
-  // The uniform split fills `waves` rounds of clusters; when the last round is far from full, cutting the sequences
-  // where an equal payload per cluster ends (scheduled mode, 0) is faster in spite of its partial results and combine
-  // pass: measured on B200 at 8192 tokens, 100 / 128 / 200 sequences -12 % / -5 % / -8 %, 64 / 74 / 148 sequences
-  // (rounds that are full or nearly so) +7 % / +2 % / +6 %.
+  // Uniform splits against the scheduled mode (0), in tile-times, from measurements on B200 at 8192 and 2048 tokens
+  // and 8..200 sequences: a cluster of the uniform mode spends its tiles + 4 per round (+ 4 more when there are
+  // partial results to write and combine); a cluster of the scheduled mode walks an equal share of all tiles and pays
+  // about 6.5 per piece of a sequence it touches, plus the combine pass when sequences are cut.  The scheduled mode
+  // wins when the uniform rounds do not come out even (100 / 128 / 200 sequences: -12 % / -5 % / -8 %) and loses
+  // when they do (64 / 74 / 148 sequences: +7 % / +2 % / +6 %).
   {
     const int tiles = (total_tiles + best - 1) / best;
-    (void)tiles;
     const long long units = base * best;
     const long long waves = (units + sm_count - 1) / sm_count;
-    if (static_cast<double>(units) < 0.9 * static_cast<double>(waves * sm_count) && total_tiles >= 8) best = 0;
+    const double cost_uniform = static_cast<double>(waves) * (tiles + 4.0 + (best > 1 ? 4.0 : 0.0));
+    const long long all_tiles = static_cast<long long>(shape->batch) * total_tiles;   // per head block
+    const long long parts = sm_count;   // clusters (SM pairs); head blocks divide them, and the tiles alike
+    const long long head_blocks = base / shape->batch;
+    const long long per_part = (all_tiles * head_blocks + parts - 1) / parts;
+    const bool even = per_part % total_tiles == 0;
+    const long long pieces = even ? per_part / total_tiles : per_part / total_tiles + 2;
+    const double cost_sched = static_cast<double>(per_part) + 6.5 * static_cast<double>(pieces) + (even ? 1.0 : 3.0);
+    if (cost_sched < cost_uniform) best = 0;
   }
   *num_splits_out = best;
   return ATTN_B200_OK;
