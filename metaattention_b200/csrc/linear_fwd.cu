@@ -340,6 +340,12 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float x_next = last ? 0.0f : load_decay(t + 1);  // consumed by the scan further down
       const float gi = g2[buf * T + row];
       const float qs = p.q_scale;
+      // Mild decay (the block's total log2-decay fits the exponent range of the 16-bit P with room for the scores):
+      // the row factor scale * exp(g_i), common to Q h and to every P_ij = scale * s_ij * exp(g_i - g_j), is taken
+      // out of both and applied once, to the finished output row; P holds s_ij * exp(-g_j) (a factor per column,
+      // at most 2^|total|) and the rows of O = Q h need no pass of their own between the two MMAs.  Blocks with a
+      // stronger decay (gated linear attention) keep the bounded factors exp(g_i - g_j) <= 1 in P and the rescale.
+      const bool mild = g2[buf * T + T - 1] >= (kBf16 ? -100.0f : -8.0f);
       if (t > 0) {
         ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh);
         tc_fence_after_sync();
@@ -379,7 +385,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         warp_arrive(v_ready);
       }
       // ---- rows of O = Q h scaled by scale * exp(g_i) ----
-      if (t > 0) {
+      if (t > 0 && !mild) {
         const float f = qs * fast_exp2(gi);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -418,7 +424,17 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           tmem_wait_ld();
           const float* gcol = g2 + buf * T + c * 32;
           const float* bcol = gb + c * 32;
-          if (c < wq) {
+          if (mild) {
+            // exp(-g_j) = exp(g_end - g_j) * exp(-g_end): the per-column table of the chunk times one number
+            const float a = fast_exp2(-gcol[31]);
+            if (c < wq) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) s[i] *= a * bcol[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) s[i] = (i <= lane) ? s[i] * (a * bcol[i]) : 0.0f;
+            }
+          } else if (c < wq) {
             const float a = qs * fast_exp2(fminf(gi - gcol[31], 0.0f));
 #pragma unroll
             for (int i = 0; i < 32; ++i) s[i] *= a * bcol[i];
@@ -474,11 +490,14 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int tok = t * T + row;
         float sum = 0.f, sq = 0.f;
         uint8_t* line = sH + wg * (T * 128) + row * 128;
+        const float fo = mild ? qs * fast_exp2(gi) : 1.0f;   // the row factor left out of Q h and P (mild decay)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float o[32];
           tmem_ld32f(tO + wg * 64 + c * 32, o);
           tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= fo;
           if (p.o_f32 != nullptr) {
             // fp32 output: this thread's 32 columns of its token row, 128 contiguous bytes
             if (tok < p.seq) {
