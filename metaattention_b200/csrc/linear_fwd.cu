@@ -54,7 +54,7 @@ struct LinearParams {
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
 enum LinearWaitSite { kLinQFull = 41, kLinKFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone, kLinVFull };
-enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarOStaged, kBarStageFree, kBarConvDone, kNumLinBarriers };
+enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarConvDone, kNumLinBarriers };
 
 template <int DK>
 struct LinearSmem {
@@ -79,7 +79,7 @@ struct LinearSmem {
 template <int DK, bool kBf16>
 __global__ void __launch_bounds__(kLinThreads, 1)
 linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const LinearParams p) {
+                  const __grid_constant__ CUtensorMap tmV, const LinearParams p) {
   using L = LinearSmem<DK>;
   constexpr int T = kLinT, DVS = kLinDvs, KC = DK / 64;
   static_assert(DK % 64 == 0 && DK <= 256, "unsupported dim_qk");
@@ -106,8 +106,6 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* st_bar = bars + kBarState;
   uint64_t* p_ready = bars + kBarPReady;
   uint64_t* v_ready = bars + kBarVReady;
-  uint64_t* o_staged = bars + kBarOStaged;
-  uint64_t* stage_free = bars + kBarStageFree;
   uint64_t* conv_done = bars + kBarConvDone;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
@@ -132,14 +130,11 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(st_bar, 1);
     mbar_init(p_ready, kLinRowThreads / 32);
     mbar_init(v_ready, kLinRowThreads / 32);
-    mbar_init(o_staged, kLinRowThreads / 32);
-    mbar_init(stage_free, 1);
     mbar_init(conv_done, kLinRowThreads / 32);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -178,11 +173,15 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024), k_mn_desc0 = make_smem_desc(smem_u32(sK), T * 128, 1024);
       const uint64_t v2_mn_desc0 = make_smem_desc(smem_u32(sV2), T * 128, 1024);
       constexpr uint64_t kChunk = (T * 128) >> 4;
-      auto issue_scores = [&]() {
-#pragma unroll
-        for (int ch = 0; ch < KC; ++ch)
-          umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + ch * kChunk, k_desc0 + ch * kChunk, idesc_s, ch > 0 ? 1u : 0u);
+      // The scores go out one 64-wide chunk of dim_qk at a time: the issuing thread is held while the pipe's queue is
+      // full, and between chunks it can serve whatever else has become possible (the output store above all).
+      int s_chunk = 0;
+      auto issue_score_chunk = [&]() -> bool {   // true once the block's last chunk is out
+        umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + s_chunk * kChunk, k_desc0 + s_chunk * kChunk, idesc_s, s_chunk > 0 ? 1u : 0u);
+        if (++s_chunk < KC) return false;
         umma_commit(s_bar);
+        s_chunk = 0;
+        return true;
       };
 
       // The tensor pipe executes in issue order and the issuing thread is held back while the pipe is full,
@@ -218,8 +217,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           while (need_s || need_qh) {
             if (need_s && mbar_test(q_full, par) && mbar_test(k_full, par)) {
               tc_fence_after_sync();
-              issue_scores();
-              need_s = false;
+              if (issue_score_chunk()) need_s = false;
             }
             if (need_qh && mbar_test(conv_done, par_prev)) {
               tc_fence_after_sync();
@@ -261,39 +259,25 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + 64 + g * 32, v_mn_desc0 + g * 512, idesc_pv, 1u);
         }
         umma_commit(pv_bar);
-        // Three follow-ups, served as they become possible: V of the next block (after P V), the output store
-        // (after the rows are staged), S of the next block (after its loads; P of this block is consumed by
-        // then because the pipe runs in order).
-        bool need_v = !last, need_s = !last, need_store = true;
+        // Two follow-ups, served as they become possible: V of the next block (after P V) and S of the next block
+        // (after its loads; P of this block is consumed by then because the pipe runs in order).  The output rows
+        // are stored by the row warps themselves.
+        bool need_v = !last, need_s = !last;
         const long long t0 = clock64();
         uint32_t spins = 0;
-        while (need_v || need_store) {   // the scores are issued here only if their loads are already there
-          if (need_v && mbar_test(pv_bar, par)) {
+        while (need_v) {   // the scores are issued here only if their loads are already there
+          if (mbar_test(pv_bar, par)) {
             load_v(t + 1);  // V was read by the row threads (before v_ready) and by P V
             need_v = false;
           }
-          if (need_store && mbar_test(o_staged, par)) {
-            // output rows staged in the state-copy buffer: full swizzled lines, rows past the end clipped by the map
-            if (p.o_f32 == nullptr) {
-              for (int c = 0; c < DVS / 64; ++c) tma_store_3d(&tmO, sH + c * (T * 128), slice * DVS + c * 64, t * T, bh);
-            }
-            tma_store_commit();
-            if (!last) {
-              tma_store_wait_read();  // the conversion pass overwrites the staging buffer
-              mbar_arrive(stage_free);
-            }
-            need_store = false;
-          }
           if (need_s && mbar_test(q_full, par ^ 1) && mbar_test(k_full, par ^ 1)) {
             tc_fence_after_sync();
-            issue_scores();
-            need_s = false;
+            if (issue_score_chunk()) need_s = false;
           }
-          if (!(alive = poll_alive(spins, t0, kLinOStaged))) break;
+          if (!(alive = poll_alive(spins, t0, kLinPv))) break;
         }
         s_pending = need_s;
       }
-      tma_store_wait_all();
     }
   } else {
     // ======================= row threads: one TMEM lane (token / state row) each =======================
@@ -330,6 +314,30 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         gb[tid] = fast_exp2(__shfl_sync(0xffffffffu, g, 31) - g);
       }
       return named_sync_and(1, kLinRowThreads, ok_in);
+    };
+
+    // 32 columns of this thread's state row: 16-bit copy to the operand buffer, and the decay of the next block
+    // onto hT.  Group `wg` owns columns [64 wg, 64 wg + 64), whose place in the buffer staged its own output rows,
+    // and its share of the columns from 128 on, which are free as soon as the state update has run.
+    constexpr int kEarlyCols = DK > 128 ? (DK - 128) / 2 : 0;   // per group
+    auto convert32 = [&](int col0, float decay_next) {
+      float hv[32];
+      tmem_ld32f(tH + col0, hv);
+      tmem_wait_ld();
+      uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
+      const int piece0 = (col0 & 63) >> 3;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 pk;
+        pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
+        pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
+        pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
+        pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
+        *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+      tmem_st32f(tH + col0, hv);
     };
 
     bool ok = scan_block(load_decay(0), 0, start_ok);
@@ -480,6 +488,17 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       warp_arrive(p_ready);
       // ---- the next block's decay scan runs under the MMAs ----
       if (!last) ok = scan_block(x_next, buf ^ 1, ok);
+      // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
+      // The staged output rows occupy the first 32 KB of the copy's buffer, i.e. its columns [0, 128).  With 256
+      // columns every group converts its share of [128, 256) as soon as the state update has run (that half held
+      // the rescaled V), under P V, and the rest once the output store has read the staged rows.
+      const float decay_next = last ? 1.0f : fast_exp2(g2[(buf ^ 1) * T + T - 1]);
+      if (!last) {
+        ok = mbar_wait(st_bar, par, ab, kLinState) && ok;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kEarlyCols / 32; ++c) convert32(128 + wg * kEarlyCols + c * 32, decay_next);
+      }
       ok = mbar_wait(pv_bar, par, ab, kLinPv) && ok;
       tc_fence_after_sync();
       // ---- output rows to the staging buffer (while the state update runs) ----
@@ -542,53 +561,39 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           atomicAdd(st, sum);
           atomicAdd(st + 1, sq);
         }
-        fence_proxy_async_smem();
+        // Each warp writes out its own 32 staged rows (4 KB): eight lanes per row, 128 contiguous bytes, four rows
+        // per instruction.  The conversion below writes every thread's state row over the line that held its
+        // output row, so nothing here crosses warps and nothing waits for a store to complete.
         tc_fence_before_sync();
-        warp_arrive(o_staged);
-      }
-      if (last) break;
-      // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
-      ok = mbar_wait(st_bar, par, ab, kLinState) && ok;
-      tc_fence_after_sync();
-      {
-        // The staged output rows occupy the first 32 KB of the copy's buffer, i.e. its columns [0, 128).  With
-        // 256 columns every group first converts its share of [128, 256) and only then waits for the output
-        // stores to have read their rows.
-        constexpr bool kEarlyPart = (DK == 256);
-        constexpr int kParts = kEarlyPart ? 2 : 1;
-        constexpr int kColsPerPart = DK / 2 / kParts;  // per group
-        const float decay_next = fast_exp2(g2[(buf ^ 1) * T + T - 1]);
+        __syncwarp();
+        if (p.o_f32 == nullptr) {
+          const int r0 = (warp & 3) * 32, piece = lane & 7;
+          const uint8_t* chunk = sH + wg * (T * 128);
+          uint8_t* gbase = static_cast<uint8_t*>(p.o) + (static_cast<long long>(bh) * p.seq * p.dim_v + slice * DVS + wg * 64) * 2 + piece * 16;
+          uint4 x[8];
 #pragma unroll
-        for (int part = 0; part < kParts; ++part) {
-          if (part == kParts - 1) ok = mbar_wait(stage_free, par, ab, kLinStageFree) && ok;
-          const int base = (kEarlyPart && part == 0 ? DK / 2 : 0) + wg * kColsPerPart;
+          for (int j = 0; j < 8; ++j) {
+            const int r = r0 + j * 4 + (lane >> 3);
+            x[j] = *reinterpret_cast<const uint4*>(chunk + r * 128 + ((piece ^ (r & 7)) << 4));
+          }
 #pragma unroll
-          for (int c = 0; c < kColsPerPart / 32; ++c) {
-            const int col0 = base + c * 32;
-            float hv[32];
-            tmem_ld32f(tH + col0, hv);
-            tmem_wait_ld();
-            uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
-            const int piece0 = (col0 & 63) >> 3;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 pk;
-              pk.x = pack2<kBf16>(hv[8 * q4 + 0], hv[8 * q4 + 1]);
-              pk.y = pack2<kBf16>(hv[8 * q4 + 2], hv[8 * q4 + 3]);
-              pk.z = pack2<kBf16>(hv[8 * q4 + 4], hv[8 * q4 + 5]);
-              pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
-              *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
-            tmem_st32f(tH + col0, hv);
+          for (int j = 0; j < 8; ++j) {
+            const int tk = t * T + r0 + j * 4 + (lane >> 3);
+            if (tk < p.seq) *reinterpret_cast<uint4*>(gbase + static_cast<long long>(tk) * p.dim_v * 2) = x[j];
           }
         }
-        tmem_wait_st();
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        warp_arrive(conv_done);
+        __syncwarp();
       }
+      if (last) break;
+      // ---- 16-bit copy of hT for the next block's Q h, rest: the columns whose place staged the output rows ----
+      if (wg * 64 < DK) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) convert32(wg * 64 + c * 32, decay_next);
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      warp_arrive(conv_done);
     }
   }
 
@@ -655,7 +660,7 @@ inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t c
 template <int DK, bool kBf16>
 int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status) {
   using L = LinearSmem<DK>;
-  CUtensorMap tmQ, tmK, tmV, tmO;
+  CUtensorMap tmQ, tmK, tmV;
   const uint64_t bh = static_cast<uint64_t>(a->batch) * a->heads;
   int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
@@ -664,9 +669,7 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
   const bool f32_out = a->dtype_out == ATTN_B200_DTYPE_FP32;
-  // with an fp32 output the 16-bit store map is not used by the kernel: it is encoded over v so that it stays valid
-  rc = encode_rows3(&tmO, f32_out ? a->v : a->o, a->dtype, a->dim_v, a->seq, bh);
-  if (rc != ATTN_B200_OK) return rc;
+  if (!f32_out && (reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
   LinearParams p;
   std::memset(&p, 0, sizeof(p));
   p.o = a->o;
@@ -694,7 +697,7 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
     return ATTN_B200_E_LAUNCH;
   }
   dim3 grid(a->dim_v / kLinDvs, static_cast<unsigned>(bh));
-  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
+  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (a->normalize) {
     const int blocks = static_cast<int>((rows * 32 + 255) / 256);
