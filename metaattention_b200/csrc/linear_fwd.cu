@@ -38,7 +38,7 @@ namespace b200 {
 constexpr int kLinT = 128;    // tokens per block
 constexpr int kLinDvs = 128;  // dim_v columns per CTA
 constexpr int kLinRowThreads = 256;              // eight warps: one TMEM lane each, two column halves
-constexpr int kLinThreads = kLinRowThreads + 32;   // plus the warp that issues TMA copies and MMAs
+constexpr int kLinThreads = kLinRowThreads + 64;   // plus the warp that issues TMA copies and MMAs and the decay-scan warp
 
 struct LinearParams {
   void* o;                 // [B,H,S,DV] 16-bit
@@ -53,8 +53,8 @@ struct LinearParams {
 
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
-enum LinearWaitSite { kLinQFull = 41, kLinKFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone, kLinVFull };
-enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarConvDone, kNumLinBarriers };
+enum LinearWaitSite { kLinQFull = 41, kLinKFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone, kLinVFull, kLinDecay };
+enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarConvDone, kBarDecay, kNumLinBarriers };
 
 template <int DK>
 struct LinearSmem {
@@ -70,7 +70,7 @@ struct LinearSmem {
   // the state-copy buffer (idle between the Q h MMA and the conversion pass), else a buffer of its own
   static constexpr bool kScaledVInH = (kHBytes >= 2 * kVBytes);
   static constexpr int kOffV2 = kScaledVInH ? kOffH + kHBytes - kVBytes : kOffH + kHBytes;
-  static constexpr int kOffG = kOffH + kHBytes + (kScaledVInH ? 0 : kVBytes);  // float g2[2][128] + float gb[128] + float wsum[8]
+  static constexpr int kOffG = kOffH + kHBytes + (kScaledVInH ? 0 : kVBytes);  // float g2[2][128] + float gb[128]
   static constexpr int kOffBar = kOffG + 3 * kLinT * 4 + 32;
   static constexpr int kOffMisc = kOffBar + 8 * kNumLinBarriers;
   static constexpr int kBytes = kOffMisc + 16 + 1024;
@@ -85,6 +85,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   static_assert(DK % 64 == 0 && DK <= 256, "unsupported dim_qk");
   constexpr uint32_t kTmemCols = 512, kColH = 0, kColS = 256, kColO = 384;
   constexpr float kLog2e = 1.4426950408889634f;
+  // A block whose total log2-decay is at least this is "mild": see the row threads' loop
+  // (never with the remainder pass of P, which exists for the accuracy the rounded rows of V would give away)
+  const float kMildLog2 = p.split_p ? 1.0f : (kBf16 ? -100.0f : -8.0f);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -95,7 +98,6 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* sV2 = smem + L::kOffV2;
   float* g2 = reinterpret_cast<float*>(smem + L::kOffG);  // [2][T] cumulative log2-decay inside a block
   float* gb = g2 + 2 * T;   // [T] exp2(g at the end of the column's 32-token chunk - g of the column), current block
-  float* wsum = gb + T;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* q_full = bars + kBarQFull;
   uint64_t* k_full = bars + kBarKFull;
@@ -107,6 +109,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* p_ready = bars + kBarPReady;
   uint64_t* v_ready = bars + kBarVReady;
   uint64_t* conv_done = bars + kBarConvDone;
+  uint64_t* g_ready = bars + kBarDecay;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
 
@@ -131,6 +134,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(p_ready, kLinRowThreads / 32);
     mbar_init(v_ready, kLinRowThreads / 32);
     mbar_init(conv_done, kLinRowThreads / 32);
+    mbar_init(g_ready, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -232,20 +236,25 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           if (!alive) break;
           s_pending = true;
         }
-        // Q may be replaced once both have run
-        if (!mbar_wait_poll(s_bar, par, ab, kLinScore)) break;
-        if (t > 0 && !mbar_wait_poll(qh_bar, par_prev, ab, kLinQh)) break;
-        if (!last) load_q(t + 1);  // Q is no longer read by any MMA of this block
         if (!last) {
-          // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step
+          // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step.  With mild decay
+          // the rescaled rows are there before Q h has finished (they replaced V in place) and this queues behind it.
           if (!mbar_wait_poll(v_ready, par, ab, kLinVReady)) break;
           tc_fence_after_sync();
+          const bool mild = g2[(t & 1) * T + T - 1] >= kMildLog2;
+          const uint64_t va_desc0 = mild ? v_mn_desc0 : v2_mn_desc0;
 #pragma unroll
           for (int g = 0; g < T / 64; ++g)
-            umma_ss_x4<128, 128>(tmem_base + kColH, v2_mn_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
+            umma_ss_x4<128, 128>(tmem_base + kColH, va_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
           umma_commit(st_bar);
+        }
+        // Q may be replaced once S and Q h have run, K once the state update has
+        if (!mbar_wait_poll(s_bar, par, ab, kLinScore)) break;
+        if (t > 0 && !mbar_wait_poll(qh_bar, par_prev, ab, kLinQh)) break;
+        if (!last) {
+          load_q(t + 1);
           if (!mbar_wait_poll(st_bar, par, ab, kLinState)) break;
-          load_k(t + 1);  // K is no longer read
+          load_k(t + 1);
         }
         // O (+)= P V
         if (!(mbar_wait_poll(p_ready, par, ab, kLinPReady) && mbar_wait_poll(v_full, par, ab, kLinVFull))) break;
@@ -279,6 +288,42 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         s_pending = need_s;
       }
     }
+  } else if (warp == kLinRowThreads / 32 + 1) {
+    // ======================= decay warp: the scan of every block's log-decays =======================
+    // Four consecutive tokens per lane.  Block t's table goes into g2[t & 1] (read by the row threads of block t and,
+    // its last entry, by those of block t - 1) and gb (read by block t's P phase only), so it may be written once the
+    // row threads are through the P phase of block t - 1.
+    bool ok = start_ok;
+    for (int t = 0; ok && t < nblk; ++t) {
+      float x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int tok = t * T + lane * 4 + k;
+        x[k] = tok < p.seq ? ld_row[tok] * kLog2e : 0.0f;
+      }
+      x[1] += x[0];
+      x[2] += x[1];
+      x[3] += x[2];
+      float run = x[3];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, run, d);
+        if (lane >= d) run += y;
+      }
+      const float pre = run - x[3];
+      const float g_end = __shfl_sync(0xffffffffu, run, lane | 7);   // last token of this lane's 32-token chunk
+      if (t > 0) ok = mbar_wait(p_ready, (t - 1) & 1, ab, kLinDecay);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float g = pre + x[k];
+        g2[(t & 1) * T + lane * 4 + k] = g;
+        gb[lane * 4 + k] = fast_exp2(g_end - g);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(g_ready);
+    }
   } else {
     // ======================= row threads: one TMEM lane (token / state row) each =======================
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -290,40 +335,18 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(bar);
     };
-    auto load_decay = [&](int t) -> float {
-      const int tok = t * T + tid;
-      return (tid < T && tok < p.seq) ? ld_row[tok] * kLog2e : 0.0f;
-    };
-    // inclusive scan of a block's log2-decays (one per thread of the first four warps) into g2[buf][0..T);
-    // two barriers of the row threads inside, the second one reducing `ok`
-    auto scan_block = [&](float x, int buf, bool ok_in) -> bool {
-      if (tid < T) {
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-          const float y = __shfl_up_sync(0xffffffffu, x, d);
-          if (lane >= d) x += y;
-        }
-        if (lane == 31) wsum[warp] = x;
-      }
-      named_sync(1, kLinRowThreads);
-      if (tid < T) {
-        float pre = 0.0f;
-        for (int w = 0; w < warp; ++w) pre += wsum[w];
-        const float g = x + pre;
-        g2[buf * T + tid] = g;
-        gb[tid] = fast_exp2(__shfl_sync(0xffffffffu, g, 31) - g);
-      }
-      return named_sync_and(1, kLinRowThreads, ok_in);
-    };
-
     // 32 columns of this thread's state row: 16-bit copy to the operand buffer, and the decay of the next block
     // onto hT.  Group `wg` owns columns [64 wg, 64 wg + 64), whose place in the buffer staged its own output rows,
     // and its share of the columns from 128 on, which are free as soon as the state update has run.
     constexpr int kEarlyCols = DK > 128 ? (DK - 128) / 2 : 0;   // per group
-    auto convert32 = [&](int col0, float decay_next) {
+    auto convert32 = [&](int col0, float decay_next, bool scaled_copy) {
       float hv[32];
       tmem_ld32f(tH + col0, hv);
       tmem_wait_ld();
+      if (scaled_copy) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+      }
       uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
       const int piece0 = (col0 & 63) >> 3;
 #pragma unroll
@@ -335,39 +358,45 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         pk.w = pack2<kBf16>(hv[8 * q4 + 6], hv[8 * q4 + 7]);
         *reinterpret_cast<uint4*>(line + (((piece0 + q4) ^ (row & 7)) << 4)) = pk;
       }
+      if (!scaled_copy) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+        for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
+      }
       tmem_st32f(tH + col0, hv);
     };
 
-    bool ok = scan_block(load_decay(0), 0, start_ok);
+    bool ok = start_ok && mbar_wait(g_ready, 0, ab, kLinDecay);
     for (int t = 0; ok && t < nblk; ++t) {
       const int buf = t & 1;
       const bool last = (t + 1 == nblk);
       const uint32_t par = t & 1;
-      const float x_next = last ? 0.0f : load_decay(t + 1);  // consumed by the scan further down
       const float gi = g2[buf * T + row];
       const float qs = p.q_scale;
-      // Mild decay (the block's total log2-decay fits the exponent range of the 16-bit P with room for the scores):
-      // the row factor scale * exp(g_i), common to Q h and to every P_ij = scale * s_ij * exp(g_i - g_j), is taken
-      // out of both and applied once, to the finished output row; P holds s_ij * exp(-g_j) (a factor per column,
-      // at most 2^|total|) and the rows of O = Q h need no pass of their own between the two MMAs.  Blocks with a
-      // stronger decay (gated linear attention) keep the bounded factors exp(g_i - g_j) <= 1 in P and the rescale.
-      const bool mild = g2[buf * T + T - 1] >= (kBf16 ? -100.0f : -8.0f);
-      if (t > 0) {
+      // Mild decay (the block's total log2-decay stays inside the exponent range of the 16-bit operands with room
+      // to spare): exp(g_i - g_j) is split as exp(g_i - g_last) * exp(g_last - g_j).  The second factor is the one
+      // the state update puts on the rows of V anyway, so the rescaled rows replace V and serve P V too; the first
+      // is a row factor that P V shares with Q h once the state's copy is taken after the block's decay
+      // (Q_i h exp(g_i) = Q_i (h exp(g_last)) exp(g_i - g_last)), and is applied once, to the finished output row.
+      // P is then the masked scores themselves, O = Q h needs no pass between the two MMAs, and the rows of V are
+      // rescaled while Q h runs.  Blocks with a stronger decay (gated linear attention) keep every factor <= 1:
+      // exp(g_i - g_j) in P, a rescale of Q h by exp(g_i), and the rescaled V in a buffer of its own.
+      const float g_last = g2[buf * T + T - 1];
+      const bool mild = g_last >= kMildLog2;
+      if (t > 0 && !mild) {
         ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh);
         tc_fence_after_sync();
       }
-      // ---- rows of V times their decay factors, into the buffer the state update reads ----
-      if (!last) {
+      // ---- rows of V times their decay factors: the A operand of the state update ----
+      if (!last || mild) {
         ok = mbar_wait(v_full, par, ab, kLinVFull) && ok;
-        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row) and written to the same place of the
-        // second buffer (with 256 state columns that is the upper half of the state copy, free once Q h has
-        // run).  Every 16-byte piece of the row gets the same factor, so neither the swizzle nor the order
-        // matters: lanes start at different pieces to stay off each other's banks (rows are 128 bytes apart).
-        const float w = fast_exp2(g2[buf * T + T - 1] - g2[buf * T + row]);
+        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row).  Every 16-byte piece of the row gets
+        // the same factor, so neither the swizzle nor the order matters: lanes start at different pieces to stay
+        // off each other's banks (rows are 128 bytes apart).  With mild decay the result replaces V (P V then takes
+        // the same rows), which touches nothing Q h reads and so runs beside it; else it goes to the second buffer
+        // (with 256 state columns the upper half of the state copy, free once Q h has run).
+        const float w = fast_exp2(g_last - gi);
         const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
-        uint4* v2line = reinterpret_cast<uint4*>(sV2 + wg * (T * 128) + row * 128);
+        uint4* v2line = reinterpret_cast<uint4*>((mild ? sV : sV2) + wg * (T * 128) + row * 128);
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
           const int piece = (q4 + lane) & 7;
@@ -390,7 +419,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           v2line[piece] = x;
         }
         fence_proxy_async_smem();
-        warp_arrive(v_ready);
+        if (!last) warp_arrive(v_ready);
       }
       // ---- rows of O = Q h scaled by scale * exp(g_i) ----
       if (t > 0 && !mild) {
@@ -433,14 +462,10 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           const float* gcol = g2 + buf * T + c * 32;
           const float* bcol = gb + c * 32;
           if (mild) {
-            // exp(-g_j) = exp(g_end - g_j) * exp(-g_end): the per-column table of the chunk times one number
-            const float a = fast_exp2(-gcol[31]);
-            if (c < wq) {
+            // the column factors are in the rows of V already: only the mask is left
+            if (c == wq) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) s[i] *= a * bcol[i];
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) s[i] = (i <= lane) ? s[i] * (a * bcol[i]) : 0.0f;
+              for (int i = 0; i < 32; ++i) s[i] = (i <= lane) ? s[i] : 0.0f;
             }
           } else if (c < wq) {
             const float a = qs * fast_exp2(fminf(gi - gcol[31], 0.0f));
@@ -486,18 +511,20 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_wait_st();
       tc_fence_before_sync();
       warp_arrive(p_ready);
-      // ---- the next block's decay scan runs under the MMAs ----
-      if (!last) ok = scan_block(x_next, buf ^ 1, ok);
+      // ---- the next block's decays (the decay warp wrote them once every warp was past this point) ----
+      if (!last) ok = mbar_wait(g_ready, (t + 1) & 1, ab, kLinDecay) && ok;
       // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
       // The staged output rows occupy the first 32 KB of the copy's buffer, i.e. its columns [0, 128).  With 256
       // columns every group converts its share of [128, 256) as soon as the state update has run (that half held
       // the rescaled V), under P V, and the rest once the output store has read the staged rows.
-      const float decay_next = last ? 1.0f : fast_exp2(g2[(buf ^ 1) * T + T - 1]);
+      const float g_next = last ? 0.0f : g2[(buf ^ 1) * T + T - 1];
+      const float decay_next = fast_exp2(g_next);
+      const bool mild_next = g_next >= kMildLog2;   // the coming block multiplies Q by the state after its decay
       if (!last) {
         ok = mbar_wait(st_bar, par, ab, kLinState) && ok;
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < kEarlyCols / 32; ++c) convert32(128 + wg * kEarlyCols + c * 32, decay_next);
+        for (int c = 0; c < kEarlyCols / 32; ++c) convert32(128 + wg * kEarlyCols + c * 32, decay_next, mild_next);
       }
       ok = mbar_wait(pv_bar, par, ab, kLinPv) && ok;
       tc_fence_after_sync();
@@ -509,7 +536,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int tok = t * T + row;
         float sum = 0.f, sq = 0.f;
         uint8_t* line = sH + wg * (T * 128) + row * 128;
-        const float fo = mild ? qs * fast_exp2(gi) : 1.0f;   // the row factor left out of Q h and P (mild decay)
+        const float fo = mild ? qs * fast_exp2(gi - g_last) : 1.0f;   // the row factor left out of Q h and P (mild decay)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           float o[32];
@@ -588,7 +615,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // ---- 16-bit copy of hT for the next block's Q h, rest: the columns whose place staged the output rows ----
       if (wg * 64 < DK) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) convert32(wg * 64 + c * 32, decay_next);
+        for (int c = 0; c < 2; ++c) convert32(wg * 64 + c * 32, decay_next, mild_next);
       }
       tmem_wait_st();
       fence_proxy_async_smem();
