@@ -79,7 +79,7 @@ struct LinearSmem {
 template <int DK, bool kBf16>
 __global__ void __launch_bounds__(kLinThreads, 1)
 linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const LinearParams p) {
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const LinearParams p) {
   using L = LinearSmem<DK>;
   constexpr int T = kLinT, DVS = kLinDvs, KC = DK / 64;
   static_assert(DK % 64 == 0 && DK <= 256, "unsupported dim_qk");
@@ -139,6 +139,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -197,6 +198,19 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       load_v(0);
       bool alive = true;
       bool s_pending = true;   // the scores of the coming block have not been issued yet
+      bool need_f = false;     // the state update of the current block has not been issued yet
+      // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step.  Call after v_ready of
+      // block t and, from the second block on, after the conversion pass of the block before.
+      auto issue_state_update = [&](int t) {
+        tc_fence_after_sync();
+        const bool mild = g2[(t & 1) * T + T - 1] >= kMildLog2;
+        const uint64_t va_desc0 = mild ? v_mn_desc0 : v2_mn_desc0;
+#pragma unroll
+        for (int g = 0; g < T / 64; ++g)
+          umma_ss_x4<128, 128>(tmem_base + kColH, va_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
+        umma_commit(st_bar);
+        need_f = false;
+      };
       // a bounded poll step shared by the loops that serve several barriers at once
       auto poll_alive = [&](uint32_t& spins, long long t0, int site) {
         if ((++spins & 0xff) == 0) {
@@ -216,6 +230,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // written by the conversion pass of the previous block): whichever can go first goes first
         {
           bool need_s = s_pending, need_qh = t > 0;
+          need_f = !last;
           const long long t0 = clock64();
           uint32_t spins = 0;
           while (need_s || need_qh) {
@@ -236,17 +251,11 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           if (!alive) break;
           s_pending = true;
         }
-        if (!last) {
-          // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step.  With mild decay
-          // the rescaled rows are there before Q h has finished (they replaced V in place) and this queues behind it.
+        // The state update follows Q h in the pipe (the row threads take its completion to mean that the state's copy
+        // is no longer read); with mild decay its operand is waiting already.
+        if (need_f) {
           if (!mbar_wait_poll(v_ready, par, ab, kLinVReady)) break;
-          tc_fence_after_sync();
-          const bool mild = g2[(t & 1) * T + T - 1] >= kMildLog2;
-          const uint64_t va_desc0 = mild ? v_mn_desc0 : v2_mn_desc0;
-#pragma unroll
-          for (int g = 0; g < T / 64; ++g)
-            umma_ss_x4<128, 128>(tmem_base + kColH, va_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
-          umma_commit(st_bar);
+          issue_state_update(t);
         }
         // Q may be replaced once S and Q h have run, K once the state update has
         if (!mbar_wait_poll(s_bar, par, ab, kLinScore)) break;
@@ -312,7 +321,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       const float pre = run - x[3];
       const float g_end = __shfl_sync(0xffffffffu, run, lane | 7);   // last token of this lane's 32-token chunk
-      if (t > 0) ok = mbar_wait(p_ready, (t - 1) & 1, ab, kLinDecay);
+      if (t > 0 && lane == 0) ok = mbar_wait_poll(p_ready, (t - 1) & 1, ab, kLinDecay);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
 #pragma unroll
@@ -365,7 +374,46 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_st32f(tH + col0, hv);
     };
 
+    // Rows of V times their decay factors, the A operand of the state update: token `row` of block tb's V (chunk `wg`)
+    // is multiplied by exp(g_last - g_row).  Every 16-byte piece of the row gets the same factor, so neither the
+    // swizzle nor the order matters: lanes start at different pieces to stay off each other's banks (rows are 128
+    // bytes apart).  With mild decay the result replaces V (P V then takes the same rows), which touches nothing
+    // another phase of the kernel uses; else it goes to the second buffer (with 256 state columns the upper half of
+    // the state copy, free once Q h has run).
+    auto rescale_v = [&](int tb, bool in_place) -> bool {
+      const bool v_ok = mbar_wait(v_full, tb & 1, ab, kLinVFull);
+      const float* g = g2 + (tb & 1) * T;
+      const float w = fast_exp2(g[T - 1] - g[row]);
+      const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
+      uint4* v2line = reinterpret_cast<uint4*>((in_place ? sV : sV2) + wg * (T * 128) + row * 128);
+#pragma unroll
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const int piece = (q4 + lane) & 7;
+        uint4 x = vline[piece];
+        uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float lo, hi;
+          if constexpr (kBf16) {
+            const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&xs[e]);
+            lo = __bfloat162float(h2.x);
+            hi = __bfloat162float(h2.y);
+          } else {
+            const __half2 h2 = *reinterpret_cast<__half2*>(&xs[e]);
+            lo = __half2float(h2.x);
+            hi = __half2float(h2.y);
+          }
+          xs[e] = pack2<kBf16>(lo * w, hi * w);
+        }
+        v2line[piece] = x;
+      }
+      fence_proxy_async_smem();
+      if (tb + 1 < nblk) warp_arrive(v_ready);
+      return v_ok;
+    };
+
     bool ok = start_ok && mbar_wait(g_ready, 0, ab, kLinDecay);
+    if (ok && g2[T - 1] >= kMildLog2) ok = rescale_v(0, true);
     for (int t = 0; ok && t < nblk; ++t) {
       const int buf = t & 1;
       const bool last = (t + 1 == nblk);
@@ -378,7 +426,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // is a row factor that P V shares with Q h once the state's copy is taken after the block's decay
       // (Q_i h exp(g_i) = Q_i (h exp(g_last)) exp(g_i - g_last)), and is applied once, to the finished output row.
       // P is then the masked scores themselves, O = Q h needs no pass between the two MMAs, and the rows of V are
-      // rescaled while Q h runs.  Blocks with a stronger decay (gated linear attention) keep every factor <= 1:
+      // rescaled a block ahead, while the output rows of the block before are being stored.  Blocks with a stronger decay (gated linear attention) keep every factor <= 1:
       // exp(g_i - g_j) in P, a rescale of Q h by exp(g_i), and the rescaled V in a buffer of its own.
       const float g_last = g2[buf * T + T - 1];
       const bool mild = g_last >= kMildLog2;
@@ -386,41 +434,8 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh);
         tc_fence_after_sync();
       }
-      // ---- rows of V times their decay factors: the A operand of the state update ----
-      if (!last || mild) {
-        ok = mbar_wait(v_full, par, ab, kLinVFull) && ok;
-        // token `row` of V (chunk `wg`) is multiplied by exp(g_last - g_row).  Every 16-byte piece of the row gets
-        // the same factor, so neither the swizzle nor the order matters: lanes start at different pieces to stay
-        // off each other's banks (rows are 128 bytes apart).  With mild decay the result replaces V (P V then takes
-        // the same rows), which touches nothing Q h reads and so runs beside it; else it goes to the second buffer
-        // (with 256 state columns the upper half of the state copy, free once Q h has run).
-        const float w = fast_exp2(g_last - gi);
-        const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
-        uint4* v2line = reinterpret_cast<uint4*>((mild ? sV : sV2) + wg * (T * 128) + row * 128);
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          const int piece = (q4 + lane) & 7;
-          uint4 x = vline[piece];
-          uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float lo, hi;
-            if constexpr (kBf16) {
-              const __nv_bfloat162 h2 = *reinterpret_cast<__nv_bfloat162*>(&xs[e]);
-              lo = __bfloat162float(h2.x);
-              hi = __bfloat162float(h2.y);
-            } else {
-              const __half2 h2 = *reinterpret_cast<__half2*>(&xs[e]);
-              lo = __half2float(h2.x);
-              hi = __half2float(h2.y);
-            }
-            xs[e] = pack2<kBf16>(lo * w, hi * w);
-          }
-          v2line[piece] = x;
-        }
-        fence_proxy_async_smem();
-        if (!last) warp_arrive(v_ready);
-      }
+      // ---- rows of V times their decay factors (mild decay: done in the previous block's tail) ----
+      if (!last && !mild) ok = rescale_v(t, false) && ok;
       // ---- rows of O = Q h scaled by scale * exp(g_i) ----
       if (t > 0 && !mild) {
         const float f = qs * fast_exp2(gi);
@@ -511,16 +526,17 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_wait_st();
       tc_fence_before_sync();
       warp_arrive(p_ready);
-      // ---- the next block's decays (the decay warp wrote them once every warp was past this point) ----
-      if (!last) ok = mbar_wait(g_ready, (t + 1) & 1, ab, kLinDecay) && ok;
       // ---- 16-bit copy of hT for the next block's Q h; hT *= exp(g_last of the next block) ----
-      // The staged output rows occupy the first 32 KB of the copy's buffer, i.e. its columns [0, 128).  With 256
-      // columns every group converts its share of [128, 256) as soon as the state update has run (that half held
-      // the rescaled V), under P V, and the rest once the output store has read the staged rows.
-      const float g_next = last ? 0.0f : g2[(buf ^ 1) * T + T - 1];
-      const float decay_next = fast_exp2(g_next);
-      const bool mild_next = g_next >= kMildLog2;   // the coming block multiplies Q by the state after its decay
+      // The staged output rows occupy the first 32 KB of the copy's buffer, i.e. its columns [0, 128).  With more
+      // columns every group converts its share of the rest as soon as the state update has run (with 256 that half
+      // held the rescaled V), under P V, and its own 64 once the output store has read the staged rows.
+      float decay_next = 1.0f;
+      bool mild_next = false;   // the coming block multiplies Q by the state after its decay
       if (!last) {
+        ok = mbar_wait(g_ready, (t + 1) & 1, ab, kLinDecay) && ok;   // written once every warp was past the P phase
+        const float g_next = g2[(buf ^ 1) * T + T - 1];
+        decay_next = fast_exp2(g_next);
+        mild_next = g_next >= kMildLog2;
         ok = mbar_wait(st_bar, par, ab, kLinState) && ok;
         tc_fence_after_sync();
 #pragma unroll
@@ -588,31 +604,23 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           atomicAdd(st, sum);
           atomicAdd(st + 1, sq);
         }
-        // Each warp writes out its own 32 staged rows (4 KB): eight lanes per row, 128 contiguous bytes, four rows
-        // per instruction.  The conversion below writes every thread's state row over the line that held its
-        // output row, so nothing here crosses warps and nothing waits for a store to complete.
+        // Each warp stores its own 32 staged rows (4 KB).  The conversion below writes every thread's state row over
+        // the line that held its output row, so nothing here crosses warps; the store is given time to read the rows
+        // while the warp rescales the coming block's V.
+        fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
-        if (p.o_f32 == nullptr) {
-          const int r0 = (warp & 3) * 32, piece = lane & 7;
-          const uint8_t* chunk = sH + wg * (T * 128);
-          uint8_t* gbase = static_cast<uint8_t*>(p.o) + (static_cast<long long>(bh) * p.seq * p.dim_v + slice * DVS + wg * 64) * 2 + piece * 16;
-          uint4 x[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int r = r0 + j * 4 + (lane >> 3);
-            x[j] = *reinterpret_cast<const uint4*>(chunk + r * 128 + ((piece ^ (r & 7)) << 4));
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int tk = t * T + r0 + j * 4 + (lane >> 3);
-            if (tk < p.seq) *reinterpret_cast<uint4*>(gbase + static_cast<long long>(tk) * p.dim_v * 2) = x[j];
-          }
+        const int tok0 = t * T + (warp & 3) * 32;
+        if (lane == 0 && p.o_f32 == nullptr && tok0 < p.seq) {
+          tma_store_3d(&tmO, sH + wg * (T * 128) + (warp & 3) * (32 * 128), slice * DVS + wg * 64, tok0, bh);
+          tma_store_commit();
         }
-        __syncwarp();
       }
       if (last) break;
-      // ---- 16-bit copy of hT for the next block's Q h, rest: the columns whose place staged the output rows ----
+      if (mild_next) ok = rescale_v(t + 1, true) && ok;
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+      // ---- 16-bit copy of hT, rest: the columns whose place staged the output rows ----
       if (wg * 64 < DK) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) convert32(wg * 64 + c * 32, decay_next, mild_next);
@@ -622,6 +630,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tc_fence_before_sync();
       warp_arrive(conv_done);
     }
+    if (lane == 0) tma_store_wait_all();   // the staged rows of the last block are still being read
   }
 
   tc_fence_before_sync();
@@ -670,13 +679,14 @@ __global__ void __launch_bounds__(256) linear_norm_kernel(void* __restrict__ o, 
   }
 }
 
-inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t outer) {
+inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t outer,
+                        uint32_t box_rows = kLinT) {
   TensorMapEncodeTiledFn enc = tensor_map_encoder();
   if (enc == nullptr) return ATTN_B200_E_LAUNCH;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
   cuuint64_t gdim[3] = {cols, rows, outer};
   cuuint64_t gstride[2] = {cols * 2, cols * rows * 2};
-  cuuint32_t box[3] = {64, kLinT, 1};
+  cuuint32_t box[3] = {64, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = dtype == ATTN_B200_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = enc(tm, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -687,7 +697,7 @@ inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t c
 template <int DK, bool kBf16>
 int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status) {
   using L = LinearSmem<DK>;
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   const uint64_t bh = static_cast<uint64_t>(a->batch) * a->heads;
   int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
@@ -696,7 +706,9 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
   const bool f32_out = a->dtype_out == ATTN_B200_DTYPE_FP32;
-  if (!f32_out && (reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  // one warp's 32 rows per store; with an fp32 output the kernel does not use the map: it is encoded over v so that it stays valid
+  rc = encode_rows3(&tmO, f32_out ? a->v : a->o, a->dtype, a->dim_v, a->seq, bh, 32);
+  if (rc != ATTN_B200_OK) return rc;
   LinearParams p;
   std::memset(&p, 0, sizeof(p));
   p.o = a->o;
@@ -724,7 +736,7 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
     return ATTN_B200_E_LAUNCH;
   }
   dim3 grid(a->dim_v / kLinDvs, static_cast<unsigned>(bh));
-  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, p);
+  kernel<<<grid, kLinThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   if (a->normalize) {
     const int blocks = static_cast<int>((rows * 32 + 255) / 256);
