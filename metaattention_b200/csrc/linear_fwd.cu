@@ -53,24 +53,30 @@ struct LinearParams {
 
 __device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.0f), 65504.0f); }
 
-enum LinearWaitSite { kLinQFull = 41, kLinKFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone, kLinVFull, kLinDecay };
-enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarQh, kBarPv, kBarState, kBarPReady, kBarVReady, kBarConvDone, kBarDecay, kNumLinBarriers };
+enum LinearWaitSite { kLinQFull = 41, kLinKFull, kLinScore, kLinQh, kLinPv, kLinState, kLinPReady, kLinVReady, kLinOStaged, kLinStageFree, kLinConvDone, kLinVFull, kLinDecay, kLinHiReady };
+enum LinearBarrier { kBarQFull = 0, kBarKFull, kBarVFull, kBarScore, kBarHiReady, kBarPv, kBarState, kBarPReady, kBarVReady, kBarConvDone, kBarDecay, kNumLinBarriers };
 
 template <int DK>
 struct LinearSmem {
   static constexpr int kQBytes = kLinT * DK * 2;
   static constexpr int kVBytes = kLinT * kLinDvs * 2;
-  // operand copy of the state; the same bytes stage one block of output rows (128 x 256 B)
-  static constexpr int kHBytes = (kLinDvs * DK * 2 > kLinT * kLinDvs * 2) ? kLinDvs * DK * 2 : kLinT * kLinDvs * 2;
+  // K and the operand copy of the state, interleaved by 64-column chunk of dim_qk: chunk c holds the 128 rows of K
+  // (tokens) and then the 128 rows of the copy (dim_v), so that one N = 256 B operand yields [S | O] = Q [K^T | h].
+  // The copy's part of chunks 0 and 1 also stages one block of output rows.
+  static constexpr int kChunkBytes = kLinT * 128;
+  static constexpr int kPairBytes = 2 * kChunkBytes;
+  static constexpr int kKhBytes = (DK / 64) * kPairBytes;
+  static constexpr int kStageExtra = DK == 64 ? kChunkBytes : 0;   // the second group's staged rows with a one-chunk copy
   static constexpr int kOffQ = 0;
-  static constexpr int kOffK = kOffQ + kQBytes;
-  static constexpr int kOffV = kOffK + kQBytes;
-  static constexpr int kOffH = kOffV + kVBytes;
-  // rows of V times their decay factors, the A operand of the state update: with dim_qk 256 the upper half of
-  // the state-copy buffer (idle between the Q h MMA and the conversion pass), else a buffer of its own
-  static constexpr bool kScaledVInH = (kHBytes >= 2 * kVBytes);
-  static constexpr int kOffV2 = kScaledVInH ? kOffH + kHBytes - kVBytes : kOffH + kHBytes;
-  static constexpr int kOffG = kOffH + kHBytes + (kScaledVInH ? 0 : kVBytes);  // float g2[2][128] + float gb[128]
+  static constexpr int kOffKh = kOffQ + kQBytes;
+  static constexpr int kOffV = kOffKh + kKhBytes;
+  static constexpr int kOffStageX = kOffV + kVBytes;
+  // rows of V times their decay factors, the A operand of the state update when the decay is not mild: with dim_qk
+  // 256 the copy's part of chunks 2 and 3 (idle between the Q h MMA and the conversion pass), else a buffer of its own
+  static constexpr bool kScaledVInH = (DK == 256);
+  static constexpr int kOffV2 = kScaledVInH ? kOffKh + 2 * kPairBytes + kChunkBytes : kOffStageX + kStageExtra;
+  static constexpr int kV2Stride = kScaledVInH ? kPairBytes : kChunkBytes;
+  static constexpr int kOffG = kOffStageX + kStageExtra + (kScaledVInH ? 0 : kVBytes);  // float g2[2][128] + float gb[128]
   static constexpr int kOffBar = kOffG + 3 * kLinT * 4 + 32;
   static constexpr int kOffMisc = kOffBar + 8 * kNumLinBarriers;
   static constexpr int kBytes = kOffMisc + 16 + 1024;
@@ -92,9 +98,9 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem + L::kOffQ;
-  uint8_t* sK = smem + L::kOffK;
+  uint8_t* sKh = smem + L::kOffKh;
   uint8_t* sV = smem + L::kOffV;
-  uint8_t* sH = smem + L::kOffH;
+  uint8_t* sStageX = smem + L::kOffStageX;
   uint8_t* sV2 = smem + L::kOffV2;
   float* g2 = reinterpret_cast<float*>(smem + L::kOffG);  // [2][T] cumulative log2-decay inside a block
   float* gb = g2 + 2 * T;   // [T] exp2(g at the end of the column's 32-token chunk - g of the column), current block
@@ -103,7 +109,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* k_full = bars + kBarKFull;
   uint64_t* v_full = bars + kBarVFull;
   uint64_t* s_bar = bars + kBarScore;
-  uint64_t* qh_bar = bars + kBarQh;
+  uint64_t* hi_ready = bars + kBarHiReady;
   uint64_t* pv_bar = bars + kBarPv;
   uint64_t* st_bar = bars + kBarState;
   uint64_t* p_ready = bars + kBarPReady;
@@ -128,7 +134,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(k_full, 1);
     mbar_init(v_full, 1);
     mbar_init(s_bar, 1);
-    mbar_init(qh_bar, 1);
+    mbar_init(hi_ready, kLinRowThreads / 32);
     mbar_init(pv_bar, 1);
     mbar_init(st_bar, 1);
     mbar_init(p_ready, kLinRowThreads / 32);
@@ -160,7 +166,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       };
       auto load_k = [&](int t) {
         mbar_arrive_expect_tx(k_full, L::kQBytes);
-        for (int c = 0; c < KC; ++c) tma_load_3d(sK + c * (T * 128), &tmK, k_full, c * 64, t * T, bh);
+        for (int c = 0; c < KC; ++c) tma_load_3d(sKh + c * L::kPairBytes, &tmK, k_full, c * 64, t * T, bh);
       };
       auto load_v = [&](int t) {
         mbar_arrive_expect_tx(v_full, L::kVBytes);
@@ -168,98 +174,64 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       };
       // kind::f16 takes one 16-bit format for both operands: a variant with fp16 intermediates next to
       // bf16 inputs (A and B formats differing) raised a CUDA fault on B200 and is not offered.
-      constexpr uint32_t idesc_s = make_idesc_f16(T, T, kBf16, false, false);       // S = Q K^T
-      constexpr uint32_t idesc_qh = make_idesc_f16(T, DVS, kBf16, false, false);    // O = Q hT^T (B = hT copy, K-major)
-      constexpr uint32_t idesc_pv = make_idesc_f16(T, DVS, kBf16, false, true);     // O += P V   (B = V, MN-major)
-      constexpr uint32_t idesc_h = make_idesc_f16(DVS, DK, kBf16, true, true);      // hT += V'^T K (A M-major, B MN-major)
+      constexpr uint32_t idesc_s = make_idesc_f16(T, T, kBf16, false, false);          // S = Q K^T (first block)
+      constexpr uint32_t idesc_sq = make_idesc_f16(T, T + DVS, kBf16, false, false);   // [S | O] = Q [K^T | hT^T]
+      constexpr uint32_t idesc_pv = make_idesc_f16(T, DVS, kBf16, false, true);        // O += P V   (B = V, MN-major)
+      constexpr uint32_t idesc_h = make_idesc_f16(DVS, DK, kBf16, true, true);         // hT += V'^T K (A M-major, B MN-major)
       // descriptors are built once; the issue loops only move the start-address field (units of 16 bytes)
-      const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024), k_desc0 = make_smem_desc(smem_u32(sK), 16, 1024);
-      const uint64_t h_desc0 = make_smem_desc(smem_u32(sH), 16, 1024);
-      const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024), k_mn_desc0 = make_smem_desc(smem_u32(sK), T * 128, 1024);
-      const uint64_t v2_mn_desc0 = make_smem_desc(smem_u32(sV2), T * 128, 1024);
-      constexpr uint64_t kChunk = (T * 128) >> 4;
-      // The scores go out one 64-wide chunk of dim_qk at a time: the issuing thread is held while the pipe's queue is
-      // full, and between chunks it can serve whatever else has become possible (the output store above all).
-      int s_chunk = 0;
-      auto issue_score_chunk = [&]() -> bool {   // true once the block's last chunk is out
-        umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + s_chunk * kChunk, k_desc0 + s_chunk * kChunk, idesc_s, s_chunk > 0 ? 1u : 0u);
-        if (++s_chunk < KC) return false;
-        umma_commit(s_bar);
-        s_chunk = 0;
-        return true;
+      const uint64_t q_desc0 = make_smem_desc(smem_u32(sQ), 16, 1024), kh_desc0 = make_smem_desc(smem_u32(sKh), 16, 1024);
+      const uint64_t v_mn_desc0 = make_smem_desc(smem_u32(sV), T * 128, 1024);
+      const uint64_t k_mn_desc0 = make_smem_desc(smem_u32(sKh), L::kPairBytes, 1024);
+      const uint64_t v2_mn_desc0 = make_smem_desc(smem_u32(sV2), L::kV2Stride, 1024);
+      constexpr uint64_t kChunk = (T * 128) >> 4, kPair = L::kPairBytes >> 4;
+      static_assert(kColO == kColS + T, "S and O are the two halves of one accumulator");
+      // Chunks [c0, c1) of dim_qk of [S | O] = Q [K^T | hT^T]: the K rows and the rows of the state's copy of a chunk
+      // lie one after the other, so both products share the reads of Q.  In the first block there is no state yet
+      // and only S is computed (P V then starts O afresh).
+      auto issue_sq = [&](int t, int c0, int c1, bool fresh) {
+        for (int ch = c0; ch < c1; ++ch)
+          umma_ss_x4<2, 2>(tmem_base + kColS, q_desc0 + ch * kChunk, kh_desc0 + ch * kPair, t == 0 ? idesc_s : idesc_sq,
+                           (fresh && ch == c0) ? 0u : 1u);
       };
+      // The copy's columns [0, 128) (chunks 0 and 1) are converted last, because their place stages the output rows;
+      // the chunks from 2 on are ready earlier and their share of [S | O] of the coming block is issued as soon as the
+      // row threads have read this block's O.
+      constexpr int kLoChunks = KC < 2 ? KC : 2;
 
       // The tensor pipe executes in issue order and the issuing thread is held back while the pipe is full,
-      // so the order below is the schedule.  Per block: Q h, state update (its A operand V' sits in a buffer
-      // of its own, so it does not wait for P V), K of the next block, P V, V of the next block, output
-      // store, and already the next block's S = Q K^T, which then runs under the conversion pass.
+      // so the order below is the schedule.  Per block: the rest of [S | O], the state update (with mild decay its
+      // operand is waiting), Q and K of the next block, P V, V of the next block, the early chunks of the next [S | O].
       load_q(0);
       load_k(0);
       load_v(0);
-      bool alive = true;
-      bool s_pending = true;   // the scores of the coming block have not been issued yet
-      bool need_f = false;     // the state update of the current block has not been issued yet
-      // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step.  Call after v_ready of
-      // block t and, from the second block on, after the conversion pass of the block before.
-      auto issue_state_update = [&](int t) {
-        tc_fence_after_sync();
-        const bool mild = g2[(t & 1) * T + T - 1] >= kMildLog2;
-        const uint64_t va_desc0 = mild ? v_mn_desc0 : v2_mn_desc0;
-#pragma unroll
-        for (int g = 0; g < T / 64; ++g)
-          umma_ss_x4<128, 128>(tmem_base + kColH, va_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
-        umma_commit(st_bar);
-        need_f = false;
-      };
-      // a bounded poll step shared by the loops that serve several barriers at once
-      auto poll_alive = [&](uint32_t& spins, long long t0, int site) {
-        if ((++spins & 0xff) == 0) {
-          if (*abort_flag) return false;
-          if (clock64() - t0 > kWaitCycleLimit) {
-            *abort_flag = 1;
-            atomicCAS(p.status, 0, kStatusTimeoutBase + site);
-            return false;
-          }
-        }
-        return true;
-      };
-      for (int t = 0; alive && t < nblk; ++t) {
+      for (int t = 0; t < nblk; ++t) {
         const bool last = (t + 1 == nblk);
         const uint32_t par = t & 1, par_prev = (t - 1) & 1;
-        // S = Q K^T (needs the loads) and, after the first block, O = Q h (needs the 16-bit copy of the state
-        // written by the conversion pass of the previous block): whichever can go first goes first
-        {
-          bool need_s = s_pending, need_qh = t > 0;
-          need_f = !last;
-          const long long t0 = clock64();
-          uint32_t spins = 0;
-          while (need_s || need_qh) {
-            if (need_s && mbar_test(q_full, par) && mbar_test(k_full, par)) {
-              tc_fence_after_sync();
-              if (issue_score_chunk()) need_s = false;
-            }
-            if (need_qh && mbar_test(conv_done, par_prev)) {
-              tc_fence_after_sync();
-#pragma unroll
-              for (int ch = 0; ch < KC; ++ch)
-                umma_ss_x4<2, 2>(tmem_base + kColO, q_desc0 + ch * kChunk, h_desc0 + ch * kChunk, idesc_qh, ch > 0 ? 1u : 0u);
-              umma_commit(qh_bar);
-              need_qh = false;
-            }
-            if (!(alive = poll_alive(spins, t0, kLinConvDone))) break;
-          }
-          if (!alive) break;
-          s_pending = true;
+        if (t == 0 || KC <= kLoChunks) {
+          if (t > 0 && !mbar_wait_poll(conv_done, par_prev, ab, kLinConvDone)) break;
+          if (!(mbar_wait_poll(q_full, par, ab, kLinQFull) && mbar_wait_poll(k_full, par, ab, kLinKFull))) break;
+          tc_fence_after_sync();
+          issue_sq(t, 0, KC, true);
+        } else {
+          if (!mbar_wait_poll(conv_done, par_prev, ab, kLinConvDone)) break;
+          tc_fence_after_sync();
+          issue_sq(t, 0, kLoChunks, false);
         }
-        // The state update follows Q h in the pipe (the row threads take its completion to mean that the state's copy
-        // is no longer read); with mild decay its operand is waiting already.
-        if (need_f) {
+        umma_commit(s_bar);
+        if (!last) {
+          // hT (+)= V'^T K; both operands are MN-major over tokens: 16 tokens = 2048 B per K step.  It follows [S | O]
+          // in the pipe: the row threads take its completion to mean that the state's copy is no longer read.
           if (!mbar_wait_poll(v_ready, par, ab, kLinVReady)) break;
-          issue_state_update(t);
+          tc_fence_after_sync();
+          const bool mild = g2[(t & 1) * T + T - 1] >= kMildLog2;
+          const uint64_t va_desc0 = mild ? v_mn_desc0 : v2_mn_desc0;
+#pragma unroll
+          for (int g = 0; g < T / 64; ++g)
+            umma_ss_x4<128, 128>(tmem_base + kColH, va_desc0 + g * 512, k_mn_desc0 + g * 512, idesc_h, (t > 0 || g > 0) ? 1u : 0u);
+          umma_commit(st_bar);
         }
-        // Q may be replaced once S and Q h have run, K once the state update has
+        // Q may be replaced once [S | O] has run, K once the state update has
         if (!mbar_wait_poll(s_bar, par, ab, kLinScore)) break;
-        if (t > 0 && !mbar_wait_poll(qh_bar, par_prev, ab, kLinQh)) break;
         if (!last) {
           load_q(t + 1);
           if (!mbar_wait_poll(st_bar, par, ab, kLinState)) break;
@@ -277,24 +249,17 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             umma_ts_x4<8, 128>(tmem_base + kColO, tmem_base + kColS + 64 + g * 32, v_mn_desc0 + g * 512, idesc_pv, 1u);
         }
         umma_commit(pv_bar);
-        // Two follow-ups, served as they become possible: V of the next block (after P V) and S of the next block
-        // (after its loads; P of this block is consumed by then because the pipe runs in order).  The output rows
-        // are stored by the row warps themselves.
-        bool need_v = !last, need_s = !last;
-        const long long t0 = clock64();
-        uint32_t spins = 0;
-        while (need_v) {   // the scores are issued here only if their loads are already there
-          if (mbar_test(pv_bar, par)) {
-            load_v(t + 1);  // V was read by the row threads (before v_ready) and by P V
-            need_v = false;
-          }
-          if (need_s && mbar_test(q_full, par ^ 1) && mbar_test(k_full, par ^ 1)) {
-            tc_fence_after_sync();
-            if (issue_score_chunk()) need_s = false;
-          }
-          if (!(alive = poll_alive(spins, t0, kLinPv))) break;
+        if (last) break;
+        if (!mbar_wait_poll(pv_bar, par, ab, kLinPv)) break;
+        load_v(t + 1);  // V was read by the row threads and by P V
+        if (KC > kLoChunks) {
+          // P of this block is consumed (P V has run); O is free once every row warp has read it
+          if (!(mbar_wait_poll(hi_ready, par, ab, kLinHiReady) && mbar_wait_poll(q_full, par ^ 1, ab, kLinQFull) &&
+                mbar_wait_poll(k_full, par ^ 1, ab, kLinKFull)))
+            break;
+          tc_fence_after_sync();
+          issue_sq(t + 1, kLoChunks, KC, true);
         }
-        s_pending = need_s;
       }
     }
   } else if (warp == kLinRowThreads / 32 + 1) {
@@ -356,7 +321,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) hv[i] *= decay_next;
       }
-      uint8_t* line = sH + (col0 >> 6) * (DVS * 128) + row * 128;
+      uint8_t* line = sKh + (col0 >> 6) * L::kPairBytes + L::kChunkBytes + row * 128;
       const int piece0 = (col0 & 63) >> 3;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -385,7 +350,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float* g = g2 + (tb & 1) * T;
       const float w = fast_exp2(g[T - 1] - g[row]);
       const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
-      uint4* v2line = reinterpret_cast<uint4*>((in_place ? sV : sV2) + wg * (T * 128) + row * 128);
+      uint4* v2line = reinterpret_cast<uint4*>((in_place ? sV + wg * (T * 128) : sV2 + wg * L::kV2Stride) + row * 128);
 #pragma unroll
       for (int q4 = 0; q4 < 8; ++q4) {
         const int piece = (q4 + lane) & 7;
@@ -430,8 +395,8 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // exp(g_i - g_j) in P, a rescale of Q h by exp(g_i), and the rescaled V in a buffer of its own.
       const float g_last = g2[buf * T + T - 1];
       const bool mild = g_last >= kMildLog2;
-      if (t > 0 && !mild) {
-        ok = mbar_wait(qh_bar, (t - 1) & 1, ab, kLinQh);
+      if (!mild) {
+        ok = mbar_wait(s_bar, par, ab, kLinQh);   // Q h has run: O may be rescaled, the copy's upper chunks overwritten
         tc_fence_after_sync();
       }
       // ---- rows of V times their decay factors (mild decay: done in the previous block's tail) ----
@@ -551,7 +516,8 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // `wg` of its row as one swizzled 128-byte line (the layout TMA expects).
         const int tok = t * T + row;
         float sum = 0.f, sq = 0.f;
-        uint8_t* line = sH + wg * (T * 128) + row * 128;
+        uint8_t* stage = (DK == 64 && wg == 1) ? sStageX : sKh + wg * L::kPairBytes + L::kChunkBytes;
+        uint8_t* line = stage + row * 128;
         const float fo = mild ? qs * fast_exp2(gi - g_last) : 1.0f;   // the row factor left out of Q h and P (mild decay)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -607,12 +573,12 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // Each warp stores its own 32 staged rows (4 KB).  The conversion below writes every thread's state row over
         // the line that held its output row, so nothing here crosses warps; the store is given time to read the rows
         // while the warp rescales the coming block's V.
-        fence_proxy_async_smem();
+        fence_proxy_async_smem();   // also orders the copy's early chunks, converted above, before the arrival
         tc_fence_before_sync();
-        __syncwarp();
+        warp_arrive(hi_ready);      // O has been read and the early chunks are in place: the next [S | O] may start
         const int tok0 = t * T + (warp & 3) * 32;
         if (lane == 0 && p.o_f32 == nullptr && tok0 < p.seq) {
-          tma_store_3d(&tmO, sH + wg * (T * 128) + (warp & 3) * (32 * 128), slice * DVS + wg * 64, tok0, bh);
+          tma_store_3d(&tmO, stage + (warp & 3) * (32 * 128), slice * DVS + wg * 64, tok0, bh);
           tma_store_commit();
         }
       }
