@@ -479,10 +479,10 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           }
         }
         // P overwrites S: 16-bit pairs in columns [0, 64), and with split_p the 16-bit remainder P - round(P) in
-        // columns [64, 128) for a second PV pass.  Those columns belong to the other group's half of S, so
-        // every thread must have its S values in registers first.
+        // columns [64, 128) for a second PV pass.  Those columns belong to the other group's half of the same rows
+        // of S, so the two warps of a lane quarter must both have their S values in registers first.
         tc_fence_before_sync();
-        ok = named_sync_and(1, kLinRowThreads, ok);
+        ok = named_sync_and(1 + (warp & 3), 64, ok);
         if (!ok) break;
         tc_fence_after_sync();
         tmem_st32(tS + wg * 32, pk);
