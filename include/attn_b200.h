@@ -261,6 +261,41 @@ int attn_b200_mla_decode(const AttnB200MlaArgs* args, void* cuda_stream);
  * (no part of it needs clearing); calls that overlap on the GPU race. */
 int attn_b200_mla_decode_static(const AttnB200MlaArgs* args, int32_t* status_word, void* cuda_stream);
 
+/* Backward of softmax attention (the built-in softmax functor; mask NONE or CAUSAL; dim_qk = dim_v = 128; grouped
+ * KV heads as in the forward).  Replaces the reference's generated backward kernels and their launcher
+ * (attention_engine/core/template/tl_template/attn/attn_tl.py: preprocess :212-244, main :309-503, postprocess
+ * :246-275, autograd wrapper :669-694; the CuTe backward behind core/template/cute_template/flash_api.cpp:462-700).
+ * o and lse are the forward's results (lse = log-sum-exp of scale * q.k over the kept keys, [batch, heads, seq_q]
+ * fp32); d_o is the gradient of o.  dq, dk, dv get the gradients in the dtype of q, k, v; every element inside the
+ * sequence bounds is written.  All strides are element strides of (batch, seq, head) with the head dim contiguous. */
+typedef struct AttnB200SoftmaxBwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;
+  void* dq;
+  void* dk;
+  void* dv;
+  int32_t batch, heads, heads_kv, seq_q, seq_kv, dim_qk, dim_v;
+  int32_t dtype;       /* ATTN_B200_DTYPE_* */
+  int32_t mask_kind;   /* ATTN_B200_MASK_NONE or ATTN_B200_MASK_CAUSAL (keep kv_idx <= q_idx) */
+  float scale;         /* softmax scale */
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+  void* workspace;     /* attn_b200_softmax_bwd_workspace_bytes() bytes of device scratch, 16-byte aligned */
+  int64_t workspace_bytes;
+} AttnB200SoftmaxBwdArgs;
+
+/* Scratch the backward needs (delta = rowsum(dO o O) and the log-sum-exp in the exp2 domain, padded to whole
+ * 128-row tiles); -1 = bad arguments. */
+int64_t attn_b200_softmax_bwd_workspace_bytes(const AttnB200SoftmaxBwdArgs* args);
+
+/* Three launches on `cuda_stream`: the preparation pass, dK/dV (one CTA per KV tile and KV head), dQ (one CTA per
+ * query tile and head).  No atomics: results are bit-reproducible. */
+int attn_b200_softmax_bwd(const AttnB200SoftmaxBwdArgs* args, void* cuda_stream);
+
 /* Reads and clears the device-side status word of device `device`
  * (0 = no kernel reported a problem).  Synchronises the device. */
 int attn_b200_last_device_status(int32_t device, int32_t* status_out);

@@ -74,7 +74,7 @@ class OnlineFunc:
 
 class _ForwardOnly(torch.autograd.Function):
     """Keeps autograd graphs well-formed: the forward runs the native kernel,
-    the backward states clearly that it does not exist."""
+    the backward states clearly that it does not exist for this program."""
 
     @staticmethod
     def forward(ctx, runner, *tensors):
@@ -82,7 +82,30 @@ class _ForwardOnly(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        raise NotImplementedError("the B200-native backend implements the forward pass only")
+        raise NotImplementedError("the B200-native backend has a backward pass for softmax attention only (score_mod = "
+                                  "scale, the softmax online_func, no mask or a causal mask, head dims 128 / 128)")
+
+
+class _SoftmaxAttention(torch.autograd.Function):
+    """Softmax attention with its native backward (attn_b200_softmax_bwd), the counterpart of the reference's
+    ``_attention`` autograd function (core/template/tl_template/attn/attn_tl.py:654-694): the forward keeps o and the
+    log-sum-exp, the backward recomputes the probabilities from them."""
+
+    @staticmethod
+    def forward(ctx, engine, q, k, v):
+        q, k, v = q.detach(), k.detach(), v.detach()
+        o = engine._run_parallel_impl(q, k, v)
+        lse = engine.last_final_rowscales[engine.final_names[0]]
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.engine = engine
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        eng = ctx.engine
+        dq, dk, dv = native.softmax_bwd(q, k, v, o, lse, d_o.to(q.dtype), eng._fparams[0], eng.mask_kind)
+        return None, dq, dk, dv
 
 
 def plan_kv_splits(batch: int, heads: int, q_len: int, kv_len: int, device) -> int:
@@ -257,8 +280,17 @@ class AttentionEngine:
         else:
             run = self._run_parallel_impl
         if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
+            if self.has_backward(q, v) and not custom:
+                return _SoftmaxAttention.apply(self, q, k, v)
             return _ForwardOnly.apply(run, q, k, v, *custom)
         return run(q, k, v, *custom)
+
+    def has_backward(self, q, v) -> bool:
+        """Whether gradients flow through this engine for these operands: the built-in softmax (a traced program that
+        is softmax attention with a probed scale), no mask or a causal one, head dims 128 / 128."""
+        return (self.functor_kind == "builtin_softmax" and self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL) and
+                self._decode_block is None and self._sparse_host is None and len(self.final_names) == 1 and
+                q.shape[-1] == 128 and v.shape[-1] == 128)
 
     def _custom_operands(self, custom, B, H, Sq, Skv, device):
         """Checks the custom input tensors against their declared shapes and returns (tensors, element strides over

@@ -76,6 +76,18 @@ class LinearArgs(C.Structure):
     ]
 
 
+class SoftmaxBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("d_o", C.c_void_p),
+        ("lse", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("heads_kv", C.c_int32), ("seq_q", C.c_int32), ("seq_kv", C.c_int32),
+        ("dim_qk", C.c_int32), ("dim_v", C.c_int32), ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("scale", C.c_float),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
+        ("do_stride", C.c_int64 * 3), ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+    ]
+
+
 class MlaShape(C.Structure):
     _fields_ = [("batch", C.c_int32), ("heads_q", C.c_int32), ("seq_kv", C.c_int32),
                 ("dim_qk", C.c_int32), ("dim_v", C.c_int32)]
@@ -104,6 +116,8 @@ SIGNATURES = {
                                          C.c_void_p, C.c_int64, C.c_void_p]),
     "attn_b200_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "attn_b200_linear_workspace_bytes": (C.c_int64, [C.POINTER(LinearArgs)]),
+    "attn_b200_softmax_bwd": (C.c_int, [C.POINTER(SoftmaxBwdArgs), C.c_void_p]),
+    "attn_b200_softmax_bwd_workspace_bytes": (C.c_int64, [C.POINTER(SoftmaxBwdArgs)]),
     "attn_b200_mla_plan": (C.c_int, [C.POINTER(MlaShape), C.c_int32, C.POINTER(C.c_int32)]),
     "attn_b200_mla_workspace_bytes": (C.c_int64, [C.POINTER(MlaShape), C.c_int32]),
     "attn_b200_mla_num_parts": (C.c_int32, [C.c_int32, C.c_int32]),
@@ -119,7 +133,7 @@ _lib = None
 
 
 def library_sources() -> list[str]:
-    return [os.path.join(CSRC_DIR, f) for f in ("attn_b200.cu", "mla_decode.cu", "linear_fwd.cu")]
+    return [os.path.join(CSRC_DIR, f) for f in ("attn_b200.cu", "mla_decode.cu", "linear_fwd.cu", "softmax_bwd.cu")]
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
@@ -279,6 +293,42 @@ def decode_tiles(block_mask, cache_seqlens, batch: int, heads_kv: int, seq_kv: i
     part = out[bh * tiles * 4 + bh * words:]
     return {"keep": keep, "partial": part, "mask_base": None, "elem_mask": col, "batch": batch, "heads": heads_kv,
             "mask_rows": 0, "_owner": (out, block_mask, cache_seqlens)}
+
+
+def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
+    """(dq, dk, dv) of softmax attention from the forward's o and lse [B, H, Sq] and the gradient of o
+    (attn_b200_softmax_bwd: mask NONE or CAUSAL, head dims 128 / 128)."""
+    for t in (q, k, v, o, d_o, lse):
+        if not t.is_cuda:
+            raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
+    if d_o.stride(-1) != 1:
+        d_o = d_o.contiguous()
+    for t in (q, k, v, o):
+        if t.stride(-1) != 1:
+            raise NativeError("last dimension must be contiguous")
+    if q.dtype not in DTYPE_CODES or any(t.dtype != q.dtype for t in (k, v, o, d_o)):
+        raise NativeError("q, k, v, o, d_o must share dtype float16 or bfloat16")
+    lse = lse.contiguous().float()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if dq.stride(-1) != 1 or dk.stride(-1) != 1 or dv.stride(-1) != 1:
+        dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))
+    a = SoftmaxBwdArgs()
+    a.q, a.k, a.v, a.o, a.d_o, a.lse = (t.data_ptr() for t in (q, k, v, o, d_o, lse))
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    B, Sq, H, D = q.shape
+    a.batch, a.heads, a.heads_kv, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, k.shape[2], Sq, k.shape[1], D, v.shape[3]
+    a.dtype, a.mask_kind, a.scale = DTYPE_CODES[q.dtype], mask_kind, float(scale)
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", d_o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        getattr(a, name + "_stride")[:] = _strides_bsh(t)
+    lib = load_library()
+    need = lib.attn_b200_softmax_bwd_workspace_bytes(C.byref(a))
+    if need < 0:
+        raise NativeError("attn_b200_softmax_bwd_workspace_bytes: bad arguments")
+    ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need
+    with torch.cuda.device(q.device):
+        check(lib.attn_b200_softmax_bwd(C.byref(a), current_stream_ptr()), "attn_b200_softmax_bwd")
+    return dq, dk, dv
 
 
 def parallel_fwd(args: ParallelArgs):

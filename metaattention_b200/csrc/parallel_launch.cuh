@@ -23,6 +23,15 @@ inline TensorMapEncodeTiledFn tensor_map_encoder() {
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
     return reinterpret_cast<TensorMapEncodeTiledFn>(p);
   }();
+  // The encoder is a driver entry point and wants a current context on the calling thread.  The runtime binds the
+  // current device's primary context to a thread only at its first call that needs one, so a thread that has made
+  // none yet (an autograd worker running a backward pass, with every per-device object of this library already
+  // cached) would get CUDA_ERROR_INVALID_CONTEXT: setting the device it already has binds the context.
+  thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) bound = true;
+  }
   return fn;
 }
 

@@ -50,6 +50,17 @@ def softmax_attention(q, k, v, causal: bool = True, softmax_scale: float | None 
     return o.reshape(B, Sq, H, v.shape[-1])
 
 
+def softmax_attention_grads(q, k, v, d_o, causal: bool = True, softmax_scale: float | None = None):
+    """(dq, dk, dv) fp32 of ``softmax_attention`` for the output gradient ``d_o``: torch autograd through the
+    restated closure, the way the reference's test obtains the gradients it compares its backward kernels with
+    (testing/test.py:106-127)."""
+    with torch.enable_grad():
+        qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+        o = softmax_attention(qf, kf, vf, causal, softmax_scale)
+        o.backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad
+
+
 def softmax_lse(q, k, causal: bool = True, softmax_scale: float | None = None):
     """Per-row log-sum-exp of the scaled, masked scores: [B,H,S] fp32.  No reference
     closure returns it; the definition is the final row scale of examples/mha.py:64-71

@@ -176,6 +176,22 @@ def main():
     out["sparse_gqa_decode"] = dict(shape=(B, H, G, S, D, D), seed=91, block=block, cache_seqlens=lens, block_mask=bmask,
                                     o=o.contiguous())
 
+    # gradients of softmax MHA: torch autograd through the reference's own closure (testing/test.py:79-104), which is
+    # what the reference's test compares its backward kernels with (testing/test.py:106-127); dO is part of the fixture
+    ref = extract(tree, source, "test_softmaxattention", "ref")
+    for name, (B, H, S, D, causal, seed) in {"softmax_bwd_causal": (1, 2, 160, 128, True, 101),
+                                              "softmax_bwd_noncausal": (1, 2, 144, 128, False, 102)}.items():
+        q, k, v = inputs.attention_bshd(B, H, S, D, D, seed)
+        d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(seed + 1000)).to(torch.bfloat16)
+        with torch.enable_grad():
+            qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+            o = ref(qf, kf, vf, causal=causal, softmax_scale=D ** -0.5)
+            o.backward(d_o.float())
+        rec = dict(shape=(B, H, S, D, D), causal=causal, seed=seed, d_o=d_o, o=o.detach().contiguous(),
+                   dq=qf.grad.contiguous(), dk=kf.grad.contiguous(), dv=vf.grad.contiguous())
+        torch.save(rec, os.path.join(HERE, f"{name}.pt"))
+        print(name, tuple(rec["dq"].shape), f"{4 * rec['dq'].numel() * 4 / 1024:.0f} KiB")
+
     torch.save(block_mask_goldens(ref_root), os.path.join(HERE, "block_masks.pt"))
     print("block_masks", len(MASK_CASES) * len(MASK_SHAPES), "cases")
 

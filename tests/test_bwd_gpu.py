@@ -1,0 +1,134 @@
+"""Backward of softmax attention (attn_b200_softmax_bwd and the engine's autograd path) against the committed
+gradients of the reference's own closure (tests/golden/softmax_bwd_*.pt: torch autograd through testing/test.py:79-104,
+the comparison the reference's test makes at :106-127) and against the CPU oracle on further shapes.
+Tolerances for 16-bit results against fp32: max-abs 2e-2, mean-abs 2e-3."""
+
+import os
+
+import pytest
+import torch
+
+from oracle import inputs, reference_math as rm
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+def check(got, want, what):
+    d = (got.float().cpu() - want.float()).abs()
+    assert torch.isfinite(got).all(), what
+    assert d.max().item() <= MAX_ABS, (what, d.max().item())
+    assert d.mean().item() <= MEAN_ABS, (what, d.mean().item())
+
+
+def native_forward(q, k, v, causal, scale):
+    from core.native import lib
+    B, S, H, _ = q.shape
+    o = torch.empty((B, S, H, v.shape[-1]), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    args = lib.fill_parallel_args(q, k, v, o, mask_kind=lib.MASK_CAUSAL if causal else lib.MASK_NONE,
+                                  functor=lib.FUNCTOR_SOFTMAX, fparams=(scale,), final_rowscales=[lse])
+    lib.parallel_fwd(args)
+    return o, lse
+
+
+@pytest.mark.parametrize("name", ["softmax_bwd_causal", "softmax_bwd_noncausal"])
+def test_against_reference_golden(name):
+    from core.native import lib
+    g = torch.load(os.path.join(GOLD, f"{name}.pt"))
+    B, H, S, D, Dv = g["shape"]
+    q, k, v = (t.cuda() for t in inputs.attention_bshd(B, H, S, D, Dv, g["seed"]))
+    scale = D ** -0.5
+    o, lse = native_forward(q, k, v, g["causal"], scale)
+    dq, dk, dv = lib.softmax_bwd(q, k, v, o, lse, g["d_o"].cuda(), scale, lib.MASK_CAUSAL if g["causal"] else lib.MASK_NONE)
+    torch.cuda.synchronize()
+    assert lib.last_device_status() == 0
+    check(o, g["o"], "o")
+    check(dq, g["dq"], "dq")
+    check(dk, g["dk"], "dk")
+    check(dv, g["dv"], "dv")
+
+
+@pytest.mark.parametrize("B,H,Hkv,Sq,Skv,causal,dtype", [
+    (1, 2, 2, 128, 128, False, torch.float16),     # one tile
+    (2, 4, 4, 512, 512, True, torch.bfloat16),     # several tiles, the diagonal ones masked
+    (1, 2, 2, 300, 300, True, torch.bfloat16),     # ragged last tile
+    (1, 4, 2, 384, 384, True, torch.bfloat16),     # grouped KV heads: dk, dv sum over the group
+    (1, 2, 1, 200, 333, False, torch.bfloat16),    # different lengths, both ragged
+    (1, 2, 2, 100, 700, False, torch.float16),     # one query tile against many KV tiles
+    (1, 1, 1, 640, 256, True, torch.bfloat16),     # causal with more queries than keys (kv <= q: top-left aligned)
+])
+def test_shapes_against_oracle(B, H, Hkv, Sq, Skv, causal, dtype):
+    from core.native import lib
+    g = torch.Generator().manual_seed(Sq * 7 + Skv)
+    q = torch.randn(B, Sq, H, 128, generator=g).to(dtype)
+    k = torch.randn(B, Skv, Hkv, 128, generator=g).to(dtype)
+    v = torch.randn(B, Skv, Hkv, 128, generator=g).to(dtype)
+    d_o = torch.randn(B, Sq, H, 128, generator=g).to(dtype)
+    scale = 128 ** -0.5
+    keep = None
+    if causal and Sq != Skv:
+        keep = torch.arange(Skv)[None, :] <= torch.arange(Sq)[:, None]
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        rm.softmax_attention(qf, kf, vf, causal, scale, keep=keep).backward(d_o.float())
+    o, lse = native_forward(q.cuda(), k.cuda(), v.cuda(), causal, scale)
+    dq, dk, dv = lib.softmax_bwd(q.cuda(), k.cuda(), v.cuda(), o, lse, d_o.cuda(), scale,
+                                 lib.MASK_CAUSAL if causal else lib.MASK_NONE)
+    torch.cuda.synchronize()
+    assert lib.last_device_status() == 0
+    check(dq, qf.grad, "dq")
+    check(dk, kf.grad, "dk")
+    check(dv, vf.grad, "dv")
+
+
+def test_results_are_reproducible():
+    """No atomics anywhere: two runs give the same bits."""
+    from core.native import lib
+    q, k, v = (t.cuda() for t in inputs.attention_bshd(2, 3, 384, 128, 128, 7))
+    d_o = torch.randn(2, 384, 3, 128, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).cuda()
+    o, lse = native_forward(q, k, v, True, 128 ** -0.5)
+    a = lib.softmax_bwd(q, k, v, o, lse, d_o, 128 ** -0.5, lib.MASK_CAUSAL)
+    b = lib.softmax_bwd(q, k, v, o, lse, d_o, 128 ** -0.5, lib.MASK_CAUSAL)
+    torch.cuda.synchronize()
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_engine_autograd(causal):
+    """The user's path: the traced softmax program (score_mod = scale, the softmax online_func) with tensors that
+    require gradients, `o.backward(d_o)` as in the reference's examples/mha.py."""
+    from examples_b200 import programs
+    B, H, S, D = 1, 4, 320, 128
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 33)
+    d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(34)).to(torch.bfloat16)
+    want = rm.softmax_attention_grads(q, k, v, d_o, causal, D ** -0.5)
+    eng = programs.softmax_engine(B, H, S, D, D, is_causal=causal)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qc, kc, vc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    check(o.detach(), rm.softmax_attention(q, k, v, causal, D ** -0.5), "o")
+    for got, ref, what in zip((qc.grad, kc.grad, vc.grad), want, ("dq", "dk", "dv")):
+        check(got, ref, what)
+
+
+def test_programs_without_a_backward_say_so():
+    from examples_b200 import programs
+    B, H, S, D = 1, 2, 128, 64
+    q, k, v = (t.cuda().requires_grad_() for t in inputs.attention_bshd(B, H, S, D, D, 35))
+    eng = programs.softmax_engine(B, H, S, D, D, is_causal=True)   # head dim 64: forward only
+    o = eng(q, k, v)
+    with pytest.raises(NotImplementedError):
+        o.sum().backward()
+
+
+def test_argument_errors():
+    from core.native import lib
+    a = lib.SoftmaxBwdArgs()
+    assert lib.load_library().attn_b200_softmax_bwd_workspace_bytes(None) == -1
+    assert lib.load_library().attn_b200_softmax_bwd(None, None) != 0
+    assert lib.load_library().attn_b200_softmax_bwd(a, None) != 0   # null tensors

@@ -32,6 +32,19 @@ def test_softmax(name):
     close(rm.softmax_attention(q, k, v, causal=g["causal"], softmax_scale=D ** -0.5), g["o"])
 
 
+@pytest.mark.parametrize("name", ["softmax_bwd_causal", "softmax_bwd_noncausal"])
+def test_softmax_gradients(name):
+    """Gradients through the oracle's closure against autograd through the reference's own (testing/test.py:79-127)."""
+    g = load(name)
+    B, H, S, D, Dv = g["shape"]
+    q, k, v = inputs.attention_bshd(B, H, S, D, Dv, g["seed"])
+    close(rm.softmax_attention(q, k, v, causal=g["causal"], softmax_scale=D ** -0.5), g["o"])
+    dq, dk, dv = rm.softmax_attention_grads(q, k, v, g["d_o"], causal=g["causal"], softmax_scale=D ** -0.5)
+    close(dq, g["dq"])
+    close(dk, g["dk"])
+    close(dv, g["dv"])
+
+
 @pytest.mark.parametrize("name", ["sigmoid_causal", "sigmoid_noncausal_scaled"])
 def test_sigmoid(name):
     g = load(name)
