@@ -398,6 +398,35 @@ def extras_parallel(sampler, peaks, launches):
     return out
 
 
+def extras_backward(peaks, launches=10):
+    """Backward of the headline shape (softmax MHA, causal, bf16, B=8 H=32 S=4096 D=128): forward once for o and lse,
+    then the three backward launches (preparation, dK/dV, dQ) timed launch by launch.  FLOPs are counted as the five
+    tile products of the algorithm (2.5x the forward), although the kernels compute S and dP twice (seven)."""
+    out = {}
+    try:
+        from core.native import lib
+        B, H, S, D = C2["B"], C2["H"], C2["S"], C2["D"]
+        q, k, v = [t.cuda() for t in oracle_inputs.attention_bshd(B, H, S, D, D, C2["seed"])]
+        d_o = torch.randn(B, S, H, D, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda").to(torch.bfloat16)
+        o = torch.empty_like(q)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device="cuda")
+        a = lib.fill_parallel_args(q, k, v, o, mask_kind=lib.MASK_CAUSAL, functor=lib.FUNCTOR_SOFTMAX, fparams=(D ** -0.5,),
+                                   final_rowscales=[lse])
+        lib.parallel_fwd(a)
+        times = time_launches(lambda: lib.softmax_bwd(q, k, v, o, lse, d_o, D ** -0.5, lib.MASK_CAUSAL), launches, 3)
+        rec = launch_stats(times)
+        fl = 2.5 * attention_flops(B, H, S, D, D, True)
+        rec["tflops"] = fl / rec["ms"] / 1e9
+        rec["roofline"] = tensor_roofline(fl, rec["ms"], peaks, sustained=False)
+        rec["note"] = "FLOPs of five tile products per (query tile, KV tile); the two kernels execute seven"
+        out["softmax_backward_causal_8x32x4096x128"] = rec
+        del q, k, v, o, d_o
+    except Exception as exc:
+        out["softmax_backward_error"] = repr(exc)[:300]
+    torch.cuda.empty_cache()
+    return out
+
+
 def mla_case(B, H, S, D, Dv, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     q = torch.randn(B, H, D, generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
@@ -738,6 +767,7 @@ def main():
             extras.update(extras_mla(sampler, peaks, 40))
             extras.update(extras_retention(sampler, peaks, 40))
             extras.update(extras_decode())
+            extras.update(extras_backward(peaks))
     sampler.stop()
 
     if rank == 0:
