@@ -48,8 +48,8 @@ struct BwdParams {
   int* status;
 };
 
-enum BwdWaitSite { kBwdXFull = 61, kBwdYFull, kBwdYEmpty, kBwdSDone, kBwdPReady, kBwdAccDone };
-enum BwdBarrier { kBarXFull = 0, kBarYFull0, kBarYFull1, kBarYEmpty0, kBarYEmpty1, kBarSDone, kBarPReadyB, kBarAccDone, kNumBwdBarriers };
+enum BwdWaitSite { kBwdXFull = 61, kBwdYFull, kBwdYEmpty, kBwdSDone, kBwdPReady, kBwdAccDone, kBwdSdpFree };
+enum BwdBarrier { kBarXFull = 0, kBarYFull0, kBarYFull1, kBarYEmpty0, kBarYEmpty1, kBarSDone, kBarPReadyB, kBarAccDone, kBarSdpFree, kNumBwdBarriers };
 
 struct BwdSmem {
   static constexpr int kTileBytes = kBwdT * kBwdD * 2;        // 32 KB: two 64-column chunks of 128 rows x 128 B
@@ -115,13 +115,15 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const void* __restrict
 // kRoleQ = false: CTA = (KV tile, KV head, batch), streams the query tiles (of every query head of its group) and
 // writes dK, dV.  kRoleQ = true: CTA = (query tile, query head, batch), streams the KV tiles and writes dQ.
 // Tensor memory: S [0,128), dP [128,256), accumulator 1 [256,384) (dV or dQ), accumulator 2 [384,512) (dK).
+// The query role has no second accumulator: it writes dS to two alternating 64-column buffers there instead of over
+// dP, so that S and dP of the next tile can be computed as soon as the row threads hold this tile's in registers.
 template <bool kRoleQ, bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
   using L = BwdSmem;
   constexpr int T = kBwdT;
-  constexpr uint32_t kTmemCols = 512, kColS = 0, kColDP = 128, kColA = 256, kColB = 384;
+  constexpr uint32_t kTmemCols = 512, kColS = 0, kColDP = 128, kColA = 256, kColB = 384, kColDS = 384;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -136,6 +138,7 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* s_done = bars + kBarSDone;
   uint64_t* p_ready = bars + kBarPReadyB;
   uint64_t* acc_done = bars + kBarAccDone;
+  uint64_t* sdp_free = bars + kBarSdpFree;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffMisc + 8);
 
@@ -159,6 +162,7 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(s_done, 1);
     mbar_init(p_ready, kBwdRowThreads / 32);
     mbar_init(acc_done, 1);
+    mbar_init(sdp_free, kBwdRowThreads / 32);
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -221,14 +225,14 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint64_t kChunk = L::kChunkBytes >> 4;
       const uint64_t x1_desc = make_smem_desc(smem_u32(sX1), 16, 1024), x2_desc = make_smem_desc(smem_u32(sX2), 16, 1024);
       bool ok = mbar_wait_poll(x_full, 0, ab, kBwdXFull);
-      for (int it = 0; ok && it < n_iter; ++it) {
-        const int st = it & 1;
+      auto stage_descs = [&](int st, uint64_t& y1_desc, uint64_t& y2_desc, uint64_t& y1_mn, uint64_t& y2_mn) {
         const uint32_t y1a = smem_u32(sY + st * L::kStageBytes), y2a = y1a + L::kTileBytes;
-        const uint64_t y1_desc = make_smem_desc(y1a, 16, 1024), y2_desc = make_smem_desc(y2a, 16, 1024);
-        const uint64_t y1_mn = make_smem_desc(y1a, L::kChunkBytes, 1024), y2_mn = make_smem_desc(y2a, L::kChunkBytes, 1024);
-        if (!mbar_wait_poll(y_full + st, (it >> 1) & 1, ab, kBwdYFull)) break;
-        tc_fence_after_sync();
-        // the pipe runs in issue order: P and dS of the tile before have been consumed when these overwrite them
+        y1_desc = make_smem_desc(y1a, 16, 1024);
+        y2_desc = make_smem_desc(y2a, 16, 1024);
+        y1_mn = make_smem_desc(y1a, L::kChunkBytes, 1024);
+        y2_mn = make_smem_desc(y2a, L::kChunkBytes, 1024);
+      };
+      auto issue_s_dp = [&](uint64_t y1_desc, uint64_t y2_desc) {
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColS, x1_desc + ch * kChunk, y1_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
@@ -236,19 +240,54 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int ch = 0; ch < 2; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColDP, x2_desc + ch * kChunk, y2_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
         umma_commit(s_done);
-        if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
-        tc_fence_after_sync();
-        if constexpr (!kRoleQ) {
+      };
+      uint64_t y1_desc, y2_desc, y1_mn, y2_mn;
+      if constexpr (kRoleQ) {
+        // S, dP of tile it + 1 are issued as soon as the row threads hold those of tile it in registers, ahead of
+        // tile it's accumulating MMA (dS sits in a buffer of its own)
+        if (ok && mbar_wait_poll(y_full, 0, ab, kBwdYFull)) {
+          tc_fence_after_sync();
+          stage_descs(0, y1_desc, y2_desc, y1_mn, y2_mn);
+          issue_s_dp(y1_desc, y2_desc);
+        } else {
+          ok = false;
+        }
+        for (int it = 0; ok && it < n_iter; ++it) {
+          const int st = it & 1;
+          const uint64_t y1_mn_cur = y1_mn;
+          if (it + 1 < n_iter) {
+            if (!(mbar_wait_poll(y_full + (st ^ 1), ((it + 1) >> 1) & 1, ab, kBwdYFull) && mbar_wait_poll(sdp_free, it & 1, ab, kBwdSdpFree))) break;
+            tc_fence_after_sync();
+            stage_descs(st ^ 1, y1_desc, y2_desc, y1_mn, y2_mn);
+            issue_s_dp(y1_desc, y2_desc);
+          }
+          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int g = 0; g < T / 64; ++g)
+            umma_ts_x4<8, 128>(tmem_base + kColA, tmem_base + kColDS + st * 64 + g * 32, y1_mn_cur + g * 512, idesc_mn, (it > 0 || g > 0) ? 1u : 0u);
+          umma_commit(y_empty + st);
+          if (it + 1 == n_iter) umma_commit(acc_done);
+        }
+      } else {
+        for (int it = 0; ok && it < n_iter; ++it) {
+          const int st = it & 1;
+          if (!mbar_wait_poll(y_full + st, (it >> 1) & 1, ab, kBwdYFull)) break;
+          tc_fence_after_sync();
+          stage_descs(st, y1_desc, y2_desc, y1_mn, y2_mn);
+          // the pipe runs in issue order: P and dS of the tile before have been consumed when these overwrite them
+          issue_s_dp(y1_desc, y2_desc);
+          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
+          tc_fence_after_sync();
 #pragma unroll
           for (int g = 0; g < T / 64; ++g)
             umma_ts_x4<8, 128>(tmem_base + kColA, tmem_base + kColS + g * 32, y2_mn + g * 512, idesc_mn, (it > 0 || g > 0) ? 1u : 0u);
-        }
 #pragma unroll
-        for (int g = 0; g < T / 64; ++g)
-          umma_ts_x4<8, 128>(tmem_base + (kRoleQ ? kColA : kColB), tmem_base + kColDP + g * 32, y1_mn + g * 512, idesc_mn,
-                             (it > 0 || g > 0) ? 1u : 0u);
-        umma_commit(y_empty + st);
-        if (it + 1 == n_iter) umma_commit(acc_done);
+          for (int g = 0; g < T / 64; ++g)
+            umma_ts_x4<8, 128>(tmem_base + kColB, tmem_base + kColDP + g * 32, y1_mn + g * 512, idesc_mn, (it > 0 || g > 0) ? 1u : 0u);
+          umma_commit(y_empty + st);
+          if (it + 1 == n_iter) umma_commit(acc_done);
+        }
       }
     }
   } else {
@@ -284,6 +323,11 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32f(tS + c0, s);
         tmem_ld32f(tDP + c0, dp);
         tmem_wait_ld();
+        if (kRoleQ && u == 1) {   // this tile's S and dP are in registers: the next tile's may be computed
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sdp_free);
+        }
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
           const float l2 = kRoleQ ? lse2_r : st_lse[c0 + k];
@@ -302,12 +346,16 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       // the 16-bit pairs of columns [64 wg, 64 wg + 64) go to 32-bit columns [32 wg, 32 wg + 32), which the other warp
       // of this lane quarter reads as fp32: both must have their values in registers first
-      tc_fence_before_sync();
-      ok = named_sync_and(1 + wq, 64, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      if constexpr (!kRoleQ) tmem_st32(tS + wg * 32, pp);
-      tmem_st32(tDP + wg * 32, pds);
+      if constexpr (kRoleQ) {
+        tmem_st32(tmem_base + lane_base + kColDS + st * 64 + wg * 32, pds);
+      } else {
+        tc_fence_before_sync();
+        ok = named_sync_and(1 + wq, 64, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        tmem_st32(tS + wg * 32, pp);
+        tmem_st32(tDP + wg * 32, pds);
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
