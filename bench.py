@@ -180,7 +180,7 @@ def prebuild_functors():
 
 def reference_root():
     """A checkout of the reference project (holding testing/test.py), or None: $ATTN_B200_REFERENCE, then baseline/_ref/
-    of this repository, then /root/reference."""
+    of this repository, then the checkout the build environment provides."""
     for cand in (os.environ.get("ATTN_B200_REFERENCE"), os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
         if cand and os.path.isfile(os.path.join(cand, "testing", "test.py")):
             return cand

@@ -261,7 +261,7 @@ int attn_b200_mla_decode(const AttnB200MlaArgs* args, void* cuda_stream);
  * (no part of it needs clearing); calls that overlap on the GPU race. */
 int attn_b200_mla_decode_static(const AttnB200MlaArgs* args, int32_t* status_word, void* cuda_stream);
 
-/* Backward of softmax attention (the built-in softmax functor; mask NONE or CAUSAL; dim_qk = dim_v = 128; grouped
+/* Backward of softmax attention (the built-in softmax functor; mask NONE or CAUSAL; dim_qk = dim_v = 128 or 64; grouped
  * KV heads as in the forward).  Replaces the reference's generated backward kernels and their launcher
  * (attention_engine/core/template/tl_template/attn/attn_tl.py: preprocess :212-244, main :309-503, postprocess
  * :246-275, autograd wrapper :669-694; the CuTe backward behind core/template/cute_template/flash_api.cpp:462-700).

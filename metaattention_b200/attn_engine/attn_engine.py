@@ -83,7 +83,7 @@ class _ForwardOnly(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         raise NotImplementedError("the B200-native backend has a backward pass for softmax attention only (score_mod = "
-                                  "scale, the softmax online_func, no mask or a causal mask, head dims 128 / 128)")
+                                  "scale, the softmax online_func, no mask or a causal mask, head dims 128 / 128 or 64 / 64)")
 
 
 class _SoftmaxAttention(torch.autograd.Function):
@@ -287,10 +287,10 @@ class AttentionEngine:
 
     def has_backward(self, q, v) -> bool:
         """Whether gradients flow through this engine for these operands: the built-in softmax (a traced program that
-        is softmax attention with a probed scale), no mask or a causal one, head dims 128 / 128."""
+        is softmax attention with a probed scale), no mask or a causal one, head dims 128 / 128 or 64 / 64."""
         return (self.functor_kind == "builtin_softmax" and self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL) and
                 self._decode_block is None and self._sparse_host is None and len(self.final_names) == 1 and
-                q.shape[-1] == 128 and v.shape[-1] == 128)
+                q.shape[-1] == v.shape[-1] and q.shape[-1] in (64, 128))
 
     def _custom_operands(self, custom, B, H, Sq, Skv, device):
         """Checks the custom input tensors against their declared shapes and returns (tensors, element strides over

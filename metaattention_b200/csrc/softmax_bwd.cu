@@ -1,4 +1,4 @@
-// Backward of softmax attention for sm_100a (head dims 128 / 128, 16-bit inputs, fp32 accumulation).
+// Backward of softmax attention for sm_100a (head dims 128 / 128 or 64 / 64, 16-bit inputs, fp32 accumulation).
 //
 //   P  = exp(scale * Q K^T - lse)            (recomputed from the forward's log-sum-exp, masked like the forward)
 //   dV = P^T dO
@@ -30,7 +30,6 @@
 namespace b200 {
 
 constexpr int kBwdT = 128;                // rows of a tile, both ways
-constexpr int kBwdD = 128;                // head dim (qk and v)
 constexpr int kBwdRowThreads = 256;       // eight warps: one TMEM lane each, two column halves
 constexpr int kBwdThreads = kBwdRowThreads + 64;   // plus the loading warp and the MMA-issuing warp
 
@@ -51,8 +50,9 @@ struct BwdParams {
 enum BwdWaitSite { kBwdXFull = 61, kBwdYFull, kBwdYEmpty, kBwdSDone, kBwdPReady, kBwdAccDone, kBwdSdpFree };
 enum BwdBarrier { kBarXFull = 0, kBarYFull0, kBarYFull1, kBarYEmpty0, kBarYEmpty1, kBarSDone, kBarPReadyB, kBarAccDone, kBarSdpFree, kNumBwdBarriers };
 
+template <int D>
 struct BwdSmem {
-  static constexpr int kTileBytes = kBwdT * kBwdD * 2;        // 32 KB: two 64-column chunks of 128 rows x 128 B
+  static constexpr int kTileBytes = kBwdT * D * 2;            // D/64 chunks of 128 rows x 128 B (64 columns)
   static constexpr int kChunkBytes = kBwdT * 128;
   static constexpr int kOffX1 = 0;
   static constexpr int kOffX2 = kOffX1 + kTileBytes;
@@ -117,12 +117,13 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const void* __restrict
 // Tensor memory: S [0,128), dP [128,256), accumulator 1 [256,384) (dV or dQ), accumulator 2 [384,512) (dK).
 // The query role has no second accumulator: it writes dS to two alternating 64-column buffers there instead of over
 // dP, so that S and dP of the next tile can be computed as soon as the row threads hold this tile's in registers.
-template <bool kRoleQ, bool kBf16>
+template <bool kRoleQ, bool kBf16, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
-  using L = BwdSmem;
-  constexpr int T = kBwdT;
+  using L = BwdSmem<D>;
+  constexpr int T = kBwdT, KC = D / 64, HALF = D / 2;   // chunks of a tile; columns of an accumulator row per warp group
+  static_assert(D == 64 || D == 128, "head dims 64 and 128");
   constexpr uint32_t kTmemCols = 512, kColS = 0, kColDP = 128, kColA = 256, kColB = 384, kColDS = 384;
 
   extern __shared__ uint8_t smem_raw[];
@@ -183,7 +184,7 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ======================= loading warp =======================
     if (lane == 0 && start_ok && n_iter > 0) {
       mbar_arrive_expect_tx(x_full, 2 * L::kTileBytes);
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < KC; ++c) {
         if constexpr (kRoleQ) {
           tma_load_rows(sX1 + c * L::kChunkBytes, &tmQ, x_full, c * 64, tile * T, hx, b, p.oq);
           tma_load_rows(sX2 + c * L::kChunkBytes, &tmDO, x_full, c * 64, tile * T, hx, b, p.odo);
@@ -200,14 +201,14 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if constexpr (kRoleQ) {
           mbar_arrive_expect_tx(y_full + st, 2 * L::kTileBytes);
           const int hk = hx / p.kv_group;
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < KC; ++c) {
             tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y_full + st, c * 64, it * T, hk, b, p.ok);
             tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y_full + st, c * 64, it * T, hk, b, p.ov);
           }
         } else {
           mbar_arrive_expect_tx(y_full + st, 2 * L::kTileBytes + L::kStatsBytes);
           const int hq = hx * p.kv_group + it / per_head, i = i0 + it % per_head;
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < KC; ++c) {
             tma_load_rows(y1 + c * L::kChunkBytes, &tmQ, y_full + st, c * 64, i * T, hq, b, p.oq);
             tma_load_rows(y2 + c * L::kChunkBytes, &tmDO, y_full + st, c * 64, i * T, hq, b, p.odo);
           }
@@ -221,7 +222,7 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // ======================= issuing warp: every MMA =======================
     if (lane == 0 && start_ok && n_iter > 0) {
       constexpr uint32_t idesc_kk = make_idesc_f16(T, T, kBf16, false, false);      // S, dP: both operands K-major
-      constexpr uint32_t idesc_mn = make_idesc_f16(T, kBwdD, kBf16, false, true);   // accumulators: B = streamed tile, MN-major
+      constexpr uint32_t idesc_mn = make_idesc_f16(T, D, kBf16, false, true);       // accumulators: B = streamed tile, MN-major
       constexpr uint64_t kChunk = L::kChunkBytes >> 4;
       const uint64_t x1_desc = make_smem_desc(smem_u32(sX1), 16, 1024), x2_desc = make_smem_desc(smem_u32(sX2), 16, 1024);
       bool ok = mbar_wait_poll(x_full, 0, ab, kBwdXFull);
@@ -234,10 +235,10 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
       auto issue_s_dp = [&](uint64_t y1_desc, uint64_t y2_desc) {
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch)
+        for (int ch = 0; ch < KC; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColS, x1_desc + ch * kChunk, y1_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ch = 0; ch < 2; ++ch)
+        for (int ch = 0; ch < KC; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColDP, x2_desc + ch * kChunk, y2_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
         umma_commit(s_done);
       };
@@ -380,8 +381,8 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         const bool in_range = r < (kRoleQ ? p.seq_q : p.seq_kv);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c0 = wg * 64 + u * 32;
+        for (int u = 0; u < HALF / 32; ++u) {
+          const int c0 = wg * HALF + u * 32;
           float v[32];
           if (n_iter > 0) {
             tmem_ld32f(tmem_base + lane_base + (a == 0 ? kColA : kColB) + c0, v);
@@ -419,9 +420,9 @@ softmax_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
 }
 
-template <bool kBf16>
+template <bool kBf16, int D>
 int launch_softmax_bwd(const AttnB200SoftmaxBwdArgs* a, cudaStream_t stream, int* status) {
-  using L = BwdSmem;
+  using L = BwdSmem<D>;
   const int T = kBwdT;
   const int heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;
   const int nq = (a->seq_q + T - 1) / T, nk = (a->seq_kv + T - 1) / T;
@@ -468,8 +469,8 @@ int launch_softmax_bwd(const AttnB200SoftmaxBwdArgs* a, cudaStream_t stream, int
                                                          a->do_stride[1], a->do_stride[2]);
     if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   }
-  auto kv_kernel = softmax_bwd_kernel<false, kBf16>;
-  auto q_kernel = softmax_bwd_kernel<true, kBf16>;
+  auto kv_kernel = softmax_bwd_kernel<false, kBf16, D>;
+  auto q_kernel = softmax_bwd_kernel<true, kBf16, D>;
   if (cudaFuncSetAttribute(kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess ||
       cudaFuncSetAttribute(q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
     cudaGetLastError();
@@ -500,7 +501,7 @@ int attn_b200_softmax_bwd(const AttnB200SoftmaxBwdArgs* a, void* cuda_stream) {
   if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
   const int heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;
   if (a->heads % heads_kv != 0) return ATTN_B200_E_INVALID_ARG;
-  if (a->dim_qk != b200::kBwdD || a->dim_v != b200::kBwdD) return ATTN_B200_E_UNSUPPORTED;
+  if (a->dim_qk != a->dim_v || (a->dim_qk != 64 && a->dim_qk != 128)) return ATTN_B200_E_UNSUPPORTED;
   if (a->mask_kind != ATTN_B200_MASK_NONE && a->mask_kind != ATTN_B200_MASK_CAUSAL) return ATTN_B200_E_UNSUPPORTED;
   if (a->batch > 65535 || a->heads > 65535) return ATTN_B200_E_UNSUPPORTED;
   const void* outs[3] = {a->dq, a->dk, a->dv};
@@ -521,8 +522,10 @@ int attn_b200_softmax_bwd(const AttnB200SoftmaxBwdArgs* a, void* cuda_stream) {
   int* status = b200::device_status_word(dev);
   if (status == nullptr) return ATTN_B200_E_LAUNCH;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  return a->dtype == ATTN_B200_DTYPE_BF16 ? b200::launch_softmax_bwd<true>(a, stream, status)
-                                           : b200::launch_softmax_bwd<false>(a, stream, status);
+  const bool bf16 = a->dtype == ATTN_B200_DTYPE_BF16;
+  if (a->dim_qk == 64)
+    return bf16 ? b200::launch_softmax_bwd<true, 64>(a, stream, status) : b200::launch_softmax_bwd<false, 64>(a, stream, status);
+  return bf16 ? b200::launch_softmax_bwd<true, 128>(a, stream, status) : b200::launch_softmax_bwd<false, 128>(a, stream, status);
 }
 
 }  // extern "C"

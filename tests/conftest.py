@@ -11,7 +11,7 @@ for p in (ROOT, os.path.join(ROOT, "metaattention_b200")):
 
 def reference_root():
     """Directory of a checkout of the reference project (the one holding examples/ and testing/test.py), or None.
-    Looked for in $ATTN_B200_REFERENCE, then baseline/_ref/ of this repository, then /root/reference."""
+    Looked for in $ATTN_B200_REFERENCE, then baseline/_ref/ of this repository, then the checkout the build environment provides."""
     for cand in (os.environ.get("ATTN_B200_REFERENCE"), os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
         if cand and os.path.isfile(os.path.join(cand, "testing", "test.py")) and os.path.isdir(os.path.join(cand, "examples")):
             return cand

@@ -3,7 +3,7 @@ closures on seeded inputs.  Run in a container that has the reference checkout:
 
     python tests/golden/make_golden.py [/path/to/reference]
 
-(default: $ATTN_B200_REFERENCE, then baseline/_ref/ of this repository, then /root/reference)
+(default: $ATTN_B200_REFERENCE, then baseline/_ref/ of this repository, then the checkout the build environment provides)
 
 The reference's functional suite (testing/test.py) cannot be imported as a
 module (it needs termcolor, matplotlib and a GPU at import time), so the

@@ -17,9 +17,12 @@ MAX_ABS, MEAN_ABS = 2e-2, 2e-3
 
 
 def check(got, want, what):
+    """max-abs 2e-2 and mean-abs 2e-3, the first scaled by the largest magnitude of the expected tensor where that
+    exceeds 1 (a 16-bit result of magnitude m carries a rounding error of up to m * 2^-9 by itself; gradients summed
+    over a group of heads or with the larger scale of head dim 64 reach 3-4)."""
     d = (got.float().cpu() - want.float()).abs()
     assert torch.isfinite(got).all(), what
-    assert d.max().item() <= MAX_ABS, (what, d.max().item())
+    assert d.max().item() <= MAX_ABS * max(1.0, want.abs().max().item()), (what, d.max().item(), want.abs().max().item())
     assert d.mean().item() <= MEAN_ABS, (what, d.mean().item())
 
 
@@ -60,14 +63,15 @@ def test_against_reference_golden(name):
     (1, 2, 2, 100, 700, False, torch.float16),     # one query tile against many KV tiles
     (1, 1, 1, 640, 256, True, torch.bfloat16),     # causal with more queries than keys (kv <= q: top-left aligned)
 ])
-def test_shapes_against_oracle(B, H, Hkv, Sq, Skv, causal, dtype):
+@pytest.mark.parametrize("D", [128, 64])
+def test_shapes_against_oracle(B, H, Hkv, Sq, Skv, causal, dtype, D):
     from core.native import lib
     g = torch.Generator().manual_seed(Sq * 7 + Skv)
-    q = torch.randn(B, Sq, H, 128, generator=g).to(dtype)
-    k = torch.randn(B, Skv, Hkv, 128, generator=g).to(dtype)
-    v = torch.randn(B, Skv, Hkv, 128, generator=g).to(dtype)
-    d_o = torch.randn(B, Sq, H, 128, generator=g).to(dtype)
-    scale = 128 ** -0.5
+    q = torch.randn(B, Sq, H, D, generator=g).to(dtype)
+    k = torch.randn(B, Skv, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(B, Skv, Hkv, D, generator=g).to(dtype)
+    d_o = torch.randn(B, Sq, H, D, generator=g).to(dtype)
+    scale = D ** -0.5
     keep = None
     if causal and Sq != Skv:
         keep = torch.arange(Skv)[None, :] <= torch.arange(Sq)[:, None]
@@ -118,9 +122,9 @@ def test_engine_autograd(causal):
 
 def test_programs_without_a_backward_say_so():
     from examples_b200 import programs
-    B, H, S, D = 1, 2, 128, 64
-    q, k, v = (t.cuda().requires_grad_() for t in inputs.attention_bshd(B, H, S, D, D, 35))
-    eng = programs.softmax_engine(B, H, S, D, D, is_causal=True)   # head dim 64: forward only
+    B, H, S, D, Dv = 1, 2, 128, 128, 256
+    q, k, v = (t.cuda().requires_grad_() for t in inputs.attention_bshd(B, H, S, D, Dv, 35))
+    eng = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)   # head dims 128 / 256: forward only
     o = eng(q, k, v)
     with pytest.raises(NotImplementedError):
         o.sum().backward()
