@@ -144,6 +144,47 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
     return o
 
 
+def _retention_fp32(qc, kc, vc, log_decay, q_scale):
+    """o_i = q_scale * sum_{j<=i} exp(G_i - G_j) (qc_i . kc_j) vc_j in fp32 on the forward kernel, for any width of the
+    contraction: the sum is linear in the scores, so a contraction wider than the kernel's 256 columns is the sum over
+    column ranges it does cover (widths 256 / 128 / 64, the last one zero-padded)."""
+    D = qc.shape[-1]
+    out, start = None, 0
+    while start < D:
+        width = next((w for w in (256, 128, 64) if D - start >= w), 64)
+        qs, ks = qc[..., start:start + width], kc[..., start:start + width]
+        if qs.shape[-1] < width:
+            pad = width - qs.shape[-1]
+            qs, ks = torch.nn.functional.pad(qs, (0, pad)), torch.nn.functional.pad(ks, (0, pad))
+        part = linear_attention_forward(qs.contiguous(), ks.contiguous(), vc, log_decay, q_scale, out_dtype=torch.float32)
+        out = part if out is None else out + part
+        start += width
+    return out
+
+
+def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0):
+    """(dq, dk, dv) of ``linear_attention_forward`` (no normalisation; the decay is not differentiated), the job of the
+    reference's three backward kernels (core/template/tl_template/linear/linear_tl.py:461-975), as five runs of the
+    forward kernel.  With D_ij = exp(G_i - G_j) for j <= i:
+
+        dq_i = q_scale * sum_{j<=i} D_ij (do_i . v_j) k_j      = retention(q = do, k = v, v = k)
+        dv_j = q_scale * sum_{i>=j} D_ij (q_i . k_j) do_i      = retention(q = k, k = q, v = do) with time reversed
+        dk_j = q_scale * sum_{i>=j} D_ij (do_i . v_j) q_i      = retention(q = v, k = do, v = q) with time reversed
+
+    Reversing time turns the anti-causal sums into causal ones; position u of the reversed sequence then carries the
+    log-decay of token T - u (0 for u = 0), so that the reversed cumulative sums reproduce the same D_ij.  The two
+    contractions over dim_v go through ``_retention_fp32`` (dim_v may exceed the kernel's 256 columns of dim_qk)."""
+    d_o = d_o.to(q.dtype)
+    B, H, T, _ = q.shape
+    ld = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T)
+    ld_rev = torch.cat([torch.zeros_like(ld[..., :1]), ld.flip(-1)[..., :-1]], dim=-1).contiguous()
+    dq = _retention_fp32(d_o, v, k, ld, q_scale)
+    qr, kr, vr, dr = q.flip(2), k.flip(2), v.flip(2), d_o.flip(2)
+    dv = _retention_fp32(kr, qr, dr, ld_rev, q_scale).flip(2)
+    dk = _retention_fp32(vr, dr, qr, ld_rev, q_scale).flip(2)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
 class _ForwardOnly(torch.autograd.Function):
     @staticmethod
     def forward(ctx, runner, *tensors):
@@ -151,7 +192,41 @@ class _ForwardOnly(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        raise NotImplementedError("the B200-native backend implements the forward pass only")
+        raise NotImplementedError("the B200-native backend differentiates linear attention only without q / k / v mods "
+                                  "(a constant factor on q is fine), without output normalisation and not with respect "
+                                  "to the decay")
+
+
+class _LinearAttention(torch.autograd.Function):
+    """Chunked linear attention with its backward (``linear_attention_backward``): the counterpart of the reference's
+    ``LinearAttention`` autograd function (core/template/tl_template/linear/linear_tl.py:1237-1333)."""
+
+    @staticmethod
+    def forward(ctx, engine, q, k, v, decay, *custom):
+        q, k, v = q.detach(), k.detach(), v.detach()
+        cenv = {id(engine.custom_io.input_tensors[n]): t.float() for n, t in zip(engine.custom_names, custom)}
+        log_decay = engine._apply("decay", decay.detach().float(), cenv)
+        H = v.shape[1]
+        qe = q.repeat_interleave(H // q.shape[1], dim=1) if q.shape[1] != H else q
+        ke = k.repeat_interleave(H // k.shape[1], dim=1) if k.shape[1] != H else k
+        o = linear_attention_forward(qe, ke, v, log_decay, q_scale=engine.q_scale)
+        ctx.save_for_backward(qe, ke, v, log_decay)
+        ctx.heads = (q.shape[1], k.shape[1])
+        ctx.q_scale = engine.q_scale
+        ctx.n_custom = len(custom)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        qe, ke, v, log_decay = ctx.saved_tensors
+        dq, dk, dv = linear_attention_backward(qe, ke, v, log_decay, d_o, ctx.q_scale)
+        B, H, T, _ = qe.shape
+        hq, hk = ctx.heads
+        if hq != H:   # heads that shared one q head: their gradients add up
+            dq = dq.view(B, hq, H // hq, T, -1).float().sum(2).to(dq.dtype)
+        if hk != H:
+            dk = dk.view(B, hk, H // hk, T, -1).float().sum(2).to(dk.dtype)
+        return (None, dq, dk, dv, None) + (None,) * ctx.n_custom
 
 
 class LinearAttentionEngine:
@@ -196,8 +271,15 @@ class LinearAttentionEngine:
         res = eval_tensor_expr(out, env)
         return res if name == "decay" else res.to(tensor.dtype)
 
+    def has_backward(self) -> bool:
+        """Gradients with respect to q, k, v flow when no mod rewrites them (a constant factor on q has been folded
+        into the kernel's scale) and the output is not normalised."""
+        return all(self._mods[n] is None for n in ("q", "k", "v")) and not self.normalize_output
+
     def _run(self, q, k, v, decay, *custom):
         if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
+            if self.has_backward() and not (isinstance(decay, torch.Tensor) and decay.requires_grad):
+                return _LinearAttention.apply(self, q, k, v, decay, *custom)
             return _ForwardOnly.apply(self._run_impl, q, k, v, decay, *custom)
         return self._run_impl(q, k, v, decay, *custom)
 

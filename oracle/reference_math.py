@@ -118,6 +118,35 @@ def retention_recurrent(q, k, v):
     return o
 
 
+def retention_grads(q, k, v, d_o):
+    """(dq, dk, dv) fp32 of ``retention_recurrent`` for the output gradient ``d_o``: torch autograd through the
+    restated closure (the reference's test differentiates its own closure the same way, testing/test.py:749-770)."""
+    with torch.enable_grad():
+        qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+        retention_recurrent(qf, kf, vf).backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+def decayed_linear_attention_grads(q, k, v, log_decay, d_o, scale: float = 1.0):
+    """(dq, dk, dv) fp32 of ``decayed_linear_attention`` (the decay is not differentiated), in closed form with the
+    decay matrix D_ij = exp(G_i - G_j), j <= i, in fp64: dq = scale (D o (dO V^T)) K, dk = scale (D o (dO V^T))^T Q,
+    dv = scale (D o (Q K^T))^T dO.  Heads of q / k shared by several heads of v get the sum of their gradients."""
+    q, k, v, ld, d_o = q.double(), k.double(), v.double(), log_decay.double(), d_o.double()
+    B, H, S, _ = v.shape
+    HQ, HK = q.shape[1], k.shape[1]
+    qe = q.repeat_interleave(H // HQ, dim=1)
+    ke = k.repeat_interleave(H // HK, dim=1)
+    G = ld.expand(B, H, S).cumsum(-1)
+    D = torch.exp((G.unsqueeze(-1) - G.unsqueeze(-2)).clamp_max(0.0)) * torch.ones(S, S, dtype=torch.float64).tril()
+    a = D * torch.einsum("bhid,bhjd->bhij", d_o, v) * scale
+    dq = torch.einsum("bhij,bhjd->bhid", a, ke)
+    dk = torch.einsum("bhij,bhid->bhjd", a, qe)
+    dv = torch.einsum("bhij,bhid->bhjd", D * torch.einsum("bhid,bhjd->bhij", qe, ke) * scale, d_o)
+    dq = dq.view(B, HQ, H // HQ, S, -1).sum(2)
+    dk = dk.view(B, HK, H // HK, S, -1).sum(2)
+    return dq.float(), dk.float(), dv.float()
+
+
 def decayed_linear_attention(q, k, v, log_decay, scale: float = 1.0):
     """o[i] = sum_{j<=i} exp(G_i - G_j) (scale q_i . k_j) v_j with G the inclusive cumulative sum of the
     per-token natural-log decay: the function computed chunk by chunk by naive_chunk_simple_gla

@@ -192,6 +192,20 @@ def main():
         torch.save(rec, os.path.join(HERE, f"{name}.pt"))
         print(name, tuple(rec["dq"].shape), f"{4 * rec['dq'].numel() * 4 / 1024:.0f} KiB")
 
+    # gradients of RetNet retention: autograd through the reference's closure (testing/test.py:738-747)
+    ref = extract(tree, source, "test_retnet_recurrent", "ref")
+    B, H, S, Dk, Dv = 1, 2, 160, 64, 128
+    q, k, v, _ = inputs.retention_bhsd(B, H, S, Dk, Dv, 111)
+    d_o = torch.randn(B, H, S, Dv, generator=torch.Generator().manual_seed(1111)).to(torch.bfloat16)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        o = ref(qf, kf, vf)
+        o.float().backward(d_o.float())
+    rec = dict(shape=(B, H, S, Dk, Dv), seed=111, d_o=d_o, o=o.detach().float().contiguous(),
+               dq=qf.grad.contiguous(), dk=kf.grad.contiguous(), dv=vf.grad.contiguous())
+    torch.save(rec, os.path.join(HERE, "retention_bwd.pt"))
+    print("retention_bwd", tuple(rec["dv"].shape))
+
     torch.save(block_mask_goldens(ref_root), os.path.join(HERE, "block_masks.pt"))
     print("block_masks", len(MASK_CASES) * len(MASK_SHAPES), "cases")
 

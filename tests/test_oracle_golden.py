@@ -45,6 +45,20 @@ def test_softmax_gradients(name):
     close(dv, g["dv"])
 
 
+def test_retention_gradients():
+    """Autograd through the oracle's retention closure, and the closed form of the decayed linear attention, against
+    autograd through the reference's own closure (testing/test.py:738-770)."""
+    g = load("retention_bwd")
+    B, H, S, Dk, Dv = g["shape"]
+    q, k, v, decay = inputs.retention_bhsd(B, H, S, Dk, Dv, g["seed"])
+    close(rm.retention_recurrent(q, k, v), g["o"], tol=2e-4)
+    for got, want in zip(rm.retention_grads(q, k, v, g["d_o"]), (g["dq"], g["dk"], g["dv"])):
+        close(got, want, tol=2e-4)
+    closed = rm.decayed_linear_attention_grads(q, k, v, decay.log(), g["d_o"], scale=Dk ** -0.5)
+    for got, want in zip(closed, (g["dq"], g["dk"], g["dv"])):
+        close(got, want, tol=2e-4)
+
+
 @pytest.mark.parametrize("name", ["sigmoid_causal", "sigmoid_noncausal_scaled"])
 def test_sigmoid(name):
     g = load(name)
