@@ -182,9 +182,11 @@ def test_full_size_config3_sampled_heads():
 
 
 def test_backward_is_refused_clearly():
+    """Programs whose backward is not built (here a lowered functor: sigmoid attention) say so when differentiated;
+    softmax attention has one (tests/test_bwd_gpu.py)."""
     B, H, S, D = 1, 1, 128, 64
     q, k, v = [t.cuda().requires_grad_(True) for t in inputs.attention_bshd(B, H, S, D, D, 1)]
-    o = programs.softmax_engine(B, H, S, D, D)(q, k, v)
+    o = programs.sigmoid_engine(B, H, S, D, D, is_causal=True)(q, k, v, torch.tensor([-3.0]).cuda())
     with pytest.raises(NotImplementedError):
         o.sum().backward()
 
