@@ -424,10 +424,10 @@ def extras_backward(peaks, launches=10):
         # RetNet retention backward on the benchmark shape: five runs of the forward kernel plus the time reversals
         # and fp32 sums around them (torch), timed as one call
         from attn_engine.linear_attn_engine import linear_attention_backward
-        qr, kr, vr, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(C4["B"], C4["H"], C4["S"], C4["Dk"], C4["Dv"], C4["seed"])]
+        qr, kr, vr, decay = [t.cuda() for t in oracle_inputs.retention_bhsd(C4["B"], C4["H"], C4["S"], C4["D"], C4["Dv"], C4["seed"])]
         ld = decay.log()
         d_or = torch.randn(vr.shape, generator=torch.Generator(device="cuda").manual_seed(8), device="cuda").to(torch.bfloat16)
-        times = time_launches(lambda: linear_attention_backward(qr, kr, vr, ld, d_or, q_scale=C4["Dk"] ** -0.5), launches, 3)
+        times = time_launches(lambda: linear_attention_backward(qr, kr, vr, ld, d_or, q_scale=C4["D"] ** -0.5), launches, 3)
         rec = launch_stats(times)
         rec["note"] = ("dq, dk, dv; the reference's three backward kernels on the same shape: 2.559 + 3.992 + 1.960 ms on H100 "
                        "(its tuned_config files)")
