@@ -296,6 +296,30 @@ int64_t attn_b200_softmax_bwd_workspace_bytes(const AttnB200SoftmaxBwdArgs* args
  * query tile and head).  No atomics: results are bit-reproducible. */
 int attn_b200_softmax_bwd(const AttnB200SoftmaxBwdArgs* args, void* cuda_stream);
 
+/* Backward of an elementwise program (a lowered score_mod with no row scales: P = f(q.k), e.g. the sigmoid and relu
+ * attention of the reference's examples; its gradient graph is what core/transform/core.py:119-199 and
+ * core/lower/lower.py:349-436 of the reference build).  There is one entry point per functor, exported by the
+ * library compiled for that functor's forward-mode derivative (`_jit/functor_*.so`), never by libattn_b200:
+ *   int attn_b200_elementwise_bwd_jit(const AttnB200ElementwiseBwdArgs* args, void* cuda_stream, int32_t* device_status);
+ * dV = P^T dO, dS = dP * f'(q.k), dK = dS^T Q, dQ = dS K; mask NONE or CAUSAL (masked pairs contribute nothing), grouped
+ * KV heads, dim_qk = dim_v = 128 or 64.  `custom[i]` points at the i-th custom input, an fp32 scalar on the device. */
+typedef struct AttnB200ElementwiseBwdArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* d_o;
+  void* dq;
+  void* dk;
+  void* dv;
+  int32_t batch, heads, heads_kv, seq_q, seq_kv, dim_qk, dim_v;
+  int32_t dtype;       /* ATTN_B200_DTYPE_* */
+  int32_t mask_kind;   /* ATTN_B200_MASK_NONE or ATTN_B200_MASK_CAUSAL */
+  int32_t reserved;
+  int64_t q_stride[3], k_stride[3], v_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+  const void* custom[ATTN_B200_MAX_CUSTOM];
+} AttnB200ElementwiseBwdArgs;
+
 /* Reads and clears the device-side status word of device `device`
  * (0 = no kernel reported a problem).  Synchronises the device. */
 int attn_b200_last_device_status(int32_t device, int32_t* status_out);

@@ -23,6 +23,7 @@ import torch
 
 from core.lower import functor as functor_lowering
 from core.lower import sparse as sparse_lowering
+from core.lower import derivative
 from core.lower.trace import probe_softmax_scale, trace_parallel
 from core.native import jit as native_jit
 from core.native import lib as native
@@ -82,8 +83,9 @@ class _ForwardOnly(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        raise NotImplementedError("the B200-native backend has a backward pass for softmax attention only (score_mod = "
-                                  "scale, the softmax online_func, no mask or a causal mask, head dims 128 / 128 or 64 / 64)")
+        raise NotImplementedError("the B200-native backend has a backward pass for softmax attention (score_mod = scale, "
+                                  "the softmax online_func) and for elementwise programs (no row scales, scalar custom "
+                                  "inputs), with no mask or a causal mask and head dims 128 / 128 or 64 / 64")
 
 
 class _SoftmaxAttention(torch.autograd.Function):
@@ -106,6 +108,29 @@ class _SoftmaxAttention(torch.autograd.Function):
         eng = ctx.engine
         dq, dk, dv = native.softmax_bwd(q, k, v, o, lse, d_o.to(q.dtype), eng._fparams[0], eng.mask_kind)
         return None, dq, dk, dv
+
+
+class _ElementwiseAttention(torch.autograd.Function):
+    """An elementwise program (P = f(q.k): sigmoid, relu attention ...) with the backward derived from its traced
+    score_mod (core/lower/derivative.py) and compiled on first use."""
+
+    @staticmethod
+    def forward(ctx, engine, n_custom, q, k, v, *custom):
+        q, k, v = q.detach(), k.detach(), v.detach()
+        custom = tuple(t.detach() if isinstance(t, torch.Tensor) else t for t in custom)
+        o = engine._run_parallel_impl(q, k, v, *custom)
+        ctx.save_for_backward(q, k, v, *custom)
+        ctx.engine = engine
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, *custom = ctx.saved_tensors
+        eng = ctx.engine
+        if eng._bwd_fn is None:
+            eng._bwd_fn = native_jit.load_backward(eng._bwd_source)
+        dq, dk, dv = native.elementwise_bwd(eng._bwd_fn, q, k, v, d_o.to(q.dtype), eng.mask_kind, custom)
+        return (None, None, dq, dk, dv) + (None,) * len(custom)
 
 
 def plan_kv_splits(batch: int, heads: int, q_len: int, kv_len: int, device) -> int:
@@ -172,6 +197,8 @@ class AttentionEngine:
         self.block_mask = None
         self._decode_block = None  # block size of a call-time block_mask (block-sparse, variable-length decode)
         self._sparse_host = None   # block-sparse walk of a general mask_mod (built once, on the CPU)
+        self._bwd_source = None    # translation unit of the backward functor library (elementwise programs)
+        self._bwd_fn = None
         self._sparse_dev = {}      # its copies by device
         self.kv_splits = None      # None = planned per call (plan_kv_splits); an int forces the split count
         self.qkv_meta = qkv_meta
@@ -272,6 +299,9 @@ class AttentionEngine:
             # compile now (works without a GPU); loading is deferred to the first call
             native_jit.build(self.functor_source)
             self._jit_fn = None
+            # the backward of an elementwise program: source now, compiled when a gradient is first asked for
+            if derivative.elementwise_program(tr) and D == Dv and D in (64, 128):
+                self._bwd_source = derivative.backward_translation_unit(derivative.emit_backward_functor(tr), D, dtype == torch.bfloat16)
         self.attention = self._run_parallel
 
     def _run_parallel(self, q, k, v, *custom, block_mask=None, cache_seqlens=None):
@@ -282,8 +312,14 @@ class AttentionEngine:
         if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
             if self.has_backward(q, v) and not custom:
                 return _SoftmaxAttention.apply(self, q, k, v)
+            if self._bwd_source is not None and self._masked_for_backward():
+                return _ElementwiseAttention.apply(self, len(custom), q, k, v, *custom)
             return _ForwardOnly.apply(run, q, k, v, *custom)
         return run(q, k, v, *custom)
+
+    def _masked_for_backward(self) -> bool:
+        return (self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL) and self._decode_block is None and
+                self._sparse_host is None)
 
     def has_backward(self, q, v) -> bool:
         """Whether gradients flow through this engine for these operands: the built-in softmax (a traced program that

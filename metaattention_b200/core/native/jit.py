@@ -83,3 +83,15 @@ def load(source: str):
         fn.argtypes = [C.POINTER(native.ParallelArgs), C.c_void_p, C.c_void_p]
         _loaded[path] = dll
     return _loaded[path].attn_b200_parallel_fwd_jit
+
+
+def load_backward(source: str):
+    """Return the bound ``attn_b200_elementwise_bwd_jit`` of the library for ``source`` (a translation unit from
+    core.lower.derivative), compiling it first if it is not cached."""
+    path = build(source)
+    if path not in _loaded:
+        _loaded[path] = C.CDLL(path)
+    fn = _loaded[path].attn_b200_elementwise_bwd_jit
+    fn.restype = C.c_int
+    fn.argtypes = [C.POINTER(native.ElementwiseBwdArgs), C.c_void_p, C.c_void_p]
+    return fn

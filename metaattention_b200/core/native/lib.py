@@ -88,6 +88,18 @@ class SoftmaxBwdArgs(C.Structure):
     ]
 
 
+class ElementwiseBwdArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("d_o", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("heads_kv", C.c_int32), ("seq_q", C.c_int32), ("seq_kv", C.c_int32),
+        ("dim_qk", C.c_int32), ("dim_v", C.c_int32), ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("reserved", C.c_int32),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("do_stride", C.c_int64 * 3),
+        ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
+        ("custom", C.c_void_p * MAX_CUSTOM),
+    ]
+
+
 class MlaShape(C.Structure):
     _fields_ = [("batch", C.c_int32), ("heads_q", C.c_int32), ("seq_kv", C.c_int32),
                 ("dim_qk", C.c_int32), ("dim_v", C.c_int32)]
@@ -328,6 +340,34 @@ def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
     a.workspace, a.workspace_bytes = ws.data_ptr(), need
     with torch.cuda.device(q.device):
         check(lib.attn_b200_softmax_bwd(C.byref(a), current_stream_ptr()), "attn_b200_softmax_bwd")
+    return dq, dk, dv
+
+
+def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=()):
+    """(dq, dk, dv) of an elementwise program through its functor library's ``attn_b200_elementwise_bwd_jit`` (``fn``);
+    ``custom``: the program's fp32 scalar inputs, as device tensors."""
+    for t in (q, k, v, d_o, *custom):
+        if not t.is_cuda:
+            raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
+    if d_o.stride(-1) != 1:
+        d_o = d_o.contiguous()
+    if q.dtype not in DTYPE_CODES or any(t.dtype != q.dtype for t in (k, v, d_o)):
+        raise NativeError("q, k, v, d_o must share dtype float16 or bfloat16")
+    dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))
+    custom = [t.to(device=q.device, dtype=torch.float32).contiguous() for t in custom]
+    a = ElementwiseBwdArgs()
+    a.q, a.k, a.v, a.d_o = (t.data_ptr() for t in (q, k, v, d_o))
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    B, Sq, H, D = q.shape
+    a.batch, a.heads, a.heads_kv, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, k.shape[2], Sq, k.shape[1], D, v.shape[3]
+    a.dtype, a.mask_kind = DTYPE_CODES[q.dtype], mask_kind
+    for name, t in (("q", q), ("k", k), ("v", v), ("do", d_o), ("dq", dq), ("dk", dk), ("dv", dv)):
+        getattr(a, name + "_stride")[:] = _strides_bsh(t)
+    for i, t in enumerate(custom):
+        a.custom[i] = t.data_ptr()
+    with torch.cuda.device(q.device):
+        status = device_status_word(q.device.index)
+        check(fn(C.byref(a), current_stream_ptr(), status), "attn_b200_elementwise_bwd_jit")
     return dq, dk, dv
 
 

@@ -192,6 +192,21 @@ def main():
         torch.save(rec, os.path.join(HERE, f"{name}.pt"))
         print(name, tuple(rec["dq"].shape), f"{4 * rec['dq'].numel() * 4 / 1024:.0f} KiB")
 
+    # gradients of sigmoid attention (an elementwise program): autograd through the reference's closure
+    # (testing/test.py:519-543) with respect to q, k, v
+    ref = extract(tree, source, "test_sigmoid_attention", "ref")
+    B, H, S, D, bias = 1, 2, 144, 128, -3.0
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 121)
+    d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(1121)).to(torch.bfloat16)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        o = ref(qf * (D ** -0.5), kf, vf, torch.tensor([bias]), causal=True)
+        o.backward(d_o.float())
+    rec = dict(shape=(B, H, S, D, D), seed=121, bias=bias, causal=True, d_o=d_o, o=o.detach().contiguous(),
+               dq=qf.grad.contiguous(), dk=kf.grad.contiguous(), dv=vf.grad.contiguous())
+    torch.save(rec, os.path.join(HERE, "sigmoid_bwd.pt"))
+    print("sigmoid_bwd", tuple(rec["dq"].shape))
+
     # gradients of RetNet retention: autograd through the reference's closure (testing/test.py:738-747)
     ref = extract(tree, source, "test_retnet_recurrent", "ref")
     B, H, S, Dk, Dv = 1, 2, 160, 64, 128

@@ -17,13 +17,14 @@ MAX_ABS, MEAN_ABS = 2e-2, 2e-3
 
 
 def check(got, want, what):
-    """max-abs 2e-2 and mean-abs 2e-3, the first scaled by the largest magnitude of the expected tensor where that
-    exceeds 1 (a 16-bit result of magnitude m carries a rounding error of up to m * 2^-9 by itself; gradients summed
-    over a group of heads or with the larger scale of head dim 64 reach 3-4)."""
+    """max-abs 2e-2 and mean-abs 2e-3, scaled by the magnitude of the expected tensor where that exceeds 1: the
+    maximum by its largest value, the mean by 1.5 x its standard deviation (rounding a result of standard deviation s to
+    bf16 costs a mean-abs error of 2.2e-3 s by itself; gradients summed over a group of heads, over hundreds of
+    un-normalised sigmoid weights, or with the larger scale of head dim 64 have s = 2-4)."""
     d = (got.float().cpu() - want.float()).abs()
     assert torch.isfinite(got).all(), what
     assert d.max().item() <= MAX_ABS * max(1.0, want.abs().max().item()), (what, d.max().item(), want.abs().max().item())
-    assert d.mean().item() <= MEAN_ABS, (what, d.mean().item())
+    assert d.mean().item() <= MEAN_ABS * max(1.0, 1.5 * want.std().item()), (what, d.mean().item(), want.std().item())
 
 
 def native_forward(q, k, v, causal, scale):
@@ -136,3 +137,64 @@ def test_argument_errors():
     assert lib.load_library().attn_b200_softmax_bwd_workspace_bytes(None) == -1
     assert lib.load_library().attn_b200_softmax_bwd(None, None) != 0
     assert lib.load_library().attn_b200_softmax_bwd(a, None) != 0   # null tensors
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# elementwise programs: the backward functor is derived from the traced score_mod and compiled on first use
+# ---------------------------------------------------------------------------------------------------------------
+
+def test_sigmoid_attention_against_reference_golden():
+    """examples/sigmoid_attn.py differentiated: gradients of the reference's own closure (testing/test.py:519-543) by
+    torch autograd, committed as tests/golden/sigmoid_bwd.pt."""
+    from examples_b200 import programs
+    g = torch.load(os.path.join(GOLD, "sigmoid_bwd.pt"))
+    B, H, S, D, Dv = g["shape"]
+    q, k, v = inputs.attention_bshd(B, H, S, D, Dv, g["seed"])
+    eng = programs.sigmoid_engine(B, H, S, D, Dv, is_causal=g["causal"], scale=D ** -0.5)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qc, kc, vc, torch.tensor([g["bias"]]).cuda())
+    o.backward(g["d_o"].cuda())
+    torch.cuda.synchronize()
+    check(o.detach(), g["o"], "o")
+    check(qc.grad, g["dq"], "dq")
+    check(kc.grad, g["dk"], "dk")
+    check(vc.grad, g["dv"], "dv")
+
+
+@pytest.mark.parametrize("causal,S,H,Hkv", [(False, 300, 2, 2), (True, 384, 4, 4)])
+def test_sigmoid_attention_shapes(causal, S, H, Hkv):
+    from examples_b200 import programs
+    B, D = 1, 128
+    g = torch.Generator().manual_seed(S)
+    q = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, generator=g).to(torch.bfloat16)
+    d_o = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    bias = torch.tensor([-2.0])
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        g_ = H // Hkv   # query head h reads KV head h // g_: the shared heads' gradients add up
+        rm.sigmoid_attention(qf * D ** -0.5, kf.repeat_interleave(g_, 2), vf.repeat_interleave(g_, 2), bias, causal).backward(d_o.float())
+    eng = programs.sigmoid_engine(B, H, S, D, D, is_causal=causal, scale=D ** -0.5)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    eng(qc, kc, vc, bias.cuda()).backward(d_o.cuda())
+    torch.cuda.synchronize()
+    for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
+        check(got, want, what)
+
+
+def test_relu_attention():
+    """examples/reluattn.py (relu of the scaled scores, head dim 64): the derivative is a comparison."""
+    from examples_b200 import programs
+    B, H, S, D = 1, 3, 192, 64
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 31, k_scale=0.5, v_scale=0.5)
+    d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(32)).to(torch.bfloat16)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        rm.relu_attention(qf, kf, vf).backward(d_o.float())
+    eng = programs.relu_engine(B, H, S, D, D)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    eng(qc, kc, vc).backward(d_o.cuda())
+    torch.cuda.synchronize()
+    for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
+        check(got, want, what)
