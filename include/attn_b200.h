@@ -156,6 +156,13 @@ typedef struct AttnB200LinearArgs {
                             keep the result in fp32 and for judging the kernel apart from the output rounding
                             (the reference casts its fp32 accumulators to the input dtype, linear_tl.py:398-400) */
   int32_t reserved;
+  const float* v_scale;  /* [batch, heads, seq] fp32 or NULL: a per-token factor on the rows of v, applied inside the
+                            kernel where they are rescaled for the state update anyway (a v_mod of the form
+                            v * t[batch, heads, seq_len], e.g. Mamba2's v * dt: the fused v_mod of the reference's
+                            core/lower/lower_linear.py:211-287) */
+  int32_t heads_q;       /* heads of q, 0 = `heads`: q is [batch, heads_q, seq, dim_qk], and head h of v reads q head
+                            h / (heads / heads_q) (Mamba2's C and B with fewer groups than v heads) */
+  int32_t heads_k;       /* the same for k */
 } AttnB200LinearArgs;
 
 /* Bytes of scratch the linear forward needs: per-row (sum, sum of squares) fp32 when normalize = 1, else 0. */

@@ -85,6 +85,10 @@ def eval_tensor_expr(sym: SymbolScalar, env: dict, memo: dict | None = None):
     return val
 
 
+def _depends_on(sym: SymbolScalar, leaf: SymbolScalar) -> bool:
+    return sym is leaf or any(_depends_on(p, leaf) for p in sym.prev)
+
+
 def _constant_multiple(out: SymbolScalar, leaf: SymbolScalar):
     """If ``out`` is ``leaf * c`` (or ``c * leaf``, ``leaf / c``) for a Python constant c, return c."""
     if out is leaf:
@@ -100,11 +104,12 @@ def _constant_multiple(out: SymbolScalar, leaf: SymbolScalar):
 
 
 def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize: bool = False, eps: float = 1e-5,
-                             out_dtype=None):
+                             out_dtype=None, v_scale=None):
     """q,k: [B,H,T,Dk]; v: [B,H,T,Dv] (fp16/bf16 CUDA); log_decay: [B,H,T] fp32, natural log of the
     per-token decay.  Returns o [B,H,T,Dv] in the input dtype, or in fp32 with ``out_dtype=torch.float32``
     (the kernel's accumulators without the output rounding).  ``normalize`` applies a per-(batch, head,
-    token) normalisation over Dv (zero mean, unit variance, no affine) to the output."""
+    token) normalisation over Dv (zero mean, unit variance, no affine) to the output.  ``v_scale`` [B,H,T] (fp32) is a
+    per-token factor on the rows of v, applied inside the kernel."""
     if out_dtype not in (None, q.dtype, torch.float32):
         raise native.NativeError("out_dtype must be the input dtype or torch.float32")
     f32_out = out_dtype == torch.float32
@@ -112,7 +117,10 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         raise native.NativeError("linear attention needs CUDA tensors")
     if q.dtype not in native.DTYPE_CODES or k.dtype != q.dtype or v.dtype != q.dtype:
         raise native.NativeError("q, k, v must share dtype float16 or bfloat16")
-    B, H, T, Dk = q.shape
+    B, _, T, Dk = q.shape
+    H = v.shape[1]
+    if H % q.shape[1] != 0 or H % k.shape[1] != 0:
+        raise native.NativeError("the heads of v must be a multiple of the heads of q and of k")
     Dv = v.shape[-1]
     if Dv % 128 != 0:
         # the kernel works on 128-column slices of dim_v: a narrower v (Mamba2's head dim 64) is padded with
@@ -120,16 +128,20 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         if normalize:
             raise native.NativeError("normalize needs dim_v to be a multiple of 128")
         pad = 128 - Dv % 128
-        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps, out_dtype)
+        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps, out_dtype, v_scale)
         return o[..., :Dv].contiguous()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     log_decay = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
+    if v_scale is not None:
+        v_scale = v_scale.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
     with torch.cuda.device(q.device):
         o = torch.empty((B, H, T, Dv), dtype=torch.float32 if f32_out else q.dtype, device=q.device)
         a = native.LinearArgs()
         a.dtype_out = native.DTYPE_OUT_FP32 if f32_out else native.DTYPE_OUT_SAME
         a.q, a.k, a.v, a.log_decay, a.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), log_decay.data_ptr(), o.data_ptr()
+        a.v_scale = v_scale.data_ptr() if v_scale is not None else None
         a.batch, a.heads, a.seq, a.dim_qk, a.dim_v = B, H, T, Dk, Dv
+        a.heads_q, a.heads_k = q.shape[1], k.shape[1]
         a.dtype = native.DTYPE_CODES[q.dtype]
         a.normalize = 1 if normalize else 0
         a.q_scale = float(q_scale)
@@ -260,6 +272,17 @@ class LinearAttentionEngine:
             if c is not None:
                 self.q_scale = c
                 self._mods["q"] = None
+        # v_mod = v * t with t free of v (Mamba2: v * dt[batch, heads, seq_len]): the factor goes into the kernel, which
+        # rescales the rows of v anyway, instead of a whole-tensor multiply before it (the fused v_mod of the
+        # reference, core/lower/lower_linear.py:211-287)
+        self._v_scale_expr = None
+        vm = self._mods["v"]
+        if vm is not None and vm.code.type == "Mul" and len(vm.prev) == 2:
+            a, b = vm.prev
+            other = b if a is self._leaves["v"] else a if b is self._leaves["v"] else None
+            if other is not None and not _depends_on(other, self._leaves["v"]):
+                self._v_scale_expr = other
+                self._mods["v"] = None
         self.attention = self._run
 
     def _apply(self, name, tensor, custom_env):
@@ -274,7 +297,7 @@ class LinearAttentionEngine:
     def has_backward(self) -> bool:
         """Gradients with respect to q, k, v flow when no mod rewrites them (a constant factor on q has been folded
         into the kernel's scale) and the output is not normalised."""
-        return all(self._mods[n] is None for n in ("q", "k", "v")) and not self.normalize_output
+        return all(self._mods[n] is None for n in ("q", "k", "v")) and self._v_scale_expr is None and not self.normalize_output
 
     def _run(self, q, k, v, decay, *custom):
         if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
@@ -290,16 +313,21 @@ class LinearAttentionEngine:
         q = self._apply("q", q, cenv)
         k = self._apply("k", k, cenv)
         v = self._apply("v", v, cenv)
+        v_scale = None
+        if self._v_scale_expr is not None:
+            t = eval_tensor_expr(self._v_scale_expr, cenv)
+            t = t if isinstance(t, torch.Tensor) else torch.tensor(float(t), device=v.device)
+            if t.dim() <= 3 and (t.dim() < 3 or t.shape[-1] in (1, v.shape[2])):
+                v_scale = t.reshape(t.shape + (1,) * (3 - t.dim())) if t.dim() < 3 else t   # leading axes: batch, heads, token
+            else:   # a factor with a feature axis: no per-token scalar, multiply before the kernel
+                f, g = _align(v.float(), t)
+                v = (f * g).to(v.dtype)
         log_decay = self._apply("decay", decay.float(), cenv)
         B, _, T, _ = q.shape
         H = v.shape[1]
         # fewer q / k heads than v heads: each group serves H / HQ consecutive heads (the grouping of the
-        # Mamba2 reference, testing/test.py:222,271)
-        if q.shape[1] != H:
-            q = q.repeat_interleave(H // q.shape[1], dim=1)
-        if k.shape[1] != H:
-            k = k.repeat_interleave(H // k.shape[1], dim=1)
-        return linear_attention_forward(q, k, v, log_decay, q_scale=self.q_scale, normalize=self.normalize_output)
+        # Mamba2 reference, testing/test.py:222,271); the kernel reads the shared head, nothing is replicated
+        return linear_attention_forward(q, k, v, log_decay, q_scale=self.q_scale, normalize=self.normalize_output, v_scale=v_scale)
 
     def __call__(self, *args, **kargs):
         return self.attention(*args, **kargs)

@@ -44,8 +44,10 @@ struct LinearParams {
   void* o;                 // [B,H,S,DV] 16-bit
   float* o_f32;            // [B,H,S,DV] fp32 output instead (rows are written straight from registers), or null
   const float* log_decay;  // [B,H,S] natural log of the per-token decay
+  const float* v_scale;    // [B,H,S] per-token factor on the rows of v, or null
   float* stats;            // [B,H,S,2] (sum, sum of squares) over dim_v, or null
   int seq, dim_v, bh;
+  int heads, heads_q, heads_k;   // heads of v; of q and k (divisors of `heads`: consecutive v heads share a q / k head)
   float q_scale;
   int split_p;             // 1: P is written as a 16-bit high part plus a 16-bit remainder (two PV passes)
   int* status;
@@ -127,6 +129,8 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int bh = blockIdx.y;
   const int nblk = (p.seq + T - 1) / T;
   const float* ld_row = p.log_decay + static_cast<long long>(bh) * p.seq;
+  const int b_idx = bh / p.heads, h_idx = bh - b_idx * p.heads;
+  const int bh_q = b_idx * p.heads_q + h_idx / (p.heads / p.heads_q), bh_k = b_idx * p.heads_k + h_idx / (p.heads / p.heads_k);
 
   if (tid == 0) {
     *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -162,11 +166,11 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (lane == 0 && start_ok) {
       auto load_q = [&](int t) {
         mbar_arrive_expect_tx(q_full, L::kQBytes);
-        for (int c = 0; c < KC; ++c) tma_load_3d(sQ + c * (T * 128), &tmQ, q_full, c * 64, t * T, bh);
+        for (int c = 0; c < KC; ++c) tma_load_3d(sQ + c * (T * 128), &tmQ, q_full, c * 64, t * T, bh_q);
       };
       auto load_k = [&](int t) {
         mbar_arrive_expect_tx(k_full, L::kQBytes);
-        for (int c = 0; c < KC; ++c) tma_load_3d(sKh + c * L::kPairBytes, &tmK, k_full, c * 64, t * T, bh);
+        for (int c = 0; c < KC; ++c) tma_load_3d(sKh + c * L::kPairBytes, &tmK, k_full, c * 64, t * T, bh_k);
       };
       auto load_v = [&](int t) {
         mbar_arrive_expect_tx(v_full, L::kVBytes);
@@ -346,16 +350,24 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // another phase of the kernel uses; else it goes to the second buffer (with 256 state columns the upper half of
     // the state copy, free once Q h has run).
     auto rescale_v = [&](int tb, bool in_place) -> bool {
+      // a per-token factor of the caller on v (v_mod = v * t[b, h, token]) rides along: fetched before the wait for V
+      const int tok = tb * T + row;
+      const float vs = (p.v_scale != nullptr && tok < p.seq) ? p.v_scale[static_cast<long long>(bh) * p.seq + tok] : 1.0f;
       const bool v_ok = mbar_wait(v_full, tb & 1, ab, kLinVFull);
       const float* g = g2 + (tb & 1) * T;
-      const float w = fast_exp2(g[T - 1] - g[row]);
-      const uint4* vline = reinterpret_cast<const uint4*>(sV + wg * (T * 128) + row * 128);
+      const float w = fast_exp2(g[T - 1] - g[row]) * vs;
+      uint4* vsrc = reinterpret_cast<uint4*>(sV + wg * (T * 128) + row * 128);
+      const uint4* vline = vsrc;
       uint4* v2line = reinterpret_cast<uint4*>((in_place ? sV + wg * (T * 128) : sV2 + wg * L::kV2Stride) + row * 128);
+      // with strong decay P V reads V itself: the caller's factor then goes onto V in place as well
+      const bool scale_v_too = !in_place && p.v_scale != nullptr;
 #pragma unroll
       for (int q4 = 0; q4 < 8; ++q4) {
         const int piece = (q4 + lane) & 7;
         uint4 x = vline[piece];
+        uint4 y = x;
         uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
+        uint32_t* ys = reinterpret_cast<uint32_t*>(&y);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float lo, hi;
@@ -369,8 +381,10 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             hi = __half2float(h2.y);
           }
           xs[e] = pack2<kBf16>(lo * w, hi * w);
+          if (scale_v_too) ys[e] = pack2<kBf16>(lo * vs, hi * vs);
         }
         v2line[piece] = x;
+        if (scale_v_too) vsrc[piece] = y;
       }
       fence_proxy_async_smem();
       if (tb + 1 < nblk) warp_arrive(v_ready);
@@ -400,7 +414,7 @@ linear_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tc_fence_after_sync();
       }
       // ---- rows of V times their decay factors (mild decay: done in the previous block's tail) ----
-      if (!last && !mild) ok = rescale_v(t, false) && ok;
+      if ((!last || p.v_scale != nullptr) && !mild) ok = rescale_v(t, false) && ok;
       // ---- rows of O = Q h scaled by scale * exp(g_i) ----
       if (t > 0 && !mild) {
         const float f = qs * fast_exp2(gi);
@@ -665,9 +679,10 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   using L = LinearSmem<DK>;
   CUtensorMap tmQ, tmK, tmV, tmO;
   const uint64_t bh = static_cast<uint64_t>(a->batch) * a->heads;
-  int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, bh);
+  const int heads_q = a->heads_q > 0 ? a->heads_q : a->heads, heads_k = a->heads_k > 0 ? a->heads_k : a->heads;
+  int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, static_cast<uint64_t>(a->batch) * heads_q);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_rows3(&tmK, a->k, a->dtype, DK, a->seq, bh);
+  rc = encode_rows3(&tmK, a->k, a->dtype, DK, a->seq, static_cast<uint64_t>(a->batch) * heads_k);
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
@@ -680,9 +695,13 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   p.o = a->o;
   p.o_f32 = f32_out ? static_cast<float*>(a->o) : nullptr;
   p.log_decay = a->log_decay;
+  p.v_scale = a->v_scale;
   p.seq = a->seq;
   p.dim_v = a->dim_v;
   p.bh = static_cast<int>(bh);
+  p.heads = a->heads;
+  p.heads_q = heads_q;
+  p.heads_k = heads_k;
   p.q_scale = a->q_scale;
   // The normalised output has an absolute tolerance whatever the head's scale.  For heads with a fast decay the
   // output is mostly the intra-block part, where the 16-bit rounding of P is the largest error (a CPU model of the
@@ -729,6 +748,8 @@ int attn_b200_linear_fwd(const AttnB200LinearArgs* a, void* cuda_stream) {
   if (a->dtype != ATTN_B200_DTYPE_FP16 && a->dtype != ATTN_B200_DTYPE_BF16) return ATTN_B200_E_INVALID_ARG;
   if (a->dtype_out != ATTN_B200_DTYPE_SAME && a->dtype_out != ATTN_B200_DTYPE_FP32) return ATTN_B200_E_INVALID_ARG;
   if (a->dim_v <= 0 || a->dim_v % b200::kLinDvs != 0) return ATTN_B200_E_UNSUPPORTED;
+  if (a->heads_q < 0 || a->heads_k < 0 || (a->heads_q > 0 && a->heads % a->heads_q != 0) || (a->heads_k > 0 && a->heads % a->heads_k != 0))
+    return ATTN_B200_E_INVALID_ARG;
   if (static_cast<long long>(a->batch) * a->heads > 65535) return ATTN_B200_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
   if (a->normalize) {

@@ -222,3 +222,23 @@ def test_more_chains_than_sms(B, H, S, Dk, Dv, dtype):
         o_one = linear_attention_forward(q[b:b + 1].cuda(), k[b:b + 1].cuda(), v[b:b + 1].cuda(), ld[b:b + 1].cuda(), q_scale=0.25)
         assert torch.equal(o_all[b:b + 1], o_one)
     assert lib.last_device_status() == 0
+
+
+@pytest.mark.parametrize("strong_decay", [False, True])
+def test_per_token_v_scale_inside_the_kernel(strong_decay):
+    """v_scale [B,H,T]: the factor of a v_mod = v * t rides on the kernel's own rescaling of the rows of v.  Both
+    arithmetic forms of a block are covered: mild decay (rescaled rows replace v) and strong decay (the factor goes onto
+    v in place, the decayed copy beside it), with a ragged last block."""
+    from attn_engine.linear_attn_engine import linear_attention_forward
+    B, H, S, D, Dv = 1, 4, 300, 64, 128
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16)
+    k = (torch.randn(B, H, S, D, generator=g) * D ** -0.5).to(torch.bfloat16)
+    v = torch.randn(B, H, S, Dv, generator=g).to(torch.bfloat16)
+    vs = torch.rand(B, H, S, generator=g) + 0.5
+    log_decay = -torch.rand(B, H, S, generator=g) * (1.5 if strong_decay else 0.05)   # 128 tokens x 1.5 nats: far past the mild range
+    o = linear_attention_forward(q.cuda(), k.cuda(), v.cuda(), log_decay.cuda(), q_scale=1.0, v_scale=vs.cuda())
+    torch.cuda.synchronize()
+    assert lib.last_device_status() == 0
+    want = rm.decayed_linear_attention(q, k, v.float() * vs[..., None], log_decay, scale=1.0)
+    check_raw(o, want)
