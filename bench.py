@@ -664,6 +664,17 @@ def run_profile_case(kind, steps, warmup):
         q, kv = [t.cuda() for t in oracle_inputs.mla_inputs(B, H, S, D, Dv, 5)]
         fn = lambda: mla_decode_forward(q, kv, Dv, D ** -0.5)  # noqa: E731
         work = {"bytes": mla_bytes(B, H, S, D, Dv)}
+    elif kind == "backward":
+        from core.native import lib
+        B, H, S, D = 2, 32, 2048, 128        # q, k, v, o, dO, dq, dk, dv: 8 x 33.5 MB = 268 MB
+        q, k, v = [t.cuda() for t in oracle_inputs.attention_bshd(B, H, S, D, D, 6)]
+        d_o = torch.randn(B, S, H, D, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda").to(torch.bfloat16)
+        o = torch.empty_like(q)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device="cuda")
+        lib.parallel_fwd(lib.fill_parallel_args(q, k, v, o, mask_kind=lib.MASK_CAUSAL, functor=lib.FUNCTOR_SOFTMAX,
+                                                fparams=(D ** -0.5,), final_rowscales=[lse]))
+        fn = lambda: lib.softmax_bwd(q, k, v, o, lse, d_o, D ** -0.5, lib.MASK_CAUSAL)  # noqa: E731
+        work = {"flops": 2.5 * attention_flops(B, H, S, D, D, True)}
     else:
         from attn_engine.linear_attn_engine import linear_attention_forward
         B, H, S, Dk, Dv = (5, 8, 2048, 256, 512) if kind == "linear_full_wave" else (2, 8, 4096, 256, 512)   # 252 / 201 MB
@@ -686,7 +697,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--heat-seconds", type=float, default=1.0,
                     help="length of the heat-up (and sustained leg) in front of the timed steps; 0 turns it off (profiler captures)")
-    ap.add_argument("--profile-kernel", choices=["mla", "linear", "linear_full_wave"], default=None,
+    ap.add_argument("--profile-kernel", choices=["mla", "linear", "linear_full_wave", "backward"], default=None,
                     help="run a few launches of one of the other kernel families on a small case and exit (for ncu captures)")
     ap.add_argument("--batch", type=int, default=None,
                     help="shrink the batch of the headline workload (for small profiler captures; not a headline number)")

@@ -294,8 +294,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int hq = kRoleQ ? hx : hx * p.kv_group + it / max(per_head, 1);
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const float l2 = !F::kUsesStats ? 0.0f : kRoleQ ? lse2_r : st_lse[c0 + k];
-          const float dl = !F::kUsesStats ? 0.0f : kRoleQ ? delta_r : st_delta[c0 + k];
+          // KV role: the statistics belong to the columns and sit in shared memory; every lane reads the same four
+          // at a time (one broadcast load per four columns instead of one per column and statistic)
+          float l2 = 0.0f, dl = 0.0f;
+          if constexpr (F::kUsesStats) {
+            if constexpr (kRoleQ) {
+              l2 = lse2_r;
+              dl = delta_r;
+            } else {
+              const float4 l4 = *reinterpret_cast<const float4*>(st_lse + c0 + (k & ~3));
+              const float4 d4 = *reinterpret_cast<const float4*>(st_delta + c0 + (k & ~3));
+              l2 = (k & 3) == 0 ? l4.x : (k & 3) == 1 ? l4.y : (k & 3) == 2 ? l4.z : l4.w;
+              dl = (k & 3) == 0 ? d4.x : (k & 3) == 1 ? d4.y : (k & 3) == 2 ? d4.z : d4.w;
+            }
+          }
           const int q_idx = kRoleQ ? tile * T + row : ys * T + c0 + k;
           const int kv_idx = kRoleQ ? ys * T + c0 + k : tile * T + row;
           float pr, ds;
