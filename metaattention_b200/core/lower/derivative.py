@@ -134,6 +134,7 @@ def emit_backward_functor(tr: TracedParallel, struct_name: str = "UserBwdFunctor
     loads = "\n".join(f"    c.cu[{k}] = *static_cast<const float*>(p.custom[{k}]);" for k in range(len(customs)))
     return f"""struct {struct_name} {{
   static constexpr bool kUsesStats = false;
+  static constexpr bool kNegInfMask = false;
   struct Ctx {{
     float cu[{n}];
   }};

@@ -12,6 +12,7 @@
 // With the KV role the lanes are KV rows and the columns query rows (S^T, dP^T), so that P^T and dS^T are the A
 // operands as they stand.  The functor F supplies
 //   F::kUsesStats            per-query-row statistics (softmax: lse and delta) travel with the query tiles
+//   F::kNegInfMask           P and dS vanish at a score of -inf: masked pairs are given that score
 //   F::Ctx F::make(params)   per-thread constants
 //   F::apply(s, dp, lse2, delta, ctx, b, h, q_idx, kv_idx, p_out, ds_out)
 // softmax_bwd.cu instantiates it for the built-in softmax; lowered score_mod functors (elementwise programs: no row
@@ -310,10 +311,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           const int q_idx = kRoleQ ? tile * T + row : ys * T + c0 + k;
           const int kv_idx = kRoleQ ? ys * T + c0 + k : tile * T + row;
+          // causal: keep kv <= q.  KV role: lanes are KV rows, columns query rows; query role the other way round.
+          // A functor whose P vanishes at a score of -inf (softmax) gets the mask through the score
+          const bool masked = diag && (kRoleQ ? (c0 + k > row) : (c0 + k < row));
           float pr, ds;
-          F::apply(s[k], dp[k], l2, dl, fctx, b, hq, q_idx, kv_idx, pr, ds);
-          // causal: keep kv <= q.  KV role: lanes are KV rows, columns query rows; query role the other way round
-          if (diag && (kRoleQ ? (c0 + k > row) : (c0 + k < row))) pr = ds = 0.0f;
+          F::apply((F::kNegInfMask && masked) ? -INFINITY : s[k], dp[k], l2, dl, fctx, b, hq, q_idx, kv_idx, pr, ds);
+          if (!F::kNegInfMask && masked) pr = ds = 0.0f;
           s[k] = pr;
           dp[k] = ds;
         }
