@@ -144,13 +144,14 @@ def emit_backward_functor(tr: TracedParallel, struct_name: str = "UserBwdFunctor
 {loads}
     return c;
   }}
-  __device__ static void apply(float s, float dp, float, float, const Ctx& c, int b, int h, int q_idx, int kv_idx, float& p_out,
-                               float& ds_out) {{
+  __device__ static void score(float s, float, const Ctx& c, int b, int h, int q_idx, int kv_idx, float& p_out, float& g_out) {{
     (void)b; (void)h; (void)q_idx; (void)kv_idx; (void)c;
 {body}
     p_out = {v};
-    ds_out = dp * {d if d is not None else '0.0f'};
+    g_out = {d if d is not None else '0.0f'};
   }}
+  __device__ static float grad(float g, float dp, float, const Ctx&) {{ return dp * g; }}
+  __device__ static float out_scale(const Ctx&) {{ return 1.0f; }}
 }};
 """
 

@@ -4,7 +4,7 @@
 //   dV = P^T dO,   dP = dO V^T,   dS = dP o dP/dS,   dK = dS^T Q,   dQ = dS K
 //
 // One kernel template in two roles.  A CTA keeps one 128-row tile pair resident (X: K_j, V_j or Q_i, dO_i) and streams
-// the other (Y: Q_i, dO_i or K_j, V_j) through a two-stage TMA ring.  Per streamed tile:
+// the other (Y1: Q_i or K_j through a three-stage TMA ring, Y2: dO_i or V_j through a two-stage one).  Per streamed tile:
 //   S  = X1 Y1^T, dP = X2 Y2^T           tcgen05 SS, fp32 in tensor memory (columns [0,128) and [128,256))
 //   row threads (thread = TMEM lane x column half): P and dS as 16-bit pairs
 //   acc1 += P  Y2   (dV; KV role only)    tcgen05 TS, A from tensor memory, B = the streamed tile MN-major
@@ -14,9 +14,19 @@
 //   F::kUsesStats            per-query-row statistics (softmax: lse and delta) travel with the query tiles
 //   F::kNegInfMask           P and dS vanish at a score of -inf: masked pairs are given that score
 //   F::Ctx F::make(params)   per-thread constants
-//   F::apply(s, dp, lse2, delta, ctx, b, h, q_idx, kv_idx, p_out, ds_out)
+//   F::score(s, lse2, ctx, b, h, q_idx, kv_idx, p_out, g_out)   P, and the factor g that turns dP into dS
+//   F::grad(g, dp, delta, ctx)                                   dS without its constant factor
+//   F::out_scale(ctx)                                            the constant factor, applied to the finished dK, dQ rows
 // softmax_bwd.cu instantiates it for the built-in softmax; lowered score_mod functors (elementwise programs: no row
 // scales) get a library of their own, compiled from the forward-mode derivative of the traced expression.
+//
+// The tensor pipe executes in issue order, and both roles lean on that to keep it and the row threads busy at once:
+//   KV role   ... dV(i) | S(i+1) | dK(i) | dP(i+1) ...   row threads: P(i) from S(i), then dS(i) from dP(i)
+//             S(i+1) overwrites P(i) behind dV(i), dP(i+1) overwrites dS(i) behind dK(i); while the rows turn dP(i)
+//             into dS(i) the pipe computes dV(i) and S(i+1), while they turn S(i+1) into P(i+1) it computes dK(i)
+//             and dP(i+1).
+//   Q role    ... S(i+1), dP(i+1) | dQ(i) ...            dS sits in two buffers of its own (the role has no second
+//             accumulator), so S, dP of the next tile are issued once the rows hold this tile's in registers.
 #pragma once
 
 #include <cstring>
@@ -31,6 +41,8 @@ namespace b200 {
 constexpr int kBwdT = 128;                // rows of a tile, both ways
 constexpr int kBwdRowThreads = 256;       // eight warps: one TMEM lane each, two column halves
 constexpr int kBwdThreads = kBwdRowThreads + 64;   // plus the loading warp and the MMA-issuing warp
+constexpr int kBwdStages1 = 3;            // ring of Y1 (read by the first and by the last MMA of its tile)
+constexpr int kBwdStages2 = 2;            // ring of Y2
 
 struct BwdParams {
   const void* custom[ATTN_B200_MAX_CUSTOM];   // device pointers of the functor's custom inputs (lowered functors)
@@ -47,8 +59,21 @@ struct BwdParams {
   int* status;
 };
 
-enum BwdWaitSite { kBwdXFull = 61, kBwdYFull, kBwdYEmpty, kBwdSDone, kBwdPReady, kBwdAccDone, kBwdSdpFree };
-enum BwdBarrier { kBarXFull = 0, kBarYFull0, kBarYFull1, kBarYEmpty0, kBarYEmpty1, kBarSDone, kBarPReadyB, kBarAccDone, kBarSdpFree, kNumBwdBarriers };
+enum BwdWaitSite { kBwdXFull = 61, kBwdYFull, kBwdYEmpty, kBwdSDone, kBwdPReady, kBwdAccDone, kBwdSdpFree, kBwdDpDone, kBwdDsReady, kBwdSmemAlign };
+enum BwdBarrier {
+  kBarXFull = 0,
+  kBarY1Full,                               // kBwdStages1 of them
+  kBarY1Empty = kBarY1Full + kBwdStages1,
+  kBarY2Full = kBarY1Empty + kBwdStages1,   // kBwdStages2 of them
+  kBarY2Empty = kBarY2Full + kBwdStages2,
+  kBarSDone = kBarY2Empty + kBwdStages2,
+  kBarDpDone,
+  kBarPReadyB,
+  kBarDsReady,
+  kBarAccDone,
+  kBarSdpFree,
+  kNumBwdBarriers
+};
 
 template <int D>
 struct BwdSmem {
@@ -56,13 +81,15 @@ struct BwdSmem {
   static constexpr int kChunkBytes = kBwdT * 128;
   static constexpr int kOffX1 = 0;
   static constexpr int kOffX2 = kOffX1 + kTileBytes;
-  static constexpr int kOffY = kOffX2 + kTileBytes;           // [2 stages][Y1, Y2]
-  static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kOffStats = kOffY + 2 * kStageBytes;   // [2 stages][lse2[128], delta[128]] fp32 (KV role)
-  static constexpr int kStatsBytes = 2 * kBwdT * 4;
-  static constexpr int kOffBar = kOffStats + 2 * kStatsBytes;
+  static constexpr int kOffY1 = kOffX2 + kTileBytes;                   // [kBwdStages1] tiles
+  static constexpr int kOffY2 = kOffY1 + kBwdStages1 * kTileBytes;     // [kBwdStages2] tiles
+  static constexpr int kOffLse = kOffY2 + kBwdStages2 * kTileBytes;    // [kBwdStages1][128] fp32, with Y1 (KV role)
+  static constexpr int kStatBytes = kBwdT * 4;
+  static constexpr int kOffDelta = kOffLse + kBwdStages1 * kStatBytes; // [kBwdStages2][128] fp32, with Y2 (KV role)
+  static constexpr int kOffBar = kOffDelta + kBwdStages2 * kStatBytes;
   static constexpr int kOffMisc = kOffBar + 8 * kNumBwdBarriers;
-  static constexpr int kBytes = kOffMisc + 16 + 1024;
+  static constexpr int kBytes = kOffMisc + 16;                // the dynamic shared memory is declared 1024-byte aligned
+  static_assert(kBytes <= 232448, "shared memory layout exceeds an SM");
 };
 
 // plain (untiled) bulk copy global -> shared, counted on an mbarrier; both addresses 16-byte aligned, bytes % 16 == 0
@@ -74,30 +101,35 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 
 // kRoleQ = false: CTA = (KV tile, KV head, batch), streams the query tiles (of every query head of its group) and
 // writes dK, dV.  kRoleQ = true: CTA = (query tile, query head, batch), streams the KV tiles and writes dQ.
-// Tensor memory: S [0,128), dP [128,256), accumulator 1 [256,384) (dV or dQ), accumulator 2 [384,512) (dK).
-// The query role has no second accumulator: it writes dS to two alternating 64-column buffers there instead of over
-// dP, so that S and dP of the next tile can be computed as soon as the row threads hold this tile's in registers.
+// Tensor memory: S [0,128), dP [128,256), accumulator 1 [256,384) (dV or dQ), accumulator 2 [384,512) (dK; the
+// query role's two dS buffers).  KV role: P is written over S, dS over dP.
 template <class F, bool kRoleQ, bool kBf16, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr int T = kBwdT, KC = D / 64, HALF = D / 2;   // chunks of a tile; columns of an accumulator row per warp group
+  constexpr int N1 = kBwdStages1, N2 = kBwdStages2;
   static_assert(D == 64 || D == 128, "head dims 64 and 128");
   constexpr uint32_t kTmemCols = 512, kColS = 0, kColDP = 128, kColA = 256, kColB = 384, kColDS = 384;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sX1 = smem + L::kOffX1;
   uint8_t* sX2 = smem + L::kOffX2;
-  uint8_t* sY = smem + L::kOffY;
-  float* sStats = reinterpret_cast<float*>(smem + L::kOffStats);
+  uint8_t* sY1 = smem + L::kOffY1;
+  uint8_t* sY2 = smem + L::kOffY2;
+  float* sLse = reinterpret_cast<float*>(smem + L::kOffLse);
+  float* sDelta = reinterpret_cast<float*>(smem + L::kOffDelta);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
   uint64_t* x_full = bars + kBarXFull;
-  uint64_t* y_full = bars + kBarYFull0;
-  uint64_t* y_empty = bars + kBarYEmpty0;
+  uint64_t* y1_full = bars + kBarY1Full;
+  uint64_t* y1_empty = bars + kBarY1Empty;
+  uint64_t* y2_full = bars + kBarY2Full;
+  uint64_t* y2_empty = bars + kBarY2Empty;
   uint64_t* s_done = bars + kBarSDone;
+  uint64_t* dp_done = bars + kBarDpDone;
   uint64_t* p_ready = bars + kBarPReadyB;
+  uint64_t* ds_ready = bars + kBarDsReady;
   uint64_t* acc_done = bars + kBarAccDone;
   uint64_t* sdp_free = bars + kBarSdpFree;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kOffMisc);
@@ -115,13 +147,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (tid == 0) {
     *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    // the operand tiles use the 128-byte swizzle, whose pattern repeats every 1024 bytes of the shared window
+    if ((smem_u32(smem) & 1023u) != 0) {
+      *abort_flag = 1;
+      atomicCAS(p.status, 0, kStatusTimeoutBase + kBwdSmemAlign);
+    }
     mbar_init(x_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(y_full + i, 1);
-      mbar_init(y_empty + i, 1);
+    for (int i = 0; i < N1; ++i) {
+      mbar_init(y1_full + i, 1);
+      mbar_init(y1_empty + i, 1);
+    }
+    for (int i = 0; i < N2; ++i) {
+      mbar_init(y2_full + i, 1);
+      mbar_init(y2_empty + i, 1);
     }
     mbar_init(s_done, 1);
+    mbar_init(dp_done, 1);
     mbar_init(p_ready, kBwdRowThreads / 32);
+    mbar_init(ds_ready, kBwdRowThreads / 32);
     mbar_init(acc_done, 1);
     mbar_init(sdp_free, kBwdRowThreads / 32);
     fence_barrier_init();
@@ -154,30 +197,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(y_empty + st, ((it >> 1) & 1) ^ 1, ab, kBwdYEmpty)) break;
-        uint8_t* y1 = sY + st * L::kStageBytes;
-        uint8_t* y2 = y1 + L::kTileBytes;
-        if constexpr (kRoleQ) {
-          mbar_arrive_expect_tx(y_full + st, 2 * L::kTileBytes);
-          const int hk = hx / p.kv_group;
-          for (int c = 0; c < KC; ++c) {
-            tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y_full + st, c * 64, it * T, hk, b, p.ok);
-            tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y_full + st, c * 64, it * T, hk, b, p.ov);
-          }
-        } else {
-          mbar_arrive_expect_tx(y_full + st, 2 * L::kTileBytes + (F::kUsesStats ? L::kStatsBytes : 0));
-          const int hq = hx * p.kv_group + it / per_head, i = i0 + it % per_head;
-          for (int c = 0; c < KC; ++c) {
-            tma_load_rows(y1 + c * L::kChunkBytes, &tmQ, y_full + st, c * 64, i * T, hq, b, p.oq);
-            tma_load_rows(y2 + c * L::kChunkBytes, &tmDO, y_full + st, c * 64, i * T, hq, b, p.odo);
-          }
-          if constexpr (F::kUsesStats) {
-            const long long off = (static_cast<long long>(b) * p.heads + hq) * p.seq_q_pad + i * T;
-            bulk_load(sStats + st * 2 * T, p.lse2 + off, T * 4, y_full + st);
-            bulk_load(sStats + st * 2 * T + T, p.delta + off, T * 4, y_full + st);
+        const int s1 = it % N1, s2 = it % N2;
+        uint8_t* y1 = sY1 + s1 * L::kTileBytes;
+        uint8_t* y2 = sY2 + s2 * L::kTileBytes;
+        // streamed tile: row offset and head in the tensors it comes from
+        const int hk = hx / p.kv_group;
+        const int hq = kRoleQ ? 0 : hx * p.kv_group + it / per_head, i = kRoleQ ? 0 : i0 + it % per_head;
+        const long long stat_off = kRoleQ ? 0 : (static_cast<long long>(b) * p.heads + hq) * p.seq_q_pad + i * T;
+        if (!mbar_wait(y1_empty + s1, ((it / N1) & 1) ^ 1, ab, kBwdYEmpty)) break;
+        mbar_arrive_expect_tx(y1_full + s1, L::kTileBytes + ((!kRoleQ && F::kUsesStats) ? L::kStatBytes : 0));
+        for (int c = 0; c < KC; ++c) {
+          if constexpr (kRoleQ) {
+            tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y1_full + s1, c * 64, it * T, hk, b, p.ok);
+          } else {
+            tma_load_rows(y1 + c * L::kChunkBytes, &tmQ, y1_full + s1, c * 64, i * T, hq, b, p.oq);
           }
         }
+        if constexpr (!kRoleQ && F::kUsesStats) bulk_load(sLse + s1 * T, p.lse2 + stat_off, L::kStatBytes, y1_full + s1);
+        if (!mbar_wait(y2_empty + s2, ((it / N2) & 1) ^ 1, ab, kBwdYEmpty)) break;
+        mbar_arrive_expect_tx(y2_full + s2, L::kTileBytes + ((!kRoleQ && F::kUsesStats) ? L::kStatBytes : 0));
+        for (int c = 0; c < KC; ++c) {
+          if constexpr (kRoleQ) {
+            tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y2_full + s2, c * 64, it * T, hk, b, p.ov);
+          } else {
+            tma_load_rows(y2 + c * L::kChunkBytes, &tmDO, y2_full + s2, c * 64, i * T, hq, b, p.odo);
+          }
+        }
+        if constexpr (!kRoleQ && F::kUsesStats) bulk_load(sDelta + s2 * T, p.delta + stat_off, L::kStatBytes, y2_full + s2);
       }
     }
   } else if (warp == kBwdRowThreads / 32 + 1) {
@@ -188,68 +234,83 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint64_t kChunk = L::kChunkBytes >> 4;
       const uint64_t x1_desc = make_smem_desc(smem_u32(sX1), 16, 1024), x2_desc = make_smem_desc(smem_u32(sX2), 16, 1024);
       bool ok = mbar_wait_poll(x_full, 0, ab, kBwdXFull);
-      auto stage_descs = [&](int st, uint64_t& y1_desc, uint64_t& y2_desc, uint64_t& y1_mn, uint64_t& y2_mn) {
-        const uint32_t y1a = smem_u32(sY + st * L::kStageBytes), y2a = y1a + L::kTileBytes;
-        y1_desc = make_smem_desc(y1a, 16, 1024);
-        y2_desc = make_smem_desc(y2a, 16, 1024);
-        y1_mn = make_smem_desc(y1a, L::kChunkBytes, 1024);
-        y2_mn = make_smem_desc(y2a, L::kChunkBytes, 1024);
-      };
-      auto issue_s_dp = [&](uint64_t y1_desc, uint64_t y2_desc) {
+      // S(it) = X1 Y1(it)^T and dP(it) = X2 Y2(it)^T, each behind the arrival of its streamed tile
+      auto issue_s = [&](int it) -> bool {
+        const int s1 = it % N1;
+        if (!mbar_wait_poll(y1_full + s1, (it / N1) & 1, ab, kBwdYFull)) return false;
+        tc_fence_after_sync();
+        const uint64_t y1_desc = make_smem_desc(smem_u32(sY1 + s1 * L::kTileBytes), 16, 1024);
 #pragma unroll
         for (int ch = 0; ch < KC; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColS, x1_desc + ch * kChunk, y1_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
+        return true;
+      };
+      auto issue_dp = [&](int it) -> bool {
+        const int s2 = it % N2;
+        if (!mbar_wait_poll(y2_full + s2, (it / N2) & 1, ab, kBwdYFull)) return false;
+        tc_fence_after_sync();
+        const uint64_t y2_desc = make_smem_desc(smem_u32(sY2 + s2 * L::kTileBytes), 16, 1024);
 #pragma unroll
         for (int ch = 0; ch < KC; ++ch)
           umma_ss_x4<2, 2>(tmem_base + kColDP, x2_desc + ch * kChunk, y2_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
-        umma_commit(s_done);
+        return true;
       };
-      uint64_t y1_desc, y2_desc, y1_mn, y2_mn;
+      // acc += A (16-bit, tensor memory columns a_col...) x streamed tile (MN-major)
+      auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, const uint8_t* y_tile, bool accumulate) {
+        const uint64_t y_mn = make_smem_desc(smem_u32(y_tile), L::kChunkBytes, 1024);
+#pragma unroll
+        for (int g = 0; g < T / 64; ++g)
+          umma_ts_x4<8, 128>(tmem_base + acc_col, tmem_base + a_col + g * 32, y_mn + g * 512, idesc_mn, (accumulate || g > 0) ? 1u : 0u);
+      };
       if constexpr (kRoleQ) {
-        // S, dP of tile it + 1 are issued as soon as the row threads hold those of tile it in registers, ahead of
-        // tile it's accumulating MMA (dS sits in a buffer of its own)
-        if (ok && mbar_wait_poll(y_full, 0, ab, kBwdYFull)) {
+        ok = ok && issue_s(0) && issue_dp(0);
+        if (ok) {
+          umma_commit(y2_empty);
+          umma_commit(s_done);
+        }
+        for (int it = 0; ok && it < n_iter; ++it) {
+          if (it + 1 < n_iter) {
+            // the row threads hold S, dP of tile it in registers: those of tile it + 1 go ahead of tile it's dQ
+            if (!mbar_wait_poll(sdp_free, it & 1, ab, kBwdSdpFree)) break;
+            if (!(issue_s(it + 1) && issue_dp(it + 1))) break;
+            umma_commit(y2_empty + (it + 1) % N2);   // V is read by dP only
+            umma_commit(s_done);
+          }
+          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
           tc_fence_after_sync();
-          stage_descs(0, y1_desc, y2_desc, y1_mn, y2_mn);
-          issue_s_dp(y1_desc, y2_desc);
+          issue_acc(kColA, kColDS + (it & 1) * 64, sY1 + (it % N1) * L::kTileBytes, it > 0);
+          umma_commit(y1_empty + it % N1);
+          if (it + 1 == n_iter) umma_commit(acc_done);
+        }
+      } else {
+        if (ok && issue_s(0)) {
+          umma_commit(s_done);
+          ok = issue_dp(0);
+          if (ok) umma_commit(dp_done);
         } else {
           ok = false;
         }
         for (int it = 0; ok && it < n_iter; ++it) {
-          const int st = it & 1;
-          const uint64_t y1_mn_cur = y1_mn;
-          if (it + 1 < n_iter) {
-            if (!(mbar_wait_poll(y_full + (st ^ 1), ((it + 1) >> 1) & 1, ab, kBwdYFull) && mbar_wait_poll(sdp_free, it & 1, ab, kBwdSdpFree))) break;
-            tc_fence_after_sync();
-            stage_descs(st ^ 1, y1_desc, y2_desc, y1_mn, y2_mn);
-            issue_s_dp(y1_desc, y2_desc);
+          const bool more = it + 1 < n_iter;
+          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
+          tc_fence_after_sync();
+          issue_acc(kColA, kColS, sY2 + (it % N2) * L::kTileBytes, it > 0);    // dV += P^T dO
+          if (more) {
+            if (!issue_s(it + 1)) break;     // over P(it), behind dV(it) in the pipe
+            umma_commit(s_done);
           }
-          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
+          if (!mbar_wait_poll(ds_ready, it & 1, ab, kBwdDsReady)) break;
           tc_fence_after_sync();
-#pragma unroll
-          for (int g = 0; g < T / 64; ++g)
-            umma_ts_x4<8, 128>(tmem_base + kColA, tmem_base + kColDS + st * 64 + g * 32, y1_mn_cur + g * 512, idesc_mn, (it > 0 || g > 0) ? 1u : 0u);
-          umma_commit(y_empty + st);
-          if (it + 1 == n_iter) umma_commit(acc_done);
-        }
-      } else {
-        for (int it = 0; ok && it < n_iter; ++it) {
-          const int st = it & 1;
-          if (!mbar_wait_poll(y_full + st, (it >> 1) & 1, ab, kBwdYFull)) break;
-          tc_fence_after_sync();
-          stage_descs(st, y1_desc, y2_desc, y1_mn, y2_mn);
-          // the pipe runs in issue order: P and dS of the tile before have been consumed when these overwrite them
-          issue_s_dp(y1_desc, y2_desc);
-          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int g = 0; g < T / 64; ++g)
-            umma_ts_x4<8, 128>(tmem_base + kColA, tmem_base + kColS + g * 32, y2_mn + g * 512, idesc_mn, (it > 0 || g > 0) ? 1u : 0u);
-#pragma unroll
-          for (int g = 0; g < T / 64; ++g)
-            umma_ts_x4<8, 128>(tmem_base + kColB, tmem_base + kColDP + g * 32, y1_mn + g * 512, idesc_mn, (it > 0 || g > 0) ? 1u : 0u);
-          umma_commit(y_empty + st);
-          if (it + 1 == n_iter) umma_commit(acc_done);
+          // dO(it) has been read by dV(it); its stage also holds delta(it), which the row threads have now used
+          umma_commit(y2_empty + it % N2);
+          issue_acc(kColB, kColDP, sY1 + (it % N1) * L::kTileBytes, it > 0);   // dK += dS^T Q
+          umma_commit(y1_empty + it % N1);
+          if (more) {
+            if (!issue_dp(it + 1)) break;    // over dS(it), behind dK(it)
+            umma_commit(dp_done);
+          } else {
+            umma_commit(acc_done);
+          }
         }
       }
     }
@@ -266,84 +327,121 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       lse2_r = p.lse2[idx];
       delta_r = p.delta[idx];
     }
+    // P and g of one element.  Causal: keep kv <= q (KV role: lanes are KV rows, columns query rows; query role the
+    // other way round); a functor whose P vanishes at a score of -inf (softmax) gets the mask through the score
+    auto score_of = [&](float s, float l2, bool diag, int ys, int hq, int col, float& pr, float& g) {
+      const int q_idx = kRoleQ ? tile * T + row : ys * T + col;
+      const int kv_idx = kRoleQ ? ys * T + col : tile * T + row;
+      const bool masked = diag && (kRoleQ ? (col > row) : (col < row));
+      F::score((F::kNegInfMask && masked) ? -INFINITY : s, l2, fctx, b, hq, q_idx, kv_idx, pr, g);
+      if (!F::kNegInfMask && masked) pr = g = 0.0f;
+    };
+    // KV role: the statistics belong to the columns and sit in shared memory; every lane reads the same four at a time
+    auto stat_of = [&](const float* base, int k) -> float {
+      const float4 v4 = *reinterpret_cast<const float4*>(base + (k & ~3));
+      return (k & 3) == 0 ? v4.x : (k & 3) == 1 ? v4.y : (k & 3) == 2 ? v4.z : v4.w;
+    };
     bool ok = start_ok;
     for (int it = 0; ok && it < n_iter; ++it) {
-      const int st = it & 1;
-      // the streamed tile index, and whether it meets the resident tile on the diagonal of a causal mask
+      // the streamed tile index, its query head, and whether it meets the resident tile on the diagonal of a causal mask
       const int ys = kRoleQ ? it : i0 + it % max(per_head, 1);
+      const int hq = kRoleQ ? hx : hx * p.kv_group + it / max(per_head, 1);
       const bool diag = p.causal && ys == tile;
-      ok = mbar_wait(y_full + st, (it >> 1) & 1, ab, kBwdYFull);   // the statistics came with the tile
-      ok = mbar_wait(s_done, it & 1, ab, kBwdSDone) && ok;
-      if (!ok) break;
-      tc_fence_after_sync();
-      const float* st_lse = sStats + st * 2 * T;
-      const float* st_delta = st_lse + T;
-      uint32_t pp[32], pds[32];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int c0 = wg * 64 + u * 32;
-        float s[32], dp[32];
-        tmem_ld32f(tS + c0, s);
-        tmem_ld32f(tDP + c0, dp);
-        tmem_wait_ld();
-        if (kRoleQ && u == 1) {   // this tile's S and dP are in registers: the next tile's may be computed
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sdp_free);
-        }
-        // the functor gives P and dS = dP * dP/dS (softmax: through lse and delta) for one element
-        const int hq = kRoleQ ? hx : hx * p.kv_group + it / max(per_head, 1);
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          // KV role: the statistics belong to the columns and sit in shared memory; every lane reads the same four
-          // at a time (one broadcast load per four columns instead of one per column and statistic)
-          float l2 = 0.0f, dl = 0.0f;
-          if constexpr (F::kUsesStats) {
-            if constexpr (kRoleQ) {
-              l2 = lse2_r;
-              dl = delta_r;
-            } else {
-              const float4 l4 = *reinterpret_cast<const float4*>(st_lse + c0 + (k & ~3));
-              const float4 d4 = *reinterpret_cast<const float4*>(st_delta + c0 + (k & ~3));
-              l2 = (k & 3) == 0 ? l4.x : (k & 3) == 1 ? l4.y : (k & 3) == 2 ? l4.z : l4.w;
-              dl = (k & 3) == 0 ? d4.x : (k & 3) == 1 ? d4.y : (k & 3) == 2 ? d4.z : d4.w;
-            }
-          }
-          const int q_idx = kRoleQ ? tile * T + row : ys * T + c0 + k;
-          const int kv_idx = kRoleQ ? ys * T + c0 + k : tile * T + row;
-          // causal: keep kv <= q.  KV role: lanes are KV rows, columns query rows; query role the other way round.
-          // A functor whose P vanishes at a score of -inf (softmax) gets the mask through the score
-          const bool masked = diag && (kRoleQ ? (c0 + k > row) : (c0 + k < row));
-          float pr, ds;
-          F::apply((F::kNegInfMask && masked) ? -INFINITY : s[k], dp[k], l2, dl, fctx, b, hq, q_idx, kv_idx, pr, ds);
-          if (!F::kNegInfMask && masked) pr = ds = 0.0f;
-          s[k] = pr;
-          dp[k] = ds;
-        }
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          pp[u * 16 + k] = pack2<kBf16>(s[2 * k], s[2 * k + 1]);
-          pds[u * 16 + k] = pack2<kBf16>(dp[2 * k], dp[2 * k + 1]);
-        }
-      }
-      // the 16-bit pairs of columns [64 wg, 64 wg + 64) go to 32-bit columns [32 wg, 32 wg + 32), which the other warp
-      // of this lane quarter reads as fp32: both must have their values in registers first
       if constexpr (kRoleQ) {
-        tmem_st32(tmem_base + lane_base + kColDS + st * 64 + wg * 32, pds);
+        ok = mbar_wait(s_done, it & 1, ab, kBwdSDone);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t pds[32];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c0 = wg * 64 + u * 32;
+          float s[32], dp[32];
+          tmem_ld32f(tS + c0, s);
+          tmem_ld32f(tDP + c0, dp);
+          tmem_wait_ld();
+          if (u == 1) {   // this tile's S and dP are in registers: the next tile's may be computed
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sdp_free);
+          }
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            float pr, g;
+            score_of(s[k], lse2_r, diag, ys, hq, c0 + k, pr, g);
+            dp[k] = F::grad(g, dp[k], delta_r, fctx);
+          }
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pds[u * 16 + k] = pack2<kBf16>(dp[2 * k], dp[2 * k + 1]);
+        }
+        tmem_st32(tmem_base + lane_base + kColDS + (it & 1) * 64 + wg * 32, pds);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready);
       } else {
+        // ---- S -> P (and g, kept in registers for the second half) ----
+        if constexpr (F::kUsesStats) ok = mbar_wait(y1_full + it % N1, (it / N1) & 1, ab, kBwdYFull);   // lse came with the tile
+        ok = mbar_wait(s_done, it & 1, ab, kBwdSDone) && ok;
+        if (!ok) break;
+        tc_fence_after_sync();
+        const float* st_lse = sLse + (it % N1) * T;
+        const float* st_delta = sDelta + (it % N2) * T;
+        float g[64];
+        uint32_t pk[32];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c0 = wg * 64 + u * 32;
+          float s[32];
+          tmem_ld32f(tS + c0, s);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            float pr;
+            score_of(s[k], F::kUsesStats ? stat_of(st_lse + c0, k) : 0.0f, diag, ys, hq, c0 + k, pr, g[u * 32 + k]);
+            s[k] = pr;
+          }
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[u * 16 + k] = pack2<kBf16>(s[2 * k], s[2 * k + 1]);
+        }
+        // the 16-bit pairs of columns [64 wg, 64 wg + 64) go to 32-bit columns [32 wg, 32 wg + 32), which the other warp
+        // of this lane quarter reads as fp32: both must have their values in registers first
         tc_fence_before_sync();
         ok = named_sync_and(1 + wq, 64, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        tmem_st32(tS + wg * 32, pp);
-        tmem_st32(tDP + wg * 32, pds);
+        tmem_st32(tS + wg * 32, pk);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready);
+        // ---- dP -> dS, beside the pipe's dV(it) and S(it + 1) ----
+        if constexpr (F::kUsesStats) ok = mbar_wait(y2_full + it % N2, (it / N2) & 1, ab, kBwdYFull);   // delta came with the tile
+        ok = mbar_wait(dp_done, it & 1, ab, kBwdDpDone) && ok;
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c0 = wg * 64 + u * 32;
+          float dp[32];
+          tmem_ld32f(tDP + c0, dp);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) dp[k] = F::grad(g[u * 32 + k], dp[k], F::kUsesStats ? stat_of(st_delta + c0, k) : 0.0f, fctx);
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[u * 16 + k] = pack2<kBf16>(dp[2 * k], dp[2 * k + 1]);
+        }
+        tc_fence_before_sync();
+        ok = named_sync_and(1 + wq, 64, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        tmem_st32(tDP + wg * 32, pk);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_ready);
       }
-      tmem_wait_st();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
     }
-    // ---- epilogue: the accumulators as 16-bit rows ----
+    // ---- epilogue: the accumulators as 16-bit rows (dK and dQ times the functor's constant factor) ----
     if (ok && n_iter > 0) {
       ok = mbar_wait(acc_done, 0, ab, kBwdAccDone);
       tc_fence_after_sync();
@@ -360,6 +458,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const long long* sd = a == 0 ? p.dv_s : p.dk_s;
           base = static_cast<uint16_t*>(a == 0 ? p.dv : p.dk) + b * sd[0] + static_cast<long long>(r) * sd[1] + hx * sd[2];
         }
+        const float f = (kRoleQ || a == 1) ? F::out_scale(fctx) : 1.0f;
         const bool in_range = r < (kRoleQ ? p.seq_q : p.seq_kv);
 #pragma unroll
         for (int u = 0; u < HALF / 32; ++u) {
@@ -377,10 +476,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
               uint4 pk;
-              pk.x = pack2<kBf16>(v[8 * q4 + 0], v[8 * q4 + 1]);
-              pk.y = pack2<kBf16>(v[8 * q4 + 2], v[8 * q4 + 3]);
-              pk.z = pack2<kBf16>(v[8 * q4 + 4], v[8 * q4 + 5]);
-              pk.w = pack2<kBf16>(v[8 * q4 + 6], v[8 * q4 + 7]);
+              pk.x = pack2<kBf16>(v[8 * q4 + 0] * f, v[8 * q4 + 1] * f);
+              pk.y = pack2<kBf16>(v[8 * q4 + 2] * f, v[8 * q4 + 3] * f);
+              pk.z = pack2<kBf16>(v[8 * q4 + 4] * f, v[8 * q4 + 5] * f);
+              pk.w = pack2<kBf16>(v[8 * q4 + 6] * f, v[8 * q4 + 7] * f);
               dst[q4] = pk;
             }
           }

@@ -24,8 +24,8 @@
 
 namespace b200 {
 
-// The built-in softmax: P = exp2(s * scale * log2e - lse2), dS = P (dP - delta) * scale; the preparation pass stores
-// delta already multiplied by the scale, so that the bracket is one FMA.
+// The built-in softmax: P = exp2(s * scale * log2e - lse2), dS = P (dP - delta) * scale; the scale is left to the
+// finished dK and dQ rows.
 struct SoftmaxBwdFunctor {
   static constexpr bool kUsesStats = true;
   static constexpr bool kNegInfMask = true;
@@ -33,20 +33,20 @@ struct SoftmaxBwdFunctor {
     float c2, scale;
   };
   __device__ static Ctx make(const BwdParams& p) { return Ctx{p.scale * 1.4426950408889634f, p.scale}; }
-  __device__ static void apply(float s, float dp, float lse2, float delta_scaled, const Ctx& c, int, int, int, int, float& p_out,
-                               float& ds_out) {
-    p_out = fast_exp2(fmaf(s, c.c2, -lse2));
-    ds_out = p_out * fmaf(dp, c.scale, -delta_scaled);
+  __device__ static void score(float s, float lse2, const Ctx& c, int, int, int, int, float& p_out, float& g_out) {
+    p_out = g_out = fast_exp2(fmaf(s, c.c2, -lse2));
   }
+  __device__ static float grad(float g, float dp, float delta, const Ctx&) { return g * (dp - delta); }
+  __device__ static float out_scale(const Ctx& c) { return c.scale; }
 };
 
-// delta[b,h,s] = scale * sum_d dO[b,s,h,d] * O[b,s,h,d] and lse2 = lse * log2(e), both padded to whole tiles (delta 0,
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d] and lse2 = lse * log2(e), both padded to whole tiles (delta 0,
 // lse2 +inf past the end).  One warp per (b, h, s); attn_tl.py:212-244 of the reference computes the same delta.
 template <bool kBf16>
 __global__ void __launch_bounds__(256) bwd_prepare_kernel(const void* __restrict__ o, const void* __restrict__ d_o,
                                                         const float* __restrict__ lse, float* __restrict__ delta,
                                                         float* __restrict__ lse2, int batch, int heads, int seq_q,
-                                                        int seq_q_pad, int dim_v, float scale, long long o_sb, long long o_ss,
+                                                        int seq_q_pad, int dim_v, long long o_sb, long long o_ss,
                                                         long long o_sh, long long do_sb, long long do_ss, long long do_sh) {
   const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) bwd_prepare_kernel(const void* __restrict
   }
   if (lane == 0) {
     const long long idx = (static_cast<long long>(b) * heads + h) * seq_q_pad + s;
-    delta[idx] = acc * scale;
+    delta[idx] = acc;
     lse2[idx] = s < seq_q ? lse[(static_cast<long long>(b) * heads + h) * seq_q + s] * 1.4426950408889634f : INFINITY;
   }
 }
@@ -91,7 +91,7 @@ int launch_softmax_bwd(const AttnB200SoftmaxBwdArgs* a, const BwdCall& call_in, 
     const long long threads = rows * 32;
     const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
     bwd_prepare_kernel<kBf16><<<blocks, 256, 0, stream>>>(a->o, a->d_o, a->lse, delta, lse2, a->batch, a->heads, a->seq_q, seq_q_pad,
-                                                         a->dim_v, a->scale, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0],
+                                                         a->dim_v, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0],
                                                          a->do_stride[1], a->do_stride[2]);
     if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   }

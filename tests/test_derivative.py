@@ -26,7 +26,7 @@ def test_emitted_functor_of_sigmoid_attention():
     assert "c.cu[0] = *static_cast<const float*>(p.custom[0]);" in src        # the bias, an fp32 scalar
     assert "b200::fast_tanh" in src and "(1.0f - " in src                       # tanh and its derivative 1 - tanh^2
     assert "0.25f" in src                                                       # the scale inside score_mod
-    assert "ds_out = dp * d" in src
+    assert "g_out = d" in src and "return dp * g;" in src
 
 
 def test_programs_with_row_scales_are_refused():
