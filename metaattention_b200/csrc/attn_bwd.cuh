@@ -228,89 +228,79 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == kBwdRowThreads / 32 + 1) {
     // ======================= issuing warp: every MMA =======================
-    if (lane == 0 && start_ok && n_iter > 0) {
+    // The whole warp runs this code converged and one elected lane issues each batch of MMAs with its commits: the
+    // descriptors then live in uniform registers, and a batch leaves at the pipe's rate whatever the row warps do
+    // (issued from inside an `if (lane == 0)` region an MMA with N = 128 took ~90 cycles under load, against the 64
+    // the pipe needs for it).
+    if (__all_sync(0xffffffffu, start_ok) && n_iter > 0) {
       constexpr uint32_t idesc_kk = make_idesc_f16(T, T, kBf16, false, false);      // S, dP: both operands K-major
       constexpr uint32_t idesc_mn = make_idesc_f16(T, D, kBf16, false, true);       // accumulators: B = streamed tile, MN-major
       constexpr uint64_t kChunk = L::kChunkBytes >> 4;
       const uint64_t x1_desc = make_smem_desc(smem_u32(sX1), 16, 1024), x2_desc = make_smem_desc(smem_u32(sX2), 16, 1024);
-      bool ok = mbar_wait_poll(x_full, 0, ab, kBwdXFull);
-      // S(it) = X1 Y1(it)^T and dP(it) = X2 Y2(it)^T, each behind the arrival of its streamed tile
-      auto issue_s = [&](int it) -> bool {
-        const int s1 = it % N1;
-        if (!mbar_wait_poll(y1_full + s1, (it / N1) & 1, ab, kBwdYFull)) return false;
+      auto wait = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait_poll(bar, parity, ab, site));
+      };
+      // out = X Y^T behind the arrival of the streamed tile, then up to two commits
+      auto issue_xy = [&](uint32_t out_col, uint64_t x_desc, const uint8_t* y_tile, uint64_t* full, uint32_t parity, uint64_t* c1,
+                          uint64_t* c2) -> bool {
+        if (!wait(full, parity, kBwdYFull)) return false;
         tc_fence_after_sync();
-        const uint64_t y1_desc = make_smem_desc(smem_u32(sY1 + s1 * L::kTileBytes), 16, 1024);
+        const uint64_t y_desc = make_smem_desc(smem_u32(y_tile), 16, 1024);
+        if (elect_one()) {
 #pragma unroll
-        for (int ch = 0; ch < KC; ++ch)
-          umma_ss_x4<2, 2>(tmem_base + kColS, x1_desc + ch * kChunk, y1_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
-        return true;
-      };
-      auto issue_dp = [&](int it) -> bool {
-        const int s2 = it % N2;
-        if (!mbar_wait_poll(y2_full + s2, (it / N2) & 1, ab, kBwdYFull)) return false;
-        tc_fence_after_sync();
-        const uint64_t y2_desc = make_smem_desc(smem_u32(sY2 + s2 * L::kTileBytes), 16, 1024);
-#pragma unroll
-        for (int ch = 0; ch < KC; ++ch)
-          umma_ss_x4<2, 2>(tmem_base + kColDP, x2_desc + ch * kChunk, y2_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
-        return true;
-      };
-      // acc += A (16-bit, tensor memory columns a_col...) x streamed tile (MN-major)
-      auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, const uint8_t* y_tile, bool accumulate) {
-        const uint64_t y_mn = make_smem_desc(smem_u32(y_tile), L::kChunkBytes, 1024);
-#pragma unroll
-        for (int g = 0; g < T / 64; ++g)
-          umma_ts_x4<8, 128>(tmem_base + acc_col, tmem_base + a_col + g * 32, y_mn + g * 512, idesc_mn, (accumulate || g > 0) ? 1u : 0u);
-      };
-      if constexpr (kRoleQ) {
-        ok = ok && issue_s(0) && issue_dp(0);
-        if (ok) {
-          umma_commit(y2_empty);
-          umma_commit(s_done);
+          for (int ch = 0; ch < KC; ++ch)
+            umma_ss_x4<2, 2>(tmem_base + out_col, x_desc + ch * kChunk, y_desc + ch * kChunk, idesc_kk, ch > 0 ? 1u : 0u);
+          if (c1 != nullptr) umma_commit(c1);
+          if (c2 != nullptr) umma_commit(c2);
         }
+        return true;
+      };
+      auto issue_s = [&](int it, uint64_t* c1) -> bool {
+        return issue_xy(kColS, x1_desc, sY1 + (it % N1) * L::kTileBytes, y1_full + it % N1, (it / N1) & 1, c1, nullptr);
+      };
+      auto issue_dp = [&](int it, uint64_t* c1, uint64_t* c2) -> bool {
+        return issue_xy(kColDP, x2_desc, sY2 + (it % N2) * L::kTileBytes, y2_full + it % N2, (it / N2) & 1, c1, c2);
+      };
+      // acc += A (16-bit, tensor memory columns a_col...) x streamed tile (MN-major), then up to three commits
+      auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, const uint8_t* y_tile, bool accumulate, uint64_t* c0, uint64_t* c1, uint64_t* c2) {
+        const uint64_t y_mn = make_smem_desc(smem_u32(y_tile), L::kChunkBytes, 1024);
+        if (elect_one()) {
+          if (c0 != nullptr) umma_commit(c0);   // for what was issued before this batch
+#pragma unroll
+          for (int g = 0; g < T / 64; ++g)
+            umma_ts_x4<8, 128>(tmem_base + acc_col, tmem_base + a_col + g * 32, y_mn + g * 512, idesc_mn, (accumulate || g > 0) ? 1u : 0u);
+          if (c1 != nullptr) umma_commit(c1);
+          if (c2 != nullptr) umma_commit(c2);
+        }
+      };
+      bool ok = wait(x_full, 0, kBwdXFull);
+      if constexpr (kRoleQ) {
+        ok = ok && issue_s(0, nullptr) && issue_dp(0, y2_empty, s_done);
         for (int it = 0; ok && it < n_iter; ++it) {
           if (it + 1 < n_iter) {
             // the row threads hold S, dP of tile it in registers: those of tile it + 1 go ahead of tile it's dQ
-            if (!mbar_wait_poll(sdp_free, it & 1, ab, kBwdSdpFree)) break;
-            if (!(issue_s(it + 1) && issue_dp(it + 1))) break;
-            umma_commit(y2_empty + (it + 1) % N2);   // V is read by dP only
-            umma_commit(s_done);
+            if (!wait(sdp_free, it & 1, kBwdSdpFree)) break;
+            if (!(issue_s(it + 1, nullptr) && issue_dp(it + 1, y2_empty + (it + 1) % N2, s_done))) break;   // V is read by dP only
           }
-          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
+          if (!wait(p_ready, it & 1, kBwdPReady)) break;
           tc_fence_after_sync();
-          issue_acc(kColA, kColDS + (it & 1) * 64, sY1 + (it % N1) * L::kTileBytes, it > 0);
-          umma_commit(y1_empty + it % N1);
-          if (it + 1 == n_iter) umma_commit(acc_done);
+          issue_acc(kColA, kColDS + (it & 1) * 64, sY1 + (it % N1) * L::kTileBytes, it > 0, nullptr, y1_empty + it % N1,
+                    it + 1 == n_iter ? acc_done : nullptr);
         }
       } else {
-        if (ok && issue_s(0)) {
-          umma_commit(s_done);
-          ok = issue_dp(0);
-          if (ok) umma_commit(dp_done);
-        } else {
-          ok = false;
-        }
+        ok = ok && issue_s(0, s_done) && issue_dp(0, dp_done, nullptr);
         for (int it = 0; ok && it < n_iter; ++it) {
           const bool more = it + 1 < n_iter;
-          if (!mbar_wait_poll(p_ready, it & 1, ab, kBwdPReady)) break;
+          if (!wait(p_ready, it & 1, kBwdPReady)) break;
           tc_fence_after_sync();
-          issue_acc(kColA, kColS, sY2 + (it % N2) * L::kTileBytes, it > 0);    // dV += P^T dO
-          if (more) {
-            if (!issue_s(it + 1)) break;     // over P(it), behind dV(it) in the pipe
-            umma_commit(s_done);
-          }
-          if (!mbar_wait_poll(ds_ready, it & 1, ab, kBwdDsReady)) break;
+          issue_acc(kColA, kColS, sY2 + (it % N2) * L::kTileBytes, it > 0, nullptr, nullptr, nullptr);    // dV += P^T dO
+          if (more && !issue_s(it + 1, s_done)) break;     // over P(it), behind dV(it) in the pipe
+          if (!wait(ds_ready, it & 1, kBwdDsReady)) break;
           tc_fence_after_sync();
           // dO(it) has been read by dV(it); its stage also holds delta(it), which the row threads have now used
-          umma_commit(y2_empty + it % N2);
-          issue_acc(kColB, kColDP, sY1 + (it % N1) * L::kTileBytes, it > 0);   // dK += dS^T Q
-          umma_commit(y1_empty + it % N1);
-          if (more) {
-            if (!issue_dp(it + 1)) break;    // over dS(it), behind dK(it)
-            umma_commit(dp_done);
-          } else {
-            umma_commit(acc_done);
-          }
+          issue_acc(kColB, kColDP, sY1 + (it % N1) * L::kTileBytes, it > 0, y2_empty + it % N2, y1_empty + it % N1,
+                    more ? nullptr : acc_done);   // dK += dS^T Q
+          if (more && !issue_dp(it + 1, dp_done, nullptr)) break;    // over dS(it), behind dK(it)
         }
       }
     }
