@@ -336,7 +336,23 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == kMmaWarp) {
     // =============== MMA issuer ===============
-    if (lane == 0 && n_max > 0 && !*abort_flag) {
+    // The whole warp runs this code converged; one elected lane issues each batch of MMAs with its commit.  The
+    // descriptors then live in uniform registers and a batch leaves at the tensor pipe's rate whatever the functor
+    // warps do: issued from inside an `if (lane == 0)` region an MMA with N = 128 took ~90 cycles beside busy warps,
+    // against the 64 the pipe needs for it.
+    if (n_max > 0 && __all_sync(0xffffffffu, !*abort_flag)) {
+      auto wait = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, ab, site));
+      };
+      auto wait_poll = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait_poll(bar, parity, ab, site));
+      };
+      auto commit2 = [&](uint64_t* c1, uint64_t* c2) {
+        if (elect_one()) {
+          umma_commit(c1);
+          if (c2 != nullptr) umma_commit(c2);
+        }
+      };
       constexpr uint32_t idesc_qk = make_idesc_f16(BM, BN, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(BM, DV, kBf16, false, true);
       // Descriptors are built once; per MMA only the start-address field moves (units of 16 bytes), and four
@@ -347,21 +363,25 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       auto issue_qk = [&](int t, int st) {
         const uint64_t a = q_desc0 + static_cast<uint64_t>(t * (L::kQBytes >> 4));
         const uint64_t bq = k_desc0 + static_cast<uint64_t>(st * (L::kKBytes >> 4));
+        if (elect_one()) {
 #pragma unroll
-        for (int ch = 0; ch < D / 64; ++ch)
-          umma_ss_x4<2, 2>(tmem_base + kColS + t * BN, a + ch * ((BM * 128) >> 4), bq + ch * ((BN * 128) >> 4), idesc_qk, ch > 0 ? 1u : 0u);
-        umma_commit(&s_full[t]);
+          for (int ch = 0; ch < D / 64; ++ch)
+            umma_ss_x4<2, 2>(tmem_base + kColS + t * BN, a + ch * ((BM * 128) >> 4), bq + ch * ((BN * 128) >> 4), idesc_qk, ch > 0 ? 1u : 0u);
+          umma_commit(&s_full[t]);
+        }
       };
       auto issue_pv = [&](int t, int st, bool first) {
         const uint64_t bv = v_desc0 + static_cast<uint64_t>(st * (L::kVBytes >> 4));
+        if (elect_one()) {
 #pragma unroll
-        for (int g = 0; g < BN / 64; ++g)   // 16 KV rows (2048 B) per K step, P advances 8 TMEM columns
-          umma_ts_x4<8, 128>(tmem_base + kColO + t * DV, tmem_base + kColS + t * BN + g * 32, bv + g * 512, idesc_pv,
-                             (!first || g > 0) ? 1u : 0u);
-        umma_commit(&o_done[t]);
+          for (int g = 0; g < BN / 64; ++g)   // 16 KV rows (2048 B) per K step, P advances 8 TMEM columns
+            umma_ts_x4<8, 128>(tmem_base + kColO + t * DV, tmem_base + kColS + t * BN + g * 32, bv + g * 512, idesc_pv,
+                               (!first || g > 0) ? 1u : 0u);
+          umma_commit(&o_done[t]);
+        }
       };
-      bool ok = mbar_wait(&q_full[0], 0, ab, kSiteQFull);
-      ok = ok && mbar_wait(&k_full[0], 0, ab, kSiteKFull);
+      bool ok = wait(&q_full[0], 0, kSiteQFull);
+      ok = ok && wait(&k_full[0], 0, kSiteKFull);
       if constexpr (kSparse) {
         // the same schedule over the union of the two tiles' KV tile sets; a tile takes part in a step when the
         // step's KV tile is in its own set, and its barrier phases count its own tiles
@@ -372,22 +392,22 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_fence_after_sync();
           if (active(0, j)) issue_qk(0, 0);
           if (NT > 1 && act1) {
-            ok = mbar_wait(&q_full[1], 0, ab, kSiteQFull);
+            ok = wait(&q_full[1], 0, kSiteQFull);
             tc_fence_after_sync();
             if (ok && active(1, j)) issue_qk(1, 0);
           }
-          umma_commit(&k_empty[0]);
+          commit2(&k_empty[0], nullptr);
         }
         for (int i = 0; i < n_max && ok; ++i) {
           const int jn = walk.next();
           const int st = i % ST;
           const int stn = (i + 1) % ST;
-          ok = mbar_wait(&v_full[st], (i / ST) & 1, ab, kSiteVFull);
-          if (ok && jn >= 0) ok = mbar_wait(&k_full[stn], ((i + 1) / ST) & 1, ab, kSiteKFull);
+          ok = wait(&v_full[st], (i / ST) & 1, kSiteVFull);
+          if (ok && jn >= 0) ok = wait(&k_full[stn], ((i + 1) / ST) & 1, kSiteKFull);
           if (!ok) break;
           for (int t = 0; t < NT; ++t) {
             if (active(t, j)) {
-              ok = mbar_wait_poll(&p_ready[t], done[t] & 1, ab, kSitePReady);
+              ok = wait_poll(&p_ready[t], done[t] & 1, kSitePReady);
               if (!ok) break;
               tc_fence_after_sync();
               issue_pv(t, st, done[t] == 0);
@@ -396,30 +416,29 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (active(t, jn)) issue_qk(t, stn);
           }
           if (!ok) break;
-          umma_commit(&v_empty[st]);
-          if (jn >= 0) umma_commit(&k_empty[stn]);
+          commit2(&v_empty[st], jn >= 0 ? &k_empty[stn] : nullptr);
           j = jn;
         }
       } else if (ok) {
         tc_fence_after_sync();
         if (active(0, j_min)) issue_qk(0, 0);
         if (NT > 1 && act1) {
-          ok = mbar_wait(&q_full[1], 0, ab, kSiteQFull);
+          ok = wait(&q_full[1], 0, kSiteQFull);
           tc_fence_after_sync();
           if (ok && active(1, j_min)) issue_qk(1, 0);
         }
-        umma_commit(&k_empty[0]);
+        commit2(&k_empty[0], nullptr);
         for (int i = 0; i < n_max && ok; ++i) {
           const int j = j_min + i;
           const int st = i % ST;
           const int stn = (i + 1) % ST;
-          ok = mbar_wait(&v_full[st], (i / ST) & 1, ab, kSiteVFull);
-          if (ok && i + 1 < n_max) ok = mbar_wait(&k_full[stn], ((i + 1) / ST) & 1, ab, kSiteKFull);
+          ok = wait(&v_full[st], (i / ST) & 1, kSiteVFull);
+          if (ok && i + 1 < n_max) ok = wait(&k_full[stn], ((i + 1) / ST) & 1, kSiteKFull);
           if (!ok) break;
           for (int t = 0; t < NT; ++t) {
             if (active(t, j)) {
               // on the serial chain of the tile: polled, a suspended wait wakes up ~150 cycles late
-              ok = mbar_wait_poll(&p_ready[t], (j - j_lo[t]) & 1, ab, kSitePReady);
+              ok = wait_poll(&p_ready[t], (j - j_lo[t]) & 1, kSitePReady);
               if (!ok) break;
               tc_fence_after_sync();
               issue_pv(t, st, j == j_lo[t]);
@@ -428,8 +447,7 @@ parallel_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (active(t, j + 1)) issue_qk(t, stn);
           }
           if (!ok) break;
-          umma_commit(&v_empty[st]);
-          if (i + 1 < n_max) umma_commit(&k_empty[stn]);
+          commit2(&v_empty[st], i + 1 < n_max ? &k_empty[stn] : nullptr);
         }
       }
     }

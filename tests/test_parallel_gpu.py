@@ -182,11 +182,12 @@ def test_full_size_config3_sampled_heads():
 
 
 def test_backward_is_refused_clearly():
-    """Programs whose backward is not built (here a lowered functor: sigmoid attention) say so when differentiated;
-    softmax attention has one (tests/test_bwd_gpu.py)."""
-    B, H, S, D = 1, 1, 128, 64
-    q, k, v = [t.cuda().requires_grad_(True) for t in inputs.attention_bshd(B, H, S, D, D, 1)]
-    o = programs.sigmoid_engine(B, H, S, D, D, is_causal=True)(q, k, v, torch.tensor([-3.0]).cuda())
+    """Programs whose backward is not built (here relu attention on head dims 128 / 256, which the backward kernel does
+    not cover) say so when differentiated; softmax, sigmoid and relu attention on 128 / 128 and 64 / 64 have one
+    (tests/test_bwd_gpu.py)."""
+    B, H, S, D, Dv = 1, 1, 128, 128, 256
+    q, k, v = [t.cuda().requires_grad_(True) for t in inputs.attention_bshd(B, H, S, D, Dv, 1)]
+    o = programs.relu_engine(B, H, S, D, Dv)(q, k, v)
     with pytest.raises(NotImplementedError):
         o.sum().backward()
 
