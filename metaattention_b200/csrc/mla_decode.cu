@@ -339,40 +339,49 @@ mla_split_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant
         }
       }
     } else if (warp == 9) {
-      if (lane == 0 && run) {
+      // The whole warp runs this loop converged and one elected lane issues each batch of twelve MMAs with its
+      // commits: descriptors and loop state then live in uniform registers and a batch leaves at the tensor pipe's
+      // rate (issued from inside an `if (lane == 0)` region an MMA with N = 128 took ~90 cycles beside the busy
+      // softmax warps, against the 64 the pipe needs for it: 36 of them per tile).
+      if (__all_sync(0xffffffffu, run)) {
         constexpr uint32_t idesc = make_idesc_f16(M, N, kBf16, false, false);
         const uint64_t chunk_desc0 = make_smem_desc(smem_u32(sChunk), 16, 1024);
         const uint64_t qr_desc0 = make_smem_desc(smem_u32(sQr), 16, 1024);
+        auto wait = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+          return __all_sync(0xffffffffu, mbar_wait(bar, parity, ab, site));
+        };
         MlaWalk walk = make_walk();
         MlaUnit unit;
         int J = 0;
         bool ok = true;
         for (int ui = 0; ok && walk.next(unit); ++ui, J += unit.n) {
-        ok = mbar_wait(&bars[L::kQReady], ui & 1, ab, kMlaQReady) && mbar_wait(&bars[L::kQrFull], ui & 1, ab, kMlaQrFull);
+        ok = wait(&bars[L::kQReady], ui & 1, kMlaQReady) && wait(&bars[L::kQrFull], ui & 1, kMlaQrFull);
         for (int jl = 0; jl < unit.n && ok; ++jl) {
           const int j = J + jl;
           const int buf = j & 1;
-          ok = mbar_wait(&bars[L::kSFree + buf], ((j >> 1) & 1) ^ 1, ab, kMlaSFree);
+          ok = wait(&bars[L::kSFree + buf], ((j >> 1) & 1) ^ 1, kMlaSFree);
           for (int u = 0; u < 3 && ok; ++u) {
             const int g = j * 3 + u, slot = g % L::kScoreSlots;
-            ok = mbar_wait(&bars[L::kSlotFull + slot], (g / L::kScoreSlots) & 1, ab, kMlaSlotFull);
+            ok = wait(&bars[L::kSlotFull + slot], (g / L::kScoreSlots) & 1, kMlaSlotFull);
             if (!ok) break;
             tc_fence_after_sync();
             // three 64-column chunks, four K steps each: operands advance by 32 bytes (A: 8 TMEM columns);
-            // one barrier check and one commit per twelve MMAs keep the issuing lane's overhead small
+            // one barrier check and one commit per twelve MMAs
             const uint64_t bdesc = chunk_desc0 + static_cast<uint64_t>(slot * (L::kSlotBytes >> 4));
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < 3; ++k) {
-              const int c = u * 3 + k;
-              const uint64_t bd = bdesc + static_cast<uint64_t>(k * (L::kChunkBytes >> 4));
-              if (c < 8)
-                umma_ts_x4<8, 2>(tmem_base + kColS + buf * N, tmem_base + kColQ + c * 32, bd, idesc, c > 0 ? 1u : 0u);
-              else
-                umma_ss_x4<2, 2>(tmem_base + kColS + buf * N, qr_desc0, bd, idesc, 1u);
+              for (int k = 0; k < 3; ++k) {
+                const int c = u * 3 + k;
+                const uint64_t bd = bdesc + static_cast<uint64_t>(k * (L::kChunkBytes >> 4));
+                if (c < 8)
+                  umma_ts_x4<8, 2>(tmem_base + kColS + buf * N, tmem_base + kColQ + c * 32, bd, idesc, c > 0 ? 1u : 0u);
+                else
+                  umma_ss_x4<2, 2>(tmem_base + kColS + buf * N, qr_desc0, bd, idesc, 1u);
+              }
+              umma_commit(&bars[L::kSlotEmpty + slot]);
+              if (u == 2) umma_commit(&bars[L::kSFull + buf]);
             }
-            umma_commit(&bars[L::kSlotEmpty + slot]);
           }
-          if (ok) umma_commit(&bars[L::kSFull + buf]);
         }
         }
       }
