@@ -155,7 +155,9 @@ typedef struct AttnB200LinearArgs {
                             [batch, heads, seq, dim_v] fp32 -- the accumulators as they are, for callers that
                             keep the result in fp32 and for judging the kernel apart from the output rounding
                             (the reference casts its fp32 accumulators to the input dtype, linear_tl.py:398-400) */
-  int32_t reserved;
+  int32_t precise;       /* 1: the decayed scores of a block enter P V as a 16-bit value plus a 16-bit remainder (two
+                            passes) instead of one 16-bit value, as the normalised output does anyway: for runs whose
+                            results are subtracted from one another afterwards (the gradient of the log-decays) */
   const float* v_scale;  /* [batch, heads, seq] fp32 or NULL: a per-token factor on the rows of v, applied inside the
                             kernel where they are rescaled for the state update anyway (a v_mod of the form
                             v * t[batch, heads, seq_len], e.g. Mamba2's v * dt: the fused v_mod of the reference's

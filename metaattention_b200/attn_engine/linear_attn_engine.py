@@ -104,12 +104,13 @@ def _constant_multiple(out: SymbolScalar, leaf: SymbolScalar):
 
 
 def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize: bool = False, eps: float = 1e-5,
-                             out_dtype=None, v_scale=None):
+                             out_dtype=None, v_scale=None, precise: bool = False):
     """q,k: [B,H,T,Dk]; v: [B,H,T,Dv] (fp16/bf16 CUDA); log_decay: [B,H,T] fp32, natural log of the
     per-token decay.  Returns o [B,H,T,Dv] in the input dtype, or in fp32 with ``out_dtype=torch.float32``
     (the kernel's accumulators without the output rounding).  ``normalize`` applies a per-(batch, head,
     token) normalisation over Dv (zero mean, unit variance, no affine) to the output.  ``v_scale`` [B,H,T] (fp32) is a
-    per-token factor on the rows of v, applied inside the kernel."""
+    per-token factor on the rows of v, applied inside the kernel.  ``precise``: the decayed scores of a block keep a
+    16-bit remainder beside their 16-bit value (a second P V pass)."""
     if out_dtype not in (None, q.dtype, torch.float32):
         raise native.NativeError("out_dtype must be the input dtype or torch.float32")
     f32_out = out_dtype == torch.float32
@@ -128,7 +129,8 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         if normalize:
             raise native.NativeError("normalize needs dim_v to be a multiple of 128")
         pad = 128 - Dv % 128
-        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps, out_dtype, v_scale)
+        o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps, out_dtype, v_scale,
+                                     precise)
         return o[..., :Dv].contiguous()
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     log_decay = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
@@ -144,6 +146,7 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         a.heads_q, a.heads_k = q.shape[1], k.shape[1]
         a.dtype = native.DTYPE_CODES[q.dtype]
         a.normalize = 1 if normalize else 0
+        a.precise = 1 if precise else 0
         a.q_scale = float(q_scale)
         a.norm_eps = float(eps)
         lib = native.load_library()
@@ -156,7 +159,7 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
     return o
 
 
-def _retention_fp32(qc, kc, vc, log_decay, q_scale):
+def _retention_fp32(qc, kc, vc, log_decay, q_scale, precise=False):
     """o_i = q_scale * sum_{j<=i} exp(G_i - G_j) (qc_i . kc_j) vc_j in fp32 on the forward kernel, for any width of the
     contraction: the sum is linear in the scores, so a contraction wider than the kernel's 256 columns is the sum over
     column ranges it does cover (widths 256 / 128 / 64, the last one zero-padded)."""
@@ -168,16 +171,17 @@ def _retention_fp32(qc, kc, vc, log_decay, q_scale):
         if qs.shape[-1] < width:
             pad = width - qs.shape[-1]
             qs, ks = torch.nn.functional.pad(qs, (0, pad)), torch.nn.functional.pad(ks, (0, pad))
-        part = linear_attention_forward(qs.contiguous(), ks.contiguous(), vc, log_decay, q_scale, out_dtype=torch.float32)
+        part = linear_attention_forward(qs.contiguous(), ks.contiguous(), vc, log_decay, q_scale, out_dtype=torch.float32,
+                                        precise=precise)
         out = part if out is None else out + part
         start += width
     return out
 
 
-def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0):
-    """(dq, dk, dv) of ``linear_attention_forward`` (no normalisation; the decay is not differentiated), the job of the
-    reference's three backward kernels (core/template/tl_template/linear/linear_tl.py:461-975), as five runs of the
-    forward kernel.  With D_ij = exp(G_i - G_j) for j <= i:
+def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0, need_dg: bool = False):
+    """(dq, dk, dv[, dg]) of ``linear_attention_forward`` (no normalisation), the job of the reference's three backward
+    kernels (core/template/tl_template/linear/linear_tl.py:461-975), as five runs of the forward kernel.  With
+    D_ij = exp(G_i - G_j) for j <= i:
 
         dq_i = q_scale * sum_{j<=i} D_ij (do_i . v_j) k_j      = retention(q = do, k = v, v = k)
         dv_j = q_scale * sum_{i>=j} D_ij (q_i . k_j) do_i      = retention(q = k, k = q, v = do) with time reversed
@@ -185,16 +189,26 @@ def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0):
 
     Reversing time turns the anti-causal sums into causal ones; position u of the reversed sequence then carries the
     log-decay of token T - u (0 for u = 0), so that the reversed cumulative sums reproduce the same D_ij.  The two
-    contractions over dim_v go through ``_retention_fp32`` (dim_v may exceed the kernel's 256 columns of dim_qk)."""
+    contractions over dim_v go through ``_retention_fp32`` (dim_v may exceed the kernel's 256 columns of dim_qk).
+
+    ``need_dg``: also the gradient with respect to the per-token log-decay, fp32 [B, H, T].  A score A_ij depends on the
+    log-decays of tokens j+1..i, so dg_t = sum_{i>=t, j<t} dA_ij A_ij; with dG_i = q_i . dq_i - k_i . dk_i (row sums
+    minus column sums of dA o A) that is the reversed cumulative sum of dG — what the reference's dqkg kernel and its
+    ``compute_final_dg`` produce per chunk (linear_tl.py:63-76, 638-814)."""
     d_o = d_o.to(q.dtype)
     B, H, T, _ = q.shape
     ld = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T)
     ld_rev = torch.cat([torch.zeros_like(ld[..., :1]), ld.flip(-1)[..., :-1]], dim=-1).contiguous()
-    dq = _retention_fp32(d_o, v, k, ld, q_scale)
+    # dg is a difference of sums over dq and dk: those runs then keep the 16-bit remainder of their decayed scores
+    dq = _retention_fp32(d_o, v, k, ld, q_scale, precise=need_dg)
     qr, kr, vr, dr = q.flip(2), k.flip(2), v.flip(2), d_o.flip(2)
     dv = _retention_fp32(kr, qr, dr, ld_rev, q_scale).flip(2)
-    dk = _retention_fp32(vr, dr, qr, ld_rev, q_scale).flip(2)
-    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+    dk = _retention_fp32(vr, dr, qr, ld_rev, q_scale, precise=need_dg).flip(2)
+    if not need_dg:
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+    d_cum = (q.float() * dq.float()).sum(-1) - (k.float() * dk.float()).sum(-1)
+    dg = d_cum.flip(-1).cumsum(-1).flip(-1)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg
 
 
 class _ForwardOnly(torch.autograd.Function):
@@ -204,41 +218,40 @@ class _ForwardOnly(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        raise NotImplementedError("the B200-native backend differentiates linear attention only without q / k / v mods "
-                                  "(a constant factor on q is fine), without output normalisation and not with respect "
-                                  "to the decay")
+        raise NotImplementedError("the B200-native backend differentiates linear attention only without output "
+                                  "normalisation")
 
 
 class _LinearAttention(torch.autograd.Function):
-    """Chunked linear attention with its backward (``linear_attention_backward``): the counterpart of the reference's
-    ``LinearAttention`` autograd function (core/template/tl_template/linear/linear_tl.py:1237-1333)."""
+    """Chunked linear attention of operands that have been through their mods, with its backward
+    (``linear_attention_backward``): the counterpart of the kernels inside the reference's ``LinearAttention`` autograd
+    function (core/template/tl_template/linear/linear_tl.py:1237-1333).  The reference differentiates the mods with
+    generated statements (``*_mod_bwd_expr``, :1322-1329); here they are torch operations in front of this function and
+    torch's autograd carries dq, dk, dv and the log-decay's gradient through them, custom inputs included."""
 
     @staticmethod
-    def forward(ctx, engine, q, k, v, decay, *custom):
-        q, k, v = q.detach(), k.detach(), v.detach()
-        cenv = {id(engine.custom_io.input_tensors[n]): t.float() for n, t in zip(engine.custom_names, custom)}
-        log_decay = engine._apply("decay", decay.detach().float(), cenv)
-        H = v.shape[1]
-        qe = q.repeat_interleave(H // q.shape[1], dim=1) if q.shape[1] != H else q
-        ke = k.repeat_interleave(H // k.shape[1], dim=1) if k.shape[1] != H else k
-        o = linear_attention_forward(qe, ke, v, log_decay, q_scale=engine.q_scale)
-        ctx.save_for_backward(qe, ke, v, log_decay)
-        ctx.heads = (q.shape[1], k.shape[1])
-        ctx.q_scale = engine.q_scale
-        ctx.n_custom = len(custom)
+    def forward(ctx, q, k, v, log_decay, q_scale):
+        o = linear_attention_forward(q.detach(), k.detach(), v.detach(), log_decay.detach(), q_scale=q_scale)
+        ctx.save_for_backward(q, k, v, log_decay)
+        ctx.q_scale = q_scale
         return o
 
     @staticmethod
     def backward(ctx, d_o):
-        qe, ke, v, log_decay = ctx.saved_tensors
-        dq, dk, dv = linear_attention_backward(qe, ke, v, log_decay, d_o, ctx.q_scale)
-        B, H, T, _ = qe.shape
-        hq, hk = ctx.heads
+        q, k, v, log_decay = ctx.saved_tensors
+        B, H, T, _ = v.shape
+        hq, hk = q.shape[1], k.shape[1]
+        qe = q.repeat_interleave(H // hq, dim=1) if hq != H else q
+        ke = k.repeat_interleave(H // hk, dim=1) if hk != H else k
+        need_dg = ctx.needs_input_grad[3]
+        res = linear_attention_backward(qe, ke, v, log_decay, d_o, ctx.q_scale, need_dg=need_dg)
+        dq, dk, dv = res[:3]
         if hq != H:   # heads that shared one q head: their gradients add up
             dq = dq.view(B, hq, H // hq, T, -1).float().sum(2).to(dq.dtype)
         if hk != H:
             dk = dk.view(B, hk, H // hk, T, -1).float().sum(2).to(dk.dtype)
-        return (None, dq, dk, dv, None) + (None,) * ctx.n_custom
+        dg = res[3].sum_to_size(log_decay.shape).to(log_decay.dtype) if need_dg else None
+        return dq, dk, dv, dg, None
 
 
 class LinearAttentionEngine:
@@ -295,16 +308,34 @@ class LinearAttentionEngine:
         return res if name == "decay" else res.to(tensor.dtype)
 
     def has_backward(self) -> bool:
-        """Gradients with respect to q, k, v flow when no mod rewrites them (a constant factor on q has been folded
-        into the kernel's scale) and the output is not normalised."""
-        return all(self._mods[n] is None for n in ("q", "k", "v")) and self._v_scale_expr is None and not self.normalize_output
+        """Gradients flow to q, k, v, the decay and the custom inputs, through every mod, unless the output is
+        normalised."""
+        return not self.normalize_output
 
     def _run(self, q, k, v, decay, *custom):
-        if any(t.requires_grad for t in (q, k, v)) and torch.is_grad_enabled():
-            if self.has_backward() and not (isinstance(decay, torch.Tensor) and decay.requires_grad):
-                return _LinearAttention.apply(self, q, k, v, decay, *custom)
+        tensors = [t for t in (q, k, v, decay) + tuple(custom) if isinstance(t, torch.Tensor)]
+        if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+            if self.has_backward():
+                return self._run_differentiable(q, k, v, decay, *custom)
             return _ForwardOnly.apply(self._run_impl, q, k, v, decay, *custom)
         return self._run_impl(q, k, v, decay, *custom)
+
+    def _run_differentiable(self, q, k, v, decay, *custom):
+        """The mods as torch operations that autograd records (a factor on v that the forward-only path hands to the
+        kernel is an explicit multiply here), then the kernel with its backward."""
+        if len(custom) != len(self.custom_names):
+            raise TypeError(f"expected custom tensors {self.custom_names}")
+        cenv = {id(self.custom_io.input_tensors[n]): t.float() for n, t in zip(self.custom_names, custom)}
+        q = self._apply("q", q, cenv)
+        k = self._apply("k", k, cenv)
+        v = self._apply("v", v, cenv)
+        if self._v_scale_expr is not None:
+            t = eval_tensor_expr(self._v_scale_expr, cenv)
+            t = t if isinstance(t, torch.Tensor) else torch.tensor(float(t), device=v.device)
+            f, g = _align(v.float(), t)
+            v = (f * g).to(v.dtype)
+        log_decay = self._apply("decay", decay.float(), cenv)
+        return _LinearAttention.apply(q, k, v, log_decay, self.q_scale)
 
     def _run_impl(self, q, k, v, decay, *custom):
         if len(custom) != len(self.custom_names):

@@ -72,7 +72,7 @@ class LinearArgs(C.Structure):
         ("batch", C.c_int32), ("heads", C.c_int32), ("seq", C.c_int32), ("dim_qk", C.c_int32), ("dim_v", C.c_int32),
         ("dtype", C.c_int32), ("normalize", C.c_int32), ("q_scale", C.c_float), ("norm_eps", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
-        ("dtype_out", C.c_int32), ("reserved", C.c_int32),
+        ("dtype_out", C.c_int32), ("precise", C.c_int32),
         ("v_scale", C.c_void_p), ("heads_q", C.c_int32), ("heads_k", C.c_int32),
     ]
 

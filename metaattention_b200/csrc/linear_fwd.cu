@@ -708,7 +708,7 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   // kernel's arithmetic gives, for gamma = 1 - 2^-5, mean-abs 3.4e-4 on an output of standard deviation 0.25, and
   // 1.1e-4 with the remainder pass), so a second PV pass over the 16-bit remainder of P is spent there.  For slow
   // decays the state path's roundings dominate and the pass changes nothing.
-  p.split_p = a->normalize ? 1 : 0;
+  p.split_p = (a->normalize || a->precise) ? 1 : 0;
   p.status = status;
   const long long rows = static_cast<long long>(bh) * a->seq;
   if (a->normalize) {

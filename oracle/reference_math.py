@@ -127,24 +127,36 @@ def retention_grads(q, k, v, d_o):
     return qf.grad, kf.grad, vf.grad
 
 
-def decayed_linear_attention_grads(q, k, v, log_decay, d_o, scale: float = 1.0):
-    """(dq, dk, dv) fp32 of ``decayed_linear_attention`` (the decay is not differentiated), in closed form with the
-    decay matrix D_ij = exp(G_i - G_j), j <= i, in fp64: dq = scale (D o (dO V^T)) K, dk = scale (D o (dO V^T))^T Q,
-    dv = scale (D o (Q K^T))^T dO.  Heads of q / k shared by several heads of v get the sum of their gradients."""
+def decayed_linear_attention_grads(q, k, v, log_decay, d_o, scale: float = 1.0, with_decay: bool = False):
+    """(dq, dk, dv) fp32 of ``decayed_linear_attention``, in closed form with the decay matrix D_ij = exp(G_i - G_j),
+    j <= i, in fp64: dq = scale (D o (dO V^T)) K, dk = scale (D o (dO V^T))^T Q, dv = scale (D o (Q K^T))^T dO.  Heads of
+    q / k shared by several heads of v get the sum of their gradients.  ``with_decay``: a fourth result, the gradient
+    with respect to ``log_decay`` (its shape), by torch autograd through the matrix form o = scale (D o Q K^T) V — how the
+    reference's test obtains the gradients it compares its kernels with (testing/test.py:106-127)."""
     q, k, v, ld, d_o = q.double(), k.double(), v.double(), log_decay.double(), d_o.double()
     B, H, S, _ = v.shape
     HQ, HK = q.shape[1], k.shape[1]
     qe = q.repeat_interleave(H // HQ, dim=1)
     ke = k.repeat_interleave(H // HK, dim=1)
+    tril = torch.ones(S, S, dtype=torch.float64).tril()
     G = ld.expand(B, H, S).cumsum(-1)
-    D = torch.exp((G.unsqueeze(-1) - G.unsqueeze(-2)).clamp_max(0.0)) * torch.ones(S, S, dtype=torch.float64).tril()
+    D = torch.exp((G.unsqueeze(-1) - G.unsqueeze(-2)).clamp_max(0.0)) * tril
     a = D * torch.einsum("bhid,bhjd->bhij", d_o, v) * scale
     dq = torch.einsum("bhij,bhjd->bhid", a, ke)
     dk = torch.einsum("bhij,bhid->bhjd", a, qe)
     dv = torch.einsum("bhij,bhid->bhjd", D * torch.einsum("bhid,bhjd->bhij", qe, ke) * scale, d_o)
     dq = dq.view(B, HQ, H // HQ, S, -1).sum(2)
     dk = dk.view(B, HK, H // HK, S, -1).sum(2)
-    return dq.float(), dk.float(), dv.float()
+    if not with_decay:
+        return dq.float(), dk.float(), dv.float()
+    with torch.enable_grad():
+        ldv = ld.clone().requires_grad_(True)
+        Gv = ldv.expand(B, H, S).cumsum(-1)
+        # masked before the exponential: above the diagonal the exponent is positive and may overflow
+        Dv_ = torch.exp((Gv.unsqueeze(-1) - Gv.unsqueeze(-2)).masked_fill(tril == 0, float("-inf")))
+        o = torch.einsum("bhij,bhjd->bhid", Dv_ * torch.einsum("bhid,bhjd->bhij", qe, ke) * scale, v)
+        (dld,) = torch.autograd.grad(o, ldv, d_o)
+    return dq.float(), dk.float(), dv.float(), dld.float()
 
 
 def decayed_linear_attention(q, k, v, log_decay, scale: float = 1.0):

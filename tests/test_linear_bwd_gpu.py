@@ -26,6 +26,20 @@ def check(got, want, what):
     assert d.mean().item() <= 3e-3 * max(1.0, want.std().item()), (what, d.mean().item(), want.std().item())
 
 
+def check_decay_grad(got, want, what):
+    """Gradients that pass through the log-decays: dg_t is a reversed running sum over the tokens of q_i . dq_i -
+    k_i . dk_i, a difference of two sums whose 16-bit rounding errors (the kernel rounds its decayed scores to 16 bits)
+    then add up along the sequence like a random walk; the runs it is formed from therefore keep a 16-bit remainder
+    of those scores (``precise``).  The reference's test means to hold g.grad to rtol 3e-2 (testing/test.py:513-518,
+    switched off there); here: mean-abs 3e-2 of the expected spread, max-abs 1e-1 of the largest value (measured: dg
+    mean-abs 2.3e-3 of the spread, Mamba2's dA, a sum over all tokens, 2.7e-2; without the remainder dg had 1.2e-2 and dA
+    9e-2)."""
+    d = (got.float().cpu() - want.float()).abs()
+    assert torch.isfinite(got).all(), what
+    assert d.max().item() <= 1e-1 * max(1.0, want.abs().max().item()), (what, d.max().item(), want.abs().max().item())
+    assert d.mean().item() <= 3e-2 * max(1.0, want.std().item()), (what, d.mean().item(), want.std().item())
+
+
 def test_against_reference_golden():
     from examples_b200 import programs
     g = torch.load(os.path.join(GOLD, "retention_bwd.pt"))
@@ -76,13 +90,61 @@ def test_gated_retention_per_token_decay():
         check(got, w_, what)
 
 
-def test_programs_with_operand_mods_say_so():
-    """Mamba2's v_mod rewrites v before the kernel: its derivative is not built."""
+def test_gated_retention_gradient_of_the_gates():
+    """A learned gate: the per-token log-decay requires grad, and its gradient (reversed sum of q . dq - k . dk) comes
+    back with dq, dk, dv; against torch autograd through the oracle's matrix form."""
     from examples_b200 import programs
-    B, HQ, HK, HV, S, D, Dv = 1, 2, 2, 4, 128, 64, 64
+    B, H, S, D, Dv = 1, 4, 300, 64, 128
+    q, k, v, g = inputs.gla_inputs(B, H, S, D, Dv, 63)
+    d_o = torch.randn(B, H, S, Dv, generator=torch.Generator().manual_seed(64)).to(q.dtype)
+    want = rm.decayed_linear_attention_grads(q, k, v, g, d_o, scale=D ** -0.5, with_decay=True)
+    eng = programs.gla_engine(B, H, S, D, Dv)
+    qc, kc, vc, gc = (t.cuda().requires_grad_() for t in (q, k, v, g))
+    o = eng(qc, kc, vc, gc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    for got, w_, what in zip((qc.grad, kc.grad, vc.grad, gc.grad), want, ("dq", "dk", "dv", "dg")):
+        assert got is not None and got.shape == w_.shape, what
+        (check_decay_grad if what == "dg" else check)(got, w_, what)
+
+
+def test_mamba2_gradients_through_the_mods():
+    """Mamba2 (v_mod = v * dt, decay_mod = dt * A, grouped q / k heads): gradients of q, k, v and of the custom inputs dt
+    and A, against autograd over the same program in fp64 torch operations (the matrix form of testing/test.py:305-343)."""
+    from examples_b200 import programs
+    B, HQ, HK, HV, S, D, Dv = 1, 2, 2, 4, 256, 64, 128
     q, k, v, dt, A = inputs.mamba2_inputs(B, HQ, HK, HV, S, D, Dv, 71)
+    d_o = torch.randn(B, HV, S, Dv, generator=torch.Generator().manual_seed(72)).to(q.dtype)
     eng = programs.mamba2_engine(B, HQ, S, D, Dv, HK=HK, HV=HV)
+    leaves = [t.cuda().requires_grad_() for t in (q, k, v, dt, A)]
+    qc, kc, vc, dtc, Ac = leaves
+    o = eng(qc, kc, vc, dtc, Ac, dtc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    ref = [t.clone().double().requires_grad_() for t in (q, k, v, dt, A)]
+    qr, kr, vr, dtr, Ar = ref
+    ld = dtr * Ar.view(1, -1, 1)
+    vv = vr * dtr.unsqueeze(-1)
+    G = ld.cumsum(-1)
+    tril = torch.ones(S, S, dtype=torch.float64).tril()
+    Dm = torch.exp((G.unsqueeze(-1) - G.unsqueeze(-2)).masked_fill(tril == 0, float("-inf")))
+    qe, ke = qr.repeat_interleave(HV // HQ, dim=1), kr.repeat_interleave(HV // HK, dim=1)
+    o_ref = torch.einsum("bhij,bhjd->bhid", Dm * torch.einsum("bhid,bhjd->bhij", qe, ke), vv)
+    check(o.detach(), o_ref.detach().float(), "o")
+    o_ref.backward(d_o.double())
+    for got, want, what in zip(leaves, ref, ("dq", "dk", "dv", "d dt", "dA")):
+        assert got.grad is not None, what
+        (check_decay_grad if what in ("d dt", "dA") else check)(got.grad, want.grad.float(), what)
+
+
+def test_normalised_output_says_so():
+    """The output normalisation of the retention benchmark has no backward: differentiating it is refused."""
+    from examples_b200 import programs
+    B, H, S, Dk, Dv = 1, 2, 128, 64, 128
+    q, k, v, decay = inputs.retention_bhsd(B, H, S, Dk, Dv, 5)
+    eng = programs.retnet_engine(B, H, S, Dk, Dv)
+    eng.normalize_output = True
     qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
-    o = eng(qc, kc, vc, dt.cuda(), A.cuda(), dt.to(torch.bfloat16).cuda())
+    o = eng(qc, kc, vc, decay.cuda())
     with pytest.raises(NotImplementedError):
-        o.sum().backward()
+        o.float().sum().backward()
