@@ -300,7 +300,7 @@ class AttentionEngine:
             native_jit.build(self.functor_source)
             self._jit_fn = None
             # the backward of an elementwise program: source now, compiled when a gradient is first asked for
-            if derivative.elementwise_program(tr) and D == Dv and D in (64, 128):
+            if derivative.elementwise_program(tr) and D in (64, 128) and Dv % D == 0:
                 self._bwd_source = derivative.backward_translation_unit(derivative.emit_backward_functor(tr), D, dtype == torch.bfloat16)
         self.attention = self._run_parallel
 
@@ -323,10 +323,11 @@ class AttentionEngine:
 
     def has_backward(self, q, v) -> bool:
         """Whether gradients flow through this engine for these operands: the built-in softmax (a traced program that
-        is softmax attention with a probed scale), no mask or a causal one, head dims 128 / 128 or 64 / 64."""
+        is softmax attention with a probed scale), no mask or a causal one, dim_qk 128 or 64 and dim_v a multiple of it
+        (the 128 / 256 of the reference's suite runs as one backward per 128-column slice of v)."""
         return (self.functor_kind == "builtin_softmax" and self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL) and
                 self._decode_block is None and self._sparse_host is None and len(self.final_names) == 1 and
-                q.shape[-1] == v.shape[-1] and q.shape[-1] in (64, 128))
+                q.shape[-1] in (64, 128) and v.shape[-1] % q.shape[-1] == 0)
 
     def _custom_operands(self, custom, B, H, Sq, Skv, device):
         """Checks the custom input tensors against their declared shapes and returns (tensors, element strides over

@@ -308,14 +308,38 @@ def decode_tiles(block_mask, cache_seqlens, batch: int, heads_kv: int, seq_kv: i
             "mask_rows": 0, "_owner": (out, block_mask, cache_seqlens)}
 
 
+def _over_dim_v_slices(run, q, k, v, d_o, o=None):
+    """dim_v a multiple of dim_qk (the 128 / 256 of the reference's suite, testing/test.py:55): the backward is linear in
+    dP = dO V^T and in delta = rowsum(dO o O), both sums over the columns of v, and dV's columns are independent, so it
+    is one kernel run per dim_qk-wide column slice of (v, o, dO) — each recomputing P — with dQ and dK added up in fp32."""
+    D, Dv = q.shape[-1], v.shape[-1]
+    if Dv == D:
+        return run(q, k, v, d_o, o)
+    if Dv % D != 0:
+        raise NativeError(f"the backward covers dim_v = a multiple of dim_qk (got {D} / {Dv})")
+    dq = dk = None
+    dvs = []
+    for c in range(0, Dv, D):
+        part = run(q, k, v[..., c:c + D], d_o[..., c:c + D], None if o is None else o[..., c:c + D])
+        dq = part[0].float() if dq is None else dq + part[0].float()
+        dk = part[1].float() if dk is None else dk + part[1].float()
+        dvs.append(part[2])
+    return dq.to(q.dtype), dk.to(k.dtype), torch.cat(dvs, dim=-1)
+
+
 def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
     """(dq, dk, dv) of softmax attention from the forward's o and lse [B, H, Sq] and the gradient of o
-    (attn_b200_softmax_bwd: mask NONE or CAUSAL, head dims 128 / 128)."""
+    (attn_b200_softmax_bwd: mask NONE or CAUSAL, head dims 128 / 128 and 64 / 64; dim_v a larger multiple of dim_qk
+    as one run per column slice)."""
     for t in (q, k, v, o, d_o, lse):
         if not t.is_cuda:
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
+    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _softmax_bwd_one(q_, k_, v_, o_, lse, do_, scale, mask_kind), q, k, v, d_o, o)
+
+
+def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
     for t in (q, k, v, o):
         if t.stride(-1) != 1:
             raise NativeError("last dimension must be contiguous")
@@ -346,12 +370,16 @@ def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
 
 def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=()):
     """(dq, dk, dv) of an elementwise program through its functor library's ``attn_b200_elementwise_bwd_jit`` (``fn``);
-    ``custom``: the program's fp32 scalar inputs, as device tensors."""
+    ``custom``: the program's fp32 scalar inputs, as device tensors.  dim_v may be a multiple of dim_qk."""
     for t in (q, k, v, d_o, *custom):
         if not t.is_cuda:
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
+    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _elementwise_bwd_one(fn, q_, k_, v_, do_, mask_kind, custom), q, k, v, d_o)
+
+
+def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom=()):
     if q.dtype not in DTYPE_CODES or any(t.dtype != q.dtype for t in (k, v, d_o)):
         raise NativeError("q, k, v, d_o must share dtype float16 or bfloat16")
     dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))

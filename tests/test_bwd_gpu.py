@@ -123,12 +123,38 @@ def test_engine_autograd(causal):
 
 def test_programs_without_a_backward_say_so():
     from examples_b200 import programs
-    B, H, S, D, Dv = 1, 2, 128, 128, 256
+    B, H, S, D, Dv = 1, 2, 128, 192, 128
     q, k, v = (t.cuda().requires_grad_() for t in inputs.attention_bshd(B, H, S, D, Dv, 35))
-    eng = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)   # head dims 128 / 256: forward only
+    eng = programs.softmax_engine(B, H, S, D, Dv, is_causal=True)   # head dims 192 / 128: forward only
     o = eng(q, k, v)
     with pytest.raises(NotImplementedError):
         o.sum().backward()
+
+
+@pytest.mark.parametrize("program,D,Dv,dtype", [("softmax", 128, 256, torch.float16), ("softmax", 128, 384, torch.bfloat16),
+                                                ("relu", 128, 256, torch.bfloat16)])
+def test_dim_v_a_multiple_of_dim_qk(program, D, Dv, dtype):
+    """The reference's suite differentiates causal softmax with head dims 128 / 256 in fp16 (testing/test.py:55,
+    73-127): one backward per dim_qk-wide column slice of v, dQ and dK added up."""
+    from examples_b200 import programs
+    B, H, S = 1, 3, 400
+    q, k, v = inputs.attention_bshd(B, H, S, D, Dv, 41, dtype=dtype, k_scale=0.5 if program == "relu" else 1.0,
+                                    v_scale=0.5 if program == "relu" else 1.0)
+    d_o = torch.randn(B, S, H, Dv, generator=torch.Generator().manual_seed(42)).to(dtype)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        ref = rm.softmax_attention(qf, kf, vf, True, D ** -0.5) if program == "softmax" else rm.relu_attention(qf, kf, vf)
+        ref.backward(d_o.float())
+    eng = (programs.softmax_engine(B, H, S, D, Dv, dtype=dtype, is_causal=True) if program == "softmax"
+           else programs.relu_engine(B, H, S, D, Dv, dtype=dtype))
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qc, kc, vc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    check(o.detach(), ref.detach(), "o")
+    for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
+        assert got.shape == want.shape, what
+        check(got, want, what)
 
 
 def test_argument_errors():

@@ -15,7 +15,8 @@ def test_which_programs_are_elementwise():
     assert programs.relu_engine(B, H, S, 64, 64)._bwd_source is not None
     soft = programs.softmax_engine(B, H, S, D, D, is_causal=True)       # built-in softmax: its own backward kernel
     assert soft._bwd_source is None and soft.functor_kind == "builtin_softmax"
-    assert programs.relu_engine(B, H, S, 128, 256)._bwd_source is None  # head dims the backward does not cover
+    assert programs.relu_engine(B, H, S, 128, 256)._bwd_source is not None  # one backward per 128-column slice of v
+    assert programs.relu_engine(B, H, S, 192, 128)._bwd_source is None  # head dims the backward does not cover
 
 
 def test_emitted_functor_of_sigmoid_attention():

@@ -182,10 +182,10 @@ def test_full_size_config3_sampled_heads():
 
 
 def test_backward_is_refused_clearly():
-    """Programs whose backward is not built (here relu attention on head dims 128 / 256, which the backward kernel does
-    not cover) say so when differentiated; softmax, sigmoid and relu attention on 128 / 128 and 64 / 64 have one
+    """Programs whose backward is not built (here relu attention on head dims 192 / 128, which the backward kernel does
+    not cover) say so when differentiated; softmax, sigmoid and relu attention with dim_qk 128 or 64 have one
     (tests/test_bwd_gpu.py)."""
-    B, H, S, D, Dv = 1, 1, 128, 128, 256
+    B, H, S, D, Dv = 1, 1, 128, 192, 128
     q, k, v = [t.cuda().requires_grad_(True) for t in inputs.attention_bshd(B, H, S, D, Dv, 1)]
     o = programs.relu_engine(B, H, S, D, Dv)(q, k, v)
     with pytest.raises(NotImplementedError):
