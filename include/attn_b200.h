@@ -174,6 +174,17 @@ int64_t attn_b200_linear_workspace_bytes(const AttnB200LinearArgs* args);
  * (core/template/tl_template/linear/linear_tl.py:36-60, :146-223, :321-401, :1240-1268). */
 int attn_b200_linear_fwd(const AttnB200LinearArgs* args, void* cuda_stream);
 
+/* Row gathers of the linear-attention backward, which runs attn_b200_linear_fwd on time-reversed operands and on column
+ * ranges of dim_v and adds up fp32 partial results (the reference's backward kernels walk the sequence backwards
+ * themselves, linear_tl.py:461-975).  All tensors [outer, seq, cols] contiguous, pointers 16-byte aligned, column
+ * counts and offsets multiples of 8.
+ *   rows_copy16:   dst[o][s'][0:width] = src[o][s][col0:col0+width] for 16-bit elements, s' = reverse ? seq-1-s : s
+ *   rows_sum_cast: dst[o][s'][:] = a[o][s][:] + b[o][s][:] (b may be NULL), fp32 -> `dtype` (fp16 / bf16) */
+int attn_b200_rows_copy16(const void* src, void* dst, int64_t outer, int32_t seq, int32_t src_cols, int32_t col0, int32_t width,
+                          int32_t reverse, void* cuda_stream);
+int attn_b200_rows_sum_cast(const float* a, const float* b, void* dst, int32_t dtype, int64_t outer, int32_t seq, int32_t cols,
+                            int32_t reverse, void* cuda_stream);
+
 /* MLA decode problem shape: one query token per sequence, one shared latent KV head. */
 typedef struct AttnB200MlaShape {
   int32_t batch, heads_q, seq_kv, dim_qk, dim_v;

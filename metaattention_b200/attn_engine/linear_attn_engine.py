@@ -159,23 +159,45 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
     return o
 
 
-def _retention_fp32(qc, kc, vc, log_decay, q_scale, precise=False):
-    """o_i = q_scale * sum_{j<=i} exp(G_i - G_j) (qc_i . kc_j) vc_j in fp32 on the forward kernel, for any width of the
-    contraction: the sum is linear in the scores, so a contraction wider than the kernel's 256 columns is the sum over
-    column ranges it does cover (widths 256 / 128 / 64, the last one zero-padded)."""
+def _rows(t, col0=0, width=None, reverse=False):
+    """Columns [col0, col0 + width) of t [B, H, T, cols], time reversed if asked, contiguous: one pass of the library's
+    row-gather kernel (torch.flip alone runs at a fifth of the copy rate)."""
+    width = t.shape[-1] - col0 if width is None else width
+    if not reverse and col0 == 0 and width == t.shape[-1]:
+        return t.contiguous()
+    if width % 8 == 0 and col0 % 8 == 0 and t.shape[-1] % 8 == 0:
+        return native.rows_copy(t, col0, width, reverse)
+    part = t[..., col0:col0 + width]
+    return (part.flip(2) if reverse else part).contiguous()
+
+
+def _sum_cast(parts, dtype, reverse=False):
+    """Sum of the fp32 partial results, rounded to ``dtype``, time reversed if asked: one pass for up to two parts."""
+    while len(parts) > 2:
+        parts = [parts[0] + parts[1]] + parts[2:]
+    if parts[0].shape[-1] % 8 == 0:
+        return native.rows_sum_cast(parts[0], parts[1] if len(parts) > 1 else None, dtype, reverse)
+    out = (parts[0] + parts[1] if len(parts) > 1 else parts[0]).to(dtype)
+    return out.flip(2) if reverse else out
+
+
+def _retention_parts(qc, kc, vc, log_decay, q_scale, precise=False, reverse_in=False):
+    """o_i = q_scale * sum_{j<=i} exp(G_i - G_j) (qc_i . kc_j) vc_j on the forward kernel with fp32 output, for any width
+    of the contraction, as a list of partial results to be added: the sum is linear in the scores, so a contraction
+    wider than the kernel's 256 columns is the sum over column ranges it does cover (widths 256 / 128 / 64, the last one
+    zero-padded).  ``reverse_in``: qc and kc are given in forward time and are reversed while their column ranges are
+    cut out (vc is taken as it is)."""
     D = qc.shape[-1]
-    out, start = None, 0
+    parts, start = [], 0
     while start < D:
         width = next((w for w in (256, 128, 64) if D - start >= w), 64)
-        qs, ks = qc[..., start:start + width], kc[..., start:start + width]
-        if qs.shape[-1] < width:
-            pad = width - qs.shape[-1]
-            qs, ks = torch.nn.functional.pad(qs, (0, pad)), torch.nn.functional.pad(ks, (0, pad))
-        part = linear_attention_forward(qs.contiguous(), ks.contiguous(), vc, log_decay, q_scale, out_dtype=torch.float32,
-                                        precise=precise)
-        out = part if out is None else out + part
+        have = min(width, D - start)
+        qs, ks = _rows(qc, start, have, reverse_in), _rows(kc, start, have, reverse_in)
+        if have < width:
+            qs, ks = torch.nn.functional.pad(qs, (0, width - have)), torch.nn.functional.pad(ks, (0, width - have))
+        parts.append(linear_attention_forward(qs, ks, vc, log_decay, q_scale, out_dtype=torch.float32, precise=precise))
         start += width
-    return out
+    return parts
 
 
 def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0, need_dg: bool = False):
@@ -189,26 +211,32 @@ def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0, nee
 
     Reversing time turns the anti-causal sums into causal ones; position u of the reversed sequence then carries the
     log-decay of token T - u (0 for u = 0), so that the reversed cumulative sums reproduce the same D_ij.  The two
-    contractions over dim_v go through ``_retention_fp32`` (dim_v may exceed the kernel's 256 columns of dim_qk).
+    contractions over dim_v go through ``_retention_parts`` (dim_v may exceed the kernel's 256 columns of dim_qk).
+    Reversals, column ranges and the sums of the partial results are single passes of the library's row kernels.
 
     ``need_dg``: also the gradient with respect to the per-token log-decay, fp32 [B, H, T].  A score A_ij depends on the
     log-decays of tokens j+1..i, so dg_t = sum_{i>=t, j<t} dA_ij A_ij; with dG_i = q_i . dq_i - k_i . dk_i (row sums
     minus column sums of dA o A) that is the reversed cumulative sum of dG — what the reference's dqkg kernel and its
-    ``compute_final_dg`` produce per chunk (linear_tl.py:63-76, 638-814)."""
+    ``compute_final_dg`` produce per chunk (linear_tl.py:63-76, 638-814).  dg is a difference of sums over dq and dk:
+    those runs then keep the 16-bit remainder of their decayed scores."""
     d_o = d_o.to(q.dtype)
     B, H, T, _ = q.shape
     ld = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T)
     ld_rev = torch.cat([torch.zeros_like(ld[..., :1]), ld.flip(-1)[..., :-1]], dim=-1).contiguous()
-    # dg is a difference of sums over dq and dk: those runs then keep the 16-bit remainder of their decayed scores
-    dq = _retention_fp32(d_o, v, k, ld, q_scale, precise=need_dg)
-    qr, kr, vr, dr = q.flip(2), k.flip(2), v.flip(2), d_o.flip(2)
-    dv = _retention_fp32(kr, qr, dr, ld_rev, q_scale).flip(2)
-    dk = _retention_fp32(vr, dr, qr, ld_rev, q_scale, precise=need_dg).flip(2)
+    dq_parts = _retention_parts(d_o, v, k, ld, q_scale, precise=need_dg)
+    dq = _sum_cast(dq_parts, q.dtype)
+    qr, kr, dr = _rows(q, reverse=True), _rows(k, reverse=True), _rows(d_o, reverse=True)
+    # dv: dim_qk fits the kernel, so it is one run that leaves the kernel in the operands' dtype
+    dv = _rows(linear_attention_forward(kr, qr, dr, ld_rev, q_scale), reverse=True)
+    dk_parts = _retention_parts(v, d_o, qr, ld_rev, q_scale, precise=need_dg, reverse_in=True)
+    dk = _sum_cast(dk_parts, k.dtype, reverse=True)
     if not need_dg:
-        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
-    d_cum = (q.float() * dq.float()).sum(-1) - (k.float() * dk.float()).sum(-1)
+        return dq, dk, dv
+    dq32 = sum(dq_parts[1:], dq_parts[0])
+    dk32_rev = sum(dk_parts[1:], dk_parts[0])
+    d_cum = (q.float() * dq32).sum(-1) - (kr.float() * dk32_rev).sum(-1).flip(-1)
     dg = d_cum.flip(-1).cumsum(-1).flip(-1)
-    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg
+    return dq, dk, dv, dg
 
 
 class _ForwardOnly(torch.autograd.Function):

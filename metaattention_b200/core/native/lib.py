@@ -128,6 +128,10 @@ SIGNATURES = {
     "attn_b200_decode_tiles": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_void_p, C.c_int64, C.c_void_p]),
     "attn_b200_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "attn_b200_rows_copy16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                        C.c_void_p]),
+    "attn_b200_rows_sum_cast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
+                                          C.c_int32, C.c_void_p]),
     "attn_b200_linear_workspace_bytes": (C.c_int64, [C.POINTER(LinearArgs)]),
     "attn_b200_softmax_bwd": (C.c_int, [C.POINTER(SoftmaxBwdArgs), C.c_void_p]),
     "attn_b200_softmax_bwd_workspace_bytes": (C.c_int64, [C.POINTER(SoftmaxBwdArgs)]),
@@ -146,7 +150,7 @@ _lib = None
 
 
 def library_sources() -> list[str]:
-    return [os.path.join(CSRC_DIR, f) for f in ("attn_b200.cu", "mla_decode.cu", "linear_fwd.cu", "softmax_bwd.cu")]
+    return [os.path.join(CSRC_DIR, f) for f in ("attn_b200.cu", "mla_decode.cu", "linear_fwd.cu", "softmax_bwd.cu", "row_ops.cu")]
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
@@ -306,6 +310,39 @@ def decode_tiles(block_mask, cache_seqlens, batch: int, heads_kv: int, seq_kv: i
     part = out[bh * tiles * 4 + bh * words:]
     return {"keep": keep, "partial": part, "mask_base": None, "elem_mask": col, "batch": batch, "heads": heads_kv,
             "mask_rows": 0, "_owner": (out, block_mask, cache_seqlens)}
+
+
+def rows_copy(src, col0: int = 0, width: int | None = None, reverse: bool = False):
+    """Contiguous copy of columns [col0, col0 + width) of a 16-bit tensor [..., seq, cols], the rows of every sequence in
+    reversed order if asked (attn_b200_rows_copy16): one pass for what torch does as flip + slice + contiguous."""
+    if not src.is_cuda:
+        raise NativeError("rows_copy needs a CUDA tensor: there is no CPU path")
+    if src.dtype not in DTYPE_CODES:
+        raise NativeError("rows_copy moves float16 / bfloat16 tensors")
+    src = src.contiguous()
+    cols, seq = src.shape[-1], src.shape[-2]
+    width = cols - col0 if width is None else width
+    dst = torch.empty(src.shape[:-1] + (width,), dtype=src.dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        check(load_library().attn_b200_rows_copy16(src.data_ptr(), dst.data_ptr(), src.numel() // (seq * cols), seq, cols, col0, width,
+                                                   1 if reverse else 0, current_stream_ptr()), "attn_b200_rows_copy16")
+    return dst
+
+
+def rows_sum_cast(a, b, dtype, reverse: bool = False):
+    """a (+ b), fp32 [..., seq, cols], rounded to ``dtype`` with the rows of every sequence reversed if asked
+    (attn_b200_rows_sum_cast)."""
+    if not a.is_cuda:
+        raise NativeError("rows_sum_cast needs CUDA tensors: there is no CPU path")
+    a = a.contiguous()
+    b = None if b is None else b.contiguous()
+    cols, seq = a.shape[-1], a.shape[-2]
+    dst = torch.empty(a.shape, dtype=dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        check(load_library().attn_b200_rows_sum_cast(a.data_ptr(), None if b is None else b.data_ptr(), dst.data_ptr(),
+                                                     DTYPE_CODES[dtype], a.numel() // (seq * cols), seq, cols, 1 if reverse else 0,
+                                                     current_stream_ptr()), "attn_b200_rows_sum_cast")
+    return dst
 
 
 def _over_dim_v_slices(run, q, k, v, d_o, o=None):

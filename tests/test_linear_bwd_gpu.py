@@ -148,3 +148,24 @@ def test_normalised_output_says_so():
     o = eng(qc, kc, vc, decay.cuda())
     with pytest.raises(NotImplementedError):
         o.float().sum().backward()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_row_kernels_against_torch(dtype):
+    """The reversed / column-sliced copy and the sum + cast + reversal of partial results, bit for bit against torch."""
+    from core.native import lib
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 3, 301, 384, generator=g).to(dtype).cuda()
+    for col0, width, rev in [(0, 384, True), (128, 256, True), (256, 128, False), (8, 24, True)]:
+        got = lib.rows_copy(x, col0, width, rev)
+        want = x[..., col0:col0 + width]
+        want = (want.flip(2) if rev else want).contiguous()
+        assert got.is_contiguous() and torch.equal(got, want), (col0, width, rev)
+    a = torch.randn(2, 3, 301, 256, generator=g).cuda()
+    b = torch.randn(2, 3, 301, 256, generator=g).cuda()
+    for second, rev in [(b, True), (None, True), (b, False)]:
+        got = lib.rows_sum_cast(a, second, dtype, rev)
+        want = (a if second is None else a + second).to(dtype)
+        assert torch.equal(got, want.flip(2) if rev else want), (second is None, rev)
+    with pytest.raises(lib.NativeError):
+        lib.rows_copy(x, 4, 16, True)      # offsets and widths in units of 8 columns (16 bytes)

@@ -19,7 +19,17 @@ def oracle_kernel(monkeypatch):
         assert not normalize
         return rm.decayed_linear_attention(q, k, v, log_decay, scale=q_scale)
 
+    def fake_rows_copy(src, col0=0, width=None, reverse=False):
+        part = src[..., col0:col0 + (src.shape[-1] - col0 if width is None else width)]
+        return (part.flip(-2) if reverse else part).contiguous()
+
+    def fake_rows_sum_cast(a, b, dtype, reverse=False):
+        out = (a if b is None else a + b).to(dtype)
+        return out.flip(-2) if reverse else out
+
     monkeypatch.setattr(le, "linear_attention_forward", fake_forward)
+    monkeypatch.setattr(le.native, "rows_copy", fake_rows_copy)
+    monkeypatch.setattr(le.native, "rows_sum_cast", fake_rows_sum_cast)
     return le
 
 
