@@ -165,6 +165,10 @@ typedef struct AttnB200LinearArgs {
   int32_t heads_q;       /* heads of q, 0 = `heads`: q is [batch, heads_q, seq, dim_qk], and head h of v reads q head
                             h / (heads / heads_q) (Mamba2's C and B with fewer groups than v heads) */
   int32_t heads_k;       /* the same for k */
+  int32_t q_ld;          /* elements between consecutive tokens of q, 0 = dim_qk: q may be a column range of a wider
+                            [batch, heads_q, seq, q_ld] tensor (pointer at the range's first column, 16-byte aligned;
+                            q_ld a multiple of 8) -- the backward contracts over column ranges of dO and v in place */
+  int32_t k_ld;          /* the same for k */
 } AttnB200LinearArgs;
 
 /* Bytes of scratch the linear forward needs: per-row (sum, sum of squares) fp32 when normalize = 1, else 0. */

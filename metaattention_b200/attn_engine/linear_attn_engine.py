@@ -103,6 +103,17 @@ def _constant_multiple(out: SymbolScalar, leaf: SymbolScalar):
     return None
 
 
+def _column_range_ld(t) -> int:
+    """The row pitch of t [B, H, T, w] if it is a column range of a contiguous [B, H, T, ld] tensor that the kernel can
+    read in place (16-byte aligned start, ld a multiple of 8), else 0."""
+    B, H, T, w = t.shape
+    ld = t.stride(2)
+    if (t.stride(3) == 1 and ld > w and ld % 8 == 0 and t.stride(1) == T * ld and t.stride(0) == H * T * ld
+            and t.data_ptr() % 16 == 0):
+        return ld
+    return 0
+
+
 def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize: bool = False, eps: float = 1e-5,
                              out_dtype=None, v_scale=None, precise: bool = False):
     """q,k: [B,H,T,Dk]; v: [B,H,T,Dv] (fp16/bf16 CUDA); log_decay: [B,H,T] fp32, natural log of the
@@ -132,7 +143,11 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         o = linear_attention_forward(q, k, torch.nn.functional.pad(v, (0, pad)), log_decay, q_scale, False, eps, out_dtype, v_scale,
                                      precise)
         return o[..., :Dv].contiguous()
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    # q and k may be column ranges of wider contiguous tensors (the backward's contractions over ranges of dim_v)
+    q_ld, k_ld = _column_range_ld(q), _column_range_ld(k)
+    q = q if q_ld else q.contiguous()
+    k = k if k_ld else k.contiguous()
+    v = v.contiguous()
     log_decay = log_decay.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
     if v_scale is not None:
         v_scale = v_scale.to(dtype=torch.float32, device=q.device).expand(B, H, T).contiguous()
@@ -144,6 +159,7 @@ def linear_attention_forward(q, k, v, log_decay, q_scale: float = 1.0, normalize
         a.v_scale = v_scale.data_ptr() if v_scale is not None else None
         a.batch, a.heads, a.seq, a.dim_qk, a.dim_v = B, H, T, Dk, Dv
         a.heads_q, a.heads_k = q.shape[1], k.shape[1]
+        a.q_ld, a.k_ld = q_ld, k_ld
         a.dtype = native.DTYPE_CODES[q.dtype]
         a.normalize = 1 if normalize else 0
         a.precise = 1 if precise else 0
@@ -163,8 +179,8 @@ def _rows(t, col0=0, width=None, reverse=False):
     """Columns [col0, col0 + width) of t [B, H, T, cols], time reversed if asked, contiguous: one pass of the library's
     row-gather kernel (torch.flip alone runs at a fifth of the copy rate)."""
     width = t.shape[-1] - col0 if width is None else width
-    if not reverse and col0 == 0 and width == t.shape[-1]:
-        return t.contiguous()
+    if not reverse:
+        return t[..., col0:col0 + width]    # read in place by the kernel (a pitch instead of a copy)
     if width % 8 == 0 and col0 % 8 == 0 and t.shape[-1] % 8 == 0:
         return native.rows_copy(t, col0, width, reverse)
     part = t[..., col0:col0 + width]

@@ -73,7 +73,7 @@ class LinearArgs(C.Structure):
         ("dtype", C.c_int32), ("normalize", C.c_int32), ("q_scale", C.c_float), ("norm_eps", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("dtype_out", C.c_int32), ("precise", C.c_int32),
-        ("v_scale", C.c_void_p), ("heads_q", C.c_int32), ("heads_k", C.c_int32),
+        ("v_scale", C.c_void_p), ("heads_q", C.c_int32), ("heads_k", C.c_int32), ("q_ld", C.c_int32), ("k_ld", C.c_int32),
     ]
 
 

@@ -660,12 +660,14 @@ __global__ void __launch_bounds__(256) linear_norm_kernel(void* __restrict__ o, 
 }
 
 inline int encode_rows3(CUtensorMap* tm, const void* base, int dtype, uint64_t cols, uint64_t rows, uint64_t outer,
-                        uint32_t box_rows = kLinT) {
+                        uint32_t box_rows = kLinT, uint64_t ld = 0) {
   TensorMapEncodeTiledFn enc = tensor_map_encoder();
   if (enc == nullptr) return ATTN_B200_E_LAUNCH;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return ATTN_B200_E_UNSUPPORTED;
+  if (ld == 0) ld = cols;
+  if (ld < cols || ld % 8 != 0) return ATTN_B200_E_UNSUPPORTED;
   cuuint64_t gdim[3] = {cols, rows, outer};
-  cuuint64_t gstride[2] = {cols * 2, cols * rows * 2};
+  cuuint64_t gstride[2] = {ld * 2, ld * rows * 2};
   cuuint32_t box[3] = {64, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = dtype == ATTN_B200_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -680,9 +682,10 @@ int launch_linear(const AttnB200LinearArgs* a, cudaStream_t stream, int* status)
   CUtensorMap tmQ, tmK, tmV, tmO;
   const uint64_t bh = static_cast<uint64_t>(a->batch) * a->heads;
   const int heads_q = a->heads_q > 0 ? a->heads_q : a->heads, heads_k = a->heads_k > 0 ? a->heads_k : a->heads;
-  int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, static_cast<uint64_t>(a->batch) * heads_q);
+  if (a->q_ld < 0 || a->k_ld < 0) return ATTN_B200_E_INVALID_ARG;
+  int rc = encode_rows3(&tmQ, a->q, a->dtype, DK, a->seq, static_cast<uint64_t>(a->batch) * heads_q, kLinT, a->q_ld);
   if (rc != ATTN_B200_OK) return rc;
-  rc = encode_rows3(&tmK, a->k, a->dtype, DK, a->seq, static_cast<uint64_t>(a->batch) * heads_k);
+  rc = encode_rows3(&tmK, a->k, a->dtype, DK, a->seq, static_cast<uint64_t>(a->batch) * heads_k, kLinT, a->k_ld);
   if (rc != ATTN_B200_OK) return rc;
   rc = encode_rows3(&tmV, a->v, a->dtype, a->dim_v, a->seq, bh);
   if (rc != ATTN_B200_OK) return rc;
