@@ -304,12 +304,14 @@ typedef struct AttnB200SoftmaxBwdArgs {
   void* dv;
   int32_t batch, heads, heads_kv, seq_q, seq_kv, dim_qk, dim_v;
   int32_t dtype;       /* ATTN_B200_DTYPE_* */
-  int32_t mask_kind;   /* ATTN_B200_MASK_NONE or ATTN_B200_MASK_CAUSAL (keep kv_idx <= q_idx) */
+  int32_t mask_kind;   /* ATTN_B200_MASK_NONE, ATTN_B200_MASK_CAUSAL (keep kv_idx <= q_idx) or ATTN_B200_MASK_BAND */
   float scale;         /* softmax scale */
   int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
   int64_t dq_stride[3], dk_stride[3], dv_stride[3];
   void* workspace;     /* attn_b200_softmax_bwd_workspace_bytes() bytes of device scratch, 16-byte aligned */
   int64_t workspace_bytes;
+  int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only, as in AttnB200ParallelArgs: tile pairs outside the band
+                                      are skipped in both launches */
 } AttnB200SoftmaxBwdArgs;
 
 /* Scratch the backward needs (delta = rowsum(dO o O) and the log-sum-exp in the exp2 domain, padded to whole
@@ -337,11 +339,12 @@ typedef struct AttnB200ElementwiseBwdArgs {
   void* dv;
   int32_t batch, heads, heads_kv, seq_q, seq_kv, dim_qk, dim_v;
   int32_t dtype;       /* ATTN_B200_DTYPE_* */
-  int32_t mask_kind;   /* ATTN_B200_MASK_NONE or ATTN_B200_MASK_CAUSAL */
+  int32_t mask_kind;   /* ATTN_B200_MASK_NONE, ATTN_B200_MASK_CAUSAL or ATTN_B200_MASK_BAND */
   int32_t reserved;
   int64_t q_stride[3], k_stride[3], v_stride[3], do_stride[3];
   int64_t dq_stride[3], dk_stride[3], dv_stride[3];
   const void* custom[ATTN_B200_MAX_CUSTOM];
+  int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only */
 } AttnB200ElementwiseBwdArgs;
 
 /* Reads and clears the device-side status word of device `device`

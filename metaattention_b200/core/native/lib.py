@@ -85,7 +85,7 @@ class SoftmaxBwdArgs(C.Structure):
         ("dim_qk", C.c_int32), ("dim_v", C.c_int32), ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("scale", C.c_float),
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
         ("do_stride", C.c_int64 * 3), ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64), ("mask_left", C.c_int32), ("mask_right", C.c_int32),
     ]
 
 
@@ -97,7 +97,7 @@ class ElementwiseBwdArgs(C.Structure):
         ("dim_qk", C.c_int32), ("dim_v", C.c_int32), ("dtype", C.c_int32), ("mask_kind", C.c_int32), ("reserved", C.c_int32),
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("do_stride", C.c_int64 * 3),
         ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
-        ("custom", C.c_void_p * MAX_CUSTOM),
+        ("custom", C.c_void_p * MAX_CUSTOM), ("mask_left", C.c_int32), ("mask_right", C.c_int32),
     ]
 
 
@@ -364,19 +364,20 @@ def _over_dim_v_slices(run, q, k, v, d_o, o=None):
     return dq.to(q.dtype), dk.to(k.dtype), torch.cat(dvs, dim=-1)
 
 
-def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
+def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band=(MASK_OPEN, MASK_OPEN)):
     """(dq, dk, dv) of softmax attention from the forward's o and lse [B, H, Sq] and the gradient of o
-    (attn_b200_softmax_bwd: mask NONE or CAUSAL, head dims 128 / 128 and 64 / 64; dim_v a larger multiple of dim_qk
-    as one run per column slice)."""
+    (attn_b200_softmax_bwd: mask NONE, CAUSAL or BAND with ``mask_band`` = (left, right); head dims 128 / 128 and
+    64 / 64; dim_v a larger multiple of dim_qk as one run per column slice)."""
     for t in (q, k, v, o, d_o, lse):
         if not t.is_cuda:
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
-    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _softmax_bwd_one(q_, k_, v_, o_, lse, do_, scale, mask_kind), q, k, v, d_o, o)
+    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _softmax_bwd_one(q_, k_, v_, o_, lse, do_, scale, mask_kind, mask_band),
+                              q, k, v, d_o, o)
 
 
-def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
+def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band):
     for t in (q, k, v, o):
         if t.stride(-1) != 1:
             raise NativeError("last dimension must be contiguous")
@@ -392,6 +393,7 @@ def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
     B, Sq, H, D = q.shape
     a.batch, a.heads, a.heads_kv, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, k.shape[2], Sq, k.shape[1], D, v.shape[3]
     a.dtype, a.mask_kind, a.scale = DTYPE_CODES[q.dtype], mask_kind, float(scale)
+    a.mask_left, a.mask_right = int(mask_band[0]), int(mask_band[1])
     for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", d_o), ("dq", dq), ("dk", dk), ("dv", dv)):
         getattr(a, name + "_stride")[:] = _strides_bsh(t)
     lib = load_library()
@@ -405,7 +407,7 @@ def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int):
     return dq, dk, dv
 
 
-def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=()):
+def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=(), mask_band=(MASK_OPEN, MASK_OPEN)):
     """(dq, dk, dv) of an elementwise program through its functor library's ``attn_b200_elementwise_bwd_jit`` (``fn``);
     ``custom``: the program's fp32 scalar inputs, as device tensors.  dim_v may be a multiple of dim_qk."""
     for t in (q, k, v, d_o, *custom):
@@ -413,10 +415,11 @@ def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=()):
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
-    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _elementwise_bwd_one(fn, q_, k_, v_, do_, mask_kind, custom), q, k, v, d_o)
+    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _elementwise_bwd_one(fn, q_, k_, v_, do_, mask_kind, custom, mask_band),
+                              q, k, v, d_o)
 
 
-def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom=()):
+def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom, mask_band):
     if q.dtype not in DTYPE_CODES or any(t.dtype != q.dtype for t in (k, v, d_o)):
         raise NativeError("q, k, v, d_o must share dtype float16 or bfloat16")
     dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))
@@ -427,6 +430,7 @@ def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom=()):
     B, Sq, H, D = q.shape
     a.batch, a.heads, a.heads_kv, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, k.shape[2], Sq, k.shape[1], D, v.shape[3]
     a.dtype, a.mask_kind = DTYPE_CODES[q.dtype], mask_kind
+    a.mask_left, a.mask_right = int(mask_band[0]), int(mask_band[1])
     for name, t in (("q", q), ("k", k), ("v", v), ("do", d_o), ("dq", dq), ("dk", dk), ("dv", dv)):
         getattr(a, name + "_stride")[:] = _strides_bsh(t)
     for i, t in enumerate(custom):

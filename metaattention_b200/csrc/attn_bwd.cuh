@@ -30,6 +30,7 @@
 #pragma once
 
 #include <cstring>
+#include <type_traits>
 
 #include "../../include/attn_b200.h"
 #include "common_host.cuh"
@@ -52,7 +53,7 @@ struct BwdParams {
   const float* lse2;    // [batch, heads, seq_q_pad] lse * log2(e); +inf past seq_q (those rows get P = 0)
   const float* delta;   // [batch, heads, seq_q_pad]
   int batch, heads, heads_kv, kv_group, seq_q, seq_kv, seq_q_pad;
-  int causal;
+  int mask_left, mask_right;   // keep q_idx - mask_left <= kv_idx <= q_idx + mask_right; ATTN_B200_MASK_OPEN = no bound
   float scale;
   long long dq_s[3], dk_s[3], dv_s[3];   // element strides (batch, seq, head)
   CoordOrder oq, ok, ov, odo;
@@ -139,11 +140,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const AbortState ab{abort_flag, p.status};
   const int tile = blockIdx.x, hx = blockIdx.y, b = blockIdx.z;
   const int nq = (p.seq_q + T - 1) / T, nk = (p.seq_kv + T - 1) / T;
-  // the streamed tiles: KV tiles [0, n_iter) for a query tile; for a KV tile the query tiles [i0, nq) of every
-  // query head of its group, head after head
-  const int i0 = p.causal ? tile : 0;
-  const int per_head = kRoleQ ? 0 : max(nq - i0, 0);
-  const int n_iter = kRoleQ ? (p.causal ? min(nk, tile + 1) : nk) : p.kv_group * per_head;
+  // The streamed tiles are those the band q_idx - left <= kv_idx <= q_idx + right lets the resident tile meet: KV tiles
+  // [j0, j0 + n_iter) for a query tile; for a KV tile the query tiles [i0, i0 + per_head) of every query head of its
+  // group, head after head.  (No mask: both sides open; causal: left open, right 0.)
+  const long long r0 = static_cast<long long>(tile) * T, r1 = r0 + T - 1;   // rows of the resident tile
+  const int i0 = static_cast<int>(max(r0 - p.mask_right, 0LL) / T);
+  const int i1 = static_cast<int>(min(static_cast<long long>(nq) - 1, (r1 + p.mask_left) / T));
+  const int j0 = static_cast<int>(max(r0 - p.mask_left, 0LL) / T);
+  const int j1 = static_cast<int>(min(static_cast<long long>(nk) - 1, (r1 + p.mask_right) / T));
+  const int per_head = kRoleQ ? 0 : max(i1 - i0 + 1, 0);
+  const int n_iter = kRoleQ ? max(j1 - j0 + 1, 0) : p.kv_group * per_head;
 
   if (tid == 0) {
     *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -208,7 +214,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive_expect_tx(y1_full + s1, L::kTileBytes + ((!kRoleQ && F::kUsesStats) ? L::kStatBytes : 0));
         for (int c = 0; c < KC; ++c) {
           if constexpr (kRoleQ) {
-            tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y1_full + s1, c * 64, it * T, hk, b, p.ok);
+            tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y1_full + s1, c * 64, (j0 + it) * T, hk, b, p.ok);
           } else {
             tma_load_rows(y1 + c * L::kChunkBytes, &tmQ, y1_full + s1, c * 64, i * T, hq, b, p.oq);
           }
@@ -218,7 +224,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive_expect_tx(y2_full + s2, L::kTileBytes + ((!kRoleQ && F::kUsesStats) ? L::kStatBytes : 0));
         for (int c = 0; c < KC; ++c) {
           if constexpr (kRoleQ) {
-            tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y2_full + s2, c * 64, it * T, hk, b, p.ov);
+            tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y2_full + s2, c * 64, (j0 + it) * T, hk, b, p.ov);
           } else {
             tma_load_rows(y2 + c * L::kChunkBytes, &tmDO, y2_full + s2, c * 64, i * T, hq, b, p.odo);
           }
@@ -317,12 +323,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       lse2_r = p.lse2[idx];
       delta_r = p.delta[idx];
     }
-    // P and g of one element.  Causal: keep kv <= q (KV role: lanes are KV rows, columns query rows; query role the
-    // other way round); a functor whose P vanishes at a score of -inf (softmax) gets the mask through the score
-    auto score_of = [&](float s, float l2, bool diag, int ys, int hq, int col, float& pr, float& g) {
+    // P and g of one element.  KV role: lanes are KV rows, columns query rows; query role the other way round.  The
+    // band keeps, for this thread's row, the columns [col_lo, col_hi] of the tile (set per streamed tile; everything
+    // when no edge of the band crosses the pair); a functor whose P vanishes at a score of -inf (softmax) gets the mask
+    // through the score
+    int col_lo = 0, col_hi = T;
+    auto score_of = [&](auto edge_tile, float s, float l2, int ys, int hq, int col, float& pr, float& g) {
       const int q_idx = kRoleQ ? tile * T + row : ys * T + col;
       const int kv_idx = kRoleQ ? ys * T + col : tile * T + row;
-      const bool masked = diag && (kRoleQ ? (col > row) : (col < row));
+      const bool masked = decltype(edge_tile)::value && (col < col_lo || col > col_hi);
       F::score((F::kNegInfMask && masked) ? -INFINITY : s, l2, fctx, b, hq, q_idx, kv_idx, pr, g);
       if (!F::kNegInfMask && masked) pr = g = 0.0f;
     };
@@ -333,36 +342,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     };
     bool ok = start_ok;
     for (int it = 0; ok && it < n_iter; ++it) {
-      // the streamed tile index, its query head, and whether it meets the resident tile on the diagonal of a causal mask
-      const int ys = kRoleQ ? it : i0 + it % max(per_head, 1);
+      // the streamed tile index, its query head, and whether an edge of the band crosses this pair of tiles
+      const int ys = kRoleQ ? j0 + it : i0 + it % max(per_head, 1);
       const int hq = kRoleQ ? hx : hx * p.kv_group + it / max(per_head, 1);
-      const bool diag = p.causal && ys == tile;
+      // Pairs of tiles that an edge of the band crosses take a second copy of the row loops, with the mask: the row
+      // phases sit on the kernel's serial chain, and two compares per element on every tile cost 15 %
+      const long long q0 = static_cast<long long>(kRoleQ ? tile : ys) * T, k0 = static_cast<long long>(kRoleQ ? ys : tile) * T;
+      const bool edge = (k0 + T - 1 > q0 + p.mask_right) || (k0 + p.mask_left < q0 + T - 1);
+      if (edge) {
+        // kv - q of (row, col) is base + col (query role) or base - col (KV role); kept where -left <= kv - q <= right
+        const long long base = kRoleQ ? k0 - q0 - row : k0 - q0 + row;
+        const long long lo = kRoleQ ? -static_cast<long long>(p.mask_left) - base : base - p.mask_right;
+        const long long hi = kRoleQ ? static_cast<long long>(p.mask_right) - base : base + p.mask_left;
+        col_lo = static_cast<int>(max(lo, 0LL));
+        col_hi = static_cast<int>(min(hi, static_cast<long long>(T)));
+      }
       if constexpr (kRoleQ) {
         ok = mbar_wait(s_done, it & 1, ab, kBwdSDone);
         if (!ok) break;
         tc_fence_after_sync();
         uint32_t pds[32];
+        auto rows_q = [&](auto edge_tile) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c0 = wg * 64 + u * 32;
-          float s[32], dp[32];
-          tmem_ld32f(tS + c0, s);
-          tmem_ld32f(tDP + c0, dp);
-          tmem_wait_ld();
-          if (u == 1) {   // this tile's S and dP are in registers: the next tile's may be computed
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sdp_free);
+          for (int u = 0; u < 2; ++u) {
+            const int c0 = wg * 64 + u * 32;
+            float s[32], dp[32];
+            tmem_ld32f(tS + c0, s);
+            tmem_ld32f(tDP + c0, dp);
+            tmem_wait_ld();
+            if (u == 1) {   // this tile's S and dP are in registers: the next tile's may be computed
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(sdp_free);
+            }
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              float pr, g;
+              score_of(edge_tile, s[k], lse2_r, ys, hq, c0 + k, pr, g);
+              dp[k] = F::grad(g, dp[k], delta_r, fctx);
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k) pds[u * 16 + k] = pack2<kBf16>(dp[2 * k], dp[2 * k + 1]);
           }
-#pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            float pr, g;
-            score_of(s[k], lse2_r, diag, ys, hq, c0 + k, pr, g);
-            dp[k] = F::grad(g, dp[k], delta_r, fctx);
-          }
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pds[u * 16 + k] = pack2<kBf16>(dp[2 * k], dp[2 * k + 1]);
-        }
+        };
+        if (edge) rows_q(std::true_type{});
+        else rows_q(std::false_type{});
         tmem_st32(tmem_base + lane_base + kColDS + (it & 1) * 64 + wg * 32, pds);
         tmem_wait_st();
         tc_fence_before_sync();
@@ -378,21 +402,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float* st_delta = sDelta + (it % N2) * T;
         float g[64];
         uint32_t pk[32];
+        auto rows_p = [&](auto edge_tile) {
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c0 = wg * 64 + u * 32;
-          float s[32];
-          tmem_ld32f(tS + c0, s);
-          tmem_wait_ld();
+          for (int u = 0; u < 2; ++u) {
+            const int c0 = wg * 64 + u * 32;
+            float s[32];
+            tmem_ld32f(tS + c0, s);
+            tmem_wait_ld();
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            float pr;
-            score_of(s[k], F::kUsesStats ? stat_of(st_lse + c0, k) : 0.0f, diag, ys, hq, c0 + k, pr, g[u * 32 + k]);
-            s[k] = pr;
+            for (int k = 0; k < 32; ++k) {
+              float pr;
+              score_of(edge_tile, s[k], F::kUsesStats ? stat_of(st_lse + c0, k) : 0.0f, ys, hq, c0 + k, pr, g[u * 32 + k]);
+              s[k] = pr;
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k) pk[u * 16 + k] = pack2<kBf16>(s[2 * k], s[2 * k + 1]);
           }
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pk[u * 16 + k] = pack2<kBf16>(s[2 * k], s[2 * k + 1]);
-        }
+        };
+        if (edge) rows_p(std::true_type{});
+        else rows_p(std::false_type{});
         // the 16-bit pairs of columns [64 wg, 64 wg + 64) go to 32-bit columns [32 wg, 32 wg + 32), which the other warp
         // of this lane quarter reads as fp32: both must have their values in registers first
         tc_fence_before_sync();
@@ -494,7 +522,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 struct BwdCall {
   const void *q, *k, *v, *d_o;
   void *dq, *dk, *dv;
-  int batch, heads, heads_kv, seq_q, seq_kv, dim, dtype, causal;
+  int batch, heads, heads_kv, seq_q, seq_kv, dim, dtype, mask_left, mask_right;
   float scale;
   const int64_t *q_stride, *k_stride, *v_stride, *do_stride, *dq_stride, *dk_stride, *dv_stride;
   const float* lse2;
@@ -531,7 +559,8 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
   p.seq_q = a.seq_q;
   p.seq_kv = a.seq_kv;
   p.seq_q_pad = nq * T;
-  p.causal = a.causal;
+  p.mask_left = a.mask_left;
+  p.mask_right = a.mask_right;
   p.scale = a.scale;
   for (int i = 0; i < 3; ++i) {
     p.dq_s[i] = a.dq_stride[i];
@@ -552,6 +581,23 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
   q_kernel<<<dim3(nq, a.heads, a.batch), kBwdThreads, L::kBytes, stream>>>(tmQ, tmK, tmV, tmDO, p);
   if (cudaGetLastError() != cudaSuccess) return ATTN_B200_E_LAUNCH;
   return ATTN_B200_OK;
+}
+
+// mask_kind and the band of an argument struct as the two band sides of a call; false = not a mask the backward covers
+inline bool bwd_mask_of(int mask_kind, int left, int right, BwdCall& call) {
+  if (mask_kind == ATTN_B200_MASK_NONE) {
+    call.mask_left = call.mask_right = ATTN_B200_MASK_OPEN;
+  } else if (mask_kind == ATTN_B200_MASK_CAUSAL) {
+    call.mask_left = ATTN_B200_MASK_OPEN;
+    call.mask_right = 0;
+  } else if (mask_kind == ATTN_B200_MASK_BAND) {
+    if (left < 0 || right < 0 || left > ATTN_B200_MASK_OPEN || right > ATTN_B200_MASK_OPEN) return false;
+    call.mask_left = left;
+    call.mask_right = right;
+  } else {
+    return false;
+  }
+  return true;
 }
 
 // Checks shared by every backward entry point (pointers, dims, strides, alignment of the outputs).

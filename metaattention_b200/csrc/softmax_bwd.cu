@@ -114,13 +114,12 @@ int64_t attn_b200_softmax_bwd_workspace_bytes(const AttnB200SoftmaxBwdArgs* a) {
 int attn_b200_softmax_bwd(const AttnB200SoftmaxBwdArgs* a, void* cuda_stream) {
   if (a == nullptr || a->o == nullptr || a->lse == nullptr) return ATTN_B200_E_INVALID_ARG;
   if (a->dim_qk != a->dim_v) return ATTN_B200_E_UNSUPPORTED;
-  if (a->mask_kind != ATTN_B200_MASK_NONE && a->mask_kind != ATTN_B200_MASK_CAUSAL) return ATTN_B200_E_UNSUPPORTED;
   b200::BwdCall call{};
+  if (!b200::bwd_mask_of(a->mask_kind, a->mask_left, a->mask_right, call)) return ATTN_B200_E_UNSUPPORTED;
   call.q = a->q; call.k = a->k; call.v = a->v; call.d_o = a->d_o;
   call.dq = a->dq; call.dk = a->dk; call.dv = a->dv;
   call.batch = a->batch; call.heads = a->heads; call.heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;
   call.seq_q = a->seq_q; call.seq_kv = a->seq_kv; call.dim = a->dim_qk; call.dtype = a->dtype;
-  call.causal = a->mask_kind == ATTN_B200_MASK_CAUSAL ? 1 : 0;
   call.scale = a->scale;
   call.q_stride = a->q_stride; call.k_stride = a->k_stride; call.v_stride = a->v_stride; call.do_stride = a->do_stride;
   call.dq_stride = a->dq_stride; call.dk_stride = a->dk_stride; call.dv_stride = a->dv_stride;

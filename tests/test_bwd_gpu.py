@@ -224,3 +224,61 @@ def test_relu_attention():
     torch.cuda.synchronize()
     for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
         check(got, want, what)
+
+
+@pytest.mark.parametrize("left,right,Sq,Skv", [(127, 0, 700, 700),      # the sliding window of the reference's tracing test
+                                               (200, 0, 512, 512),      # window edges inside tiles
+                                               (64, 32, 400, 400),      # a band around the diagonal
+                                               (300, 300, 384, 640)])   # wide band, more keys than queries
+def test_band_masks_against_oracle(left, right, Sq, Skv):
+    """Sliding windows (ATTN_B200_MASK_BAND, keep q - left <= kv <= q + right): tile pairs outside the band are skipped
+    in both launches, pairs an edge crosses are masked element by element; against autograd over the oracle with the
+    same keep matrix (the reference's backward applies any mask_mod element-wise, attn_tl.py:430-461)."""
+    from core.native import lib
+    B, H, D, dtype = 1, 2, 128, torch.bfloat16
+    g = torch.Generator().manual_seed(left * 7 + right)
+    q = torch.randn(B, Sq, H, D, generator=g).to(dtype)
+    k = torch.randn(B, Skv, H, D, generator=g).to(dtype)
+    v = torch.randn(B, Skv, H, D, generator=g).to(dtype)
+    d_o = torch.randn(B, Sq, H, D, generator=g).to(dtype)
+    scale = D ** -0.5
+    qi, ki = torch.arange(Sq)[:, None], torch.arange(Skv)[None, :]
+    keep = (ki >= qi - left) & (ki <= qi + right)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        rm.softmax_attention(qf, kf, vf, False, scale, keep=keep).backward(d_o.float())
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o = torch.empty_like(qc)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device="cuda")
+    args = lib.fill_parallel_args(qc, kc, vc, o, mask_kind=lib.MASK_BAND, mask_band=(left, right), functor=lib.FUNCTOR_SOFTMAX,
+                                  fparams=(scale,), final_rowscales=[lse])
+    lib.parallel_fwd(args)
+    dq, dk, dv = lib.softmax_bwd(qc, kc, vc, o, lse, d_o.cuda(), scale, lib.MASK_BAND, (left, right))
+    torch.cuda.synchronize()
+    assert lib.last_device_status() == 0
+    check(dq, qf.grad, "dq")
+    check(dk, kf.grad, "dk")
+    check(dv, vf.grad, "dv")
+
+
+def test_sliding_window_engine_autograd():
+    """A traced mask_mod that is a sliding window (attention_engine/tests/test_torchtrace.py:5-6) with softmax: the
+    engine classifies it as a band and differentiates it."""
+    from examples_b200 import programs
+    B, H, S, D = 1, 2, 520, 128
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 51)
+    d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(52)).to(torch.bfloat16)
+    qi, ki = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    keep = (qi >= ki) & (qi < ki + 128)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        ref = rm.softmax_attention(qf, kf, vf, False, D ** -0.5, keep=keep)
+        ref.backward(d_o.float())
+    eng = programs.masked_softmax_engine(B, H, S, D, D, programs.sliding_window_mask)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qc, kc, vc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    check(o.detach(), ref.detach(), "o")
+    for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
+        check(got, want, what)
