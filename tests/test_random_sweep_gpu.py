@@ -97,3 +97,89 @@ def test_random_sweep(seed):
             _linear_case(rnd, g)
         else:
             _attention_case(rnd, g, kind)
+
+
+def _grad_close(kind, cfg, got, want, frac_max=2e-2, frac_mean=3e-3):
+    """Gradients (16-bit against fp32): max-abs 2e-2 of the expected tensor's largest value, mean-abs 3e-3 of 1.5 x its
+    spread, each at least 1 (tests/test_bwd_gpu.py and tests/test_linear_bwd_gpu.py say why the scales are needed)."""
+    got = got.float().cpu()
+    assert torch.isfinite(got).all(), (kind, cfg)
+    d = (got - want.float()).abs()
+    assert d.max().item() <= frac_max * max(1.0, want.abs().max().item()), (kind, cfg, d.max().item(), want.abs().max().item())
+    assert d.mean().item() <= frac_mean * max(1.0, 1.5 * want.std().item()), (kind, cfg, d.mean().item(), want.std().item())
+
+
+def _attention_backward_case(rnd, g):
+    D = rnd.choice([64, 128])
+    Dv = D * rnd.choice([1, 1, 2]) if D == 128 else D      # the forward covers dim_v = k x 128 only with dim_qk 128
+    dt = rnd.choice([torch.bfloat16, torch.float16])
+    B, Hkv = rnd.randint(1, 2), rnd.randint(1, 3)
+    H = Hkv * rnd.choice([1, 1, 2])
+    Sq = rnd.choice([100, 128, 257, 384, 700])
+    Skv = Sq if rnd.random() < 0.7 else rnd.choice([200, 512, 900])
+    mask = rnd.choice(["none", "causal", "band"]) if Sq == Skv else rnd.choice(["none", "band"])
+    q = torch.randn(B, Sq, H, D, generator=g).to(dt)
+    k = torch.randn(B, Skv, Hkv, D, generator=g).to(dt)
+    v = torch.randn(B, Skv, Hkv, Dv, generator=g).to(dt)
+    d_o = torch.randn(B, Sq, H, Dv, generator=g).to(dt)
+    qi, ki = torch.arange(Sq).view(-1, 1), torch.arange(Skv).view(1, -1)
+    left, right = lib.MASK_OPEN, lib.MASK_OPEN
+    if mask == "causal":
+        keep, kind_code = ki <= qi, lib.MASK_CAUSAL
+    elif mask == "band":
+        left = rnd.choice([0, 5, 64, 127, 200, lib.MASK_OPEN])
+        right = rnd.choice([0, 0, 3, 100, lib.MASK_OPEN]) if Sq == Skv else rnd.choice([Skv, lib.MASK_OPEN])
+        keep, kind_code = (ki >= qi - left) & (ki <= qi + right), lib.MASK_BAND
+    else:
+        keep, kind_code = torch.ones(Sq, Skv, dtype=torch.bool), lib.MASK_NONE
+    scale = D ** -0.5
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        rm.softmax_attention(qf, kf, vf, False, scale, keep=keep).backward(d_o.float())
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    o = torch.empty((B, Sq, H, Dv), dtype=dt, device="cuda")
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device="cuda")
+    lib.parallel_fwd(lib.fill_parallel_args(qc, kc, vc, o, mask_kind=kind_code, mask_band=(left, right), functor=lib.FUNCTOR_SOFTMAX,
+                                            fparams=(scale,), final_rowscales=[lse]))
+    dq, dk, dv = lib.softmax_bwd(qc, kc, vc, o, lse, d_o.cuda(), scale, kind_code, (left, right))
+    torch.cuda.synchronize()
+    cfg = (B, H, Hkv, Sq, Skv, D, Dv, dt, mask, left, right)
+    assert lib.last_device_status() == 0, cfg
+    for got, want, what in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
+        _grad_close("attention backward " + what, cfg, got, want)
+
+
+def _linear_backward_case(rnd, g):
+    from attn_engine.linear_attn_engine import linear_attention_backward
+    B, H = rnd.randint(1, 2), rnd.randint(1, 3)
+    S = rnd.choice([100, 128, 257, 400])
+    Dk, Dv = rnd.choice([64, 128, 256]), rnd.choice([128, 256, 384, 512])
+    dt = rnd.choice([torch.bfloat16, torch.float16])
+    q = torch.randn(B, H, S, Dk, generator=g).to(dt)
+    k = (torch.randn(B, H, S, Dk, generator=g) * Dk ** -0.5).to(dt)
+    v = torch.randn(B, H, S, Dv, generator=g).to(dt)
+    d_o = torch.randn(B, H, S, Dv, generator=g).to(dt)
+    log_decay = -torch.rand(B, H, S, generator=g) * rnd.choice([0.02, 0.1, 0.5])
+    with_dg = rnd.random() < 0.5
+    want = rm.decayed_linear_attention_grads(q, k, v, log_decay, d_o, scale=Dk ** -0.5, with_decay=with_dg)
+    got = linear_attention_backward(q.cuda(), k.cuda(), v.cuda(), log_decay.cuda(), d_o.cuda(), q_scale=Dk ** -0.5, need_dg=with_dg)
+    torch.cuda.synchronize()
+    cfg = (B, H, S, Dk, Dv, dt, with_dg)
+    assert lib.last_device_status() == 0, cfg
+    for gt, w, what in zip(got, want, ("dq", "dk", "dv", "dg")):
+        if what == "dg":    # a running sum of differences of sums: looser (tests/test_linear_bwd_gpu.py::check_decay_grad)
+            _grad_close("linear backward dg", cfg, gt, w, frac_max=1e-1, frac_mean=2e-2)
+        else:
+            _grad_close("linear backward " + what, cfg, gt, w)
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_sweep_backward(seed):
+    """The backward kernels over random shapes, dtypes, head groups, ragged lengths and masks (none, causal, bands)."""
+    rnd = random.Random(seed)
+    for _ in range(14):
+        g = torch.Generator().manual_seed(rnd.randrange(1 << 30))
+        if rnd.random() < 0.65:
+            _attention_backward_case(rnd, g)
+        else:
+            _linear_backward_case(rnd, g)
