@@ -395,7 +395,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else {
         // ---- S -> P (and g, kept in registers for the second half) ----
         if constexpr (F::kUsesStats) ok = mbar_wait(y1_full + it % N1, (it / N1) & 1, ab, kBwdYFull);   // lse came with the tile
-        ok = mbar_wait(s_done, it & 1, ab, kBwdSDone) && ok;
+        ok = mbar_wait_poll(s_done, it & 1, ab, kBwdSDone) && ok;
         if (!ok) break;
         tc_fence_after_sync();
         const float* st_lse = sLse + (it % N1) * T;
