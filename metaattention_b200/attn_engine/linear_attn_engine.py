@@ -197,18 +197,17 @@ def _sum_cast(parts, dtype, reverse=False):
     return out.flip(2) if reverse else out
 
 
-def _retention_parts(qc, kc, vc, log_decay, q_scale, precise=False, reverse_in=False):
+def _retention_parts(qc, kc, vc, log_decay, q_scale, precise=False):
     """o_i = q_scale * sum_{j<=i} exp(G_i - G_j) (qc_i . kc_j) vc_j on the forward kernel with fp32 output, for any width
     of the contraction, as a list of partial results to be added: the sum is linear in the scores, so a contraction
     wider than the kernel's 256 columns is the sum over column ranges it does cover (widths 256 / 128 / 64, the last one
-    zero-padded).  ``reverse_in``: qc and kc are given in forward time and are reversed while their column ranges are
-    cut out (vc is taken as it is)."""
+    zero-padded).  The kernel reads the column ranges of qc and kc in place."""
     D = qc.shape[-1]
     parts, start = [], 0
     while start < D:
         width = next((w for w in (256, 128, 64) if D - start >= w), 64)
         have = min(width, D - start)
-        qs, ks = _rows(qc, start, have, reverse_in), _rows(kc, start, have, reverse_in)
+        qs, ks = _rows(qc, start, have), _rows(kc, start, have)
         if have < width:
             qs, ks = torch.nn.functional.pad(qs, (0, width - have)), torch.nn.functional.pad(ks, (0, width - have))
         parts.append(linear_attention_forward(qs, ks, vc, log_decay, q_scale, out_dtype=torch.float32, precise=precise))
@@ -244,7 +243,9 @@ def linear_attention_backward(q, k, v, log_decay, d_o, q_scale: float = 1.0, nee
     qr, kr, dr = _rows(q, reverse=True), _rows(k, reverse=True), _rows(d_o, reverse=True)
     # dv: dim_qk fits the kernel, so it is one run that leaves the kernel in the operands' dtype
     dv = _rows(linear_attention_forward(kr, qr, dr, ld_rev, q_scale), reverse=True)
-    dk_parts = _retention_parts(v, d_o, qr, ld_rev, q_scale, precise=need_dg, reverse_in=True)
+    # dk contracts over column ranges of the reversed v and dO: dO is reversed already (whole, for dv) and v is reversed
+    # once; the kernel reads the ranges in place
+    dk_parts = _retention_parts(_rows(v, reverse=True), dr, qr, ld_rev, q_scale, precise=need_dg)
     dk = _sum_cast(dk_parts, k.dtype, reverse=True)
     if not need_dg:
         return dq, dk, dv
