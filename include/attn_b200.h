@@ -43,6 +43,8 @@ extern "C" {
 #define ATTN_B200_MASK_NONE 0
 #define ATTN_B200_MASK_CAUSAL 1        /* keep q_idx >= kv_idx (top-left aligned)           */
 #define ATTN_B200_MASK_BAND 2          /* keep q_idx - mask_left <= kv_idx <= q_idx + mask_right (sliding windows) */
+#define ATTN_B200_MASK_BITS 3          /* backward entry points only: any mask that does not depend on batch or head, as
+                                          keep bits (mask_bits_q / mask_bits_kv of the argument structs) */
 #define ATTN_B200_MASK_OPEN 0x3fffffff /* value of mask_left / mask_right for a side without a bound */
 
 /* Built-in functors of the parallel pattern (score_mod + online_func pairs
@@ -304,7 +306,7 @@ typedef struct AttnB200SoftmaxBwdArgs {
   void* dv;
   int32_t batch, heads, heads_kv, seq_q, seq_kv, dim_qk, dim_v;
   int32_t dtype;       /* ATTN_B200_DTYPE_* */
-  int32_t mask_kind;   /* ATTN_B200_MASK_NONE, ATTN_B200_MASK_CAUSAL (keep kv_idx <= q_idx) or ATTN_B200_MASK_BAND */
+  int32_t mask_kind;   /* ATTN_B200_MASK_NONE, _CAUSAL (keep kv_idx <= q_idx), _BAND or _BITS */
   float scale;         /* softmax scale */
   int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
   int64_t dq_stride[3], dk_stride[3], dv_stride[3];
@@ -312,6 +314,14 @@ typedef struct AttnB200SoftmaxBwdArgs {
   int64_t workspace_bytes;
   int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only, as in AttnB200ParallelArgs: tile pairs outside the band
                                       are skipped in both launches */
+  /* ATTN_B200_MASK_BITS only (device, 16-byte aligned): the keep matrix of the mask and its transpose as bits, for the
+   * launch that owns query rows and the one that owns KV rows.  With nq, nk = 128-row tiles of seq_q, seq_kv:
+   * mask_bits_q uint32 [nq*128][nk][4]: bit (c & 31) of word c >> 5 of [q][j] = keep (q, 128 j + c);
+   * mask_bits_kv uint32 [nk*128][nq][4]: bit (c & 31) of word c >> 5 of [kv][i] = keep (128 i + c, kv);
+   * rows and columns past the sequence ends are 0.  Every pair of tiles is visited (the reference's backward applies
+   * mask_mod element-wise to every tile as well, attn_tl.py:430-461). */
+  const void* mask_bits_q;
+  const void* mask_bits_kv;
 } AttnB200SoftmaxBwdArgs;
 
 /* Scratch the backward needs (delta = rowsum(dO o O) and the log-sum-exp in the exp2 domain, padded to whole
@@ -339,12 +349,14 @@ typedef struct AttnB200ElementwiseBwdArgs {
   void* dv;
   int32_t batch, heads, heads_kv, seq_q, seq_kv, dim_qk, dim_v;
   int32_t dtype;       /* ATTN_B200_DTYPE_* */
-  int32_t mask_kind;   /* ATTN_B200_MASK_NONE, ATTN_B200_MASK_CAUSAL or ATTN_B200_MASK_BAND */
+  int32_t mask_kind;   /* ATTN_B200_MASK_NONE, _CAUSAL, _BAND or _BITS */
   int32_t reserved;
   int64_t q_stride[3], k_stride[3], v_stride[3], do_stride[3];
   int64_t dq_stride[3], dk_stride[3], dv_stride[3];
   const void* custom[ATTN_B200_MAX_CUSTOM];
   int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only */
+  const void* mask_bits_q;         /* ATTN_B200_MASK_BITS only, as in AttnB200SoftmaxBwdArgs */
+  const void* mask_bits_kv;
 } AttnB200ElementwiseBwdArgs;
 
 /* Reads and clears the device-side status word of device `device`

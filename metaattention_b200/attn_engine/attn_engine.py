@@ -106,7 +106,8 @@ class _SoftmaxAttention(torch.autograd.Function):
     def backward(ctx, d_o):
         q, k, v, o, lse = ctx.saved_tensors
         eng = ctx.engine
-        dq, dk, dv = native.softmax_bwd(q, k, v, o, lse, d_o.to(q.dtype), eng._fparams[0], eng.mask_kind, eng.mask_band)
+        dq, dk, dv = native.softmax_bwd(q, k, v, o, lse, d_o.to(q.dtype), eng._fparams[0], eng.mask_kind, eng.mask_band,
+                                        eng._mask_bits(q.device))
         return None, dq, dk, dv
 
 
@@ -129,7 +130,8 @@ class _ElementwiseAttention(torch.autograd.Function):
         eng = ctx.engine
         if eng._bwd_fn is None:
             eng._bwd_fn = native_jit.load_backward(eng._bwd_source)
-        dq, dk, dv = native.elementwise_bwd(eng._bwd_fn, q, k, v, d_o.to(q.dtype), eng.mask_kind, custom, eng.mask_band)
+        dq, dk, dv = native.elementwise_bwd(eng._bwd_fn, q, k, v, d_o.to(q.dtype), eng.mask_kind, custom, eng.mask_band,
+                                            eng._mask_bits(q.device))
         return (None, None, dq, dk, dv) + (None,) * len(custom)
 
 
@@ -318,17 +320,25 @@ class AttentionEngine:
         return run(q, k, v, *custom)
 
     def _masked_for_backward(self) -> bool:
+        """Masks the backward kernels take: none, causal, bands, and any other mask_mod that does not use the batch or
+        head index (as keep bits)."""
         return (self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL, native.MASK_BAND) and self._decode_block is None and
-                self._sparse_host is None)
+                (self._sparse_host is None or "bits_q" in self._sparse_host))
+
+    def _mask_bits(self, device):
+        """(bits_q, bits_kv) on ``device`` for a general mask_mod, else None."""
+        if self._sparse_host is None or "bits_q" not in self._sparse_host:
+            return None
+        if device not in self._sparse_dev:
+            self._sparse_dev[device] = sparse_lowering.to_device(self._sparse_host, device)
+        return self._sparse_dev[device]["bits_q"], self._sparse_dev[device]["bits_kv"]
 
     def has_backward(self, q, v) -> bool:
         """Whether gradients flow through this engine for these operands: the built-in softmax (a traced program that
-        is softmax attention with a probed scale), no mask, a causal one or a band (sliding windows), dim_qk 128 or 64
-        and dim_v a multiple of it (the 128 / 256 of the reference's suite runs as one backward per 128-column slice of
-        v)."""
-        return (self.functor_kind == "builtin_softmax" and
-                self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL, native.MASK_BAND) and
-                self._decode_block is None and self._sparse_host is None and len(self.final_names) == 1 and
+        is softmax attention with a probed scale), no mask, a causal one, a band (sliding windows) or any other mask_mod
+        that does not use the batch or head index, dim_qk 128 or 64 and dim_v a multiple of it (the 128 / 256 of the
+        reference's suite runs as one backward per 128-column slice of v)."""
+        return (self.functor_kind == "builtin_softmax" and self._masked_for_backward() and len(self.final_names) == 1 and
                 q.shape[-1] in (64, 128) and v.shape[-1] % q.shape[-1] == 0)
 
     def _custom_operands(self, custom, B, H, Sq, Skv, device):

@@ -39,6 +39,7 @@ ERRORS = {
 DTYPE_CODES = {torch.float16: 0, torch.bfloat16: 1}
 DTYPE_OUT_SAME, DTYPE_OUT_FP32 = 0, 2
 MASK_NONE, MASK_CAUSAL, MASK_BAND = 0, 1, 2
+MASK_BITS = 3            # backward only: any mask without batch / head dependence, as keep bits
 MASK_OPEN = 0x3fffffff   # mask_left / mask_right of a band side without a bound
 FUNCTOR_SOFTMAX = 0
 
@@ -86,6 +87,7 @@ class SoftmaxBwdArgs(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
         ("do_stride", C.c_int64 * 3), ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64), ("mask_left", C.c_int32), ("mask_right", C.c_int32),
+        ("mask_bits_q", C.c_void_p), ("mask_bits_kv", C.c_void_p),
     ]
 
 
@@ -98,6 +100,7 @@ class ElementwiseBwdArgs(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("do_stride", C.c_int64 * 3),
         ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
         ("custom", C.c_void_p * MAX_CUSTOM), ("mask_left", C.c_int32), ("mask_right", C.c_int32),
+        ("mask_bits_q", C.c_void_p), ("mask_bits_kv", C.c_void_p),
     ]
 
 
@@ -364,20 +367,32 @@ def _over_dim_v_slices(run, q, k, v, d_o, o=None):
     return dq.to(q.dtype), dk.to(k.dtype), torch.cat(dvs, dim=-1)
 
 
-def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band=(MASK_OPEN, MASK_OPEN)):
+def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band=(MASK_OPEN, MASK_OPEN), mask_bits=None):
     """(dq, dk, dv) of softmax attention from the forward's o and lse [B, H, Sq] and the gradient of o
     (attn_b200_softmax_bwd: mask NONE, CAUSAL or BAND with ``mask_band`` = (left, right); head dims 128 / 128 and
-    64 / 64; dim_v a larger multiple of dim_qk as one run per column slice)."""
+    64 / 64; dim_v a larger multiple of dim_qk as one run per column slice).  ``mask_bits`` = (bits_q, bits_kv), the keep
+    matrix of a general mask and its transpose as device int32 tensors (core/lower/sparse.py:mask_bit_matrices), replaces
+    the mask kind by MASK_BITS."""
     for t in (q, k, v, o, d_o, lse):
         if not t.is_cuda:
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
-    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _softmax_bwd_one(q_, k_, v_, o_, lse, do_, scale, mask_kind, mask_band),
+    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _softmax_bwd_one(q_, k_, v_, o_, lse, do_, scale, mask_kind, mask_band, mask_bits),
                               q, k, v, d_o, o)
 
 
-def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band):
+def _set_mask_bits(a, mask_bits, q, k):
+    """Fills mask_kind / mask_bits_* of a backward argument struct from (bits_q, bits_kv) after checking their shapes."""
+    bq, bk = mask_bits
+    nq, nk = -(-q.shape[1] // 128), -(-k.shape[1] // 128)
+    for t, shape in ((bq, (nq * 128, nk, 4)), (bk, (nk * 128, nq, 4))):
+        if not (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous() and tuple(t.shape) == shape):
+            raise NativeError(f"mask bits: expected a contiguous CUDA int32 tensor of shape {shape}, got {tuple(t.shape)}")
+    a.mask_kind, a.mask_bits_q, a.mask_bits_kv = MASK_BITS, bq.data_ptr(), bk.data_ptr()
+
+
+def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band, mask_bits=None):
     for t in (q, k, v, o):
         if t.stride(-1) != 1:
             raise NativeError("last dimension must be contiguous")
@@ -394,6 +409,8 @@ def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_ba
     a.batch, a.heads, a.heads_kv, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, k.shape[2], Sq, k.shape[1], D, v.shape[3]
     a.dtype, a.mask_kind, a.scale = DTYPE_CODES[q.dtype], mask_kind, float(scale)
     a.mask_left, a.mask_right = int(mask_band[0]), int(mask_band[1])
+    if mask_bits is not None:
+        _set_mask_bits(a, mask_bits, q, k)
     for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("do", d_o), ("dq", dq), ("dk", dk), ("dv", dv)):
         getattr(a, name + "_stride")[:] = _strides_bsh(t)
     lib = load_library()
@@ -407,7 +424,7 @@ def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_ba
     return dq, dk, dv
 
 
-def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=(), mask_band=(MASK_OPEN, MASK_OPEN)):
+def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=(), mask_band=(MASK_OPEN, MASK_OPEN), mask_bits=None):
     """(dq, dk, dv) of an elementwise program through its functor library's ``attn_b200_elementwise_bwd_jit`` (``fn``);
     ``custom``: the program's fp32 scalar inputs, as device tensors.  dim_v may be a multiple of dim_qk."""
     for t in (q, k, v, d_o, *custom):
@@ -415,11 +432,11 @@ def elementwise_bwd(fn, q, k, v, d_o, mask_kind: int, custom=(), mask_band=(MASK
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
     if d_o.stride(-1) != 1:
         d_o = d_o.contiguous()
-    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _elementwise_bwd_one(fn, q_, k_, v_, do_, mask_kind, custom, mask_band),
+    return _over_dim_v_slices(lambda q_, k_, v_, do_, o_: _elementwise_bwd_one(fn, q_, k_, v_, do_, mask_kind, custom, mask_band, mask_bits),
                               q, k, v, d_o)
 
 
-def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom, mask_band):
+def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom, mask_band, mask_bits=None):
     if q.dtype not in DTYPE_CODES or any(t.dtype != q.dtype for t in (k, v, d_o)):
         raise NativeError("q, k, v, d_o must share dtype float16 or bfloat16")
     dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))
@@ -431,6 +448,8 @@ def _elementwise_bwd_one(fn, q, k, v, d_o, mask_kind: int, custom, mask_band):
     a.batch, a.heads, a.heads_kv, a.seq_q, a.seq_kv, a.dim_qk, a.dim_v = B, H, k.shape[2], Sq, k.shape[1], D, v.shape[3]
     a.dtype, a.mask_kind = DTYPE_CODES[q.dtype], mask_kind
     a.mask_left, a.mask_right = int(mask_band[0]), int(mask_band[1])
+    if mask_bits is not None:
+        _set_mask_bits(a, mask_bits, q, k)
     for name, t in (("q", q), ("k", k), ("v", v), ("do", d_o), ("dq", dq), ("dk", dk), ("dv", dv)):
         getattr(a, name + "_stride")[:] = _strides_bsh(t)
     for i, t in enumerate(custom):

@@ -54,6 +54,11 @@ struct BwdParams {
   const float* delta;   // [batch, heads, seq_q_pad]
   int batch, heads, heads_kv, kv_group, seq_q, seq_kv, seq_q_pad;
   int mask_left, mask_right;   // keep q_idx - mask_left <= kv_idx <= q_idx + mask_right; ATTN_B200_MASK_OPEN = no bound
+  // kBits kernels (any mask that does not depend on batch or head, as keep bits): bits_q[q][kv tile][4 words] = the
+  // 128 keep bits of query row q in that KV tile, bits_kv[kv][query tile][4 words] the same matrix transposed; both
+  // padded with zeros to whole tiles.  Every pair of tiles is visited.
+  const uint32_t* bits_q;
+  const uint32_t* bits_kv;
   float scale;
   long long dq_s[3], dk_s[3], dv_s[3];   // element strides (batch, seq, head)
   CoordOrder oq, ok, ov, odo;
@@ -104,7 +109,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 // writes dK, dV.  kRoleQ = true: CTA = (query tile, query head, batch), streams the KV tiles and writes dQ.
 // Tensor memory: S [0,128), dP [128,256), accumulator 1 [256,384) (dV or dQ), accumulator 2 [384,512) (dK; the
 // query role's two dS buffers).  KV role: P is written over S, dS over dP.
-template <class F, bool kRoleQ, bool kBf16, int D>
+template <class F, bool kRoleQ, bool kBf16, int D, bool kBits = false>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
@@ -328,10 +333,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // when no edge of the band crosses the pair); a functor whose P vanishes at a score of -inf (softmax) gets the mask
     // through the score
     int col_lo = 0, col_hi = T;
+    uint4 keep_bits = make_uint4(0, 0, 0, 0);   // kBits: this thread's row of the streamed tile
     auto score_of = [&](auto edge_tile, float s, float l2, int ys, int hq, int col, float& pr, float& g) {
       const int q_idx = kRoleQ ? tile * T + row : ys * T + col;
       const int kv_idx = kRoleQ ? ys * T + col : tile * T + row;
-      const bool masked = decltype(edge_tile)::value && (col < col_lo || col > col_hi);
+      bool masked;
+      if constexpr (kBits) {
+        const uint32_t w = (col >> 5) == 0 ? keep_bits.x : (col >> 5) == 1 ? keep_bits.y : (col >> 5) == 2 ? keep_bits.z : keep_bits.w;
+        masked = ((w >> (col & 31)) & 1u) == 0u;
+      } else {
+        masked = decltype(edge_tile)::value && (col < col_lo || col > col_hi);
+      }
       F::score((F::kNegInfMask && masked) ? -INFINITY : s, l2, fctx, b, hq, q_idx, kv_idx, pr, g);
       if (!F::kNegInfMask && masked) pr = g = 0.0f;
     };
@@ -348,8 +360,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // Pairs of tiles that an edge of the band crosses take a second copy of the row loops, with the mask: the row
       // phases sit on the kernel's serial chain, and two compares per element on every tile cost 15 %
       const long long q0 = static_cast<long long>(kRoleQ ? tile : ys) * T, k0 = static_cast<long long>(kRoleQ ? ys : tile) * T;
-      const bool edge = (k0 + T - 1 > q0 + p.mask_right) || (k0 + p.mask_left < q0 + T - 1);
-      if (edge) {
+      const bool edge = kBits || (k0 + T - 1 > q0 + p.mask_right) || (k0 + p.mask_left < q0 + T - 1);
+      if constexpr (kBits) {
+        const uint32_t* bits = kRoleQ ? p.bits_q : p.bits_kv;
+        const long long pitch = 4LL * (kRoleQ ? nk : nq);   // words per row: four per streamed tile
+        keep_bits = *reinterpret_cast<const uint4*>(bits + (static_cast<long long>(tile) * T + row) * pitch + 4LL * ys);
+      } else if (edge) {
         // kv - q of (row, col) is base + col (query role) or base - col (KV role); kept where -left <= kv - q <= right
         const long long base = kRoleQ ? k0 - q0 - row : k0 - q0 + row;
         const long long lo = kRoleQ ? -static_cast<long long>(p.mask_left) - base : base - p.mask_right;
@@ -528,6 +544,7 @@ struct BwdCall {
   const float* lse2;
   const float* delta;
   const void* const* custom;
+  const uint32_t *bits_q, *bits_kv;   // both or neither: keep bits of a general mask (the band then has to be open)
 };
 
 // dK/dV launch (one CTA per KV tile and KV head) and dQ launch (one per query tile and head) for functor F.
@@ -561,6 +578,8 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
   p.seq_q_pad = nq * T;
   p.mask_left = a.mask_left;
   p.mask_right = a.mask_right;
+  p.bits_q = a.bits_q;
+  p.bits_kv = a.bits_kv;
   p.scale = a.scale;
   for (int i = 0; i < 3; ++i) {
     p.dq_s[i] = a.dq_stride[i];
@@ -569,8 +588,9 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
   }
   for (int i = 0; i < ATTN_B200_MAX_CUSTOM; ++i) p.custom[i] = a.custom != nullptr ? a.custom[i] : nullptr;
   p.status = status;
-  auto kv_kernel = attn_bwd_kernel<F, false, kBf16, D>;
-  auto q_kernel = attn_bwd_kernel<F, true, kBf16, D>;
+  const bool with_bits = a.bits_q != nullptr;
+  auto kv_kernel = with_bits ? attn_bwd_kernel<F, false, kBf16, D, true> : attn_bwd_kernel<F, false, kBf16, D, false>;
+  auto q_kernel = with_bits ? attn_bwd_kernel<F, true, kBf16, D, true> : attn_bwd_kernel<F, true, kBf16, D, false>;
   if (cudaFuncSetAttribute(kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess ||
       cudaFuncSetAttribute(q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
     cudaGetLastError();
@@ -583,9 +603,16 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
   return ATTN_B200_OK;
 }
 
-// mask_kind and the band of an argument struct as the two band sides of a call; false = not a mask the backward covers
-inline bool bwd_mask_of(int mask_kind, int left, int right, BwdCall& call) {
-  if (mask_kind == ATTN_B200_MASK_NONE) {
+// mask_kind, the band and the keep bits of an argument struct as the mask of a call; false = not a mask the backward covers
+inline bool bwd_mask_of(int mask_kind, int left, int right, const void* bits_q, const void* bits_kv, BwdCall& call) {
+  call.bits_q = call.bits_kv = nullptr;
+  if (mask_kind == ATTN_B200_MASK_BITS) {
+    if (bits_q == nullptr || bits_kv == nullptr) return false;
+    if (((reinterpret_cast<uintptr_t>(bits_q) | reinterpret_cast<uintptr_t>(bits_kv)) & 15) != 0) return false;
+    call.bits_q = static_cast<const uint32_t*>(bits_q);
+    call.bits_kv = static_cast<const uint32_t*>(bits_kv);
+    call.mask_left = call.mask_right = ATTN_B200_MASK_OPEN;
+  } else if (mask_kind == ATTN_B200_MASK_NONE) {
     call.mask_left = call.mask_right = ATTN_B200_MASK_OPEN;
   } else if (mask_kind == ATTN_B200_MASK_CAUSAL) {
     call.mask_left = ATTN_B200_MASK_OPEN;

@@ -282,3 +282,34 @@ def test_sliding_window_engine_autograd():
     check(o.detach(), ref.detach(), "o")
     for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
         check(got, want, what)
+
+
+@pytest.mark.parametrize("which", ["document", "checker"])
+def test_general_masks_through_the_engine(which):
+    """A mask_mod that is not a band (here: causal inside documents of 200 tokens; and a pattern with holes) and does not
+    use the batch or head index: the engine hands its keep matrix and the transpose to the backward as bits
+    (ATTN_B200_MASK_BITS) and both launches mask element by element, as the reference's backward does with any
+    mask_mod (attn_tl.py:430-461).  Against autograd over the oracle with the same keep matrix."""
+    from examples_b200 import programs
+    B, H, S, D = 1, 2, 700, 128
+    if which == "document":
+        mask_mod = lambda b, h, q_idx, kv_idx: torch.logical_and(q_idx >= kv_idx, (q_idx // 200) == (kv_idx // 200))  # noqa: E731
+    else:
+        mask_mod = lambda b, h, q_idx, kv_idx: torch.logical_or(q_idx == kv_idx, ((q_idx // 64) + (kv_idx // 96)) % 3 == 0)  # noqa: E731
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 61)
+    d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(62)).to(torch.bfloat16)
+    qi, ki = torch.arange(S)[:, None], torch.arange(S)[None, :]
+    keep = mask_mod(0, 0, qi, ki)
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        ref = rm.softmax_attention(qf, kf, vf, False, D ** -0.5, keep=keep)
+        ref.backward(d_o.float())
+    eng = programs.masked_softmax_engine(B, H, S, D, D, mask_mod)
+    assert eng._sparse_host is not None and "bits_q" in eng._sparse_host
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qc, kc, vc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    check(o.detach(), ref.detach(), "o")
+    for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
+        check(got, want, what)
