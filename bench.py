@@ -420,7 +420,24 @@ def extras_backward(peaks, launches=10):
         rec["roofline"] = tensor_roofline(fl, rec["ms"], peaks, sustained=False)
         rec["note"] = "FLOPs of five tile products per (query tile, KV tile); the two kernels execute seven"
         out["softmax_backward_causal_8x32x4096x128"] = rec
-        del q, k, v, o, d_o
+        # the same shape under masks that skip tiles: a sliding window and causal documents of 1024 tokens (a general
+        # mask_mod: keep bits and tile bitmaps from the front-end)
+        from examples_b200 import programs
+        win = (1023, 0)
+        a = lib.fill_parallel_args(q, k, v, o, mask_kind=lib.MASK_BAND, mask_band=win, functor=lib.FUNCTOR_SOFTMAX,
+                                   fparams=(D ** -0.5,), final_rowscales=[lse])
+        lib.parallel_fwd(a)
+        ms = statistics.median(time_launches(lambda: lib.softmax_bwd(q, k, v, o, lse, d_o, D ** -0.5, lib.MASK_BAND, win), launches, 3))
+        out["softmax_backward_sliding_window_1024"] = {"ms": ms}
+        doc = programs.masked_softmax_engine(B, H, S, D, D, lambda b_, h_, qi, ki: torch.logical_and(qi >= ki, (qi // 1024) == (ki // 1024)))
+        o_doc = doc(q, k, v)
+        lse_doc = doc.last_final_rowscales[doc.final_names[0]]
+        bits = doc._mask_bits(q.device)
+        ms = statistics.median(time_launches(lambda: lib.softmax_bwd(q, k, v, o_doc, lse_doc, d_o, D ** -0.5, lib.MASK_NONE, mask_bits=bits),
+                                             launches, 3))
+        out["softmax_backward_document_mask_1024"] = {"ms": ms, "kept_tiles": doc._sparse_host["kept_tiles"],
+                                                      "all_tiles": doc._sparse_host["all_tiles"]}
+        del q, k, v, o, d_o, o_doc
         # RetNet retention backward on the benchmark shape: five runs of the forward kernel plus the time reversals
         # and fp32 sums around them (torch), timed as one call
         from attn_engine.linear_attn_engine import linear_attention_backward

@@ -318,10 +318,15 @@ typedef struct AttnB200SoftmaxBwdArgs {
    * launch that owns query rows and the one that owns KV rows.  With nq, nk = 128-row tiles of seq_q, seq_kv:
    * mask_bits_q uint32 [nq*128][nk][4]: bit (c & 31) of word c >> 5 of [q][j] = keep (q, 128 j + c);
    * mask_bits_kv uint32 [nk*128][nq][4]: bit (c & 31) of word c >> 5 of [kv][i] = keep (128 i + c, kv);
-   * rows and columns past the sequence ends are 0.  Every pair of tiles is visited (the reference's backward applies
-   * mask_mod element-wise to every tile as well, attn_tl.py:430-461). */
+   * rows and columns past the sequence ends are 0.  (The reference's backward applies mask_mod element-wise to every
+   * tile, attn_tl.py:430-461.) */
   const void* mask_bits_q;
   const void* mask_bits_kv;
+  /* optional with the bits (both or neither; device): which pairs of tiles keep anything, so that the others are
+   * skipped.  mask_tiles_q uint32 [nq][ceil(nk / 32)]: bit (j & 31) of word j >> 5 of row i = the pair (query tile i, KV
+   * tile j) keeps something; mask_tiles_kv uint32 [nk][ceil(nq / 32)] the same matrix transposed. */
+  const void* mask_tiles_q;
+  const void* mask_tiles_kv;
 } AttnB200SoftmaxBwdArgs;
 
 /* Scratch the backward needs (delta = rowsum(dO o O) and the log-sum-exp in the exp2 domain, padded to whole
@@ -357,6 +362,8 @@ typedef struct AttnB200ElementwiseBwdArgs {
   int32_t mask_left, mask_right;   /* ATTN_B200_MASK_BAND only */
   const void* mask_bits_q;         /* ATTN_B200_MASK_BITS only, as in AttnB200SoftmaxBwdArgs */
   const void* mask_bits_kv;
+  const void* mask_tiles_q;
+  const void* mask_tiles_kv;
 } AttnB200ElementwiseBwdArgs;
 
 /* Reads and clears the device-side status word of device `device`

@@ -331,7 +331,8 @@ class AttentionEngine:
             return None
         if device not in self._sparse_dev:
             self._sparse_dev[device] = sparse_lowering.to_device(self._sparse_host, device)
-        return self._sparse_dev[device]["bits_q"], self._sparse_dev[device]["bits_kv"]
+        d = self._sparse_dev[device]
+        return d["bits_q"], d["bits_kv"], d["tiles_q"], d["tiles_kv"]
 
     def has_backward(self, q, v) -> bool:
         """Whether gradients flow through this engine for these operands: the built-in softmax (a traced program that

@@ -167,7 +167,7 @@ extern "C" int attn_b200_elementwise_bwd_jit(const AttnB200ElementwiseBwdArgs* a
   if (a == nullptr || device_status == nullptr) return ATTN_B200_E_INVALID_ARG;
   if (a->dim_qk != {dim} || a->dim_v != {dim} || a->dtype != {1 if bf16 else 0}) return ATTN_B200_E_UNSUPPORTED;
   b200::BwdCall call{{}};
-  if (!b200::bwd_mask_of(a->mask_kind, a->mask_left, a->mask_right, a->mask_bits_q, a->mask_bits_kv, call)) return ATTN_B200_E_UNSUPPORTED;
+  if (!b200::bwd_mask_of(a->mask_kind, a->mask_left, a->mask_right, a->mask_bits_q, a->mask_bits_kv, a->mask_tiles_q, a->mask_tiles_kv, call)) return ATTN_B200_E_UNSUPPORTED;
   call.q = a->q; call.k = a->k; call.v = a->v; call.d_o = a->d_o;
   call.dq = a->dq; call.dk = a->dk; call.dv = a->dv;
   call.batch = a->batch; call.heads = a->heads; call.heads_kv = a->heads_kv > 0 ? a->heads_kv : a->heads;

@@ -65,7 +65,8 @@ def build_block_sparse(mask_mod, B: int, H: int, q_len: int, kv_len: int) -> dic
     elem = torch.cat(masks) if masks else torch.zeros(1, TILE, 4, dtype=torch.int32)
     out_bits = {}
     if not per_bh:   # the backward takes the keep matrix and its transpose as bits (one matrix for all batches and heads)
-        out_bits["bits_q"], out_bits["bits_kv"] = mask_bit_matrices(_eval_mask_2d(mask_mod, 0, 0, q_len, kv_len, "cpu"))
+        out_bits["bits_q"], out_bits["bits_kv"], out_bits["tiles_q"], out_bits["tiles_kv"] = mask_bit_matrices(
+            _eval_mask_2d(mask_mod, 0, 0, q_len, kv_len, "cpu"))
     return {**out_bits, "keep": _pack_bits(keep), "partial": _pack_bits(part), "mask_base": base.to(torch.int32).view(SB, SH, nq),
             "elem_mask": elem.contiguous(), "batch": SB, "heads": SH, "mask_rows": TILE,
             "kept_tiles": int(keep.sum()), "partial_tiles": int(part.sum()), "all_tiles": SB * SH * nq * nk}
@@ -73,18 +74,23 @@ def build_block_sparse(mask_mod, B: int, H: int, q_len: int, kv_len: int) -> dic
 
 def mask_bit_matrices(dense: torch.Tensor):
     """The keep matrix [q_len, kv_len] of a mask and its transpose as the bit tensors the backward kernels take
-    (include/attn_b200.h, ATTN_B200_MASK_BITS): int32 [nq*128, nk, 4] and [nk*128, nq, 4], zero-padded to whole tiles."""
+    (include/attn_b200.h, ATTN_B200_MASK_BITS): int32 [nq*128, nk, 4] and [nk*128, nq, 4], zero-padded to whole tiles,
+    and the bitmaps of the tile pairs that keep anything, int32 [nq, ceil(nk/32)] and its transpose [nk, ceil(nq/32)]."""
     q_len, kv_len = dense.shape
     nq, nk = -(-q_len // TILE), -(-kv_len // TILE)
     padded = torch.nn.functional.pad(dense, (0, nk * TILE - kv_len, 0, nq * TILE - q_len), value=False)
     bits_q = _pack_bits(padded.contiguous()).view(nq * TILE, nk, 4)
     bits_kv = _pack_bits(padded.t().contiguous()).view(nk * TILE, nq, 4)
-    return bits_q.contiguous(), bits_kv.contiguous()
+    kept = padded.view(nq, TILE, nk, TILE).any(dim=3).any(dim=1)   # [nq, nk]
+    pad_to = lambda m: torch.nn.functional.pad(m, (0, -m.shape[1] % 32), value=False)   # noqa: E731
+    tiles_q = _pack_bits(pad_to(kept).contiguous())
+    tiles_kv = _pack_bits(pad_to(kept.t()).contiguous())
+    return bits_q.contiguous(), bits_kv.contiguous(), tiles_q.contiguous(), tiles_kv.contiguous()
 
 
 def to_device(sparse: dict, device) -> dict:
     out = dict(sparse)
-    for key in ("keep", "partial", "mask_base", "elem_mask", "bits_q", "bits_kv"):
+    for key in ("keep", "partial", "mask_base", "elem_mask", "bits_q", "bits_kv", "tiles_q", "tiles_kv"):
         if sparse.get(key) is not None:
             out[key] = sparse[key].to(device)
     return out

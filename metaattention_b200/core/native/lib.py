@@ -87,7 +87,7 @@ class SoftmaxBwdArgs(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("o_stride", C.c_int64 * 3),
         ("do_stride", C.c_int64 * 3), ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64), ("mask_left", C.c_int32), ("mask_right", C.c_int32),
-        ("mask_bits_q", C.c_void_p), ("mask_bits_kv", C.c_void_p),
+        ("mask_bits_q", C.c_void_p), ("mask_bits_kv", C.c_void_p), ("mask_tiles_q", C.c_void_p), ("mask_tiles_kv", C.c_void_p),
     ]
 
 
@@ -100,7 +100,7 @@ class ElementwiseBwdArgs(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3), ("do_stride", C.c_int64 * 3),
         ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
         ("custom", C.c_void_p * MAX_CUSTOM), ("mask_left", C.c_int32), ("mask_right", C.c_int32),
-        ("mask_bits_q", C.c_void_p), ("mask_bits_kv", C.c_void_p),
+        ("mask_bits_q", C.c_void_p), ("mask_bits_kv", C.c_void_p), ("mask_tiles_q", C.c_void_p), ("mask_tiles_kv", C.c_void_p),
     ]
 
 
@@ -370,9 +370,9 @@ def _over_dim_v_slices(run, q, k, v, d_o, o=None):
 def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band=(MASK_OPEN, MASK_OPEN), mask_bits=None):
     """(dq, dk, dv) of softmax attention from the forward's o and lse [B, H, Sq] and the gradient of o
     (attn_b200_softmax_bwd: mask NONE, CAUSAL or BAND with ``mask_band`` = (left, right); head dims 128 / 128 and
-    64 / 64; dim_v a larger multiple of dim_qk as one run per column slice).  ``mask_bits`` = (bits_q, bits_kv), the keep
-    matrix of a general mask and its transpose as device int32 tensors (core/lower/sparse.py:mask_bit_matrices), replaces
-    the mask kind by MASK_BITS."""
+    64 / 64; dim_v a larger multiple of dim_qk as one run per column slice).  ``mask_bits`` = (bits_q, bits_kv[, tiles_q,
+    tiles_kv]), the keep matrix of a general mask and its transpose as device int32 tensors and, optionally, the bitmaps of
+    the tile pairs that keep anything (core/lower/sparse.py:mask_bit_matrices), replaces the mask kind by MASK_BITS."""
     for t in (q, k, v, o, d_o, lse):
         if not t.is_cuda:
             raise NativeError("the backward kernel needs CUDA tensors: there is no CPU path")
@@ -384,12 +384,17 @@ def softmax_bwd(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band=(M
 
 def _set_mask_bits(a, mask_bits, q, k):
     """Fills mask_kind / mask_bits_* of a backward argument struct from (bits_q, bits_kv) after checking their shapes."""
-    bq, bk = mask_bits
+    bq, bk = mask_bits[:2]
     nq, nk = -(-q.shape[1] // 128), -(-k.shape[1] // 128)
-    for t, shape in ((bq, (nq * 128, nk, 4)), (bk, (nk * 128, nq, 4))):
+    want = [(bq, (nq * 128, nk, 4)), (bk, (nk * 128, nq, 4))]
+    if len(mask_bits) == 4:   # + bitmaps of the tiles that keep anything
+        want += [(mask_bits[2], (nq, -(-nk // 32))), (mask_bits[3], (nk, -(-nq // 32)))]
+    for t, shape in want:
         if not (t.is_cuda and t.dtype == torch.int32 and t.is_contiguous() and tuple(t.shape) == shape):
             raise NativeError(f"mask bits: expected a contiguous CUDA int32 tensor of shape {shape}, got {tuple(t.shape)}")
     a.mask_kind, a.mask_bits_q, a.mask_bits_kv = MASK_BITS, bq.data_ptr(), bk.data_ptr()
+    if len(mask_bits) == 4:
+        a.mask_tiles_q, a.mask_tiles_kv = mask_bits[2].data_ptr(), mask_bits[3].data_ptr()
 
 
 def _softmax_bwd_one(q, k, v, o, lse, d_o, scale: float, mask_kind: int, mask_band, mask_bits=None):

@@ -59,6 +59,11 @@ struct BwdParams {
   // padded with zeros to whole tiles.  Every pair of tiles is visited.
   const uint32_t* bits_q;
   const uint32_t* bits_kv;
+  // optional with the bits: which tiles keep anything at all, so that the others are not visited.  tiles_q[query tile]
+  // [tile_words_k] = bitmap over the KV tiles, tiles_kv[KV tile][tile_words_q] = bitmap over the query tiles
+  const uint32_t* tiles_q;
+  const uint32_t* tiles_kv;
+  int tile_words_k, tile_words_q;
   float scale;
   long long dq_s[3], dk_s[3], dv_s[3];   // element strides (batch, seq, head)
   CoordOrder oq, ok, ov, odo;
@@ -104,6 +109,29 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+
+// The set bits of one row of a tile bitmap, in order, over and over (the KV role walks its row once per query head of
+// its group).  The caller knows how many there are and never asks an empty row.
+struct KeptTiles {
+  const uint32_t* words;
+  int nwords, w;
+  uint32_t bits;
+  __device__ KeptTiles(const uint32_t* p, int n) : words(p), nwords(n), w(-1), bits(0) {}
+  __device__ int next() {
+    while (bits == 0) {
+      if (++w >= nwords) w = 0;
+      bits = words[w];
+    }
+    const int j = w * 32 + __ffs(bits) - 1;
+    bits &= bits - 1;
+    return j;
+  }
+  __device__ int count() const {
+    int c = 0;
+    for (int i = 0; i < nwords; ++i) c += __popc(words[i]);
+    return c;
+  }
+};
 
 // kRoleQ = false: CTA = (KV tile, KV head, batch), streams the query tiles (of every query head of its group) and
 // writes dK, dV.  kRoleQ = true: CTA = (query tile, query head, batch), streams the KV tiles and writes dQ.
@@ -153,8 +181,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int i1 = static_cast<int>(min(static_cast<long long>(nq) - 1, (r1 + p.mask_left) / T));
   const int j0 = static_cast<int>(max(r0 - p.mask_left, 0LL) / T);
   const int j1 = static_cast<int>(min(static_cast<long long>(nk) - 1, (r1 + p.mask_right) / T));
-  const int per_head = kRoleQ ? 0 : max(i1 - i0 + 1, 0);
-  const int n_iter = kRoleQ ? max(j1 - j0 + 1, 0) : p.kv_group * per_head;
+  // with keep bits and a tile bitmap: the tiles whose bit is set in this tile's row of the bitmap
+  const bool walk_tiles = kBits && p.tiles_q != nullptr;
+  const uint32_t* tiles_row = !walk_tiles ? nullptr
+                              : kRoleQ  ? p.tiles_q + static_cast<long long>(tile) * p.tile_words_k
+                                        : p.tiles_kv + static_cast<long long>(tile) * p.tile_words_q;
+  const int tiles_words = kRoleQ ? p.tile_words_k : p.tile_words_q;
+  const int n_kept = walk_tiles ? KeptTiles(tiles_row, tiles_words).count() : 0;
+  const int per_head = kRoleQ ? 0 : (walk_tiles ? n_kept : max(i1 - i0 + 1, 0));
+  const int n_iter = kRoleQ ? (walk_tiles ? n_kept : max(j1 - j0 + 1, 0)) : p.kv_group * per_head;
 
   if (tid == 0) {
     *abort_flag = (*reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -207,19 +242,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tma_load_rows(sX2 + c * L::kChunkBytes, &tmV, x_full, c * 64, tile * T, hx, b, p.ov);
         }
       }
+      KeptTiles kept(tiles_row, tiles_words);
       for (int it = 0; it < n_iter; ++it) {
         const int s1 = it % N1, s2 = it % N2;
+        const int ys = walk_tiles ? kept.next() : (kRoleQ ? j0 + it : i0 + it % max(per_head, 1));   // the streamed tile
         uint8_t* y1 = sY1 + s1 * L::kTileBytes;
         uint8_t* y2 = sY2 + s2 * L::kTileBytes;
         // streamed tile: row offset and head in the tensors it comes from
         const int hk = hx / p.kv_group;
-        const int hq = kRoleQ ? 0 : hx * p.kv_group + it / per_head, i = kRoleQ ? 0 : i0 + it % per_head;
+        const int hq = kRoleQ ? 0 : hx * p.kv_group + it / per_head, i = ys;
         const long long stat_off = kRoleQ ? 0 : (static_cast<long long>(b) * p.heads + hq) * p.seq_q_pad + i * T;
         if (!mbar_wait(y1_empty + s1, ((it / N1) & 1) ^ 1, ab, kBwdYEmpty)) break;
         mbar_arrive_expect_tx(y1_full + s1, L::kTileBytes + ((!kRoleQ && F::kUsesStats) ? L::kStatBytes : 0));
         for (int c = 0; c < KC; ++c) {
           if constexpr (kRoleQ) {
-            tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y1_full + s1, c * 64, (j0 + it) * T, hk, b, p.ok);
+            tma_load_rows(y1 + c * L::kChunkBytes, &tmK, y1_full + s1, c * 64, ys * T, hk, b, p.ok);
           } else {
             tma_load_rows(y1 + c * L::kChunkBytes, &tmQ, y1_full + s1, c * 64, i * T, hq, b, p.oq);
           }
@@ -229,7 +266,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_arrive_expect_tx(y2_full + s2, L::kTileBytes + ((!kRoleQ && F::kUsesStats) ? L::kStatBytes : 0));
         for (int c = 0; c < KC; ++c) {
           if constexpr (kRoleQ) {
-            tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y2_full + s2, c * 64, (j0 + it) * T, hk, b, p.ov);
+            tma_load_rows(y2 + c * L::kChunkBytes, &tmV, y2_full + s2, c * 64, ys * T, hk, b, p.ov);
           } else {
             tma_load_rows(y2 + c * L::kChunkBytes, &tmDO, y2_full + s2, c * 64, i * T, hq, b, p.odo);
           }
@@ -353,9 +390,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       return (k & 3) == 0 ? v4.x : (k & 3) == 1 ? v4.y : (k & 3) == 2 ? v4.z : v4.w;
     };
     bool ok = start_ok;
+    KeptTiles kept(tiles_row, tiles_words);
     for (int it = 0; ok && it < n_iter; ++it) {
       // the streamed tile index, its query head, and whether an edge of the band crosses this pair of tiles
-      const int ys = kRoleQ ? j0 + it : i0 + it % max(per_head, 1);
+      const int ys = walk_tiles ? kept.next() : (kRoleQ ? j0 + it : i0 + it % max(per_head, 1));
       const int hq = kRoleQ ? hx : hx * p.kv_group + it / max(per_head, 1);
       // Pairs of tiles that an edge of the band crosses take a second copy of the row loops, with the mask: the row
       // phases sit on the kernel's serial chain, and two compares per element on every tile cost 15 %
@@ -545,6 +583,7 @@ struct BwdCall {
   const float* delta;
   const void* const* custom;
   const uint32_t *bits_q, *bits_kv;   // both or neither: keep bits of a general mask (the band then has to be open)
+  const uint32_t *tiles_q, *tiles_kv; // with the bits, optional (both or neither): bitmaps of the tiles that keep anything
 };
 
 // dK/dV launch (one CTA per KV tile and KV head) and dQ launch (one per query tile and head) for functor F.
@@ -580,6 +619,10 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
   p.mask_right = a.mask_right;
   p.bits_q = a.bits_q;
   p.bits_kv = a.bits_kv;
+  p.tiles_q = a.bits_q != nullptr ? a.tiles_q : nullptr;
+  p.tiles_kv = a.bits_q != nullptr ? a.tiles_kv : nullptr;
+  p.tile_words_k = (nk + 31) / 32;
+  p.tile_words_q = (nq + 31) / 32;
   p.scale = a.scale;
   for (int i = 0; i < 3; ++i) {
     p.dq_s[i] = a.dq_stride[i];
@@ -604,10 +647,14 @@ int launch_attn_bwd(const BwdCall& a, cudaStream_t stream, int* status) {
 }
 
 // mask_kind, the band and the keep bits of an argument struct as the mask of a call; false = not a mask the backward covers
-inline bool bwd_mask_of(int mask_kind, int left, int right, const void* bits_q, const void* bits_kv, BwdCall& call) {
-  call.bits_q = call.bits_kv = nullptr;
+inline bool bwd_mask_of(int mask_kind, int left, int right, const void* bits_q, const void* bits_kv, const void* tiles_q,
+                        const void* tiles_kv, BwdCall& call) {
+  call.bits_q = call.bits_kv = call.tiles_q = call.tiles_kv = nullptr;
   if (mask_kind == ATTN_B200_MASK_BITS) {
     if (bits_q == nullptr || bits_kv == nullptr) return false;
+    if ((tiles_q == nullptr) != (tiles_kv == nullptr)) return false;
+    call.tiles_q = static_cast<const uint32_t*>(tiles_q);
+    call.tiles_kv = static_cast<const uint32_t*>(tiles_kv);
     if (((reinterpret_cast<uintptr_t>(bits_q) | reinterpret_cast<uintptr_t>(bits_kv)) & 15) != 0) return false;
     call.bits_q = static_cast<const uint32_t*>(bits_q);
     call.bits_kv = static_cast<const uint32_t*>(bits_kv);

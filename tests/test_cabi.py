@@ -36,9 +36,9 @@ def test_struct_layouts_match_header(tmp_path):
         "AttnB200LinearArgs": (lib.LinearArgs, ["log_decay", "dim_v", "normalize", "q_scale", "workspace", "workspace_bytes", "precise", "v_scale", "heads_k", "q_ld", "k_ld"]),
         "AttnB200MlaShape": (lib.MlaShape, ["dim_v"]),
         "AttnB200SoftmaxBwdArgs": (lib.SoftmaxBwdArgs, ["lse", "dv", "dim_v", "scale", "q_stride", "dv_stride", "workspace_bytes",
-                                                        "mask_left", "mask_right", "mask_bits_q", "mask_bits_kv"]),
+                                                        "mask_left", "mask_right", "mask_bits_q", "mask_bits_kv", "mask_tiles_q", "mask_tiles_kv"]),
         "AttnB200ElementwiseBwdArgs": (lib.ElementwiseBwdArgs, ["d_o", "dv", "mask_kind", "q_stride", "custom", "mask_left",
-                                                                "mask_bits_q", "mask_bits_kv"]),
+                                                                "mask_bits_q", "mask_bits_kv", "mask_tiles_kv"]),
         "AttnB200MlaArgs": (lib.MlaArgs, ["kv_rope", "o", "workspace_bytes", "shape", "scale", "seq_lens", "block_table",
                                           "block_table_stride", "page_size", "num_pages"]),
     }
