@@ -173,13 +173,48 @@ def _linear_backward_case(rnd, g):
             _grad_close("linear backward " + what, cfg, gt, w)
 
 
+def _general_mask_backward_case(rnd, g):
+    """A mask_mod with holes (not a band) through the engine: keep bits + tile bitmaps in the backward."""
+    D = rnd.choice([64, 128])
+    dt = rnd.choice([torch.bfloat16, torch.float16])
+    B, H, S = rnd.randint(1, 2), rnd.randint(1, 3), rnd.choice([200, 384, 640, 900])
+    a, b_, c = rnd.choice([32, 64, 100, 200]), rnd.choice([48, 96, 128, 300]), rnd.choice([2, 3, 4])
+    causal_too = rnd.random() < 0.5
+
+    def mask_mod(b, h, q_idx, kv_idx):
+        m = torch.logical_or(q_idx == kv_idx, ((q_idx // a) + (kv_idx // b_)) % c == 0)
+        return torch.logical_and(m, q_idx >= kv_idx) if causal_too else m
+    q = torch.randn(B, S, H, D, generator=g).to(dt)
+    k = torch.randn(B, S, H, D, generator=g).to(dt)
+    v = torch.randn(B, S, H, D, generator=g).to(dt)
+    d_o = torch.randn(B, S, H, D, generator=g).to(dt)
+    keep = mask_mod(0, 0, torch.arange(S).view(-1, 1), torch.arange(S).view(1, -1))
+    scale = D ** -0.5
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        rm.softmax_attention(qf, kf, vf, False, scale, keep=keep).backward(d_o.float())
+    meta = (meta_tensor(B, H, S, D, dtype=dt), meta_tensor(B, H, S, D, dtype=dt), meta_tensor(B, H, S, D, dtype=dt))
+    e = AttentionEngine(meta, CustomIO({}), score_mod=lambda s_, c_, b, h, qq, kk: s_ * scale, mask_mod=mask_mod,
+                        online_func=programs.NaturalSoftmax())
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    e(qc, kc, vc).backward(d_o.cuda())
+    torch.cuda.synchronize()
+    cfg = (B, H, S, D, dt, a, b_, c, causal_too)
+    assert lib.last_device_status() == 0, cfg
+    for got, want, what in ((qc.grad, qf.grad, "dq"), (kc.grad, kf.grad, "dk"), (vc.grad, vf.grad, "dv")):
+        _grad_close("general-mask backward " + what, cfg, got, want)
+
+
 @pytest.mark.parametrize("seed", [21, 22])
 def test_random_sweep_backward(seed):
     """The backward kernels over random shapes, dtypes, head groups, ragged lengths and masks (none, causal, bands)."""
     rnd = random.Random(seed)
     for _ in range(14):
         g = torch.Generator().manual_seed(rnd.randrange(1 << 30))
-        if rnd.random() < 0.65:
+        r = rnd.random()
+        if r < 0.5:
             _attention_backward_case(rnd, g)
+        elif r < 0.7:
+            _general_mask_backward_case(rnd, g)
         else:
             _linear_backward_case(rnd, g)
