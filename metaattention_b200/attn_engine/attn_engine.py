@@ -274,6 +274,7 @@ class AttentionEngine:
             self.mask_kind = native.MASK_NONE
         self.sparse_walk = self._sparse_host is not None or self._decode_block is not None
         neg_inf_mask = str(mask_value).strip() in ("-inf", "-float('inf')")
+        self._neg_inf_mask = neg_inf_mask
         self.traced = trace_parallel(score_mod, online_func, self.custom_fwd_inputs)
         tr = self.traced
         if len(tr.custom) > native.MAX_CUSTOM:
@@ -322,6 +323,11 @@ class AttentionEngine:
     def _masked_for_backward(self) -> bool:
         """Masks the backward kernels take: none, causal, bands, and any other mask_mod that does not use the batch or
         head index (as keep bits)."""
+        masked = self.mask_kind != native.MASK_NONE or self._sparse_host is not None
+        if masked and not self._neg_inf_mask:
+            # with another mask value the forward masks nothing element-wise (as the reference: core/lower/lower.py:637-638)
+            # while a backward would: refused rather than inconsistent
+            return False
         return (self.mask_kind in (native.MASK_NONE, native.MASK_CAUSAL, native.MASK_BAND) and self._decode_block is None and
                 (self._sparse_host is None or "bits_q" in self._sparse_host))
 

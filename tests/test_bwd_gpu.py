@@ -313,3 +313,30 @@ def test_general_masks_through_the_engine(which):
     check(o.detach(), ref.detach(), "o")
     for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
         check(got, want, what)
+
+
+def test_elementwise_program_under_a_general_mask():
+    """relu attention (no online_func) with causal documents of 150 tokens: the derived backward functor with keep bits."""
+    from attn_engine import AttentionEngine
+    from core import CustomIO, meta_tensor
+    B, H, S, D = 1, 2, 500, 64
+    scale = D ** -0.5
+    mask_mod = lambda b, h, q_idx, kv_idx: torch.logical_and(q_idx >= kv_idx, (q_idx // 150) == (kv_idx // 150))  # noqa: E731
+    q, k, v = inputs.attention_bshd(B, H, S, D, D, 71, k_scale=0.5, v_scale=0.5)
+    d_o = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(72)).to(torch.bfloat16)
+    keep = mask_mod(0, 0, torch.arange(S)[:, None], torch.arange(S)[None, :])
+    with torch.enable_grad():
+        qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+        s = torch.einsum("bshd,bthd->bhst", qf, kf) * scale
+        ref = torch.einsum("bhst,bthd->bshd", torch.relu(s) * keep, vf)
+        ref.backward(d_o.float())
+    meta = (meta_tensor(B, H, S, D, dtype=torch.bfloat16),) * 3
+    eng = AttentionEngine(meta, CustomIO({}), score_mod=lambda sc, c, b, h, qq, kk: (sc * scale).max(0), mask_mod=mask_mod,
+                          online_func=None)   # mask_value "-inf": relu(-inf) = 0 (with "0" the forward masks nothing, as the reference)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    o = eng(qc, kc, vc)
+    o.backward(d_o.cuda())
+    torch.cuda.synchronize()
+    check(o.detach(), ref.detach(), "o")
+    for got, want, what in zip((qc.grad, kc.grad, vc.grad), (qf.grad, kf.grad, vf.grad), ("dq", "dk", "dv")):
+        check(got, want, what)
